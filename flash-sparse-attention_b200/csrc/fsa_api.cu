@@ -1,0 +1,295 @@
+// extern "C" boundary of libfsa_b200.so: argument validation, TMA descriptor construction, kernel
+// selection. No torch types, no allocation, no host<->device synchronisation.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <string.h>
+#include "../../include/fsa_b200.h"
+#include "fsa_aux.h"
+#include "fsa_params.h"
+#include "fsa_schedule.h"
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+    (void)cudaGetLastError();
+  }
+  return fn;
+}
+
+CUtensorMapDataType tma_dtype(int dt) {
+  switch (dt) {
+    case FSA_DT_BF16: return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    case FSA_DT_FP16: return CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    default: return CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  }
+}
+int dtype_bytes(int dt) { return (dt == FSA_DT_BF16 || dt == FSA_DT_FP16) ? 2 : (dt == FSA_DT_F32 ? 4 : 1); }
+
+// 4-D map over a [d3, d2, d1, head_dim] tensor (head_dim contiguous); strides in elements.
+int make_map4(CUtensorMap* map, int dt, const void* base, uint64_t head_dim, uint64_t d1, int64_t s1, uint64_t d2,
+              int64_t s2, uint64_t d3, int64_t s3, uint32_t box0, uint32_t box1, uint32_t box2) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return FSA_ERR_NO_DRIVER;
+  const uint64_t es = dtype_bytes(dt);
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((s1 * es) & 15) || ((s2 * es) & 15) || ((s3 * es) & 15))
+    return FSA_ERR_INVALID_ARG;
+  if (d1 == 0 || d2 == 0 || d3 == 0) return FSA_ERR_INVALID_ARG;
+  cuuint64_t dims[4] = {head_dim, d1, d2, d3};
+  cuuint64_t strides[3] = {(cuuint64_t)s1 * es, (cuuint64_t)s2 * es, (cuuint64_t)s3 * es};
+  cuuint32_t box[4] = {box0, box1, box2, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, tma_dtype(dt), 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FSA_OK : FSA_ERR_LAUNCH;
+}
+
+int cdiv(int a, int b) { return (a + b - 1) / b; }
+
+}  // namespace
+
+extern "C" {
+
+int fsa_abi_version(void) { return FSA_ABI_VERSION; }
+
+const char* fsa_status_string(int code) {
+  switch (code) {
+    case FSA_OK: return "ok";
+    case FSA_ERR_INVALID_ARG: return "invalid argument (null pointer, bad size, or stride/base not 16-byte aligned)";
+    case FSA_ERR_UNSUPPORTED: return "unsupported combination (head_dim must be 64 or 128, dtype bf16/fp16, ...)";
+    case FSA_ERR_LAUNCH: return "CUDA error at launch or tensor-map creation";
+    case FSA_ERR_NO_DRIVER: return "CUDA driver entry point cuTensorMapEncodeTiled unavailable";
+    default: return "unknown status";
+  }
+}
+
+void fsa_debug_fwd_schedule(int seqlen_q, int seqlen_k, int m_block, int split_idx, const int32_t window[4],
+                            int num_splits, int tile_n, int tile_m, int is_causal, int is_local, int is_split,
+                            int gpack, int32_t out9[9]) {
+  FsaWindow w = {window[0], window[1], window[2], window[3]};
+  FsaFwdSched s = fsa_fwd_schedule(seqlen_q, seqlen_k, m_block, split_idx, w, num_splits, tile_n, tile_m,
+                                   is_causal != 0, is_local != 0, is_split != 0, gpack);
+  out9[0] = s.n_min;
+  out9[1] = s.n_max;
+  out9[2] = s.n_max_no_mask;
+  out9[3] = s.win_min;
+  out9[4] = s.win_max;
+  out9[5] = s.win_min_no_mask;
+  out9[6] = s.win_max_no_mask;
+  out9[7] = s.sink_min;
+  out9[8] = s.sink_max;
+}
+
+void fsa_debug_bwd_schedule(int seqlen_q, int seqlen_k, int n_block, int split_idx, const int32_t window[4],
+                            int num_splits, int tile_n, int tile_m, int is_causal, int is_local, int is_split,
+                            int32_t out9[9]) {
+  FsaWindow w = {window[0], window[1], window[2], window[3]};
+  FsaBwdSched s = fsa_bwd_schedule(seqlen_q, seqlen_k, n_block, split_idx, w, num_splits, tile_n, tile_m,
+                                   is_causal != 0, is_local != 0, is_split != 0);
+  out9[0] = s.m_min;
+  out9[1] = s.m_max;
+  out9[2] = s.m_min_no_mask;
+  out9[3] = s.win_min;
+  out9[4] = s.win_max;
+  out9[5] = s.win_min_no_mask;
+  out9[6] = s.win_max_no_mask;
+  out9[7] = s.sink_min;
+  out9[8] = s.sink_max;
+}
+
+static int fwd_geometry(const FsaFwdArgs* a, int* gpack, int* num_m_blocks, int* hgrid, int* sk_static,
+                        int* n_tiles_k) {
+  if (a->heads_kv <= 0 || a->heads_q % a->heads_kv != 0) return FSA_ERR_INVALID_ARG;
+  const int G = a->heads_q / a->heads_kv;
+  const bool pack = (a->flags & FSA_F_PACK_GQA) && G > 1;
+  *gpack = pack ? G : 1;
+  if (pack && (128 % G) != 0) return FSA_ERR_UNSUPPORTED;
+  *num_m_blocks = cdiv(a->seqlen_q * *gpack, 128);
+  *hgrid = pack ? a->heads_kv : a->heads_q;
+  *sk_static = a->page_table ? a->page_table_stride * a->page_size : a->seqlen_k;
+  *n_tiles_k = cdiv(*sk_static, 128);
+  return FSA_OK;
+}
+
+size_t fsa_fwd_tile_map_bytes(const FsaFwdArgs* a) {
+  int gpack, nmb, hgrid, sk, ntk;
+  if (!a || fwd_geometry(a, &gpack, &nmb, &hgrid, &sk, &ntk) != FSA_OK) return 0;
+  const int ns = (a->flags & FSA_F_SPLIT) ? a->num_splits : 1;
+  return (size_t)a->batch * hgrid * nmb * ns * ntk;
+}
+
+int fsa_fwd(const FsaFwdArgs* a, void* stream_) {
+  if (!a || !a->q || !a->k || !a->v || !a->out || !a->lse || !a->status) return FSA_ERR_INVALID_ARG;
+  if (a->batch <= 0 || a->heads_q <= 0 || a->head_dim <= 0) return FSA_ERR_INVALID_ARG;
+  if (a->head_dim != 64 && a->head_dim != 128) return FSA_ERR_UNSUPPORTED;
+  if (a->dtype != FSA_DT_BF16 && a->dtype != FSA_DT_FP16) return FSA_ERR_UNSUPPORTED;
+  if (a->kind != FSA_KIND_DENSE && a->kind != FSA_KIND_SPARSE) return FSA_ERR_UNSUPPORTED;
+  if ((a->tile_m && a->tile_m != 128) || (a->tile_n && a->tile_n != 128)) return FSA_ERR_UNSUPPORTED;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  const bool varlen_q = a->cu_seqlens_q != nullptr, varlen_k = a->cu_seqlens_k != nullptr;
+  const bool paged = a->page_table != nullptr;
+  const bool split = (a->flags & FSA_F_SPLIT) != 0;
+  const int ns = split ? a->num_splits : 1;
+  if (ns <= 0) return FSA_ERR_INVALID_ARG;
+  if (split && (!a->out_partial || !a->lse_partial)) return FSA_ERR_INVALID_ARG;
+  if ((a->flags & FSA_F_LOCAL) && !a->window_sizes) return FSA_ERR_INVALID_ARG;
+  if (paged && (varlen_k || (a->page_size != 32 && a->page_size != 64 && a->page_size != 128 && a->page_size != 256)))
+    return FSA_ERR_UNSUPPORTED;
+  if (a->seqlen_q <= 0) return FSA_OK;  // nothing to do
+
+  int gpack, num_m_blocks, hgrid, sk_static, n_tiles_k;
+  int rc = fwd_geometry(a, &gpack, &num_m_blocks, &hgrid, &sk_static, &n_tiles_k);
+  if (rc != FSA_OK) return rc;
+  const int G = a->heads_q / a->heads_kv;
+
+  fsa::FwdKernelParams p;
+  memset(&p, 0, sizeof(p));
+  const long long rows_q = varlen_q ? a->total_q : (long long)a->batch * a->seqlen_q;
+  // Q: [B, Sq, Hq, D] or [total_q, Hq, D]
+  {
+    const uint64_t d_rows = varlen_q ? (uint64_t)a->total_q : (uint64_t)a->seqlen_q;
+    const uint64_t d_b = varlen_q ? 1 : (uint64_t)a->batch;
+    const int64_t s_b = varlen_q ? a->q_stride_s * (int64_t)a->total_q : a->q_stride_b;
+    rc = make_map4(&p.map_q, a->dtype, a->q, a->head_dim, a->heads_q, a->q_stride_h, d_rows, a->q_stride_s, d_b, s_b,
+                   64, gpack, 128 / gpack);
+    if (rc != FSA_OK) return rc;
+  }
+  {
+    uint64_t d_rows, d_b;
+    int64_t ks_b, vs_b;
+    uint32_t box_rows = 128;
+    if (paged) {
+      d_rows = a->page_size;
+      d_b = a->num_pages;
+      ks_b = a->k_stride_b;
+      vs_b = a->v_stride_b;
+      box_rows = a->page_size < 128 ? a->page_size : 128;
+    } else if (varlen_k) {
+      d_rows = a->total_k;
+      d_b = 1;
+      ks_b = a->k_stride_s * (int64_t)a->total_k;
+      vs_b = a->v_stride_s * (int64_t)a->total_k;
+    } else {
+      d_rows = a->seqlen_k;
+      d_b = a->batch;
+      ks_b = a->k_stride_b;
+      vs_b = a->v_stride_b;
+    }
+    if (d_rows == 0) return FSA_ERR_INVALID_ARG;
+    rc = make_map4(&p.map_k, a->dtype, a->k, a->head_dim, a->heads_kv, a->k_stride_h, d_rows, a->k_stride_s, d_b, ks_b,
+                   64, 1, box_rows);
+    if (rc != FSA_OK) return rc;
+    rc = make_map4(&p.map_v, a->dtype, a->v, a->head_dim, a->heads_kv, a->v_stride_h, d_rows, a->v_stride_s, d_b, vs_b,
+                   64, 1, box_rows);
+    if (rc != FSA_OK) return rc;
+  }
+  p.cu_q = a->cu_seqlens_q;
+  p.cu_k = a->cu_seqlens_k;
+  p.used_q = a->seqused_q;
+  p.used_k = a->seqused_k;
+  p.page_table = a->page_table;
+  p.windows = a->window_sizes;
+  p.alpha = a->alpha;
+  p.delta = a->delta;
+  p.status = a->status;
+  p.tile_map = a->tile_map;
+  if (split) {
+    p.out = a->out_partial;
+    p.lse = a->lse_partial;
+    p.o_sb = (long long)a->seqlen_q * a->heads_q * a->head_dim;
+    p.o_sm = (long long)a->heads_q * a->head_dim;
+    p.o_sh = a->head_dim;
+    p.o_ss = rows_q * a->heads_q * a->head_dim;
+    p.l_sb = a->seqlen_q;
+    p.l_sh = rows_q;
+    p.l_ss = rows_q * a->heads_q;
+  } else {
+    p.out = a->out;
+    p.lse = a->lse;
+    p.o_sb = a->o_stride_b;
+    p.o_sm = a->o_stride_s;
+    p.o_sh = a->o_stride_h;
+    p.o_ss = 0;
+    p.l_sb = a->lse_stride_b;
+    p.l_sh = a->lse_stride_h;
+    p.l_ss = 0;
+  }
+  if ((p.o_sm % 8) || (p.o_sh % 8) || (p.o_sb % 8)) return FSA_ERR_INVALID_ARG;  // 16-byte row stores
+  p.B = a->batch;
+  p.Hq = a->heads_q;
+  p.Hkv = a->heads_kv;
+  p.G = G;
+  p.gpack = gpack;
+  p.sq = a->seqlen_q;
+  p.sk = sk_static;
+  p.num_splits = ns;
+  p.num_m_blocks = num_m_blocks;
+  p.num_pairs = cdiv(num_m_blocks, 2);
+  p.hgrid = hgrid;
+  p.page_size = a->page_size;
+  p.pt_stride = a->page_table_stride;
+  p.win_stride = a->window_stride;
+  p.n_tiles_k = n_tiles_k;
+  p.scale_log2 = a->softmax_scale * 1.44269504089f;
+  p.softmax_thr = a->softmax_threshold;
+  p.gate_thr = a->gate_threshold;
+  p.v_scale = 1.0f;
+  unsigned f = 0;
+  if (a->flags & FSA_F_CAUSAL) f |= fsa::F_CAUSAL;
+  if (a->flags & FSA_F_LOCAL) f |= fsa::F_LOCAL;
+  if (split) f |= fsa::F_SPLIT | fsa::F_LSE_LOG2;
+  if (varlen_q) f |= fsa::F_VARLEN_Q;
+  if (varlen_k) f |= fsa::F_VARLEN_K;
+  if (paged) f |= fsa::F_PAGED;
+  if (gpack > 1) f |= fsa::F_PACK_GQA;
+  if (a->seqused_q) f |= fsa::F_USED_Q;
+  if (a->seqused_k) f |= fsa::F_USED_K;
+  if (varlen_k || paged || a->seqused_k) f |= fsa::F_KV_RAGGED;
+  if (a->flags & FSA_F_LOGSIGMOID) f |= fsa::F_LOGSIGMOID;
+  if (a->flags & FSA_F_ADAPT_GATE) f |= fsa::F_ADAPT_GATE;
+  p.flags = f;
+
+  cudaError_t e = fsa::launch_fwd(p, a->kind, a->dtype, a->head_dim, stream);
+  if (e == cudaErrorInvalidValue) return FSA_ERR_UNSUPPORTED;
+  if (e != cudaSuccess) return FSA_ERR_LAUNCH;
+
+  if (split) {
+    fsa::CombineParams c;
+    memset(&c, 0, sizeof(c));
+    c.out_partial = a->out_partial;
+    c.lse_partial = a->lse_partial;
+    c.out = a->out;
+    c.lse = a->lse;
+    c.op_ss = p.o_ss;
+    c.lp_ss = p.l_ss;
+    c.lp_sh = p.l_sh;
+    c.o_sb = varlen_q ? 0 : a->o_stride_b;
+    c.o_sm = a->o_stride_s;
+    c.o_sh = a->o_stride_h;
+    c.l_sb = varlen_q ? 0 : a->lse_stride_b;
+    c.l_sh = a->lse_stride_h;
+    c.rows = (int)rows_q;
+    c.rows_per_batch = varlen_q ? a->total_q : a->seqlen_q;
+    c.heads = a->heads_q;
+    c.head_dim = a->head_dim;
+    c.num_splits = ns;
+    e = fsa::launch_combine(c, a->dtype, stream);
+    if (e != cudaSuccess) return FSA_ERR_LAUNCH;
+  }
+  return FSA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,54 @@
+// Kernel-side parameter blocks (internal; the C ABI structs in include/fsa_b200.h are translated
+// into these by fsa_api.cu).
+#pragma once
+#include <cuda.h>
+#include <stdint.h>
+
+namespace fsa {
+
+enum : unsigned {
+  F_CAUSAL = 1u << 0,
+  F_LOCAL = 1u << 1,
+  F_SPLIT = 1u << 2,     // split-KV (forward/decode) or split-QO (backward)
+  F_VARLEN_Q = 1u << 3,  // rows of Q/O addressed through cu_seqlens_q
+  F_VARLEN_K = 1u << 4,
+  F_PAGED = 1u << 5,
+  F_PACK_GQA = 1u << 6,
+  F_USED_Q = 1u << 7,  // seqused_q present
+  F_USED_K = 1u << 8,
+  F_LOGSIGMOID = 1u << 9,
+  F_ADAPT_GATE = 1u << 10,
+  F_GATHER = 1u << 11,
+  F_LSE_LOG2 = 1u << 12,   // store lse in base 2 (split partials), else natural log
+  F_KV_RAGGED = 1u << 13,  // rows past the key length may hold foreign data: zero V tails in smem
+};
+
+enum { KIND_DENSE = 0, KIND_SPARSE = 1, KIND_GATED = 2 };
+enum { DT_BF16 = 0, DT_FP16 = 1, DT_E4M3 = 2, DT_E5M2 = 3, DT_F32 = 4 };
+
+struct alignas(64) FwdKernelParams {
+  CUtensorMap map_q, map_k, map_v;
+  void* out;         // T* [rows, Hq, D] or float* partial when F_SPLIT
+  float* lse;        // final or partial
+  const int* cu_q;   // [B+1] or null
+  const int* cu_k;
+  const int* used_q;  // [B] or null
+  const int* used_k;
+  const int* page_table;  // [B, pt_stride]
+  const int* windows;     // [Hkv, win_stride] = sink, left, right, near
+  const void* alpha;      // gated: [B, Hq, Sq] (row-contiguous), element type T
+  const void* delta;      // gated: [B, Hkv, Sk]
+  int* status;            // device word: 0 ok, non-zero = a bounded wait expired
+  uint8_t* tile_map;      // optional [B, Hgrid, num_m_blocks, num_splits, n_tiles_k]: 1 computed, 2 skipped
+  long long o_sb, o_sm, o_sh, o_ss;
+  long long l_sb, l_sh, l_ss;
+  long long a_sb, a_sh, d_sb, d_sh;
+  int B, Hq, Hkv, G, gpack;
+  int sq, sk;  // static lengths (max lengths for varlen)
+  int num_splits, num_m_blocks, num_pairs, hgrid;
+  int page_size, pt_stride, win_stride, n_tiles_k;
+  float scale_log2, softmax_thr, gate_thr, v_scale;
+  unsigned flags;
+};
+
+}  // namespace fsa

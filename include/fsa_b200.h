@@ -1,0 +1,126 @@
+/*
+ * C ABI of libfsa_b200.so - sm_100a attention kernels behind the flash-sparse-attention operator API.
+ *
+ * Every entry point takes plain device pointers, sizes and element strides; it never allocates,
+ * frees or keeps a pointer past its return, never synchronises the host with the device and launches
+ * on the CUDA stream handed in (a cudaStream_t passed as void*), so a call sequence can be captured
+ * into a CUDA graph by the caller. All workspaces are caller-owned. Return value: 0 on success, a
+ * negative FSA_ERR_* code otherwise (fsa_status_string() names it); nothing throws or aborts.
+ *
+ * Each function states which host launcher of the reference Python package it stands in for
+ * (paths relative to the reference repository root).
+ */
+#ifndef FSA_B200_H_
+#define FSA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FSA_ABI_VERSION 1
+
+enum {
+  FSA_OK = 0,
+  FSA_ERR_INVALID_ARG = -1, /* null pointer, bad size, misaligned stride */
+  FSA_ERR_UNSUPPORTED = -2, /* valid request outside what the kernels implement */
+  FSA_ERR_LAUNCH = -3,      /* CUDA reported an error at launch / descriptor creation */
+  FSA_ERR_NO_DRIVER = -4    /* cuTensorMapEncodeTiled could not be resolved (no CUDA driver) */
+};
+
+enum { FSA_KIND_DENSE = 0, FSA_KIND_SPARSE = 1, FSA_KIND_GATED = 2 };
+enum { FSA_DT_BF16 = 0, FSA_DT_FP16 = 1, FSA_DT_E4M3 = 2, FSA_DT_E5M2 = 3, FSA_DT_F32 = 4 };
+
+/* flags shared by the argument blocks */
+enum {
+  FSA_F_CAUSAL = 1u << 0,
+  FSA_F_LOCAL = 1u << 1,
+  FSA_F_SPLIT = 1u << 2,      /* split-KV (forward, decode) / split-QO (backward) */
+  FSA_F_PACK_GQA = 1u << 3,   /* rows of one query tile interleave the G heads of a KV head */
+  FSA_F_LOGSIGMOID = 1u << 4, /* gated: gate = logsigmoid(alpha*delta), else alpha*delta */
+  FSA_F_ADAPT_GATE = 1u << 5
+};
+
+/*
+ * Forward pass. Stands in for _flash_{dense,sparse,gated}_attn_forward and their varlen twins
+ * (flash_sparse_attn/ops/triton/flash_sparse_fwd.py:520-758 and :761-988, flash_dense_fwd.py,
+ * flash_gated_fwd.py) including the split-KV combine (flash_fwd_combine.py:164-232).
+ *
+ * Layouts (element strides, innermost head_dim stride must be 1):
+ *   q   [batch, seqlen_q, heads_q, head_dim]            or packed [total_q, heads_q, head_dim]
+ *   k,v [batch, seqlen_k, heads_kv, head_dim]           or packed [total_k, heads_kv, head_dim]
+ *                                                       or paged  [num_pages, page_size, heads_kv, head_dim]
+ *   out like q; lse [batch, heads_q, seqlen_q] fp32     or packed [heads_q, total_q]
+ *   out_partial [num_splits, rows, heads_q, head_dim] fp32, lse_partial [num_splits, heads_q, rows] fp32
+ *     with rows = batch*seqlen_q (or total_q); only read/written when FSA_F_SPLIT is set.
+ *   window_sizes int32 [heads_kv, 4] = (sink, left, right, near) as in
+ *     flash_sparse_attn/ops/triton/scheduler.py:56-61.
+ * Packed (varlen) mode is selected by cu_seqlens_q / cu_seqlens_k being non-null; paged mode by
+ * page_table being non-null.
+ */
+typedef struct FsaFwdArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  float* lse;
+  float* out_partial;
+  float* lse_partial;
+  const void* alpha; /* gated: [batch, heads_q, seqlen_q] (or [heads_q, total_q]), dtype of q */
+  const void* delta; /* gated: [batch, heads_kv, seqlen_k] (or [heads_kv, total_k]) */
+  const float* q_descale; /* FP8 inputs: device scalars (x = x_fp8 * descale); null otherwise */
+  const float* k_descale;
+  const float* v_descale;
+  const int32_t* cu_seqlens_q; /* [batch + 1] */
+  const int32_t* cu_seqlens_k;
+  const int32_t* seqused_q; /* [batch] */
+  const int32_t* seqused_k;
+  const int32_t* page_table;   /* [batch, page_table_stride] */
+  const int32_t* window_sizes; /* [heads_kv, window_stride] */
+  int32_t* status;             /* device word, zeroed by the caller once; set non-zero when a kernel gave up */
+  uint8_t* tile_map;           /* optional debug output, see fsa_fwd_tile_map_bytes(); may be null */
+  int64_t q_stride_b, q_stride_s, q_stride_h;
+  int64_t k_stride_b, k_stride_s, k_stride_h; /* paged: _b = page stride */
+  int64_t v_stride_b, v_stride_s, v_stride_h;
+  int64_t o_stride_b, o_stride_s, o_stride_h;
+  int64_t lse_stride_b, lse_stride_h;
+  int32_t batch, seqlen_q, seqlen_k; /* varlen: max_seqlen_q / max_seqlen_k */
+  int32_t total_q, total_k;          /* varlen: rows of the packed tensors */
+  int32_t heads_q, heads_kv, head_dim;
+  int32_t num_pages, page_size, page_table_stride, window_stride;
+  int32_t num_splits;
+  int32_t tile_m, tile_n; /* 0 = default (128, 128) */
+  int32_t kind, dtype;
+  uint32_t flags;
+  float softmax_scale, softmax_threshold, gate_threshold;
+} FsaFwdArgs;
+
+int fsa_fwd(const FsaFwdArgs* args, void* stream);
+
+/* Bytes of the optional per-tile debug map for these arguments: one byte per
+ * (batch, grid head, 128-row query tile, split, 128-key tile): 0 = not visited, 1 = computed,
+ * 2 = skipped by the softmax threshold, 3 = skipped by the gate bound. */
+size_t fsa_fwd_tile_map_bytes(const FsaFwdArgs* args);
+
+/* Integer schedule of one forward query tile, for checking against the reference's
+ * AttnFwdBlockScheduler.create (flash_sparse_attn/ops/triton/scheduler.py:836-948). out9 receives
+ * n_min, n_max, n_max_no_mask, win_min, win_max, win_min_no_mask, win_max_no_mask, sink_min, sink_max.
+ * Pure host arithmetic: callable without a GPU. */
+void fsa_debug_fwd_schedule(int seqlen_q, int seqlen_k, int m_block, int split_idx, const int32_t window[4],
+                            int num_splits, int tile_n, int tile_m, int is_causal, int is_local, int is_split,
+                            int qhead_per_kvhead_packgqa, int32_t out9[9]);
+/* Same for one backward key tile (AttnBwdBlockScheduler.create, scheduler.py:994-1101): m_min, m_max,
+ * m_min_no_mask, win_min, win_max, win_min_no_mask, win_max_no_mask, sink_min, sink_max. */
+void fsa_debug_bwd_schedule(int seqlen_q, int seqlen_k, int n_block, int split_idx, const int32_t window[4],
+                            int num_splits, int tile_n, int tile_m, int is_causal, int is_local, int is_split,
+                            int32_t out9[9]);
+
+const char* fsa_status_string(int code);
+int fsa_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FSA_B200_H_ */
