@@ -17,8 +17,10 @@
 //
 // TMEM columns: S0 | S1 | O0 | O1, 128 each (O uses HD columns). P (16-bit) is written back over the
 // first 64 columns of its own S block and consumed from TMEM as the A operand of P V.
-// The running output lives in registers: every P V lands in a fresh O tile that the owning
-// softmax thread adds to its row accumulator before it publishes the next P.
+// The output accumulates in TMEM across key tiles. A softmax thread keeps a reference maximum per
+// row that is only moved (and O rescaled in TMEM) when the true running maximum has drifted by
+// more than 2^8 from it: sums and outputs stay exact up to rounding because every term carries the
+// same reference, and the skip rule reads the same in terms of the reference pair (m, l).
 #include "fsa_ptx.cuh"
 #include "fsa_params.h"
 #include "fsa_schedule.h"
@@ -47,7 +49,7 @@ struct FwdBars {
   uint64_t q_full;
   uint64_t k_full[KSTAGES], k_empty[KSTAGES];
   uint64_t v_full[VSTAGES], v_empty[VSTAGES];
-  uint64_t s_full[2], p_full[2], o_full[2], vote[2], wg_sync[2];
+  uint64_t s_full[2], p_full[2], o_final[2], vote[2], wg_sync[2];
   uint32_t tmem_base;
   int abort_flag;
   int skip_flag[2][2];   // [group][parity of the group's tile counter]
@@ -61,23 +63,53 @@ struct SeqInfo {
 };
 
 // Row-local view of the masks in flash_sparse_attn/ops/triton/mask.py:60-102: for one query row
-// the visible key columns form up to three intervals.
+// the visible key columns form up to three intervals (near band, distant band, sink prefix).
 struct RowMask {
-  int diag;     // last causally visible column: q_idx + (sk - sq)
-  int near_lo;  // near band  = (near_lo, diag]
+  int diag;            // last causally visible column: q_idx + (sk - sq)
+  int near_lo;         // near band    = (near_lo, diag]
   int far_lo, far_hi;  // distant band = (far_lo, far_hi]
-  int sink_hi;  // sink = [0, sink_hi)
+  int sink_hi;         // sink         = [0, sink_hi) intersected with [0, diag]
   int sk;
   bool row_ok;
 };
 
-__device__ __forceinline__ bool col_visible(const RowMask& rm, int mode, int k) {
-  if (!(rm.row_ok && k < rm.sk)) return false;
-  if (mode == FSA_MASK_SEQLEN) return true;
-  if (mode == FSA_MASK_CAUSAL) return k <= rm.diag;
-  bool ok = (k <= rm.diag && k > rm.near_lo) || (k <= rm.far_hi && k > rm.far_lo);
-  if (mode == FSA_MASK_LOCAL_SINK) ok = ok || (k < rm.sink_hi && k <= rm.diag);
-  return ok;
+// Visible columns of one row inside key tile [k0, k0 + TN), as three half-open intervals of the
+// tile-local index, already clipped to the key length. Unused intervals are empty (len 0).
+struct TileMask {
+  int lo[3];
+  unsigned len[3];
+};
+
+__device__ __forceinline__ TileMask make_tile_mask(const RowMask& rm, int mode, int k0) {
+  TileMask tm;
+  const int seq_hi = rm.row_ok ? min(rm.sk - k0, TN) : 0;
+  auto clip = [&](int idx, int a, int b) {  // [a, b) in key coordinates -> tile-local, clipped
+    a = max(a - k0, 0);
+    b = min(b - k0, seq_hi);
+    tm.lo[idx] = a;
+    tm.len[idx] = b > a ? unsigned(b - a) : 0u;
+  };
+  if (mode == FSA_MASK_SEQLEN) {
+    clip(0, 0, rm.sk);
+    clip(1, 0, 0);
+    clip(2, 0, 0);
+  } else if (mode == FSA_MASK_CAUSAL) {
+    clip(0, 0, rm.diag + 1);
+    clip(1, 0, 0);
+    clip(2, 0, 0);
+  } else {
+    clip(0, rm.near_lo + 1, rm.diag + 1);
+    clip(1, rm.far_lo + 1, rm.far_hi + 1);
+    if (mode == FSA_MASK_LOCAL_SINK)
+      clip(2, 0, min(rm.sink_hi, rm.diag + 1));
+    else
+      clip(2, 0, 0);
+  }
+  return tm;
+}
+__device__ __forceinline__ bool tile_col_visible(const TileMask& tm, int i) {
+  return (unsigned(i - tm.lo[0]) < tm.len[0]) | (unsigned(i - tm.lo[1]) < tm.len[1]) |
+         (unsigned(i - tm.lo[2]) < tm.len[2]);
 }
 
 template <int HD, typename T, int KIND>
@@ -168,7 +200,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     for (int q = 0; q < 2; ++q) {
       mbar_init(&bars->s_full[q], 1);
       mbar_init(&bars->p_full[q], 4);  // one arrival per warp of the group
-      mbar_init(&bars->o_full[q], 1);
+      mbar_init(&bars->o_final[q], 1);
       mbar_init(&bars->vote[q], 1);
       mbar_init(&bars->wg_sync[q], 4);
     }
@@ -293,6 +325,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     const uint32_t sQ = smem_u32(smem + SM::kQ), sK = smem_u32(smem + SM::kK), sV = smem_u32(smem + SM::kV);
     bool ok = !*abort_flag;
     int cnt[2] = {0, 0};
+    bool o_started[2] = {false, false};
     int n = first_tile();
     auto issue_s = [&](int q, int ks) {
       if (lane == 0) {
@@ -354,12 +387,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
 #pragma unroll
               for (int kk = 0; kk < KK_PV; ++kk) {
                 umma_ts(tmem_base + TMEM_O0 + q * 128, tmem_base + TMEM_S0 + q * 128 + kk * 8,
-                        umma_smem_desc(sV + vs * SM::kTileBytes + kk * 2048, TN * 128, 1024), idesc_o, kk > 0);
+                        umma_smem_desc(sV + vs * SM::kTileBytes + kk * 2048, TN * 128, 1024), idesc_o,
+                        (kk > 0 || o_started[q]) ? 1u : 0u);
               }
-              umma_commit(&bars->o_full[q]);
             }
             __syncwarp();
+            o_started[q] = true;
             any_pv = true;
+          }
+          // last key tile of this group: tell it when its output is complete
+          if (fsa_fwd_next_tile_below(sched[q], n, local) < 0) {
+            if (lane == 0) umma_commit(&bars->o_final[q]);
+            __syncwarp();
           }
         }
         if (n_next >= 0 && fsa_fwd_tile_mode(sched[q], n_next, causal, local) >= 0) {
@@ -412,6 +451,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     rm.far_hi = rm.diag - si.w.near_ - si.w.right;
     rm.far_lo = rm.far_hi - si.w.left;
     rm.sink_hi = si.w.sink;
+    const FsaFwdSched my = sched[q];  // registers, not the indexed copy
 
     float thr_log2 = 0.f;
     if (KIND != KIND_DENSE) {
@@ -420,30 +460,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       thr_log2 = log2f(fmaxf(fminf(p.softmax_thr / visible, 1.0f), 0.0f));
     }
     const float c = p.scale_log2;
-    float row_max = -INFINITY, row_sum = 0.f;
-    float o_acc[HD];
-#pragma unroll
-    for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
-    bool pending_o = false;
-    int cnt_s = 0, cnt_o = 0;
+    float m_ref = -INFINITY;  // reference maximum all stored exponentials are relative to
+    float l_ref = 0.f;        // sum of exp2((s - m_ref) * c)
+    bool have_o = false;      // some P V has been issued for this tile
+    int cnt_s = 0;
     bool ok = !*abort_flag;
-    const bool has_work = q_valid[q] && !fsa_fwd_sched_empty(sched[q]);
+    const bool has_work = q_valid[q] && !fsa_fwd_sched_empty(my);
 
-    auto add_o_tile = [&](float scale) {
-      // o_acc = (o_acc + O_tile) * scale
-#pragma unroll
-      for (int ch = 0; ch < OCH; ++ch) {
-        uint32_t r[32];
-        tmem_ld32(tO + ch * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o_acc[ch * 32 + i] = (o_acc[ch * 32 + i] + __uint_as_float(r[i])) * scale;
-      }
-    };
-
-    for (int n = fsa_fwd_next_tile_below(sched[q], 1 << 28, local); n >= 0 && ok && has_work;
-         n = fsa_fwd_next_tile_below(sched[q], n, local)) {
-      const int mode = fsa_fwd_tile_mode(sched[q], n, causal, local);
+    for (int n = fsa_fwd_next_tile_below(my, 1 << 28, local); n >= 0 && ok && has_work;
+         n = fsa_fwd_next_tile_below(my, n, local)) {
+      const int mode = fsa_fwd_tile_mode(my, n, causal, local);
       ok = mbar_wait(&bars->s_full[q], cnt_s & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
@@ -451,31 +477,37 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       cnt_s++;
       const int k0 = n * TN;
 
-      // ---- pass 1: masked row maximum ----------------------------------------------------------
-      // (TMEM loads are warp-collective: every lane takes the same path, per-row special cases
-      // are applied to the values afterwards)
-      float m_cur = -INFINITY;
+      // ---- scores of this row: TMEM -> registers (warp-collective loads, one wait) ---------------
+      uint32_t sr[TN];
 #pragma unroll
-      for (int ch = 0; ch < TN / 32; ++ch) {
-        uint32_t r[32];
-        tmem_ld32(tS + ch * 32, r);
-        tmem_ld_wait();
-        if (mode == FSA_MASK_NONE) {
+      for (int ch = 0; ch < TN / 32; ++ch) tmem_ld32(tS + ch * 32, &sr[ch * 32]);
+      tmem_ld_wait();
+      if (mode != FSA_MASK_NONE) {
+        const TileMask tm = make_tile_mask(rm, mode, k0);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) m_cur = fmaxf(m_cur, __uint_as_float(r[i]));
-        } else {
+        for (int i = 0; i < TN; ++i)
+          if (!tile_col_visible(tm, i)) sr[i] = 0xff800000u;  // -inf
+      } else if (!rm.row_ok) {
+        // rows past the query length read as zero scores in fully visible tiles
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (col_visible(rm, mode, k0 + ch * 32 + i)) m_cur = fmaxf(m_cur, __uint_as_float(r[i]));
-        }
+        for (int i = 0; i < TN; ++i) sr[i] = 0u;
       }
-      // rows past the query length read as zero scores in fully visible tiles
-      if (mode == FSA_MASK_NONE && !rm.row_ok) m_cur = 0.f;
+
+      // ---- row maximum ------------------------------------------------------------------------------
+      float mx[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        mx[j] = fmaxf(__uint_as_float(sr[j * 32]), __uint_as_float(sr[j * 32 + 1]));
+#pragma unroll
+        for (int i = 2; i < 32; i += 2)
+          mx[j] = max3(mx[j], __uint_as_float(sr[j * 32 + i]), __uint_as_float(sr[j * 32 + i + 1]));
+      }
+      const float m_cur = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
 
       // ---- tile skip vote (flash_sparse_attn/ops/triton/activations.py:129-138) -----------------
       bool skip = false;
       if (KIND != KIND_DENSE) {
-        const float d = (m_cur - row_max) * c - log2f(row_sum);
+        const float d = (m_cur - m_ref) * c - log2f(l_ref);
         const float val = d - thr_log2;
         const unsigned want = __ballot_sync(0xffffffffu, val >= 0.0f);
         const unsigned drop = __ballot_sync(0xffffffffu, val < 0.0f);
@@ -510,48 +542,46 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
         continue;
       }
 
-      // ---- online softmax update ------------------------------------------------------------------
-      float m_new = fmaxf(m_cur, row_max);
-      if (mode != FSA_MASK_NONE) m_new = fmaxf(m_new, -1e6f);
-      const float scale = ex2_approx((row_max - m_new) * c);
-      row_max = m_new;
-      const float m_c = m_new * c;
-
-      // the previous P V result must be folded in before its TMEM tile is overwritten
-      if (pending_o) {
-        ok = mbar_wait(&bars->o_full[q], cnt_o & 1, abort_flag);
-        if (!ok) break;
-        cnt_o++;
-        tc_fence_after();
-        add_o_tile(scale);
-        pending_o = false;
-      } else {
+      // ---- move the reference maximum only when it lags by more than 2^8 -------------------------
+      float m_cand = fmaxf(m_cur, m_ref);
+      if (mode != FSA_MASK_NONE) m_cand = fmaxf(m_cand, -1e6f);
+      const bool need = !((m_cand - m_ref) * c <= 8.0f);  // also true on the first tile (m_ref = -inf)
+      float scale = 1.0f;
+      if (need) {
+        scale = ex2_approx((m_ref - m_cand) * c);
+        m_ref = m_cand;
+        l_ref *= scale;
+      }
+      // s_full for this tile was committed after the previous P V of this group, so O is at rest
+      if (have_o && __any_sync(0xffffffffu, need)) {
 #pragma unroll
-        for (int i = 0; i < HD; ++i) o_acc[i] *= scale;
+        for (int ch = 0; ch < OCH; ++ch) {
+          uint32_t r[32];
+          tmem_ld32(tO + ch * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * scale);
+          tmem_st32(tO + ch * 32, r);
+        }
       }
 
-      // ---- pass 2: P = exp2(S*c - m*c), row sum, publish P in TMEM ----------------------------------
-      float sum = 0.f;
+      // ---- P = exp2(S*c - m*c), row sum, publish P (16-bit pairs) over the S columns -----------------
+      const float2 c2 = make_float2(c, c);
+      const float neg_mc = -(m_ref * c);
+      const float2 nm2 = make_float2(neg_mc, neg_mc);
+      float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
       for (int ch = 0; ch < TN / 32; ++ch) {
-        uint32_t r[32];
-        tmem_ld32(tS + ch * 32, r);
-        tmem_ld_wait();
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float s0 = __uint_as_float(r[i]), s1 = __uint_as_float(r[i + 1]);
-          if (mode == FSA_MASK_NONE) {
-            if (!rm.row_ok) s0 = s1 = 0.f;
-          } else {
-            if (!col_visible(rm, mode, k0 + ch * 32 + i)) s0 = -INFINITY;
-            if (!col_visible(rm, mode, k0 + ch * 32 + i + 1)) s1 = -INFINITY;
-          }
-          const float p0 = ex2_approx(fmaf(s0, c, -m_c));
-          const float p1 = ex2_approx(fmaf(s1, c, -m_c));
-          sum += p0;
-          sum += p1;
-          pk[i >> 1] = pack2<T>(p0, p1);
+          const float2 t = fma2(make_float2(__uint_as_float(sr[ch * 32 + i]), __uint_as_float(sr[ch * 32 + i + 1])),
+                                c2, nm2);
+          float2 e;
+          e.x = ex2_approx(t.x);
+          e.y = ex2_approx(t.y);
+          sum2[(i >> 1) & 1] = add2(sum2[(i >> 1) & 1], e);
+          pk[i >> 1] = pack2<T>(e.x, e.y);
         }
         tmem_st16(tS + ch * 16, pk);
       }
@@ -559,46 +589,56 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_full[q]);
-      row_sum = row_sum * scale + sum;
-      pending_o = true;
-    }
-
-    if (ok && pending_o) {
-      ok = mbar_wait(&bars->o_full[q], cnt_o & 1, abort_flag);
-      if (ok) {
-        tc_fence_after();
-        add_o_tile(1.0f);
-      }
+      l_ref += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
+      have_o = true;
     }
 
     // ---- epilogue (flash_sparse_attn/ops/triton/activations.py:169-203) ---------------------------
-    if (ok && q_valid[q] && rm.row_ok) {
-      const bool dead = (row_sum == 0.0f) || (row_sum != row_sum);
-      const float inv = dead ? 1.0f : p.v_scale / row_sum;
-      float lse = dead ? -INFINITY : row_max * c + log2f(row_sum);
+    if (ok && have_o) {
+      ok = mbar_wait(&bars->o_final[q], 0, abort_flag);
+      tc_fence_after();
+    }
+    if (ok && q_valid[q]) {
+      const bool dead = (l_ref == 0.0f) || (l_ref != l_ref);
+      const float inv = dead ? 1.0f : p.v_scale / l_ref;
+      float lse = dead ? -INFINITY : m_ref * c + log2f(l_ref);
       if (!(p.flags & F_LSE_LOG2)) lse *= 0.6931471805599453f;
       const long long tok = si.off_q + q_idx;
-      p.lse[(long long)((p.flags & F_VARLEN_Q) ? 0 : si.b) * p.l_sb + (long long)q_head * p.l_sh +
-            (long long)si.split * p.l_ss + ((p.flags & F_VARLEN_Q) ? tok : q_idx)] = lse;
+      if (rm.row_ok)
+        p.lse[(long long)((p.flags & F_VARLEN_Q) ? 0 : si.b) * p.l_sb + (long long)q_head * p.l_sh +
+              (long long)si.split * p.l_ss + ((p.flags & F_VARLEN_Q) ? tok : q_idx)] = lse;
       const long long obase = (long long)((p.flags & F_VARLEN_Q) ? 0 : si.b) * p.o_sb + tok * p.o_sm +
                               (long long)q_head * p.o_sh + (long long)si.split * p.o_ss;
-      if (p.flags & F_SPLIT) {
-        float* dst = reinterpret_cast<float*>(p.out) + obase;
 #pragma unroll
-        for (int i = 0; i < HD; i += 4) {
-          *reinterpret_cast<float4*>(dst + i) =
-              make_float4(o_acc[i] * inv, o_acc[i + 1] * inv, o_acc[i + 2] * inv, o_acc[i + 3] * inv);
+      for (int ch = 0; ch < OCH; ++ch) {
+        uint32_t r[32];
+        if (have_o) {
+          tmem_ld32(tO + ch * 32, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
         }
-      } else {
-        T* dst = reinterpret_cast<T*>(p.out) + obase;
+        if (rm.row_ok) {
+          if (p.flags & F_SPLIT) {
+            float* dst = reinterpret_cast<float*>(p.out) + obase + ch * 32;
 #pragma unroll
-        for (int i = 0; i < HD; i += 8) {
-          uint4 v;
-          v.x = pack2<T>(o_acc[i] * inv, o_acc[i + 1] * inv);
-          v.y = pack2<T>(o_acc[i + 2] * inv, o_acc[i + 3] * inv);
-          v.z = pack2<T>(o_acc[i + 4] * inv, o_acc[i + 5] * inv);
-          v.w = pack2<T>(o_acc[i + 6] * inv, o_acc[i + 7] * inv);
-          *reinterpret_cast<uint4*>(dst + i) = v;
+            for (int i = 0; i < 32; i += 4)
+              *reinterpret_cast<float4*>(dst + i) =
+                  make_float4(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv,
+                              __uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+          } else {
+            T* dst = reinterpret_cast<T*>(p.out) + obase + ch * 32;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 v;
+              v.x = pack2<T>(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+              v.y = pack2<T>(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+              v.z = pack2<T>(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+              v.w = pack2<T>(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + i) = v;
+            }
+          }
         }
       }
     }
