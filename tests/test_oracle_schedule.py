@@ -1,0 +1,124 @@
+"""The oracle's tile schedule is an exact cover of the eager mask, and the library's C schedule
+(host arithmetic behind the C ABI) agrees with the oracle number for number."""
+
+import itertools
+import random
+
+import pytest
+
+from oracle import schedule as S
+
+WINDOWS = [[0, 256, 0, 0], [0, 0, 0, 256], [0, 1024, 0, 0], [64, 94, 188, 256], [64, 94, 0, 256], [0, 300, 100, 200],
+           [40, 100, 37, 77]]
+SHAPES = [(1024, 1024), (987, 1024), (300, 1024)]
+TILES = [(64, 64), (128, 128), (128, 64), (64, 128)]
+
+
+def _cover_fwd(sq, sk, window, tm, tn, causal, local, ns, split, gpack=1):
+    seen = {}
+    m_blocks = -(-sq * gpack // tm)
+    for mb in range(m_blocks):
+        for sp in range(ns):
+            sched = S.fwd_schedule(sq, sk, mb, sp, window, ns, tn, tm, causal, local, split, gpack)
+            if sched.is_empty():
+                continue
+            for n, mode in S.fwd_tiles(sched, causal, local):
+                for r in range(tm):
+                    qi = (mb * tm + r) // gpack
+                    g = (mb * tm + r) % gpack
+                    if qi >= sq:
+                        continue
+                    for kk in range(n * tn, min((n + 1) * tn, sk)):
+                        if S.visible(qi, kk, sq, sk, window, mode):
+                            key = (qi, g, kk)
+                            seen[key] = seen.get(key, 0) + 1
+    return seen
+
+
+def _expected(sq, sk, window, causal, local, gpack=1):
+    exp = set()
+    for qi in range(sq):
+        for kk in range(sk):
+            if S.allowed(qi, kk, sq, sk, window, causal, local):
+                for g in range(gpack):
+                    exp.add((qi, g, kk))
+    return exp
+
+
+@pytest.mark.parametrize("window", WINDOWS[:4])
+@pytest.mark.parametrize("ns", [1, 3])
+def test_fwd_exact_cover_local(window, ns):
+    # small sizes keep the pure-Python brute force to seconds; windows scaled down with them
+    scale = 8
+    w = [x // scale for x in window]
+    for (sq, sk), (tm, tn) in itertools.product([(128, 128), (123, 128), (37, 128)], [(16, 16), (32, 16), (16, 32)]):
+        seen = _cover_fwd(sq, sk, w, tm, tn, True, True, ns, ns > 1)
+        assert set(seen) == _expected(sq, sk, w, True, True), (sq, sk, tm, tn, w, ns)
+        assert all(v == 1 for v in seen.values())
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("ns", [1, 2, 5])
+def test_fwd_exact_cover_nonlocal(causal, ns):
+    for (sq, sk), (tm, tn) in itertools.product([(128, 128), (123, 128), (37, 128), (128, 100)], [(16, 16), (32, 16)]):
+        if causal and sq > sk:
+            continue
+        seen = _cover_fwd(sq, sk, [0, 0, 0, 0], tm, tn, causal, False, ns, ns > 1)
+        assert set(seen) == _expected(sq, sk, [0, 0, 0, 0], causal, False)
+        assert all(v == 1 for v in seen.values())
+
+
+def test_fwd_exact_cover_pack_gqa():
+    for gpack in (2, 4):
+        seen = _cover_fwd(60, 96, [0, 0, 0, 0], 16, 16, True, False, 1, False, gpack)
+        assert set(seen) == _expected(60, 96, [0, 0, 0, 0], True, False, gpack)
+        assert all(v == 1 for v in seen.values())
+
+
+@pytest.mark.parametrize("local", [False, True])
+@pytest.mark.parametrize("ns", [1, 3])
+def test_bwd_exact_cover(local, ns):
+    window = [8, 12, 23, 32] if local else [0, 0, 0, 0]
+    for (sq, sk), (tm, tn), causal in itertools.product([(128, 128), (123, 128), (37, 128)], [(16, 16), (32, 16), (16, 32)],
+                                                        [True, False]):
+        if local and not causal:
+            continue
+        seen = {}
+        for nb in range(-(-sk // tn)):
+            for sp in range(ns):
+                sched = S.bwd_schedule(sq, sk, nb, sp, window, ns, tn, tm, causal, local, ns > 1)
+                if sched.is_empty():
+                    continue
+                for m, mode in S.bwd_tiles(sched, causal, local):
+                    for qi in range(m * tm, min((m + 1) * tm, sq)):
+                        for kk in range(nb * tn, min((nb + 1) * tn, sk)):
+                            if S.visible(qi, kk, sq, sk, window, mode):
+                                seen[(qi, kk)] = seen.get((qi, kk), 0) + 1
+        exp = {(qi, kk) for qi in range(sq) for kk in range(sk) if S.allowed(qi, kk, sq, sk, window, causal, local)}
+        assert set(seen) == exp, (sq, sk, tm, tn, causal, local, ns)
+        assert all(v == 1 for v in seen.values())
+
+
+def test_c_schedule_matches_oracle():
+    from flash_sparse_attn import _lib
+
+    rng = random.Random(0)
+    for _ in range(3000):
+        tm, tn = rng.choice(TILES)
+        sk = rng.randint(1, 3000)
+        sq = rng.choice([1, sk, rng.randint(1, sk)])
+        local = rng.random() < 0.6
+        causal = rng.random() < 0.6
+        window = [rng.choice([0, 17, 64, 130]), rng.randint(0, 600), rng.randint(0, 400), rng.randint(0, 700)]
+        ns = rng.choice([1, 1, 2, 3, 7])
+        split = ns > 1 or rng.random() < 0.2
+        gpack = rng.choice([1, 1, 2, 4, 8])
+        mb = rng.randint(0, max(0, -(-sq * gpack // tm) - 1))
+        sp = rng.randint(0, ns - 1)
+        ref = S.fwd_schedule(sq, sk, mb, sp, window, ns, tn, tm, causal, local, split, gpack).as_list()
+        got = _lib.debug_fwd_schedule(sq, sk, mb, sp, window, ns, tn, tm, causal, local, split, gpack)
+        assert got == ref, ("fwd", sq, sk, mb, sp, window, ns, tn, tm, causal, local, split, gpack)
+        nb = rng.randint(0, max(0, -(-sk // tn) - 1))
+        ref = S.bwd_schedule(sq, sk, nb, sp, window, ns, tn, tm, causal, local, split).as_list()
+        got = _lib.debug_bwd_schedule(sq, sk, nb, sp, window, ns, tn, tm, causal, local, split)
+        assert got == ref, ("bwd", sq, sk, nb, sp, window, ns, tn, tm, causal, local, split)
