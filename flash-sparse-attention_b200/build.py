@@ -19,6 +19,7 @@ SOURCES = [
     "fsa_api.cu",
     "fsa_aux.cu",
     "fsa_fwd_sm100.cu",
+    "fsa_bwd_sm100.cu",
 ]
 
 NVCC_FLAGS = [

@@ -38,6 +38,21 @@ CUtensorMapDataType tma_dtype(int dt) {
 }
 int dtype_bytes(int dt) { return (dt == FSA_DT_BF16 || dt == FSA_DT_FP16) ? 2 : (dt == FSA_DT_F32 ? 4 : 1); }
 
+// 3-D map over the fp32 dQ accumulator [heads, rows, head_dim] with 32 x 32 boxes (one warp's share).
+int make_map_dq(CUtensorMap* map, const float* base, uint64_t head_dim, uint64_t rows, uint64_t heads) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return FSA_ERR_NO_DRIVER;
+  if (reinterpret_cast<uintptr_t>(base) & 15) return FSA_ERR_INVALID_ARG;
+  cuuint64_t dims[3] = {head_dim, rows, heads};
+  cuuint64_t strides[2] = {head_dim * 4, rows * head_dim * 4};
+  cuuint32_t box[3] = {32, 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FSA_OK : FSA_ERR_LAUNCH;
+}
+
 // 4-D map over a [d3, d2, d1, head_dim] tensor (head_dim contiguous); strides in elements.
 int make_map4(CUtensorMap* map, int dt, const void* base, uint64_t head_dim, uint64_t d1, int64_t s1, uint64_t d2,
               int64_t s2, uint64_t d3, int64_t s3, uint32_t box0, uint32_t box1, uint32_t box2) {
@@ -288,6 +303,175 @@ int fsa_fwd(const FsaFwdArgs* a, void* stream_) {
     c.num_splits = ns;
     e = fsa::launch_combine(c, a->dtype, stream);
     if (e != cudaSuccess) return FSA_ERR_LAUNCH;
+  }
+  return FSA_OK;
+}
+
+int64_t fsa_bwd_padded_rows(int batch, int seqlen_q, int total_q, int is_varlen) {
+  if (is_varlen) return ((int64_t)total_q + 128ll * batch + 127) / 128 * 128;
+  return (int64_t)batch * (((int64_t)seqlen_q + 127) / 128 * 128);
+}
+
+int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
+  if (!a || !a->q || !a->k || !a->v || !a->out || !a->dout || !a->lse || !a->dq || !a->dk || !a->dv || !a->status)
+    return FSA_ERR_INVALID_ARG;
+  if (!a->lse2_ws || !a->dpsum_ws || !a->dq_accum) return FSA_ERR_INVALID_ARG;
+  if (a->batch <= 0 || a->heads_q <= 0 || a->heads_kv <= 0 || a->heads_q % a->heads_kv) return FSA_ERR_INVALID_ARG;
+  if (a->head_dim != 64 && a->head_dim != 128) return FSA_ERR_UNSUPPORTED;
+  if (a->dtype != FSA_DT_BF16 && a->dtype != FSA_DT_FP16) return FSA_ERR_UNSUPPORTED;
+  if (a->kind != FSA_KIND_DENSE && a->kind != FSA_KIND_SPARSE) return FSA_ERR_UNSUPPORTED;
+  if ((a->tile_m && a->tile_m != 128) || (a->tile_n && a->tile_n != 128)) return FSA_ERR_UNSUPPORTED;
+  if ((a->flags & FSA_F_LOCAL) && !a->window_sizes) return FSA_ERR_INVALID_ARG;
+  if (a->dk_stride_b % 8 || a->dk_stride_s % 8 || a->dk_stride_h % 8) return FSA_ERR_INVALID_ARG;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  const bool varlen_q = a->cu_seqlens_q != nullptr, varlen_k = a->cu_seqlens_k != nullptr;
+  const int ns = (a->flags & FSA_F_SPLIT) ? a->num_splits : 1;
+  if (ns <= 0) return FSA_ERR_INVALID_ARG;
+  const bool split = ns > 1;
+  if (split && (!a->dk_partial || !a->dv_partial)) return FSA_ERR_INVALID_ARG;
+  if (a->seqlen_q <= 0 || a->seqlen_k <= 0) return FSA_OK;
+  const int64_t R = fsa_bwd_padded_rows(a->batch, a->seqlen_q, a->total_q, varlen_q);
+  const long long rows_k = varlen_k ? a->total_k : (long long)a->batch * a->seqlen_k;
+
+  // pre-pass + accumulator reset
+  fsa::BwdPreParams pre;
+  memset(&pre, 0, sizeof(pre));
+  pre.out = a->out;
+  pre.dout = a->dout;
+  pre.lse = a->lse;
+  pre.lse2_ws = a->lse2_ws;
+  pre.dpsum_ws = a->dpsum_ws;
+  pre.cu_q = a->cu_seqlens_q;
+  pre.o_sb = a->o_stride_b;
+  pre.o_sm = a->o_stride_s;
+  pre.o_sh = a->o_stride_h;
+  pre.do_sb = a->do_stride_b;
+  pre.do_sm = a->do_stride_s;
+  pre.do_sh = a->do_stride_h;
+  pre.l_sb = a->lse_stride_b;
+  pre.l_sh = a->lse_stride_h;
+  pre.ws_sh = R;
+  pre.B = a->batch;
+  pre.sq = a->seqlen_q;
+  pre.total_q = a->total_q;
+  pre.heads = a->heads_q;
+  pre.head_dim = a->head_dim;
+  pre.varlen = varlen_q;
+  if (fsa::launch_bwd_pre(pre, a->dtype, stream) != cudaSuccess) return FSA_ERR_LAUNCH;
+  if (cudaMemsetAsync(a->dq_accum, 0, sizeof(float) * (size_t)a->heads_q * R * a->head_dim, stream) != cudaSuccess)
+    return FSA_ERR_LAUNCH;
+
+  fsa::BwdKernelParams p;
+  memset(&p, 0, sizeof(p));
+  int rc;
+  {
+    const uint64_t d_rows = varlen_q ? (uint64_t)a->total_q : (uint64_t)a->seqlen_q;
+    const uint64_t d_b = varlen_q ? 1 : (uint64_t)a->batch;
+    rc = make_map4(&p.map_q, a->dtype, a->q, a->head_dim, a->heads_q, a->q_stride_h, d_rows, a->q_stride_s, d_b,
+                   varlen_q ? a->q_stride_s * (int64_t)a->total_q : a->q_stride_b, 64, 1, 128);
+    if (rc != FSA_OK) return rc;
+    rc = make_map4(&p.map_do, a->dtype, a->dout, a->head_dim, a->heads_q, a->do_stride_h, d_rows, a->do_stride_s, d_b,
+                   varlen_q ? a->do_stride_s * (int64_t)a->total_q : a->do_stride_b, 64, 1, 128);
+    if (rc != FSA_OK) return rc;
+  }
+  {
+    const uint64_t d_rows = varlen_k ? (uint64_t)a->total_k : (uint64_t)a->seqlen_k;
+    const uint64_t d_b = varlen_k ? 1 : (uint64_t)a->batch;
+    rc = make_map4(&p.map_k, a->dtype, a->k, a->head_dim, a->heads_kv, a->k_stride_h, d_rows, a->k_stride_s, d_b,
+                   varlen_k ? a->k_stride_s * (int64_t)a->total_k : a->k_stride_b, 64, 1, 128);
+    if (rc != FSA_OK) return rc;
+    rc = make_map4(&p.map_v, a->dtype, a->v, a->head_dim, a->heads_kv, a->v_stride_h, d_rows, a->v_stride_s, d_b,
+                   varlen_k ? a->v_stride_s * (int64_t)a->total_k : a->v_stride_b, 64, 1, 128);
+    if (rc != FSA_OK) return rc;
+  }
+  rc = make_map_dq(&p.map_dq, a->dq_accum, a->head_dim, R, a->heads_q);
+  if (rc != FSA_OK) return rc;
+  p.lse2_ws = a->lse2_ws;
+  p.dpsum_ws = a->dpsum_ws;
+  p.cu_q = a->cu_seqlens_q;
+  p.cu_k = a->cu_seqlens_k;
+  p.used_q = a->seqused_q;
+  p.used_k = a->seqused_k;
+  p.windows = a->window_sizes;
+  p.status = a->status;
+  p.tile_map = a->tile_map;
+  if (split) {
+    p.dk_out = a->dk_partial;
+    p.dv_out = a->dv_partial;
+    p.dkv_sb = (long long)a->seqlen_k * a->heads_kv * a->head_dim;
+    p.dkv_sn = (long long)a->heads_kv * a->head_dim;
+    p.dkv_sh = a->head_dim;
+    p.dkv_ss = rows_k * a->heads_kv * a->head_dim;
+  } else {
+    p.dk_out = a->dk;
+    p.dv_out = a->dv;
+    p.dkv_sb = a->dk_stride_b;
+    p.dkv_sn = a->dk_stride_s;
+    p.dkv_sh = a->dk_stride_h;
+    p.dkv_ss = 0;
+  }
+  p.ws_sh = R;
+  p.B = a->batch;
+  p.Hq = a->heads_q;
+  p.Hkv = a->heads_kv;
+  p.G = a->heads_q / a->heads_kv;
+  p.sq = a->seqlen_q;
+  p.sk = a->seqlen_k;
+  p.num_splits = ns;
+  p.n_tiles_k = cdiv(a->seqlen_k, 128);
+  p.num_m_blocks = cdiv(a->seqlen_q, 128);
+  p.win_stride = a->window_stride;
+  p.scale_log2 = a->softmax_scale * 1.44269504089f;
+  p.softmax_scale = a->softmax_scale;
+  p.softmax_thr = a->softmax_threshold;
+  unsigned f = 0;
+  if (a->flags & FSA_F_CAUSAL) f |= fsa::F_CAUSAL;
+  if (a->flags & FSA_F_LOCAL) f |= fsa::F_LOCAL;
+  if (split) f |= fsa::F_SPLIT;
+  if (varlen_q) f |= fsa::F_VARLEN_Q;
+  if (varlen_k) f |= fsa::F_VARLEN_K;
+  if (a->seqused_q) f |= fsa::F_USED_Q;
+  if (a->seqused_k) f |= fsa::F_USED_K;
+  p.flags = f;
+  cudaError_t e = fsa::launch_bwd(p, a->kind, a->dtype, a->head_dim, stream);
+  if (e == cudaErrorInvalidValue) return FSA_ERR_UNSUPPORTED;
+  if (e != cudaSuccess) return FSA_ERR_LAUNCH;
+
+  fsa::BwdPostParams post;
+  memset(&post, 0, sizeof(post));
+  post.dq_accum = a->dq_accum;
+  post.dq = a->dq;
+  post.cu_q = a->cu_seqlens_q;
+  post.dq_sb = a->dq_stride_b;
+  post.dq_sm = a->dq_stride_s;
+  post.dq_sh = a->dq_stride_h;
+  post.ws_sh = R;
+  post.B = a->batch;
+  post.sq = a->seqlen_q;
+  post.total_q = a->total_q;
+  post.heads = a->heads_q;
+  post.head_dim = a->head_dim;
+  post.varlen = varlen_q;
+  post.scale = a->softmax_scale;
+  if (fsa::launch_bwd_post(post, a->dtype, stream) != cudaSuccess) return FSA_ERR_LAUNCH;
+
+  if (split) {
+    for (int which = 0; which < 2; ++which) {
+      fsa::SplitSumParams sp;
+      memset(&sp, 0, sizeof(sp));
+      sp.partial = which == 0 ? a->dk_partial : a->dv_partial;
+      sp.out = which == 0 ? a->dk : a->dv;
+      sp.part_ss = p.dkv_ss;
+      sp.o_sb = varlen_k ? 0 : a->dk_stride_b;
+      sp.o_sn = a->dk_stride_s;
+      sp.o_sh = a->dk_stride_h;
+      sp.rows = (int)rows_k;
+      sp.rows_per_batch = varlen_k ? a->total_k : a->seqlen_k;
+      sp.heads = a->heads_kv;
+      sp.head_dim = a->head_dim;
+      sp.num_splits = ns;
+      if (fsa::launch_split_sum(sp, a->dtype, stream) != cudaSuccess) return FSA_ERR_LAUNCH;
+    }
   }
   return FSA_OK;
 }

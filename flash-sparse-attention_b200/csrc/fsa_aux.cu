@@ -62,7 +62,162 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
   }
 }
 
+template <typename T>
+__device__ __forceinline__ float2 unpack2(uint32_t v);
+template <>
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) {
+  return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+}
+template <>
+__device__ __forceinline__ float2 unpack2<__half>(uint32_t v) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&v));
+}
+
+// Row position inside the tile-padded workspaces: every sequence starts on a multiple of 128 rows
+// (same rule as flash_sparse_attn/ops/triton/seqlen_info.py:86 with TILE_M = 128).
+__device__ __forceinline__ long long padded_row(int varlen, const int* cu_q, int b, int sq_static, int q) {
+  if (varlen) return (long long)((cu_q[b] + b * 128) / 128) * 128 + q;
+  return (long long)b * ((sq_static + 127) / 128) * 128 + q;
+}
+
+// One warp per (query row, head). flash_sparse_attn/ops/triton/flash_bwd_preprocess.py:170-195.
+template <typename T>
+__global__ void __launch_bounds__(256) bwd_pre_kernel(BwdPreParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long rows = p.varlen ? p.total_q : (long long)p.B * p.sq;
+  if (item >= rows * p.heads) return;
+  const int h = (int)(item % p.heads);
+  const long long row = item / p.heads;
+  int b, q;
+  long long tok;
+  if (p.varlen) {
+    // locate the sequence of this packed row (B is small: linear scan)
+    b = 0;
+    while (b + 1 < p.B && p.cu_q[b + 1] <= row) ++b;
+    q = (int)(row - p.cu_q[b]);
+    tok = row;
+  } else {
+    b = (int)(row / p.sq);
+    q = (int)(row - (long long)b * p.sq);
+    tok = q;
+  }
+  const T* o = reinterpret_cast<const T*>(p.out) + (p.varlen ? 0 : (long long)b * p.o_sb) + tok * p.o_sm + (long long)h * p.o_sh;
+  const T* d = reinterpret_cast<const T*>(p.dout) + (p.varlen ? 0 : (long long)b * p.do_sb) + tok * p.do_sm + (long long)h * p.do_sh;
+  float acc = 0.f;
+  for (int i = lane * 2; i < p.head_dim; i += 64) {
+    const float2 a = unpack2<T>(*reinterpret_cast<const uint32_t*>(o + i));
+    const float2 g = unpack2<T>(*reinterpret_cast<const uint32_t*>(d + i));
+    acc += a.x * g.x + a.y * g.y;
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (lane == 0) {
+    const float lse = p.lse[(p.varlen ? 0 : (long long)b * p.l_sb) + (long long)h * p.l_sh + tok];
+    float l2 = (lse == lse) ? lse * 1.4426950408889634f : 1e6f;
+    l2 = fmaxf(l2, -1e6f);
+    const long long w = (long long)h * p.ws_sh + padded_row(p.varlen, p.cu_q, b, p.sq, q);
+    p.lse2_ws[w] = l2;
+    p.dpsum_ws[w] = acc;
+  }
+}
+
+// One warp per (query row, head). flash_sparse_attn/ops/triton/flash_bwd_postprocess.py:60-105.
+template <typename T>
+__global__ void __launch_bounds__(256) bwd_post_kernel(BwdPostParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long rows = p.varlen ? p.total_q : (long long)p.B * p.sq;
+  if (item >= rows * p.heads) return;
+  const int h = (int)(item % p.heads);
+  const long long row = item / p.heads;
+  int b, q;
+  long long tok;
+  if (p.varlen) {
+    b = 0;
+    while (b + 1 < p.B && p.cu_q[b + 1] <= row) ++b;
+    q = (int)(row - p.cu_q[b]);
+    tok = row;
+  } else {
+    b = (int)(row / p.sq);
+    q = (int)(row - (long long)b * p.sq);
+    tok = q;
+  }
+  const float* src = p.dq_accum + ((long long)h * p.ws_sh + padded_row(p.varlen, p.cu_q, b, p.sq, q)) * p.head_dim;
+  T* dst = reinterpret_cast<T*>(p.dq) + (p.varlen ? 0 : (long long)b * p.dq_sb) + tok * p.dq_sm + (long long)h * p.dq_sh;
+  for (int i = lane * 4; i < p.head_dim; i += 128) {
+    const float4 v = *reinterpret_cast<const float4*>(src + i);
+    uint2 o;
+    o.x = pack2<T>(v.x * p.scale, v.y * p.scale);
+    o.y = pack2<T>(v.z * p.scale, v.w * p.scale);
+    *reinterpret_cast<uint2*>(dst + i) = o;
+  }
+}
+
+// One warp per (key row, head): sum the split partials in split order (fixed order, deterministic).
+template <typename T>
+__global__ void __launch_bounds__(256) split_sum_kernel(SplitSumParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (long long)p.rows * p.heads) return;
+  const int h = (int)(item % p.heads);
+  const long long row = item / p.heads;
+  const int b = (int)(row / p.rows_per_batch);
+  const long long n = row - (long long)b * p.rows_per_batch;
+  const float* src = p.partial + (row * p.heads + h) * p.head_dim;
+  T* dst = reinterpret_cast<T*>(p.out) + (long long)b * p.o_sb + n * p.o_sn + (long long)h * p.o_sh;
+  for (int i = lane * 4; i < p.head_dim; i += 128) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < p.num_splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(src + (long long)s * p.part_ss + i);
+      acc.x += v.x;
+      acc.y += v.y;
+      acc.z += v.z;
+      acc.w += v.w;
+    }
+    uint2 o;
+    o.x = pack2<T>(acc.x, acc.y);
+    o.y = pack2<T>(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(dst + i) = o;
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_bwd_pre(const BwdPreParams& p, int dtype, cudaStream_t stream) {
+  const long long rows = p.varlen ? p.total_q : (long long)p.B * p.sq;
+  const long long items = rows * p.heads;
+  if (items <= 0) return cudaSuccess;
+  const unsigned grid = (unsigned)((items + 7) / 8);
+  if (dtype == DT_BF16)
+    bwd_pre_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
+  else
+    bwd_pre_kernel<__half><<<grid, 256, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_bwd_post(const BwdPostParams& p, int dtype, cudaStream_t stream) {
+  const long long rows = p.varlen ? p.total_q : (long long)p.B * p.sq;
+  const long long items = rows * p.heads;
+  if (items <= 0) return cudaSuccess;
+  const unsigned grid = (unsigned)((items + 7) / 8);
+  if (dtype == DT_BF16)
+    bwd_post_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
+  else
+    bwd_post_kernel<__half><<<grid, 256, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_split_sum(const SplitSumParams& p, int dtype, cudaStream_t stream) {
+  const long long items = (long long)p.rows * p.heads;
+  if (items <= 0) return cudaSuccess;
+  const unsigned grid = (unsigned)((items + 7) / 8);
+  if (dtype == DT_BF16)
+    split_sum_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
+  else
+    split_sum_kernel<__half><<<grid, 256, 0, stream>>>(p);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_combine(const CombineParams& p, int dtype, cudaStream_t stream) {
   const long long items = (long long)p.rows * p.heads;

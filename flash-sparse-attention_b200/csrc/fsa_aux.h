@@ -20,6 +20,40 @@ struct CombineParams {
   int rows, rows_per_batch, heads, head_dim, num_splits;
 };
 
+// Backward pre-pass over every (query row, head): dpsum = sum_d O*dO, lse2 = lse * log2(e) (NaN -> 1e6,
+// clamped at -1e6), both written at tile-padded row positions.
+struct BwdPreParams {
+  const void* out;
+  const void* dout;
+  const float* lse;
+  float* lse2_ws;
+  float* dpsum_ws;
+  const int* cu_q;
+  long long o_sb, o_sm, o_sh, do_sb, do_sm, do_sh, l_sb, l_sh, ws_sh;
+  int B, sq, total_q, heads, head_dim, varlen;
+};
+// Backward post-pass: dq = dq_accum * scale in the 16-bit type.
+struct BwdPostParams {
+  const float* dq_accum;  // [Hq, ws_sh, D]
+  void* dq;
+  const int* cu_q;
+  long long dq_sb, dq_sm, dq_sh, ws_sh;
+  int B, sq, total_q, heads, head_dim, varlen;
+  float scale;
+};
+// Sum of per-split fp32 partials [splits, n] into a strided 16-bit tensor of rows x heads x head_dim.
+struct SplitSumParams {
+  const float* partial;
+  void* out;
+  long long part_ss;  // elements between splits
+  long long o_sb, o_sn, o_sh;
+  int rows, rows_per_batch, heads, head_dim, num_splits;
+};
+
+cudaError_t launch_bwd_pre(const BwdPreParams& p, int dtype, cudaStream_t stream);
+cudaError_t launch_bwd_post(const BwdPostParams& p, int dtype, cudaStream_t stream);
+cudaError_t launch_split_sum(const SplitSumParams& p, int dtype, cudaStream_t stream);
+cudaError_t launch_bwd(const BwdKernelParams& p, int kind, int dtype, int head_dim, cudaStream_t stream);
 cudaError_t launch_combine(const CombineParams& p, int dtype, cudaStream_t stream);
 cudaError_t launch_fwd(const FwdKernelParams& p, int kind, int dtype, int head_dim, cudaStream_t stream);
 

@@ -1,0 +1,703 @@
+// Backward attention for sm_100a: five tcgen05 GEMMs per (key tile, query tile) pair with TMEM
+// accumulators, TMA-fed Q / dO ring, warp-specialised roles.
+//
+// One CTA owns one 128-key tile of one KV head and walks every 128-row query tile that attends to
+// it, for each of the G query heads of the group in turn. dK and dV therefore accumulate inside the
+// CTA (TMEM) across tiles AND across the group's heads - no atomics and a fixed summation order -
+// while each dQ tile is added into an fp32 accumulator with a TMA reduce-add.
+// It stands in for `_bwd_{dense,sparse}_kernel`
+// (flash_sparse_attn/ops/triton/flash_sparse_bwd.py:29-473, flash_dense_bwd.py) at TILE_M = TILE_N =
+// 128: same tile schedule (scheduler.py:994-1101), same masks, the same stateless skip rule on the
+// true probabilities (flash_sparse_bwd.py:61-79). Unlike the reference's grid over query heads, the
+// G heads of a KV head are looped inside the CTA, which is what removes the fp32 atomics on dK/dV
+// (scheduler.py:2194-2206).
+//
+// Everything is computed transposed so that one thread owns one KEY row (TMEM lane):
+//   S^T  = K Q^T              [keys x queries]      P^T = exp2(S^T * c - lse2[q])
+//   dP^T = V dO^T
+//   dS^T = P^T o (dP^T - dpsum[q])
+//   dV  += P^T dO      (A = P^T from TMEM)
+//   dK  += dS^T Q      (A = dS^T from shared memory, K-major)
+//   dQ   = dS K        (A = dS^T from shared memory, read MN-major)
+//
+// Roles (384 threads): warps 0-7 compute (warps 0-3 own query columns 0-63 of the tile, warps 4-7
+// columns 64-127; both cover all 128 key lanes), warp 8 producer (TMA), warp 9 MMA issuer.
+// TMEM columns: [0,128) S^T, then P^T packed into [0,32) and [96,128) | [128,256) dP^T, later dQ |
+// [256,384) dV | [384,512) dK.
+#include "fsa_ptx.cuh"
+#include "fsa_params.h"
+#include "fsa_schedule.h"
+#include "fsa_aux.h"
+
+namespace fsa {
+
+namespace {
+
+constexpr int TM = 128;  // query rows per step
+constexpr int TN = 128;  // keys per CTA
+constexpr int NTHREADS = 384;
+
+template <int HD>
+struct BwdSmem {
+  static constexpr int kTile = 128 * HD * 2;
+  static constexpr int kK = 0;
+  static constexpr int kV = kK + kTile;
+  static constexpr int kQ = kV + kTile;        // 2 stages
+  static constexpr int kDO = kQ + 2 * kTile;   // 2 stages
+  static constexpr int kDS = kDO + 2 * kTile;  // dS^T (16-bit, 128 x 128) / dQ staging (8 warps x 4 KB)
+  static constexpr int kAux = kDS + 32768;     // lse2[2][128], dpsum[2][128]
+  static constexpr int kBar = kAux + 2048;
+  static constexpr int kTotal = kBar + 256;
+};
+
+struct BwdBars {
+  uint64_t kv_full, qdo_full[2], qdo_empty[2];
+  uint64_t s_full, p_full, dp_full, ds_full, dq_full, dq_empty, ds_free, vote_sync, acc_full;
+  uint32_t tmem_base;
+  int abort_flag;
+  int skip_flag[2];
+  int vote_any[2][8];
+};
+static_assert(sizeof(BwdBars) <= 256, "barrier block too large");
+
+// Visible query columns of one key row inside query tile [q0, q0 + TM), as up to three half-open
+// intervals of the tile-local index (mask.py:52-102 read along the query axis).
+struct ColMask {
+  int lo[3];
+  unsigned len[3];
+};
+
+struct SegList {
+  int beg[6], end[6], mode[6];
+  int n;
+  int total;
+};
+
+// Query tiles visited by one key tile, in the reference's phase order
+// (flash_sparse_bwd.py:315-464): every phase ascending.
+__device__ __forceinline__ SegList make_segments(const FsaBwdSched& s, bool causal, bool local) {
+  SegList l;
+  l.n = 0;
+  l.total = 0;
+  auto add = [&](int b, int e, int mode) {
+    if (e > b) {
+      l.beg[l.n] = b;
+      l.end[l.n] = e;
+      l.mode[l.n] = mode;
+      l.n++;
+      l.total += e - b;
+    }
+  };
+  if (causal || local) add(s.m_min, s.m_min_no_mask, local ? FSA_MASK_LOCAL : FSA_MASK_CAUSAL);
+  if (!local) add((causal || local) ? s.m_min_no_mask : s.m_min, s.m_max, FSA_MASK_NONE);
+  if (local) {
+    add(s.win_min, s.win_min_no_mask, FSA_MASK_LOCAL);
+    add(s.win_min_no_mask, s.win_max_no_mask, FSA_MASK_NONE);
+    add(s.win_max_no_mask, s.win_max, FSA_MASK_LOCAL);
+    add(s.sink_min, s.sink_max, FSA_MASK_LOCAL_SINK);
+  }
+  return l;
+}
+__device__ __forceinline__ void seg_at(const SegList& l, int j, int* m, int* mode) {
+  *m = 0;
+  *mode = FSA_MASK_NONE;
+#pragma unroll
+  for (int i = 0; i < 6; ++i) {
+    if (i < l.n) {
+      const int len = l.end[i] - l.beg[i];
+      if (j >= 0 && j < len) {
+        *m = l.beg[i] + j;
+        *mode = l.mode[i];
+      }
+      j -= len;
+    }
+  }
+}
+
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, const void* src, int c0, int c1, int c2) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+template <int HD, typename T, int KIND>
+__global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant__ BwdKernelParams p) {
+  using SM = BwdSmem<HD>;
+  constexpr int KK_D = HD / 16;   // MMAs over the head dimension (S^T, dP^T)
+  constexpr int KK_M = TM / 16;   // MMAs over the query rows (dV, dK)
+  constexpr int KK_N = TN / 16;   // MMAs over the keys (dQ)
+  constexpr int HALF = HD / 2;    // output columns per compute group
+  constexpr bool IS_BF16 = !__is_same(T, __half);
+  constexpr uint32_t TMEM_S = 0, TMEM_DP = 128, TMEM_DV = 256, TMEM_DK = 384;
+
+  extern __shared__ __align__(1024) uint8_t smem[];
+  BwdBars* bars = reinterpret_cast<BwdBars*>(smem + SM::kBar);
+  volatile int* abort_flag = &bars->abort_flag;
+  float* s_lse = reinterpret_cast<float*>(smem + SM::kAux);          // [2][128]
+  float* s_dps = reinterpret_cast<float*>(smem + SM::kAux + 1024);   // [2][128]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool causal = p.flags & F_CAUSAL, local = p.flags & F_LOCAL, split_qo = p.flags & F_SPLIT;
+
+  // ---- work decode ------------------------------------------------------------------------------
+  int idx = blockIdx.x;
+  const int n_block = idx % p.n_tiles_k;
+  idx /= p.n_tiles_k;
+  const int hkv = idx % p.Hkv;
+  idx /= p.Hkv;
+  const int b = idx / p.num_splits;
+  const int split = idx - b * p.num_splits;
+  const int off_q = (p.flags & F_VARLEN_Q) ? p.cu_q[b] : 0;
+  const int off_k = (p.flags & F_VARLEN_K) ? p.cu_k[b] : 0;
+  const int sq = (p.flags & F_USED_Q) ? p.used_q[b] : ((p.flags & F_VARLEN_Q) ? p.cu_q[b + 1] - off_q : p.sq);
+  const int sk = (p.flags & F_USED_K) ? p.used_k[b] : ((p.flags & F_VARLEN_K) ? p.cu_k[b + 1] - off_k : p.sk);
+  if (n_block * TN >= sk) return;  // nothing of this key tile exists (before any allocation)
+  if (smem_u32(smem) & 1023u) {    // the tile buffers need a 1024-byte aligned base
+    if (tid == 0) atomicExch(p.status, 2);
+    return;
+  }
+  const long long pad_off = (p.flags & F_VARLEN_Q) ? (long long)((off_q + b * 128) / 128) * 128
+                                                   : (long long)b * ((p.sq + 127) / 128) * 128;
+  FsaWindow w = {0, 0, 0, 0};
+  if (local) {
+    const int* wp = p.windows + (long long)hkv * p.win_stride;
+    w.sink = wp[0];
+    w.left = wp[1];
+    w.right = wp[2];
+    w.near_ = wp[3];
+  }
+  const FsaBwdSched sched = fsa_bwd_schedule(sq, sk, n_block, split, w, p.num_splits, TN, TM, causal, local, split_qo);
+  const SegList segs = make_segments(sched, causal, local);
+  const int NT = segs.total;       // query tiles per head
+  const int N_IT = NT * p.G;       // steps of this CTA
+
+  // ---- setup ---------------------------------------------------------------------------------
+  if (tid == 0) {
+    mbar_init(&bars->kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->qdo_full[s], 1);
+      mbar_init(&bars->qdo_empty[s], 1);
+    }
+    mbar_init(&bars->s_full, 1);
+    mbar_init(&bars->p_full, 8);
+    mbar_init(&bars->dp_full, 1);
+    mbar_init(&bars->ds_full, 8);
+    mbar_init(&bars->dq_full, 1);
+    mbar_init(&bars->dq_empty, 8);
+    mbar_init(&bars->ds_free, 8);
+    mbar_init(&bars->vote_sync, 8);
+    mbar_init(&bars->acc_full, 1);
+    bars->abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
+    mbar_fence_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+  const int bq = (p.flags & F_VARLEN_Q) ? 0 : b;
+  const int bk = (p.flags & F_VARLEN_K) ? 0 : b;
+
+  if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+    if (warp == 8) {
+      // =============================== producer ==============================================
+      if (lane == 0 && !*abort_flag) {
+        tma_prefetch_desc(&p.map_q);
+        tma_prefetch_desc(&p.map_do);
+        tma_prefetch_desc(&p.map_k);
+        tma_prefetch_desc(&p.map_v);
+        mbar_arrive_expect_tx(&bars->kv_full, 2 * SM::kTile);
+        for (int d = 0; d < HD; d += 64) {
+          tma_load_4d(smem + SM::kK + (d / 64) * (TN * 128), &p.map_k, &bars->kv_full, d, hkv, off_k + n_block * TN, bk);
+          tma_load_4d(smem + SM::kV + (d / 64) * (TN * 128), &p.map_v, &bars->kv_full, d, hkv, off_k + n_block * TN, bk);
+        }
+        bool ok = true;
+        for (int it = 0; it < N_IT && ok; ++it) {
+          const int st = it & 1, use = it >> 1;
+          if (use > 0) ok = mbar_wait(&bars->qdo_empty[st], (use - 1) & 1, abort_flag);
+          if (!ok) break;
+          const int g = it / NT;
+          int m, mode;
+          seg_at(segs, it - g * NT, &m, &mode);
+          const int head = hkv * p.G + g;
+          mbar_arrive_expect_tx(&bars->qdo_full[st], 2 * SM::kTile + 1024);
+          for (int d = 0; d < HD; d += 64) {
+            tma_load_4d(smem + SM::kQ + st * SM::kTile + (d / 64) * (TM * 128), &p.map_q, &bars->qdo_full[st], d, head,
+                        off_q + m * TM, bq);
+            tma_load_4d(smem + SM::kDO + st * SM::kTile + (d / 64) * (TM * 128), &p.map_do, &bars->qdo_full[st], d,
+                        head, off_q + m * TM, bq);
+          }
+          const long long wrow = (long long)head * p.ws_sh + pad_off + (long long)m * TM;
+          bulk_load_1d(s_lse + st * 128, p.lse2_ws + wrow, 512, &bars->qdo_full[st]);
+          bulk_load_1d(s_dps + st * 128, p.dpsum_ws + wrow, 512, &bars->qdo_full[st]);
+        }
+      }
+      __syncwarp();
+    } else if (warp == 9) {
+      // =============================== MMA issuer ==============================================
+      constexpr uint32_t idesc_s = umma_idesc_f16(TN, TM, IS_BF16, false, false);   // S^T, dP^T: [keys x queries]
+      constexpr uint32_t idesc_dv = umma_idesc_f16(TN, HD, IS_BF16, false, true);   // dV: A from TMEM, B = dO MN-major
+      constexpr uint32_t idesc_dk = umma_idesc_f16(TN, HD, IS_BF16, false, true);   // dK: A = dS^T K-major, B = Q MN-major
+      constexpr uint32_t idesc_dq = umma_idesc_f16(TM, HD, IS_BF16, true, true);    // dQ: A = dS^T MN-major, B = K MN-major
+      const uint32_t sK = smem_u32(smem + SM::kK), sV = smem_u32(smem + SM::kV), sQ = smem_u32(smem + SM::kQ),
+                     sDO = smem_u32(smem + SM::kDO), sDS = smem_u32(smem + SM::kDS);
+      bool ok = !*abort_flag && N_IT > 0;
+      auto issue_st = [&](int st) {
+        if (lane == 0) {
+#pragma unroll
+          for (int kk = 0; kk < KK_D; ++kk) {
+            const uint32_t koff = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
+            umma_ss(tmem_base + TMEM_S, umma_smem_desc(sK + koff, 16, 1024),
+                    umma_smem_desc(sQ + st * SM::kTile + koff, 16, 1024), idesc_s, kk > 0);
+          }
+          umma_commit(&bars->s_full);
+        }
+        __syncwarp();
+      };
+      if (ok) {
+        ok = mbar_wait(&bars->kv_full, 0, abort_flag);
+        ok = ok && mbar_wait(&bars->qdo_full[0], 0, abort_flag);
+        tc_fence_after();
+        if (ok) issue_st(0);
+      }
+      int n_live = 0;  // steps that were not skipped so far
+      bool acc_started = false;
+      for (int it = 0; it < N_IT && ok; ++it) {
+        const int st = it & 1;
+        ok = mbar_wait(&bars->p_full, it & 1, abort_flag);
+        if (!ok) break;
+        const bool skip = (KIND != KIND_DENSE) && bars->skip_flag[it & 1];
+        tc_fence_after();
+        if (!skip) {
+          if (n_live > 0) ok = mbar_wait(&bars->dq_empty, (n_live - 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          if (lane == 0) {
+#pragma unroll
+            for (int kk = 0; kk < KK_D; ++kk) {
+              const uint32_t koff = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
+              umma_ss(tmem_base + TMEM_DP, umma_smem_desc(sV + koff, 16, 1024),
+                      umma_smem_desc(sDO + st * SM::kTile + koff, 16, 1024), idesc_s, kk > 0);
+            }
+            umma_commit(&bars->dp_full);
+#pragma unroll
+            for (int kk = 0; kk < KK_M; ++kk) {
+              const uint32_t a_col = (kk < 4) ? kk * 8 : 96 + (kk - 4) * 8;
+              umma_ts(tmem_base + TMEM_DV, tmem_base + TMEM_S + a_col,
+                      umma_smem_desc(sDO + st * SM::kTile + kk * 2048, TM * 128, 1024), idesc_dv,
+                      (kk > 0 || acc_started) ? 1u : 0u);
+            }
+          }
+          __syncwarp();
+        }
+        if (it + 1 < N_IT) {
+          ok = mbar_wait(&bars->qdo_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          issue_st((it + 1) & 1);
+        }
+        if (!skip) {
+          ok = mbar_wait(&bars->ds_full, n_live & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          if (lane == 0) {
+#pragma unroll
+            for (int kk = 0; kk < KK_M; ++kk) {
+              umma_ss(tmem_base + TMEM_DK, umma_smem_desc(sDS + (kk >> 2) * (128 * 128) + (kk & 3) * 32, 16, 1024),
+                      umma_smem_desc(sQ + st * SM::kTile + kk * 2048, TM * 128, 1024), idesc_dk,
+                      (kk > 0 || acc_started) ? 1u : 0u);
+            }
+#pragma unroll
+            for (int kk = 0; kk < KK_N; ++kk) {
+              umma_ss(tmem_base + TMEM_DP, umma_smem_desc(sDS + kk * 2048, 128 * 128, 1024),
+                      umma_smem_desc(sK + kk * 2048, TN * 128, 1024), idesc_dq, kk > 0);
+            }
+            umma_commit(&bars->dq_full);
+          }
+          __syncwarp();
+          acc_started = true;
+          n_live++;
+        }
+        if (lane == 0) umma_commit(&bars->qdo_empty[st]);
+        __syncwarp();
+      }
+      if (lane == 0) umma_commit(&bars->acc_full);
+      __syncwarp();
+    }
+  } else {
+    // =============================== compute warps ===========================================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    const int cw = warp;            // 0..7
+    const int wg = cw >> 2;         // which half of the query columns / output columns
+    const int wq = cw & 3;          // TMEM lane quadrant
+    const int row = wq * 32 + lane; // key row (S^T, dP^T, dV, dK) or query row (dQ)
+    const uint32_t lane_addr = uint32_t(wq * 32) << 16;
+    const int k_idx = n_block * TN + row;
+    const bool row_ok = k_idx < sk;
+    const int off = sk - sq;
+    const float c = p.scale_log2;
+    uint8_t* ds_buf = smem + SM::kDS;
+    uint8_t* stage = ds_buf + cw * 4096;
+
+    bool ok = !*abort_flag;
+    uint32_t pk[32];  // P^T of the step in flight, packed pairs (this thread's 64 query columns)
+    int n_live = 0, n_staged = 0;
+    bool skip_cur = false;
+
+    auto col_mask = [&](int mode, int m) {
+      ColMask cm;
+      const int q0 = m * TM;
+      const int seq_hi = row_ok ? min(sq - q0, TM) : 0;
+      auto clip = [&](int i, long long a, long long bnd) {
+        long long lo = a - q0, hi = bnd - q0;
+        if (lo < 0) lo = 0;
+        if (hi > seq_hi) hi = seq_hi;
+        cm.lo[i] = (int)lo;
+        cm.len[i] = hi > lo ? unsigned(hi - lo) : 0u;
+      };
+      const long long base = (long long)k_idx - off;  // first causally visible query
+      if (mode == FSA_MASK_NONE || mode == FSA_MASK_SEQLEN) {
+        clip(0, 0, sq);
+        clip(1, 0, 0);
+        clip(2, 0, 0);
+      } else if (mode == FSA_MASK_CAUSAL) {
+        clip(0, base, (long long)sq);
+        clip(1, 0, 0);
+        clip(2, 0, 0);
+      } else {
+        clip(0, base, base + w.near_);
+        clip(1, base + w.near_ + w.right, base + w.near_ + w.right + w.left);
+        if (mode == FSA_MASK_LOCAL_SINK && k_idx < w.sink)
+          clip(2, base, (long long)sq);
+        else
+          clip(2, 0, 0);
+      }
+      return cm;
+    };
+    auto visible = [&](const ColMask& cm, int i) {
+      return (unsigned(i - cm.lo[0]) < cm.len[0]) | (unsigned(i - cm.lo[1]) < cm.len[1]) |
+             (unsigned(i - cm.lo[2]) < cm.len[2]);
+    };
+
+    // ---- P step: scores -> probabilities (and the skip vote) ------------------------------------
+    auto p_step = [&](int it) -> bool {  // returns the skip decision
+      const int st = it & 1, par = it & 1;
+      const int g = it / NT;
+      int m, mode;
+      seg_at(segs, it - g * NT, &m, &mode);
+      if (!mbar_wait(&bars->s_full, par, abort_flag)) {
+        ok = false;
+        return true;
+      }
+      // lse2 / dpsum arrived with the Q tile; observing the barrier makes them visible here
+      if (!mbar_wait(&bars->qdo_full[st], (it >> 1) & 1, abort_flag)) {
+        ok = false;
+        return true;
+      }
+      tc_fence_after();
+      uint32_t sr[64];
+      tmem_ld32(tmem_base + lane_addr + TMEM_S + wg * 64, &sr[0]);
+      tmem_ld32(tmem_base + lane_addr + TMEM_S + wg * 64 + 32, &sr[32]);
+      tmem_ld_wait();
+      const bool ragged = ((m + 1) * TM > sq) || ((n_block + 1) * TN > sk);
+      const bool masked = (mode != FSA_MASK_NONE) || ragged;
+      const ColMask cm = col_mask(mode, m);
+      const float4* lse4 = reinterpret_cast<const float4*>(s_lse + st * 128 + wg * 64);
+      float x[64];  // log2 of the probabilities
+#pragma unroll
+      for (int i = 0; i < 64; i += 4) {
+        const float4 l = lse4[i >> 2];
+        x[i] = fmaf(__uint_as_float(sr[i]), c, -l.x);
+        x[i + 1] = fmaf(__uint_as_float(sr[i + 1]), c, -l.y);
+        x[i + 2] = fmaf(__uint_as_float(sr[i + 2]), c, -l.z);
+        x[i + 3] = fmaf(__uint_as_float(sr[i + 3]), c, -l.w);
+      }
+      if (masked) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (!visible(cm, wg * 64 + i)) x[i] = -INFINITY;
+      }
+      bool skip = false;
+      if (KIND != KIND_DENSE) {
+        // skip iff max over the tile of (log2 p - thr_log2[q]) < 0 (flash_sparse_bwd.py:61-79);
+        // thresholds of this group's 64 query columns live two per lane and travel by shuffle
+        const int q_a = m * TM + wg * 64 + lane, q_b = q_a + 32;
+        const float vis_a = causal ? float(q_a + off + 1) : float(sk);
+        const float vis_b = causal ? float(q_b + off + 1) : float(sk);
+        const float thr_a = log2f(fmaxf(fminf(p.softmax_thr / vis_a, 1.0f), 0.0f));
+        const float thr_b = log2f(fmaxf(fminf(p.softmax_thr / vis_b, 1.0f), 0.0f));
+        bool want = false, drop = false;
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const float t = __shfl_sync(0xffffffffu, i < 32 ? thr_a : thr_b, i & 31);
+          const float v = x[i] - t;
+          want |= (v >= 0.0f);
+          drop |= (v < 0.0f);
+        }
+        const unsigned w_any = __ballot_sync(0xffffffffu, want);
+        const unsigned d_any = __ballot_sync(0xffffffffu, drop);
+        if (lane == 0) {
+          bars->vote_any[par][cw] = (w_any ? 1 : 0) | (d_any ? 2 : 0);
+          mbar_arrive(&bars->vote_sync);
+        }
+        if (!mbar_wait(&bars->vote_sync, par, abort_flag)) {
+          ok = false;
+          return true;
+        }
+        int v = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v |= bars->vote_any[par][i];
+        skip = !(v & 1) && (v & 2);
+        if (cw == 0 && lane == 0) {
+          bars->skip_flag[par] = skip ? 1 : 0;
+          if (p.tile_map) {
+            const int head = hkv * p.G + g;
+            p.tile_map[((((long long)b * p.Hq + head) * p.n_tiles_k + n_block) * p.num_splits + split) *
+                           p.num_m_blocks + m] = skip ? 2 : 1;
+          }
+          __threadfence_block();
+        }
+      }
+      if (!skip) {
+#pragma unroll
+        for (int i = 0; i < 64; i += 2) pk[i >> 1] = pack2<T>(ex2_approx(x[i]), ex2_approx(x[i + 1]));
+        const uint32_t pcol = (wg == 0) ? 0u : 96u;
+        tmem_st16(tmem_base + lane_addr + TMEM_S + pcol, &pk[0]);
+        tmem_st16(tmem_base + lane_addr + TMEM_S + pcol + 16, &pk[16]);
+        tmem_st_wait();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->p_full);
+      return skip;
+    };
+
+    // ---- dS step: dS^T = P^T o (dP^T - dpsum) into shared memory ------------------------------------
+    auto ds_step = [&](int it) {
+      const int st = it & 1;
+      if (!mbar_wait(&bars->dp_full, n_live & 1, abort_flag)) {
+        ok = false;
+        return;
+      }
+      tc_fence_after();
+      uint32_t dr[64];
+      tmem_ld32(tmem_base + lane_addr + TMEM_DP + wg * 64, &dr[0]);
+      tmem_ld32(tmem_base + lane_addr + TMEM_DP + wg * 64 + 32, &dr[32]);
+      tmem_ld_wait();
+      // the dS buffer doubles as dQ staging: all warps must be done with the previous staging reads
+      if (n_staged > 0 && !mbar_wait(&bars->ds_free, (n_staged - 1) & 1, abort_flag)) {
+        ok = false;
+        return;
+      }
+      const float4* dps4 = reinterpret_cast<const float4*>(s_dps + st * 128 + wg * 64);
+      uint8_t* slab = ds_buf + wg * (128 * 128);
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        const float4 d0 = dps4[ch * 2], d1 = dps4[ch * 2 + 1];
+        const float dps[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          const uint32_t pp = pk[(ch * 8 + j) >> 1];
+          float p0, p1;
+          if (IS_BF16) {
+            p0 = __uint_as_float(pp << 16);
+            p1 = __uint_as_float(pp & 0xffff0000u);
+          } else {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pp));
+            p0 = f.x;
+            p1 = f.y;
+          }
+          // both factors are rounded to the 16-bit type before the product, like the reference
+          const uint32_t tt = pack2<T>(__uint_as_float(dr[ch * 8 + j]) - dps[j],
+                                       __uint_as_float(dr[ch * 8 + j + 1]) - dps[j + 1]);
+          float t0, t1;
+          if (IS_BF16) {
+            t0 = __uint_as_float(tt << 16);
+            t1 = __uint_as_float(tt & 0xffff0000u);
+          } else {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&tt));
+            t0 = f.x;
+            t1 = f.y;
+          }
+          // p == 0 marks masked entries: keep them exactly zero whatever sits in the other factor
+          o[j >> 1] = pack2<T>(p0 == 0.f ? 0.f : p0 * t0, p1 == 0.f ? 0.f : p1 * t1);
+        }
+        *reinterpret_cast<uint4*>(slab + sw128_offset(row, ch)) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->ds_full);
+    };
+
+    // ---- dQ step: TMEM -> shared staging -> TMA reduce-add into the fp32 accumulator ----------------
+    auto dq_step = [&](int it) {
+      const int g = it / NT;
+      int m, mode;
+      seg_at(segs, it - g * NT, &m, &mode);
+      const int head = hkv * p.G + g;
+      if (!mbar_wait(&bars->dq_full, n_live & 1, abort_flag)) {
+        ok = false;
+        return;
+      }
+      tc_fence_after();
+#pragma unroll
+      for (int ch = 0; ch < HALF / 32; ++ch) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + lane_addr + TMEM_DP + wg * HALF + ch * 32, r);
+        tmem_ld_wait();
+        if (ch == HALF / 32 - 1) {
+          // all of this warp's dQ values are in registers: the TMEM block may be overwritten
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->dq_empty);
+        }
+        if (ch > 0) {
+          if (lane == 0) bulk_wait_read0();
+          __syncwarp();
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+              make_uint4(r[j * 4], r[j * 4 + 1], r[j * 4 + 2], r[j * 4 + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_reduce_add_3d(&p.map_dq, stage, wg * HALF + ch * 32, (int)(pad_off + (long long)m * TM + wq * 32), head);
+          bulk_commit();
+        }
+      }
+      if (lane == 0) {
+        bulk_wait_read0();
+        mbar_arrive(&bars->ds_free);
+      }
+      __syncwarp();
+      n_staged++;
+    };
+
+    if (ok && N_IT > 0) skip_cur = p_step(0);
+    for (int it = 0; it < N_IT && ok; ++it) {
+      if (!skip_cur) ds_step(it);
+      bool skip_next = false;
+      if (ok && it + 1 < N_IT) skip_next = p_step(it + 1);
+      if (ok && !skip_cur) {
+        dq_step(it);
+        n_live++;
+      }
+      skip_cur = skip_next;
+    }
+
+    // ---- epilogue: dK (scaled) and dV of this key tile ------------------------------------------------
+    if (ok) {
+      bool have = false;
+      if (N_IT > 0) {
+        ok = mbar_wait(&bars->acc_full, 0, abort_flag);
+        tc_fence_after();
+        have = n_live > 0;
+      }
+      if (ok) {
+        const long long rowk = off_k + k_idx;
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+          const uint32_t tcol = which == 0 ? TMEM_DV : TMEM_DK;
+          const float mul = which == 0 ? 1.0f : p.softmax_scale;
+          void* outp = which == 0 ? p.dv_out : p.dk_out;
+          const long long base = (long long)((p.flags & F_VARLEN_K) ? 0 : b) * p.dkv_sb + rowk * p.dkv_sn +
+                                 (long long)hkv * p.dkv_sh + (long long)split * p.dkv_ss + wg * HALF;
+#pragma unroll
+          for (int ch = 0; ch < HALF / 32; ++ch) {
+            uint32_t r[32];
+            if (have) {
+              tmem_ld32(tmem_base + lane_addr + tcol + wg * HALF + ch * 32, r);
+              tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = 0u;
+            }
+            if (row_ok) {
+              if (p.flags & F_SPLIT) {
+                float* dst = reinterpret_cast<float*>(outp) + base + ch * 32;
+#pragma unroll
+                for (int i = 0; i < 32; i += 4)
+                  *reinterpret_cast<float4*>(dst + i) =
+                      make_float4(__uint_as_float(r[i]) * mul, __uint_as_float(r[i + 1]) * mul,
+                                  __uint_as_float(r[i + 2]) * mul, __uint_as_float(r[i + 3]) * mul);
+              } else {
+                T* dst = reinterpret_cast<T*>(outp) + base + ch * 32;
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                  uint4 v;
+                  v.x = pack2<T>(__uint_as_float(r[i]) * mul, __uint_as_float(r[i + 1]) * mul);
+                  v.y = pack2<T>(__uint_as_float(r[i + 2]) * mul, __uint_as_float(r[i + 3]) * mul);
+                  v.z = pack2<T>(__uint_as_float(r[i + 4]) * mul, __uint_as_float(r[i + 5]) * mul);
+                  v.w = pack2<T>(__uint_as_float(r[i + 6]) * mul, __uint_as_float(r[i + 7]) * mul);
+                  *reinterpret_cast<uint4*>(dst + i) = v;
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+    if (lane == 0) bulk_wait0();
+    __syncwarp();
+  }
+
+  // ---- teardown ------------------------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && *abort_flag) atomicExch(p.status, 1);
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int HD, typename T, int KIND>
+cudaError_t launch_one(const BwdKernelParams& p, cudaStream_t stream) {
+  auto kern = bwd_kernel<HD, T, KIND>;
+  constexpr int smem = BwdSmem<HD>::kTotal;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const long long grid = (long long)p.n_tiles_k * p.Hkv * p.B * p.num_splits;
+  if (grid <= 0) return cudaSuccess;
+  kern<<<(unsigned)grid, NTHREADS, smem, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_bwd(const BwdKernelParams& p, int kind, int dtype, int head_dim, cudaStream_t stream) {
+#define FSA_BWD_CASE(HD_, T_, DT_)                                               \
+  if (head_dim == HD_ && dtype == DT_) {                                         \
+    if (kind == KIND_DENSE) return launch_one<HD_, T_, KIND_DENSE>(p, stream);   \
+    if (kind == KIND_SPARSE) return launch_one<HD_, T_, KIND_SPARSE>(p, stream); \
+  }
+  FSA_BWD_CASE(128, __nv_bfloat16, DT_BF16)
+  FSA_BWD_CASE(128, __half, DT_FP16)
+  FSA_BWD_CASE(64, __nv_bfloat16, DT_BF16)
+  FSA_BWD_CASE(64, __half, DT_FP16)
+#undef FSA_BWD_CASE
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace fsa

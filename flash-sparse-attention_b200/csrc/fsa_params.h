@@ -51,4 +51,26 @@ struct alignas(64) FwdKernelParams {
   unsigned flags;
 };
 
+struct alignas(64) BwdKernelParams {
+  CUtensorMap map_q, map_k, map_v, map_do, map_dq;
+  const float* lse2_ws;   // [Hq, ws_sh] base-2 log-sum-exp, tile-padded rows
+  const float* dpsum_ws;  // [Hq, ws_sh] rowsum(O * dO)
+  void* dk_out;           // T* [rows_k, Hkv, D] (strided) or float partial [splits, ...] when F_SPLIT
+  void* dv_out;
+  const int* cu_q;
+  const int* cu_k;
+  const int* used_q;
+  const int* used_k;
+  const int* windows;
+  int* status;
+  uint8_t* tile_map;  // optional [B, Hq, n_tiles_k, num_splits, num_m_blocks]
+  long long dkv_sb, dkv_sn, dkv_sh, dkv_ss;
+  long long ws_sh;
+  int B, Hq, Hkv, G;
+  int sq, sk;
+  int num_splits, n_tiles_k, num_m_blocks, win_stride;
+  float scale_log2, softmax_scale, softmax_thr;
+  unsigned flags;
+};
+
 }  // namespace fsa

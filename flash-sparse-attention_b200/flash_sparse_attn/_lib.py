@@ -87,6 +87,73 @@ class FsaFwdArgs(ctypes.Structure):
     ]
 
 
+class FsaBwdArgs(ctypes.Structure):
+    _fields_ = [
+        ("q", c_void_p),
+        ("k", c_void_p),
+        ("v", c_void_p),
+        ("out", c_void_p),
+        ("dout", c_void_p),
+        ("lse", c_void_p),
+        ("dq", c_void_p),
+        ("dk", c_void_p),
+        ("dv", c_void_p),
+        ("lse2_ws", c_void_p),
+        ("dpsum_ws", c_void_p),
+        ("dq_accum", c_void_p),
+        ("dk_partial", c_void_p),
+        ("dv_partial", c_void_p),
+        ("cu_seqlens_q", c_void_p),
+        ("cu_seqlens_k", c_void_p),
+        ("seqused_q", c_void_p),
+        ("seqused_k", c_void_p),
+        ("window_sizes", c_void_p),
+        ("status", c_void_p),
+        ("tile_map", c_void_p),
+        ("q_stride_b", c_int64),
+        ("q_stride_s", c_int64),
+        ("q_stride_h", c_int64),
+        ("k_stride_b", c_int64),
+        ("k_stride_s", c_int64),
+        ("k_stride_h", c_int64),
+        ("v_stride_b", c_int64),
+        ("v_stride_s", c_int64),
+        ("v_stride_h", c_int64),
+        ("o_stride_b", c_int64),
+        ("o_stride_s", c_int64),
+        ("o_stride_h", c_int64),
+        ("do_stride_b", c_int64),
+        ("do_stride_s", c_int64),
+        ("do_stride_h", c_int64),
+        ("dq_stride_b", c_int64),
+        ("dq_stride_s", c_int64),
+        ("dq_stride_h", c_int64),
+        ("dk_stride_b", c_int64),
+        ("dk_stride_s", c_int64),
+        ("dk_stride_h", c_int64),
+        ("lse_stride_b", c_int64),
+        ("lse_stride_h", c_int64),
+        ("batch", c_int32),
+        ("seqlen_q", c_int32),
+        ("seqlen_k", c_int32),
+        ("total_q", c_int32),
+        ("total_k", c_int32),
+        ("heads_q", c_int32),
+        ("heads_kv", c_int32),
+        ("head_dim", c_int32),
+        ("window_stride", c_int32),
+        ("num_splits", c_int32),
+        ("tile_m", c_int32),
+        ("tile_n", c_int32),
+        ("kind", c_int32),
+        ("dtype", c_int32),
+        ("flags", c_uint32),
+        ("softmax_scale", c_float),
+        ("softmax_threshold", c_float),
+        ("gate_threshold", c_float),
+    ]
+
+
 _lib = None
 
 
@@ -112,6 +179,10 @@ def load():
     lib.fsa_fwd.argtypes = [POINTER(FsaFwdArgs), c_void_p]
     lib.fsa_fwd_tile_map_bytes.restype = c_size_t
     lib.fsa_fwd_tile_map_bytes.argtypes = [POINTER(FsaFwdArgs)]
+    lib.fsa_bwd.restype = c_int
+    lib.fsa_bwd.argtypes = [POINTER(FsaBwdArgs), c_void_p]
+    lib.fsa_bwd_padded_rows.restype = c_int64
+    lib.fsa_bwd_padded_rows.argtypes = [c_int, c_int, c_int, c_int]
     lib.fsa_debug_fwd_schedule.restype = None
     lib.fsa_debug_fwd_schedule.argtypes = [c_int] * 4 + [POINTER(c_int32)] + [c_int] * 7 + [POINTER(c_int32)]
     lib.fsa_debug_bwd_schedule.restype = None

@@ -104,6 +104,68 @@ int fsa_fwd(const FsaFwdArgs* args, void* stream);
  * 2 = skipped by the softmax threshold, 3 = skipped by the gate bound. */
 size_t fsa_fwd_tile_map_bytes(const FsaFwdArgs* args);
 
+/*
+ * Backward pass. Stands in for _flash_{dense,sparse}_attn_backward and the varlen twins
+ * (flash_sparse_attn/ops/triton/flash_sparse_bwd.py:491-748 and :751-1026) including the pre-process
+ * (flash_bwd_preprocess.py:198-266), the post-process (flash_bwd_postprocess.py:151-213) and the
+ * reduction over QO splits (flash_sparse_bwd.py:741-746).
+ *
+ * q/k/v/out/dout/dq/dk/dv use the forward layouts (dout, dq like q; dk, dv like k). lse is the forward
+ * output (natural log). Caller-owned fp32 workspaces, all sized with R = fsa_bwd_padded_rows():
+ *   lse2_ws  [heads_q, R]            dpsum_ws [heads_q, R]
+ *   dq_accum [heads_q, R, head_dim]  (zeroed by this call)
+ *   dk_partial, dv_partial [num_splits, rows_k, heads_kv, head_dim] only when FSA_F_SPLIT and
+ *   num_splits > 1 (rows_k = batch*seqlen_k or total_k); otherwise null.
+ * dq is accumulated with TMA reduce-adds in fp32 (summation order across key tiles is not fixed,
+ * like the reference's atomics); dk and dv are reduced inside one CTA per key tile in a fixed order.
+ */
+typedef struct FsaBwdArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* out;
+  const void* dout;
+  const float* lse;
+  void* dq;
+  void* dk;
+  void* dv;
+  float* lse2_ws;
+  float* dpsum_ws;
+  float* dq_accum;
+  float* dk_partial;
+  float* dv_partial;
+  const int32_t* cu_seqlens_q;
+  const int32_t* cu_seqlens_k;
+  const int32_t* seqused_q;
+  const int32_t* seqused_k;
+  const int32_t* window_sizes;
+  int32_t* status;
+  uint8_t* tile_map; /* optional [batch, heads_q, key tiles, splits, query tiles]; may be null */
+  int64_t q_stride_b, q_stride_s, q_stride_h;
+  int64_t k_stride_b, k_stride_s, k_stride_h;
+  int64_t v_stride_b, v_stride_s, v_stride_h;
+  int64_t o_stride_b, o_stride_s, o_stride_h;
+  int64_t do_stride_b, do_stride_s, do_stride_h;
+  int64_t dq_stride_b, dq_stride_s, dq_stride_h;
+  int64_t dk_stride_b, dk_stride_s, dk_stride_h; /* dv must share dk's strides */
+  int64_t lse_stride_b, lse_stride_h;
+  int32_t batch, seqlen_q, seqlen_k;
+  int32_t total_q, total_k;
+  int32_t heads_q, heads_kv, head_dim;
+  int32_t window_stride;
+  int32_t num_splits;
+  int32_t tile_m, tile_n; /* 0 = default (128, 128) */
+  int32_t kind, dtype;
+  uint32_t flags;
+  float softmax_scale, softmax_threshold, gate_threshold;
+} FsaBwdArgs;
+
+int fsa_bwd(const FsaBwdArgs* args, void* stream);
+
+/* Rows of the tile-padded backward workspaces: every sequence starts on a multiple of 128 rows
+ * (batch*ceil128(seqlen_q), or ceil128(total_q + 128*batch) for packed input). Host arithmetic. */
+int64_t fsa_bwd_padded_rows(int batch, int seqlen_q, int total_q, int is_varlen);
+
 /* Integer schedule of one forward query tile, for checking against the reference's
  * AttnFwdBlockScheduler.create (flash_sparse_attn/ops/triton/scheduler.py:836-948). out9 receives
  * n_min, n_max, n_max_no_mask, win_min, win_max, win_min_no_mask, win_max_no_mask, sink_min, sink_max.
