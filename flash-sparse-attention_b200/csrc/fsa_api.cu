@@ -74,11 +74,24 @@ int make_map4(CUtensorMap* map, int dt, const void* base, uint64_t head_dim, uin
 
 int cdiv(int a, int b) { return (a + b - 1) / b; }
 
+cudaEvent_t g_ev_before = nullptr, g_ev_after = nullptr;
+void mark_before(cudaStream_t s) {
+  if (g_ev_before) cudaEventRecord(g_ev_before, s);
+}
+void mark_after(cudaStream_t s) {
+  if (g_ev_after) cudaEventRecord(g_ev_after, s);
+}
+
 }  // namespace
 
 extern "C" {
 
 int fsa_abi_version(void) { return FSA_ABI_VERSION; }
+
+void fsa_set_profile_events(void* before, void* after) {
+  g_ev_before = reinterpret_cast<cudaEvent_t>(before);
+  g_ev_after = reinterpret_cast<cudaEvent_t>(after);
+}
 
 const char* fsa_status_string(int code) {
   switch (code) {
@@ -277,7 +290,9 @@ int fsa_fwd(const FsaFwdArgs* a, void* stream_) {
   if (a->flags & FSA_F_ADAPT_GATE) f |= fsa::F_ADAPT_GATE;
   p.flags = f;
 
+  mark_before(stream);
   cudaError_t e = fsa::launch_fwd(p, a->kind, a->dtype, a->head_dim, stream);
+  mark_after(stream);
   if (e == cudaErrorInvalidValue) return FSA_ERR_UNSUPPORTED;
   if (e != cudaSuccess) return FSA_ERR_LAUNCH;
 
@@ -433,7 +448,9 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
   if (a->seqused_q) f |= fsa::F_USED_Q;
   if (a->seqused_k) f |= fsa::F_USED_K;
   p.flags = f;
+  mark_before(stream);
   cudaError_t e = fsa::launch_bwd(p, a->kind, a->dtype, a->head_dim, stream);
+  mark_after(stream);
   if (e == cudaErrorInvalidValue) return FSA_ERR_UNSUPPORTED;
   if (e != cudaSuccess) return FSA_ERR_LAUNCH;
 

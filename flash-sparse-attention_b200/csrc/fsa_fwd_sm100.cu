@@ -517,12 +517,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
           bars->vote_any[q][par][wq] = (want ? 1 : 0) | (drop ? 2 : 0);
           mbar_arrive(&bars->wg_sync[q]);
         }
-        ok = mbar_wait(&bars->wg_sync[q], par, abort_flag);
-        if (!ok) break;
-        const int v = bars->vote_any[q][par][0] | bars->vote_any[q][par][1] | bars->vote_any[q][par][2] |
-                      bars->vote_any[q][par][3];
-        // max over rows ignores NaN rows; a tile is skipped iff that max is < 0
-        skip = !(v & 1) && (v & 2);
+        // a warp holding a row that wants the tile already knows the outcome ("keep") and moves on;
+        // only warps whose rows all vote "skip" have to hear from the others. Every warp still
+        // arrives once per tile, and none can reach the next tile's vote before all have arrived
+        // here (the next S tile is only issued after all four warps published P or the skip).
+        if (!want) {
+          ok = mbar_wait(&bars->wg_sync[q], par, abort_flag);
+          if (!ok) break;
+          const int v = bars->vote_any[q][par][0] | bars->vote_any[q][par][1] | bars->vote_any[q][par][2] |
+                        bars->vote_any[q][par][3];
+          // max over rows ignores NaN rows; a tile is skipped iff that max is < 0
+          skip = !(v & 1) && (v & 2);
+        }
         if (wq == 0 && lane == 0) {
           bars->skip_flag[q][par] = skip ? 1 : 0;
           if (p.tile_map) {

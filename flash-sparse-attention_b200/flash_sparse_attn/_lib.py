@@ -183,6 +183,8 @@ def load():
     lib.fsa_bwd.argtypes = [POINTER(FsaBwdArgs), c_void_p]
     lib.fsa_bwd_padded_rows.restype = c_int64
     lib.fsa_bwd_padded_rows.argtypes = [c_int, c_int, c_int, c_int]
+    lib.fsa_set_profile_events.restype = None
+    lib.fsa_set_profile_events.argtypes = [c_void_p, c_void_p]
     lib.fsa_debug_fwd_schedule.restype = None
     lib.fsa_debug_fwd_schedule.argtypes = [c_int] * 4 + [POINTER(c_int32)] + [c_int] * 7 + [POINTER(c_int32)]
     lib.fsa_debug_bwd_schedule.restype = None
@@ -239,6 +241,13 @@ def check_status(device=None):
         if v != 0:
             t.zero_()
             raise RuntimeError(f"fsa kernel reported device status {v} (a pipeline wait expired)")
+
+
+def set_profile_events(before=None, after=None):
+    """Have the next operator calls of this thread record `before` / `after` (torch.cuda.Event, already
+    recorded once so that their handles exist) around their main kernel; None, None switches it off."""
+    load().fsa_set_profile_events(before.cuda_event if before is not None else None,
+                                  after.cuda_event if after is not None else None)
 
 
 def current_stream_ptr(device) -> int:

@@ -102,6 +102,10 @@ def attn_backward(
             seqlen_q=seqlen_k, seqlen_k=seqlen_q, num_SMs=utils.device_num_sms(device), TILE_M=TILE_N,
             TILE_N=TILE_M, is_local=is_local, num_heads_kv=num_heads_kv,
         )
+        # one CTA per (key tile, KV head, batch): when that already oversubscribes the SMs, splitting the
+        # query range only adds fp32 partials of dK/dV
+        if batch * num_heads_kv * (-(-seqlen_k // TILE_N)) >= 2 * utils.device_num_sms(device):
+            num_splits = 1
     elif not is_split_qo:
         num_splits = 1
     use_split = bool(is_split_qo) and num_splits > 1

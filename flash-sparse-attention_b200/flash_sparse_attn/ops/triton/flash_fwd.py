@@ -113,6 +113,12 @@ def attn_forward(
             seqlen_q=seqlen_q * group_packed, seqlen_k=seqlen_k, num_SMs=utils.device_num_sms(device),
             TILE_M=TILE_M, TILE_N=TILE_N, is_local=is_local, num_heads_kv=num_heads_kv,
         )
+        # The reference's rule only looks at the query tiles of ONE (batch, head). When batch x heads
+        # already gives every SM several CTAs, splitting only adds fp32 partial traffic: keep one split.
+        m_pairs = -(-seqlen_q * group_packed // (2 * TILE_M))
+        ctas = batch * (num_heads_kv if group_packed > 1 else num_heads_q) * m_pairs
+        if ctas >= 2 * utils.device_num_sms(device):
+            num_splits = 1
     elif not is_split_kv:
         num_splits = 1
     # a single split is the unsplit kernel (same schedule, no workspace, no combine pass)

@@ -179,6 +179,14 @@ void fsa_debug_bwd_schedule(int seqlen_q, int seqlen_k, int n_block, int split_i
                             int num_splits, int tile_n, int tile_m, int is_causal, int is_local, int is_split,
                             int32_t out9[9]);
 
+/* Measurement hook (process-wide host state, no device work of its own): the next
+ * fsa_fwd / fsa_bwd / fsa_decode calls record CUDA event `before` right before and
+ * `after` right after their MAIN kernel on the launch stream (cudaEvent_t handles passed as void*).
+ * Null, null switches the hook off. No counterpart in the reference (its benchmarks time whole
+ * operator calls, tests/benchmark_forward.py:114); it exists so that a benchmark can time one
+ * kernel inside a full step without a profiler. */
+void fsa_set_profile_events(void* before, void* after);
+
 const char* fsa_status_string(int code);
 int fsa_abi_version(void);
 
