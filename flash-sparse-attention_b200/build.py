@@ -20,6 +20,7 @@ SOURCES = [
     "fsa_aux.cu",
     "fsa_fwd_sm100.cu",
     "fsa_bwd_sm100.cu",
+    "fsa_dec_sm100.cu",
 ]
 
 NVCC_FLAGS = [

@@ -108,8 +108,9 @@ void fsa_debug_fwd_schedule(int seqlen_q, int seqlen_k, int m_block, int split_i
                             int num_splits, int tile_n, int tile_m, int is_causal, int is_local, int is_split,
                             int gpack, int32_t out9[9]) {
   FsaWindow w = {window[0], window[1], window[2], window[3]};
+  // bit 1 of is_split selects the exact-cover variant used by the decode kernel
   FsaFwdSched s = fsa_fwd_schedule(seqlen_q, seqlen_k, m_block, split_idx, w, num_splits, tile_n, tile_m,
-                                   is_causal != 0, is_local != 0, is_split != 0, gpack);
+                                   is_causal != 0, is_local != 0, (is_split & 1) != 0, gpack, (is_split & 2) != 0);
   out9[0] = s.n_min;
   out9[1] = s.n_max;
   out9[2] = s.n_max_no_mask;
@@ -489,6 +490,133 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
       sp.num_splits = ns;
       if (fsa::launch_split_sum(sp, a->dtype, stream) != cudaSuccess) return FSA_ERR_LAUNCH;
     }
+  }
+  return FSA_OK;
+}
+
+int fsa_combine(const float* out_partial, const float* lse_partial, void* out, float* lse, int num_partials,
+                int rows, int heads, int head_dim, int dtype, void* stream_) {
+  if (!out_partial || !lse_partial || !out || !lse || num_partials <= 0 || rows < 0 || heads <= 0)
+    return FSA_ERR_INVALID_ARG;
+  if (dtype != FSA_DT_BF16 && dtype != FSA_DT_FP16) return FSA_ERR_UNSUPPORTED;
+  fsa::CombineParams c;
+  memset(&c, 0, sizeof(c));
+  c.out_partial = out_partial;
+  c.lse_partial = lse_partial;
+  c.out = out;
+  c.lse = lse;
+  c.op_ss = (long long)rows * heads * head_dim;
+  c.lp_ss = (long long)rows * heads;
+  c.lp_sh = rows;
+  c.o_sb = (long long)heads * head_dim;
+  c.o_sm = 0;
+  c.o_sh = head_dim;
+  c.l_sb = heads;
+  c.l_sh = 1;
+  c.rows = rows;
+  c.rows_per_batch = 1;
+  c.heads = heads;
+  c.head_dim = head_dim;
+  c.num_splits = num_partials;
+  cudaError_t e = fsa::launch_combine(c, dtype, reinterpret_cast<cudaStream_t>(stream_));
+  if (e == cudaErrorInvalidValue) return FSA_ERR_UNSUPPORTED;
+  return e == cudaSuccess ? FSA_OK : FSA_ERR_LAUNCH;
+}
+
+int fsa_decode(const FsaDecArgs* a, void* stream_) {
+  if (!a || !a->q || !a->k || !a->v || !a->status) return FSA_ERR_INVALID_ARG;
+  if (a->batch <= 0 || a->heads_q <= 0 || a->heads_kv <= 0 || a->heads_q % a->heads_kv) return FSA_ERR_INVALID_ARG;
+  if (a->head_dim != 64 && a->head_dim != 128) return FSA_ERR_UNSUPPORTED;
+  if (a->dtype != FSA_DT_BF16 && a->dtype != FSA_DT_FP16) return FSA_ERR_UNSUPPORTED;
+  if (a->kind != FSA_KIND_DENSE && a->kind != FSA_KIND_SPARSE) return FSA_ERR_UNSUPPORTED;
+  if ((a->flags & FSA_F_LOCAL) && !a->window_sizes) return FSA_ERR_INVALID_ARG;
+  const bool paged = a->page_table != nullptr, gather = a->gather_kv_indices != nullptr;
+  const bool varlen_k = a->cu_seqlens_k != nullptr;
+  if (paged && varlen_k) return FSA_ERR_UNSUPPORTED;
+  if (paged && a->page_size <= 0) return FSA_ERR_INVALID_ARG;
+  const int ns = a->num_splits > 0 ? a->num_splits : 1;
+  const bool partial = ns > 1 || a->partial_only;
+  if (partial && (!a->out_partial || !a->lse_partial)) return FSA_ERR_INVALID_ARG;
+  if (!a->partial_only && (!a->out || !a->lse)) return FSA_ERR_INVALID_ARG;
+  if ((a->k_stride_s % 8) || (a->k_stride_h % 8) || (a->k_stride_b % 8) ||
+      (reinterpret_cast<uintptr_t>(a->k) & 15) || (reinterpret_cast<uintptr_t>(a->v) & 15))
+    return FSA_ERR_INVALID_ARG;  // 16-byte row copies
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+
+  fsa::DecKernelParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = a->q;
+  p.k = a->k;
+  p.v = a->v;
+  p.out = a->out;
+  p.lse = a->lse;
+  p.out_partial = a->out_partial;
+  p.lse_partial = a->lse_partial;
+  p.cu_k = a->cu_seqlens_k;
+  p.used_k = a->seqused_k;
+  p.page_table = a->page_table;
+  p.gather_idx = a->gather_kv_indices;
+  p.windows = a->window_sizes;
+  p.tile_map = a->tile_map;
+  p.q_sb = a->q_stride_b;
+  p.q_sh = a->q_stride_h;
+  p.k_sb = a->k_stride_b;
+  p.k_sn = a->k_stride_s;
+  p.k_sh = a->k_stride_h;
+  p.o_sb = a->o_stride_b;
+  p.o_sh = a->o_stride_h;
+  p.l_sb = a->lse_stride_b;
+  p.l_sh = a->lse_stride_h;
+  p.B = a->batch;
+  p.Hq = a->heads_q;
+  p.Hkv = a->heads_kv;
+  p.G = a->heads_q / a->heads_kv;
+  p.sk = paged ? a->page_table_stride * a->page_size : a->seqlen_k;
+  p.sk_capacity = a->seqlen_k;
+  p.topk = a->topk;
+  p.num_splits = ns;
+  p.page_size = a->page_size;
+  p.pt_stride = a->page_table_stride;
+  p.gi_stride = a->gather_stride;
+  p.win_stride = a->window_stride;
+  p.n_tiles = cdiv(gather ? a->topk : p.sk, 16);
+  p.scale_log2 = a->softmax_scale * 1.44269504089f;
+  p.softmax_thr = a->softmax_threshold;
+  unsigned f = 0;
+  if ((a->flags & FSA_F_LOCAL) && !gather) f |= fsa::F_LOCAL;
+  if (partial) f |= fsa::F_SPLIT;
+  if (varlen_k) f |= fsa::F_VARLEN_K;
+  if (paged) f |= fsa::F_PAGED;
+  if (gather) f |= fsa::F_GATHER;
+  if (a->seqused_k) f |= fsa::F_USED_K;
+  p.flags = f;
+  mark_before(stream);
+  cudaError_t e = fsa::launch_dec(p, a->kind, a->dtype, a->head_dim, stream);
+  mark_after(stream);
+  if (e == cudaErrorInvalidValue) return FSA_ERR_UNSUPPORTED;
+  if (e != cudaSuccess) return FSA_ERR_LAUNCH;
+  if (partial && !a->partial_only) {
+    fsa::CombineParams c;
+    memset(&c, 0, sizeof(c));
+    c.out_partial = a->out_partial;
+    c.lse_partial = a->lse_partial;
+    c.out = a->out;
+    c.lse = a->lse;
+    c.op_ss = (long long)a->batch * a->heads_q * a->head_dim;
+    c.lp_ss = (long long)a->batch * a->heads_q;
+    c.lp_sh = a->batch;
+    c.o_sb = a->o_stride_b;
+    c.o_sm = 0;
+    c.o_sh = a->o_stride_h;
+    c.l_sb = a->lse_stride_b;
+    c.l_sh = a->lse_stride_h;
+    c.rows = a->batch;
+    c.rows_per_batch = 1;
+    c.heads = a->heads_q;
+    c.head_dim = a->head_dim;
+    c.num_splits = ns;
+    e = fsa::launch_combine(c, a->dtype, stream);
+    if (e != cudaSuccess) return FSA_ERR_LAUNCH;
   }
   return FSA_OK;
 }

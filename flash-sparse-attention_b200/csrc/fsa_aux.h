@@ -54,6 +54,7 @@ cudaError_t launch_bwd_pre(const BwdPreParams& p, int dtype, cudaStream_t stream
 cudaError_t launch_bwd_post(const BwdPostParams& p, int dtype, cudaStream_t stream);
 cudaError_t launch_split_sum(const SplitSumParams& p, int dtype, cudaStream_t stream);
 cudaError_t launch_bwd(const BwdKernelParams& p, int kind, int dtype, int head_dim, cudaStream_t stream);
+cudaError_t launch_dec(const DecKernelParams& p, int kind, int dtype, int head_dim, cudaStream_t stream);
 cudaError_t launch_combine(const CombineParams& p, int dtype, cudaStream_t stream);
 cudaError_t launch_fwd(const FwdKernelParams& p, int kind, int dtype, int head_dim, cudaStream_t stream);
 

@@ -1,0 +1,425 @@
+// Decode attention (one query position per sequence) for sm_100a: a bandwidth kernel.
+//
+// One CTA serves one KV head of one sequence (and one KV split). The G query heads of that KV head
+// are the rows of a 16-row tile (packed GQA, like the reference's decode: scheduler.py:2455-2461).
+// The CTA's key range is cut into four contiguous sub-ranges, one per warp; each warp streams its
+// keys in 16-key tiles through a private 3-stage cp.async ring (16-byte copies, zero-fill for
+// masked / out-of-range rows), runs a complete flash-decoding recurrence on them with mma.sync
+// m16n8k16 (the arithmetic is ~8 FLOP/byte, far below the tensor roofline, so the legacy MMA path
+// is enough and keeps the kernel free to run several CTAs per SM), and the four partial states are
+// merged in shared memory at the end. In terms of the reference's schedule every warp is one KV
+// split: the tile ranges come from the same functions with 4 x num_splits splits
+// (block_info.py:5-123 for contiguous / paged caches, :321-349 for gathered top-k lists).
+//
+// Key addressing covers the reference's three modes and their combination:
+//   contiguous  row = key position                               (flash_sparse_dec.py:673-678)
+//   paged       row = page_table[b, pos / page] * page + pos % page   (paged_kv.py:10-30)
+//   gathered    pos = gather_kv_indices[b, i], negative = masked     (topk_gather_kv.py:5-77)
+//   gathered + paged: the gathered logical position goes through the page table (the reference
+//   rejects this combination, assert_inputs.py:303-305; here it is defined as the composition).
+#include <mma.h>
+#include "fsa_aux.h"
+#include "fsa_params.h"
+#include "fsa_ptx.cuh"
+#include "fsa_schedule.h"
+
+namespace fsa {
+
+namespace {
+
+constexpr int DTN = 16;      // keys per warp tile
+constexpr int DSTAGES = 3;   // cp.async ring depth per warp
+constexpr int DWARPS = 4;
+
+template <int HD>
+struct DecSmem {
+  static constexpr int kRow = HD * 2;                 // bytes per key row
+  static constexpr int kTile = DTN * kRow;            // one K or V tile
+  static constexpr int kWarp = DSTAGES * 2 * kTile;   // ring of one warp
+  static constexpr int kMerge = DWARPS * (16 * HD * 4 + 16 * 8);  // O, m, l of every warp
+  static constexpr int kTotal = (DWARPS * kWarp > kMerge ? DWARPS * kWarp : kMerge);
+};
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int sz = valid ? 16 : 0;  // src-size 0 -> the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+template <typename T>
+__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma16816<__half>(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int HD, typename T, int KIND>
+__global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelParams p) {
+  using SM = DecSmem<HD>;
+  constexpr int CH = HD / 8;  // 16-byte chunks per key row
+  extern __shared__ __align__(128) uint8_t dsm[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+
+  int idx = blockIdx.x;
+  const int hkv = idx % p.Hkv;
+  idx /= p.Hkv;
+  const int b = idx / p.num_splits;
+  const int split = idx - b * p.num_splits;
+  const bool gather = p.flags & F_GATHER, paged = p.flags & F_PAGED, local = p.flags & F_LOCAL;
+  const int off_k = (p.flags & F_VARLEN_K) ? p.cu_k[b] : 0;
+  const int sk = (p.flags & F_USED_K) ? p.used_k[b] : ((p.flags & F_VARLEN_K) ? p.cu_k[b + 1] - off_k : p.sk);
+  const int bk = (p.flags & F_VARLEN_K) ? 0 : b;
+  FsaWindow w = {0, 0, 0, 0};
+  if (local) {
+    const int* wp = p.windows + (long long)hkv * p.win_stride;
+    w.sink = wp[0];
+    w.left = wp[1];
+    w.right = wp[2];
+    w.near_ = wp[3];
+  }
+  const int nsub = p.num_splits * DWARPS;
+  const int sub = split * DWARPS + warp;
+  const FsaFwdSched sched = gather ? fsa_topk_schedule(p.topk, sub, nsub, DTN)
+                                   : fsa_fwd_schedule(1, sk, 0, sub, w, nsub, DTN, 16, false, local, true, p.G,
+                                                      /*cover_single_query=*/true);
+  const bool loc_sched = local && !gather;
+  const float c = p.scale_log2;
+  const float thr_log2 = (KIND != KIND_DENSE) ? log2f(fmaxf(fminf(p.softmax_thr / float(sk), 1.0f), 0.0f)) : 0.f;
+  const int* gidx = gather ? p.gather_idx + (long long)b * p.gi_stride : nullptr;
+  const int* ptab = paged ? p.page_table + (long long)b * p.pt_stride : nullptr;
+  const int capacity = paged ? p.pt_stride * p.page_size
+                             : ((p.flags & F_VARLEN_K) ? p.cu_k[b + 1] - off_k : p.sk_capacity);
+
+  uint8_t* ring = dsm + warp * SM::kWarp;
+  const char* kbase = reinterpret_cast<const char*>(p.k);
+  const char* vbase = reinterpret_cast<const char*>(p.v);
+
+  // Address (in elements) of key `pos` of this sequence / head inside the K (and V) tensor; -1 = no row.
+  auto row_elem = [&](int pos) -> long long {
+    if (pos < 0 || pos >= capacity) return -1;
+    if (paged) {
+      const int page = ptab[pos / p.page_size];
+      return (long long)page * p.k_sb + (long long)(pos % p.page_size) * p.k_sn + (long long)hkv * p.k_sh;
+    }
+    return (long long)bk * p.k_sb + (long long)(off_k + pos) * p.k_sn + (long long)hkv * p.k_sh;
+  };
+
+  // Issue the copies of tile n into ring slot `slot`; returns the bitmask of keys that exist.
+  auto issue_tile = [&](int n, int slot) -> unsigned {
+    long long e = -1;
+    int pos = -1;
+    if (lane < DTN) {
+      const int i = n * DTN + lane;
+      if (gather)
+        pos = (i < p.topk) ? gidx[i] : -1;
+      else
+        pos = (i < sk) ? i : -1;
+      e = row_elem(pos);
+    }
+    const unsigned present = __ballot_sync(0xffffffffu, e >= 0) & 0xffffu;
+    uint8_t* kt = ring + slot * 2 * SM::kTile;
+    uint8_t* vt = kt + SM::kTile;
+#pragma unroll
+    for (int it = 0; it < DTN * CH / 32; ++it) {
+      const int item = it * 32 + lane;
+      const int r = item / CH, ch = item % CH;
+      const long long er = __shfl_sync(0xffffffffu, e, r);
+      const bool ok = er >= 0;
+      const long long src = ok ? (er + ch * 8) * 2 : 0;
+      const uint32_t dsto = r * SM::kRow + ((ch ^ (r & 7)) << 4);
+      cp_async16(kt + dsto, kbase + src, ok);
+      cp_async16(vt + dsto, vbase + src, ok);
+    }
+    return present;
+  };
+
+  const int n_mtiles = (p.G + 15) / 16;
+  for (int mt = 0; mt < n_mtiles; ++mt) {
+    // ---- Q fragments of this warp (all warps hold the same rows) --------------------------------
+    uint32_t qa[HD / 16][4];
+    {
+      const int r0 = mt * 16 + g, r1 = r0 + 8;
+      const T* q0 = reinterpret_cast<const T*>(p.q) + (long long)b * p.q_sb + (long long)(hkv * p.G + r0) * p.q_sh;
+      const T* q1 = reinterpret_cast<const T*>(p.q) + (long long)b * p.q_sb + (long long)(hkv * p.G + r1) * p.q_sh;
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; ++kk) {
+        qa[kk][0] = (r0 < p.G) ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 2 * t) : 0u;
+        qa[kk][1] = (r1 < p.G) ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 2 * t) : 0u;
+        qa[kk][2] = (r0 < p.G) ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 8 + 2 * t) : 0u;
+        qa[kk][3] = (r1 < p.G) ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 8 + 2 * t) : 0u;
+      }
+    }
+    const bool row0_ok = mt * 16 + g < p.G, row1_ok = mt * 16 + g + 8 < p.G;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+
+    // ---- ring prologue ----------------------------------------------------------------------------
+    int n_load = fsa_fwd_next_tile_below(sched, 1 << 28, loc_sched);
+    unsigned present_q[DSTAGES];
+    int slot_load = 0;
+#pragma unroll
+    for (int s = 0; s < DSTAGES - 1; ++s) {
+      present_q[s] = 0;
+      if (n_load >= 0) {
+        present_q[s] = issue_tile(n_load, s);
+        n_load = fsa_fwd_next_tile_below(sched, n_load, loc_sched);
+      }
+      cp_async_commit();
+    }
+    present_q[DSTAGES - 1] = 0;
+    slot_load = DSTAGES - 1;
+    int slot = 0;
+    for (int n = fsa_fwd_next_tile_below(sched, 1 << 28, loc_sched); n >= 0;
+         n = fsa_fwd_next_tile_below(sched, n, loc_sched)) {
+      // keep the ring full, then wait for the oldest tile
+      unsigned pres_new = 0;
+      if (n_load >= 0) {
+        pres_new = issue_tile(n_load, slot_load);
+        n_load = fsa_fwd_next_tile_below(sched, n_load, loc_sched);
+      }
+      cp_async_commit();
+      present_q[slot_load] = pres_new;
+      slot_load = (slot_load + 1) % DSTAGES;
+      cp_async_wait<DSTAGES - 1>();
+      __syncwarp();
+      const unsigned present = present_q[slot];
+      const uint32_t kt = smem_u32(ring + slot * 2 * SM::kTile);
+      const uint32_t vt = kt + SM::kTile;
+
+      // ---- visibility of the 16 keys (row-uniform: every packed row is the same query position) ------
+      unsigned vis = present;
+      if (!gather) {
+        const int mode = fsa_fwd_tile_mode(sched, n, true, local);
+        if (mode != FSA_MASK_NONE) {
+          const int k_idx = n * DTN + (lane & 15);
+          const int diag = sk - 1;
+          bool okk = k_idx < sk;
+          if (mode == FSA_MASK_LOCAL || mode == FSA_MASK_LOCAL_SINK) {
+            const int near = diag - k_idx;
+            bool band = (near >= 0 && near < w.near_) ||
+                        (near >= w.near_ + w.right && near < w.near_ + w.right + w.left);
+            if (mode == FSA_MASK_LOCAL_SINK) band = band || (k_idx < w.sink && near >= 0);
+            okk = okk && band;
+          }
+          vis &= __ballot_sync(0xffffffffu, okk) & 0xffffu;
+        }
+      }
+
+      // ---- S = Q K^T over this tile: 2 key groups of 8 ------------------------------------------------
+      float s[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; kk += 2) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int r = 8 * j + (lane & 7);
+          const int ch = 2 * kk + (lane >> 3);
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4(kt + r * SM::kRow + ((ch ^ (r & 7)) << 4), b0, b1, b2, b3);
+          mma16816<T>(s[j], qa[kk], b0, b1);
+          mma16816<T>(s[j], qa[kk + 1], b2, b3);
+        }
+      }
+      // mask: element (j, e) is key 8j + 2t + (e & 1)
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (!((vis >> (8 * j + 2 * t + (e & 1))) & 1u)) s[j][e] = -INFINITY;
+
+      float m_cur[2];
+      m_cur[0] = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+      m_cur[1] = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        m_cur[r] = fmaxf(m_cur[r], __shfl_xor_sync(0xffffffffu, m_cur[r], 1));
+        m_cur[r] = fmaxf(m_cur[r], __shfl_xor_sync(0xffffffffu, m_cur[r], 2));
+      }
+
+      bool skip = false;
+      if (KIND != KIND_DENSE) {
+        // flash_sparse_attn/ops/triton/activations.py:129-138 over the real rows of the tile
+        const float v0 = (m_cur[0] - m_run[0]) * c - log2f(l_run[0]) - thr_log2;
+        const float v1 = (m_cur[1] - m_run[1]) * c - log2f(l_run[1]) - thr_log2;
+        const bool want = (row0_ok && v0 >= 0.f) || (row1_ok && v1 >= 0.f);
+        const bool drop = (row0_ok && v0 < 0.f) || (row1_ok && v1 < 0.f);
+        skip = !__any_sync(0xffffffffu, want) && __any_sync(0xffffffffu, drop);
+        if (p.tile_map && lane == 0 && mt == 0)
+          p.tile_map[((long long)b * p.Hkv + hkv) * p.n_tiles + n] = skip ? 2 : 1;
+      }
+      if (!skip) {
+        float scale[2];
+        uint32_t pa[4];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          float m_new = fmaxf(m_cur[r], m_run[r]);
+          m_new = fmaxf(m_new, -1e6f);
+          scale[r] = ex2_approx((m_run[r] - m_new) * c);
+          m_run[r] = m_new;
+        }
+        const float mc0 = m_run[0] * c, mc1 = m_run[1] * c;
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const float p0 = ex2_approx(fmaf(s[j][0], c, -mc0)), p1 = ex2_approx(fmaf(s[j][1], c, -mc0));
+          const float p2 = ex2_approx(fmaf(s[j][2], c, -mc1)), p3 = ex2_approx(fmaf(s[j][3], c, -mc1));
+          sum0 += p0 + p1;
+          sum1 += p2 + p3;
+          pa[2 * j] = pack2<T>(p0, p1);
+          pa[2 * j + 1] = pack2<T>(p2, p3);
+        }
+        sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+        sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+        sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
+        sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+        l_run[0] = l_run[0] * scale[0] + sum0;
+        l_run[1] = l_run[1] * scale[1] + sum1;
+        if (__any_sync(0xffffffffu, scale[0] != 1.f || scale[1] != 1.f)) {
+#pragma unroll
+          for (int j = 0; j < HD / 8; ++j) {
+            o[j][0] *= scale[0];
+            o[j][1] *= scale[0];
+            o[j][2] *= scale[1];
+            o[j][3] *= scale[1];
+          }
+        }
+        // ---- O += P V -----------------------------------------------------------------------------------
+#pragma unroll
+        for (int jd = 0; jd < HD / 16; ++jd) {
+          const int r = (lane & 7) + 8 * ((lane >> 3) & 1);
+          const int ch = 2 * jd + (lane >> 4);
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4_t(vt + r * SM::kRow + ((ch ^ (r & 7)) << 4), b0, b1, b2, b3);
+          mma16816<T>(o[2 * jd], pa, b0, b1);
+          mma16816<T>(o[2 * jd + 1], pa, b2, b3);
+        }
+      }
+      __syncwarp();
+      slot = (slot + 1) % DSTAGES;
+    }
+    cp_async_wait<0>();
+    __syncthreads();  // every warp is done with its ring: the space becomes the merge buffer
+
+    // ---- merge the four warps (flash_sparse_attn/ops/triton/flash_dec_combine.py:15-153 in spirit) -----
+    float* mo = reinterpret_cast<float*>(dsm) + warp * (16 * HD + 32);
+    float* mm = mo + 16 * HD;
+    float* ml = mm + 16;
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) {
+      *reinterpret_cast<float2*>(mo + g * HD + 8 * j + 2 * t) = make_float2(o[j][0], o[j][1]);
+      *reinterpret_cast<float2*>(mo + (g + 8) * HD + 8 * j + 2 * t) = make_float2(o[j][2], o[j][3]);
+    }
+    if (t == 0) {
+      mm[g] = m_run[0];
+      mm[g + 8] = m_run[1];
+      ml[g] = l_run[0];
+      ml[g + 8] = l_run[1];
+    }
+    __syncthreads();
+    const float* all = reinterpret_cast<const float*>(dsm);
+    for (int item = tid; item < 16 * (HD / 4); item += DWARPS * 32) {
+      const int r = item / (HD / 4), d0 = (item % (HD / 4)) * 4;
+      const int row = mt * 16 + r;
+      if (row >= p.G) continue;
+      float m_tot = -INFINITY;
+#pragma unroll
+      for (int ww = 0; ww < DWARPS; ++ww) m_tot = fmaxf(m_tot, all[ww * (16 * HD + 32) + 16 * HD + r]);
+      float l_tot = 0.f;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int ww = 0; ww < DWARPS; ++ww) {
+        const float* base = all + ww * (16 * HD + 32);
+        const float mw = base[16 * HD + r], lw = base[16 * HD + 16 + r];
+        const float wgt = (mw == -INFINITY || lw == 0.f) ? 0.f : ex2_approx((mw - m_tot) * c);
+        l_tot += lw * wgt;
+        const float4 ov = *reinterpret_cast<const float4*>(base + r * HD + d0);
+        acc.x += ov.x * wgt;
+        acc.y += ov.y * wgt;
+        acc.z += ov.z * wgt;
+        acc.w += ov.w * wgt;
+      }
+      const bool dead = (l_tot == 0.f) || (l_tot != l_tot);
+      const float inv = dead ? 1.f : 1.f / l_tot;
+      const int head = hkv * p.G + row;
+      if (p.flags & F_SPLIT) {
+        float* dst = p.out_partial + (((long long)split * p.B + b) * p.Hq + head) * HD + d0;
+        *reinterpret_cast<float4*>(dst) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+        if (d0 == 0)
+          p.lse_partial[((long long)split * p.Hq + head) * p.B + b] = dead ? -INFINITY : m_tot * c + log2f(l_tot);
+      } else {
+        T* dst = reinterpret_cast<T*>(p.out) + (long long)b * p.o_sb + (long long)head * p.o_sh + d0;
+        uint2 v;
+        v.x = pack2<T>(acc.x * inv, acc.y * inv);
+        v.y = pack2<T>(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(dst) = v;
+        if (d0 == 0)
+          p.lse[(long long)b * p.l_sb + (long long)head * p.l_sh] =
+              dead ? -INFINITY : (m_tot * c + log2f(l_tot)) * 0.6931471805599453f;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+template <int HD, typename T, int KIND>
+cudaError_t launch_one(const DecKernelParams& p, cudaStream_t stream) {
+  auto kern = dec_kernel<HD, T, KIND>;
+  constexpr int smem = DecSmem<HD>::kTotal;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const long long grid = (long long)p.Hkv * p.B * p.num_splits;
+  if (grid <= 0) return cudaSuccess;
+  kern<<<(unsigned)grid, DWARPS * 32, smem, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_dec(const DecKernelParams& p, int kind, int dtype, int head_dim, cudaStream_t stream) {
+#define FSA_DEC_CASE(HD_, T_, DT_)                                               \
+  if (head_dim == HD_ && dtype == DT_) {                                         \
+    if (kind == KIND_DENSE) return launch_one<HD_, T_, KIND_DENSE>(p, stream);   \
+    if (kind == KIND_SPARSE) return launch_one<HD_, T_, KIND_SPARSE>(p, stream); \
+  }
+  FSA_DEC_CASE(128, __nv_bfloat16, DT_BF16)
+  FSA_DEC_CASE(128, __half, DT_FP16)
+  FSA_DEC_CASE(64, __nv_bfloat16, DT_BF16)
+  FSA_DEC_CASE(64, __half, DT_FP16)
+#undef FSA_DEC_CASE
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace fsa

@@ -73,4 +73,26 @@ struct alignas(64) BwdKernelParams {
   unsigned flags;
 };
 
+struct DecKernelParams {
+  const void* q;  // [B, Hq, D]
+  const void* k;  // [B, Sk, Hkv, D] | packed [Tk, Hkv, D] | paged [pages, page, Hkv, D]
+  const void* v;
+  void* out;           // [B, Hq, D]
+  float* lse;          // [B, Hq]
+  float* out_partial;  // [splits, B, Hq, D]
+  float* lse_partial;  // [splits, Hq, B] base-2
+  const int* cu_k;
+  const int* used_k;
+  const int* page_table;
+  const int* gather_idx;
+  const int* windows;
+  uint8_t* tile_map;  // optional [B, Hkv, n_tiles] over 16-key tiles
+  long long q_sb, q_sh, k_sb, k_sn, k_sh, o_sb, o_sh, l_sb, l_sh;
+  int B, Hq, Hkv, G;
+  int sk, sk_capacity, topk;
+  int num_splits, page_size, pt_stride, gi_stride, win_stride, n_tiles;
+  float scale_log2, softmax_thr;
+  unsigned flags;
+};
+
 }  // namespace fsa

@@ -55,9 +55,17 @@ FSA_HD void fsa_split_range(int total, int ns, int s, int* off, int* cnt) {
 }
 
 // block_info.py:5-123
+//
+// `cover_single_query`: with one query position, local windows and split-KV the reference starts the
+// near-diagonal range at ceil((n_idx_near + 1) / TILE_N) (block_info.py:60-64). When the near band
+// does not begin on a tile boundary that drops the band's first, partial tile: those keys are visible
+// in the reference's eager ground truth (tests/test_utils.py:541-563) but never visited by its
+// kernel. false reproduces the reference's numbers exactly; true rounds down like the general path,
+// so that the visited tiles cover the mask exactly (what the decode kernel uses).
 FSA_HD void fsa_n_block_min_max(int sq, int sk, int m_block, int split_idx, FsaWindow w, int num_splits, int TN,
                                 int TM, bool causal, bool local, bool split_kv, int gpack, int* o_n_min,
-                                int* o_n_max, int* o_win_min, int* o_win_max, int* o_sink_min, int* o_sink_max) {
+                                int* o_n_max, int* o_win_min, int* o_win_max, int* o_sink_min, int* o_sink_max,
+                                bool cover_single_query = false) {
   int n_block_max = fsa_cdiv(sk, TN);
   int n_block_min = 0;
   int win_max = n_block_max, win_min = 0;
@@ -89,7 +97,8 @@ FSA_HD void fsa_n_block_min_max(int sq, int sk, int m_block, int split_idx, FsaW
   }
   if (split_kv) {
     if (local) {
-      int diag_min = (sq == 1) ? fsa_imax(fsa_cdiv(fsa_imax(n_idx_near + 1, 0), TN), 0) : n_block_min;
+      int diag_min = (sq == 1 && !cover_single_query) ? fsa_imax(fsa_cdiv(fsa_imax(n_idx_near + 1, 0), TN), 0)
+                                                      : n_block_min;
       diag_min = fsa_imax(diag_min, sink_excl);
       const int diag_max = n_block_max;
       win_max = fsa_imax(win_max, win_min);
@@ -154,10 +163,11 @@ FSA_HD int fsa_n_block_min_before_local_mask(int sq, int sk, int m_block, int n_
 
 // scheduler.py:836-948 (forward) — also used for decode with sq = 1, m_block = 0 (scheduler.py:1180-1260).
 FSA_HD FsaFwdSched fsa_fwd_schedule(int sq, int sk, int m_block, int split_idx, FsaWindow w, int num_splits, int TN,
-                                    int TM, bool causal, bool local, bool split_kv, int gpack) {
+                                    int TM, bool causal, bool local, bool split_kv, int gpack,
+                                    bool cover_single_query = false) {
   FsaFwdSched s;
   fsa_n_block_min_max(sq, sk, m_block, split_idx, w, num_splits, TN, TM, causal, local, split_kv, gpack, &s.n_min,
-                      &s.n_max, &s.win_min, &s.win_max, &s.sink_min, &s.sink_max);
+                      &s.n_max, &s.win_min, &s.win_max, &s.sink_min, &s.sink_max, cover_single_query);
   s.n_max_no_mask = fsa_n_block_min_causal_local_mask(sq, sk, m_block, s.n_min, 0, 0, TN, TM, false, gpack);
   if (split_kv) s.n_max_no_mask = fsa_imin(s.n_max_no_mask, s.n_max);
   if (local) {

@@ -154,6 +154,54 @@ class FsaBwdArgs(ctypes.Structure):
     ]
 
 
+class FsaDecArgs(ctypes.Structure):
+    _fields_ = [
+        ("q", c_void_p),
+        ("k", c_void_p),
+        ("v", c_void_p),
+        ("out", c_void_p),
+        ("lse", c_void_p),
+        ("out_partial", c_void_p),
+        ("lse_partial", c_void_p),
+        ("cu_seqlens_k", c_void_p),
+        ("seqused_k", c_void_p),
+        ("page_table", c_void_p),
+        ("gather_kv_indices", c_void_p),
+        ("window_sizes", c_void_p),
+        ("status", c_void_p),
+        ("tile_map", c_void_p),
+        ("q_stride_b", c_int64),
+        ("q_stride_h", c_int64),
+        ("k_stride_b", c_int64),
+        ("k_stride_s", c_int64),
+        ("k_stride_h", c_int64),
+        ("o_stride_b", c_int64),
+        ("o_stride_h", c_int64),
+        ("lse_stride_b", c_int64),
+        ("lse_stride_h", c_int64),
+        ("batch", c_int32),
+        ("seqlen_k", c_int32),
+        ("total_k", c_int32),
+        ("heads_q", c_int32),
+        ("heads_kv", c_int32),
+        ("head_dim", c_int32),
+        ("topk", c_int32),
+        ("gather_stride", c_int32),
+        ("num_pages", c_int32),
+        ("page_size", c_int32),
+        ("page_table_stride", c_int32),
+        ("window_stride", c_int32),
+        ("num_splits", c_int32),
+        ("partial_only", c_int32),
+        ("kind", c_int32),
+        ("dtype", c_int32),
+        ("flags", c_uint32),
+        ("softmax_scale", c_float),
+        ("softmax_threshold", c_float),
+        ("gate_threshold", c_float),
+    ]
+
+
 _lib = None
 
 
@@ -183,6 +231,10 @@ def load():
     lib.fsa_bwd.argtypes = [POINTER(FsaBwdArgs), c_void_p]
     lib.fsa_bwd_padded_rows.restype = c_int64
     lib.fsa_bwd_padded_rows.argtypes = [c_int, c_int, c_int, c_int]
+    lib.fsa_decode.restype = c_int
+    lib.fsa_decode.argtypes = [POINTER(FsaDecArgs), c_void_p]
+    lib.fsa_combine.restype = c_int
+    lib.fsa_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
     lib.fsa_set_profile_events.restype = None
     lib.fsa_set_profile_events.argtypes = [c_void_p, c_void_p]
     lib.fsa_debug_fwd_schedule.restype = None
@@ -254,12 +306,13 @@ def current_stream_ptr(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
-def debug_fwd_schedule(sq, sk, m_block, split_idx, window, num_splits, tile_n, tile_m, causal, local, split, gpack):
+def debug_fwd_schedule(sq, sk, m_block, split_idx, window, num_splits, tile_n, tile_m, causal, local, split, gpack,
+                       cover_single_query=False):
     lib = load()
     w = (c_int32 * 4)(*[int(x) for x in window])
     out = (c_int32 * 9)()
     lib.fsa_debug_fwd_schedule(sq, sk, m_block, split_idx, w, num_splits, tile_n, tile_m, int(causal), int(local),
-                               int(split), gpack, out)
+                               int(split) | (2 if cover_single_query else 0), gpack, out)
     return list(out)
 
 

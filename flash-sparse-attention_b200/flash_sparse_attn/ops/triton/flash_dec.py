@@ -1,5 +1,179 @@
-"""Host launcher of the decode pass (filled in by the decode kernels)."""
+"""Host launcher of the decode pass.
+
+Serves the dense and sparse kv-cache operators (contiguous, packed, paged and / or gathered keys); it
+plays the role of ``_flash_{dense,sparse}_attn_decode`` / ``..._varlen_decode`` of the reference
+(flash_sparse_attn/ops/triton/flash_sparse_dec.py:519-744, :747-952). Shapes only decide the launch
+(no device data is read on the host, nothing synchronises), so the call can be captured into a CUDA
+graph once the output buffers are passed in, as the reference's README describes for decode.
+"""
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from flash_sparse_attn import _lib
+from flash_sparse_attn.ops.triton import assert_inputs, utils
+
+_KIND = {"dense": _lib.KIND_DENSE, "sparse": _lib.KIND_SPARSE, "gated": _lib.KIND_GATED}
+KEYS_PER_WARP_TILE = 16
+WARPS = 4
 
 
-def attn_decode(kind, *args, **kwargs):
-    raise NotImplementedError("decode kernels are not built yet")
+def decode_num_splits(batch: int, num_heads_kv: int, keys: int, num_sms: int) -> int:
+    """Number of KV splits when the caller gives none: one CTA serves (sequence, KV head, split) and two
+    CTAs share an SM; pick the split count that fills whole waves best, while every warp keeps at
+    least 128 keys."""
+    slots = 2 * max(num_sms, 1)
+    max_ns = max(1, min(32, keys // (WARPS * 128)))
+    best, best_eff = 1, -1.0
+    for ns in range(1, max_ns + 1):
+        ctas = batch * num_heads_kv * ns
+        eff = ctas / (-(-ctas // slots) * slots)
+        if eff > best_eff + 1e-9:
+            best, best_eff = ns, eff
+    return best
+
+
+def attn_decode(
+    kind: str,
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    alpha: Optional[torch.Tensor] = None,
+    delta: Optional[torch.Tensor] = None,
+    cu_seqlens_k: Optional[torch.Tensor] = None,
+    max_seqlen_k: Optional[int] = None,
+    softmax_scale: Optional[float] = None,
+    query_scale: Optional[torch.Tensor] = None,
+    key_scale: Optional[torch.Tensor] = None,
+    value_scale: Optional[torch.Tensor] = None,
+    window_sizes: Optional[torch.Tensor] = None,
+    softmax_threshold: Optional[float] = None,
+    gate_threshold: Optional[float] = None,
+    is_logsigmoid_gate: bool = True,
+    is_local: bool = False,
+    is_quant: bool = False,
+    num_splits: Optional[int] = None,
+    page_table: Optional[torch.Tensor] = None,
+    gather_kv_indices: Optional[torch.Tensor] = None,
+    seqused_k: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+    lse: Optional[torch.Tensor] = None,
+    is_autotune: bool = True,
+    tile_mn: Optional[Tuple[int, int]] = None,
+    skip_checks: bool = False,
+    tile_map: Optional[torch.Tensor] = None,
+    partial_only: bool = False,
+    workspace: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+):
+    """Returns ``(out, lse)``; with ``partial_only`` returns ``(out_partial [ns,B,Hq,D] fp32,
+    lse_partial [ns,Hq,B] fp32 base-2)`` instead (used by context-parallel decode).
+    ``workspace`` optionally supplies the two partial buffers so that no allocation happens."""
+    if kind == "gated":
+        raise NotImplementedError("the gated decode kernel is not built yet")
+    if is_quant:
+        raise NotImplementedError("FP8 KV-cache decode is not built yet")
+    if not query.is_cuda:
+        raise RuntimeError("flash_sparse_attn (B200 build) only runs on CUDA tensors; there is no CPU path")
+    device = query.device
+    batch, num_heads_q, head_dim = query.shape
+    varlen = cu_seqlens_k is not None
+    page_size = None
+    if varlen:
+        total_k, num_heads_kv, _ = key.shape
+        seqlen_k = int(max_seqlen_k)
+    elif page_table is not None:
+        _, page_size, num_heads_kv, _ = key.shape
+        seqlen_k = page_table.shape[1] * page_size
+        total_k = 0
+    else:
+        _, seqlen_k, num_heads_kv, _ = key.shape
+        total_k = 0
+    softmax_scale = softmax_scale if softmax_scale is not None else 1.0 / (head_dim**0.5)
+    softmax_threshold = softmax_threshold if softmax_threshold is not None else 1.0
+    is_gather = gather_kv_indices is not None
+    if is_local and window_sizes is None:
+        window_sizes = utils.window_sizes_heuristic(seqlen_k, num_heads_kv, device)
+
+    if not skip_checks:
+        assert_inputs.assert_dec_inputs(
+            query, key, value, query_scale=query_scale, key_scale=key_scale, value_scale=value_scale,
+            window_sizes=window_sizes, alpha=alpha, delta=delta, cu_seqlens_k=cu_seqlens_k, seqused_k=seqused_k,
+            page_table=page_table, gather_kv_indices=gather_kv_indices, num_heads_q=num_heads_q,
+            num_heads_kv=num_heads_kv, head_dim=head_dim, page_size=page_size, is_quant=is_quant, device=device,
+        )
+
+    keys = gather_kv_indices.shape[-1] if is_gather else seqlen_k
+    if num_splits is None:
+        num_splits = decode_num_splits(batch, num_heads_kv, keys, utils.device_num_sms(device))
+    num_splits = max(1, int(num_splits))
+
+    if out is None and not partial_only:
+        out = torch.empty(query.shape, dtype=query.dtype, device=device)
+    if lse is None and not partial_only:
+        lse = torch.empty((batch, num_heads_q), dtype=torch.float32, device=device)
+    out_partial = lse_partial = None
+    if num_splits > 1 or partial_only:
+        if workspace is not None:
+            out_partial, lse_partial = workspace
+        else:
+            out_partial = torch.empty((num_splits, batch, num_heads_q, head_dim), dtype=torch.float32, device=device)
+            lse_partial = torch.empty((num_splits, num_heads_q, batch), dtype=torch.float32, device=device)
+
+    a = _lib.FsaDecArgs()
+    a.q, a.k, a.v = query.data_ptr(), key.data_ptr(), value.data_ptr()
+    a.out, a.lse = _lib.ptr(out), _lib.ptr(lse)
+    a.out_partial, a.lse_partial = _lib.ptr(out_partial), _lib.ptr(lse_partial)
+    a.cu_seqlens_k, a.seqused_k = _lib.ptr(cu_seqlens_k), _lib.ptr(seqused_k)
+    a.page_table, a.gather_kv_indices = _lib.ptr(page_table), _lib.ptr(gather_kv_indices)
+    a.window_sizes = _lib.ptr(window_sizes)
+    a.status = _lib.status_word(device).data_ptr()
+    a.tile_map = _lib.ptr(tile_map)
+    a.q_stride_b, a.q_stride_h = query.stride(0), query.stride(1)
+    if varlen:
+        a.k_stride_b, a.k_stride_s, a.k_stride_h = 0, key.stride(0), key.stride(1)
+    else:
+        a.k_stride_b, a.k_stride_s, a.k_stride_h = key.stride(0), key.stride(1), key.stride(2)
+    if value.stride() != key.stride():
+        raise RuntimeError("key and value must share one memory layout")
+    if out is not None:
+        a.o_stride_b, a.o_stride_h = out.stride(0), out.stride(1)
+        a.lse_stride_b, a.lse_stride_h = lse.stride(0), lse.stride(1)
+    a.batch, a.seqlen_k, a.total_k = batch, seqlen_k, total_k
+    a.heads_q, a.heads_kv, a.head_dim = num_heads_q, num_heads_kv, head_dim
+    if is_gather:
+        a.topk, a.gather_stride = gather_kv_indices.shape[-1], gather_kv_indices.stride(0)
+    if page_table is not None:
+        a.num_pages, a.page_size, a.page_table_stride = key.shape[0], page_size, page_table.stride(0)
+    a.window_stride = window_sizes.stride(0) if window_sizes is not None else 0
+    a.num_splits = num_splits
+    a.partial_only = int(partial_only)
+    a.kind = _KIND[kind]
+    a.dtype = _lib.dtype_code(query.dtype)
+    a.flags = _lib.F_LOCAL if is_local else 0
+    a.softmax_scale = float(softmax_scale)
+    a.softmax_threshold = float(softmax_threshold)
+    a.gate_threshold = 0.0
+
+    with torch.cuda.device(device):
+        rc = _lib.load().fsa_decode(ctypes.byref(a), _lib.current_stream_ptr(device))
+    _lib.check(rc, f"fsa_decode[{kind}]")
+    if partial_only:
+        return out_partial, lse_partial
+    return out, lse
+
+
+def combine_partials(out_partial: torch.Tensor, lse_partial: torch.Tensor, dtype: torch.dtype):
+    """Merge partial decode results ``[P, B, Hq, D]`` / ``[P, Hq, B]`` (base-2 lse) into ``(out [B,Hq,D],
+    lse [B,Hq])`` with the library's combine kernel."""
+    parts, batch, heads, head_dim = out_partial.shape
+    device = out_partial.device
+    out = torch.empty((batch, heads, head_dim), dtype=dtype, device=device)
+    lse = torch.empty((batch, heads), dtype=torch.float32, device=device)
+    with torch.cuda.device(device):
+        rc = _lib.load().fsa_combine(out_partial.data_ptr(), lse_partial.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                     parts, batch, heads, head_dim, _lib.dtype_code(dtype),
+                                     _lib.current_stream_ptr(device))
+    _lib.check(rc, "fsa_combine")
+    return out, lse

@@ -166,9 +166,72 @@ int fsa_bwd(const FsaBwdArgs* args, void* stream);
  * (batch*ceil128(seqlen_q), or ceil128(total_q + 128*batch) for packed input). Host arithmetic. */
 int64_t fsa_bwd_padded_rows(int batch, int seqlen_q, int total_q, int is_varlen);
 
+/*
+ * Decode: one query position per sequence against a KV cache. Stands in for
+ * _flash_{dense,sparse}_attn_decode and the varlen twins
+ * (flash_sparse_attn/ops/triton/flash_sparse_dec.py:519-744, :747-952) including the split combine
+ * (flash_dec_combine.py:156-222).
+ *   q [batch, heads_q, head_dim]; out like q; lse [batch, heads_q] fp32
+ *   k, v: [batch, seqlen_k, heads_kv, head_dim] | packed [total_k, heads_kv, head_dim] + cu_seqlens_k |
+ *         paged [num_pages, page_size, heads_kv, head_dim] + page_table [batch, page_table_stride]
+ *   gather_kv_indices int32 [batch, topk]: logical key positions to attend to, negative = masked; then
+ *     neither windows nor sequence lengths apply (flash_sparse_dec.py:321-357). May be combined with a
+ *     page table: the position is translated through it (not available in the reference,
+ *     assert_inputs.py:303-305).
+ *   out_partial [num_splits, batch, heads_q, head_dim], lse_partial [num_splits, heads_q, batch] fp32
+ *     (base-2 lse): written when num_splits > 1 or when partial_only is set. With partial_only the
+ *     call stops after the partials (no combine), for callers that merge partials of several
+ *     devices themselves with fsa_combine.
+ */
+typedef struct FsaDecArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  float* lse;
+  float* out_partial;
+  float* lse_partial;
+  const int32_t* cu_seqlens_k;
+  const int32_t* seqused_k;
+  const int32_t* page_table;
+  const int32_t* gather_kv_indices;
+  const int32_t* window_sizes;
+  int32_t* status;
+  uint8_t* tile_map; /* optional [batch, heads_kv, 16-key tiles]; may be null */
+  int64_t q_stride_b, q_stride_h;
+  int64_t k_stride_b, k_stride_s, k_stride_h; /* v must share k's strides */
+  int64_t o_stride_b, o_stride_h;
+  int64_t lse_stride_b, lse_stride_h;
+  int32_t batch, seqlen_k, total_k;
+  int32_t heads_q, heads_kv, head_dim;
+  int32_t topk, gather_stride;
+  int32_t num_pages, page_size, page_table_stride, window_stride;
+  int32_t num_splits;
+  int32_t partial_only;
+  int32_t kind, dtype;
+  uint32_t flags;
+  float softmax_scale, softmax_threshold, gate_threshold;
+} FsaDecArgs;
+
+int fsa_decode(const FsaDecArgs* args, void* stream);
+
+/*
+ * Merge `num_partials` partial attention results (base-2 log-sum-exp weights) into the final output:
+ * the combine step of flash_sparse_attn/ops/triton/flash_dec_combine.py:15-153 /
+ * flash_fwd_combine.py:15-161, exposed so that partials gathered from several devices (KV-sequence
+ * context parallelism) can be merged with the same arithmetic.
+ *   out_partial [num_partials, rows, heads, head_dim] fp32, lse_partial [num_partials, heads, rows] fp32
+ *   out [rows, heads, head_dim] (contiguous, dtype), lse [rows, heads] fp32 natural log
+ */
+int fsa_combine(const float* out_partial, const float* lse_partial, void* out, float* lse, int num_partials,
+                int rows, int heads, int head_dim, int dtype, void* stream);
+
 /* Integer schedule of one forward query tile, for checking against the reference's
  * AttnFwdBlockScheduler.create (flash_sparse_attn/ops/triton/scheduler.py:836-948). out9 receives
  * n_min, n_max, n_max_no_mask, win_min, win_max, win_min_no_mask, win_max_no_mask, sink_min, sink_max.
+ * is_split: bit 0 = split-KV; bit 1 = the decode kernel's variant, which for a single query position rounds
+ * the start of the near-diagonal range down instead of up (the reference's rounding,
+ * block_info.py:60-64, leaves the first partial tile of the near band unvisited).
  * Pure host arithmetic: callable without a GPU. */
 void fsa_debug_fwd_schedule(int seqlen_q, int seqlen_k, int m_block, int split_idx, const int32_t window[4],
                             int num_splits, int tile_n, int tile_m, int is_causal, int is_local, int is_split,

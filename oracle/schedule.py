@@ -84,7 +84,8 @@ class BwdSched:
 # --------------------------------------------------------------------------------------------------
 # forward / decode: key-tile ranges of one query tile (block_info.py:5-123)
 # --------------------------------------------------------------------------------------------------
-def n_block_min_max(sq, sk, m_block, split_idx, window, num_splits, TN, TM, causal, local, split_kv, gpack):
+def n_block_min_max(sq, sk, m_block, split_idx, window, num_splits, TN, TM, causal, local, split_kv, gpack,
+                    cover_single_query=False):
     sink, left, right, near = window
     n_max = _cdiv(sk, TN)
     n_min = 0
@@ -112,7 +113,10 @@ def n_block_min_max(sq, sk, m_block, split_idx, window, num_splits, TN, TM, caus
         win_min = max(max(_tdiv(n_idx - near - right - left, TN), 0), sink_excl)
     if split_kv:
         if local:
-            diag_min = max(_cdiv(max(n_idx_near + 1, 0), TN), 0) if sq == 1 else n_min
+            # cover_single_query=True is NOT the reference: it rounds down so that the first, partial tile of
+            # the near band is visited too (the reference's rounding leaves those keys out; see the
+            # decode coverage test)
+            diag_min = max(_cdiv(max(n_idx_near + 1, 0), TN), 0) if (sq == 1 and not cover_single_query) else n_min
             diag_min = max(diag_min, sink_excl)
             diag_max = n_max
             win_max = max(win_max, win_min)
@@ -162,11 +166,12 @@ def _n_min_before_local_mask(sq, sk, m_block, n_min, window, TN, TM, local, gpac
     return max(n_min, _cdiv(n_idx - near - right - left, TN))
 
 
-def fwd_schedule(sq, sk, m_block, split_idx, window, num_splits, TN, TM, causal, local, split_kv, gpack=1) -> FwdSched:
+def fwd_schedule(sq, sk, m_block, split_idx, window, num_splits, TN, TM, causal, local, split_kv, gpack=1,
+                 cover_single_query=False) -> FwdSched:
     """AttnFwdBlockScheduler.create (scheduler.py:836-948); decode uses sq=1, m_block=0, causal=False,
     split_kv=True (scheduler.py:1180-1260)."""
     n_min, n_max, win_min, win_max, sink_min, sink_max = n_block_min_max(
-        sq, sk, m_block, split_idx, window, num_splits, TN, TM, causal, local, split_kv, gpack)
+        sq, sk, m_block, split_idx, window, num_splits, TN, TM, causal, local, split_kv, gpack, cover_single_query)
     n_max_no_mask = _n_min_causal_local_mask(sq, sk, m_block, n_min, 0, 0, TN, TM, False, gpack)
     if split_kv:
         n_max_no_mask = min(n_max_no_mask, n_max)

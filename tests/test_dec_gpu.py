@@ -1,0 +1,175 @@
+"""GPU parity of the decode operators (through the C ABI) against the CPU oracle and the golden
+fixtures: contiguous, packed, paged and gathered KV, their combination, local windows, splits."""
+
+import pytest
+import torch
+
+from fixtures import assert_close, load
+from oracle import eager
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _ops():
+    import flash_sparse_attn as fsa
+
+    return fsa
+
+
+def _sync():
+    torch.cuda.synchronize()
+    _ops().check_status()
+
+
+def _qkv(seed, b, sk, hq, hkv, d, dtype=torch.bfloat16):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(b, hq, d, generator=g).to(dtype), torch.randn(b, sk, hkv, d, generator=g).to(dtype),
+            torch.randn(b, sk, hkv, d, generator=g).to(dtype))
+
+
+def test_golden_decode():
+    fsa = _ops()
+    g = load("decode")
+    q, k, v = (g[n].to(DEV) for n in ("q", "k", "v"))
+    out, lse = fsa.flash_dense_attn_with_kvcache_func(q, k, v, return_lse=True)
+    _sync()
+    assert_close("dense", out, g["out_dense"])
+    out = fsa.flash_sparse_attn_with_kvcache_func(q, k, v, softmax_threshold=-128.0)
+    _sync()
+    assert_close("sparse", out, g["out_dense"])
+    cu = g["cu_seqlens"].to(torch.int32).to(DEV)
+    out = fsa.flash_sparse_attn_varlen_with_kvcache_func(q, g["k_packed"].to(DEV), g["v_packed"].to(DEV), cu, 200,
+                                                         softmax_threshold=-128.0)
+    _sync()
+    assert_close("varlen", out, g["out_varlen"])
+    out = fsa.flash_sparse_attn_with_kvcache_func(q, k, v, softmax_threshold=-128.0,
+                                                  gather_kv_indices=g["gather_idx"].to(torch.int32).to(DEV))
+    _sync()
+    assert_close("gather", out, g["out_gather"], rtol=2.5e-2, atol=2.5e-2)
+
+
+def test_golden_local_decode():
+    fsa = _ops()
+    g = load("decode_local")
+    b, s, hq, hkv, d = g["shape"].tolist()
+    torch.manual_seed(int(g["seed"]))
+    q = torch.randn(b, hq, d, dtype=torch.bfloat16)
+    k = torch.randn(b, s, hkv, d, dtype=torch.bfloat16)
+    v = torch.randn(b, s, hkv, d, dtype=torch.bfloat16)
+    for ns in (None, 1, 3):
+        out = fsa.flash_sparse_attn_with_kvcache_func(q.to(DEV), k.to(DEV), v.to(DEV), is_local=True,
+                                                      softmax_threshold=-128.0, num_splits=ns)
+        _sync()
+        assert_close(f"local-{ns}", out, g["out"])
+
+
+# the reference's decode grid (tests/test_sparse_base_decode.py): output buffers x local x head_dim
+@pytest.mark.parametrize("kind", ["dense", "sparse"])
+@pytest.mark.parametrize("use_buffers", [False, True])
+@pytest.mark.parametrize("local", [False, True])
+@pytest.mark.parametrize("head_dim", [64, 128])
+@pytest.mark.parametrize("hq,hkv", [(32, 2), (8, 8), (6, 2)])
+def test_decode_grid(kind, use_buffers, local, head_dim, hq, hkv):
+    fsa = _ops()
+    b, sk = 2, 1500
+    q, k, v = _qkv(0, b, sk, hq, hkv, head_dim)
+    ws = torch.tensor([[32, 200, 100, 160]] * hkv, dtype=torch.int32) if local else None
+    if local:
+        ws[-1] = torch.tensor([0, 300, 0, 64], dtype=torch.int32)
+    ref, ref_lse = eager.decode(q, k, v, is_local=local, window_sizes=ws, return_lse=True)
+    out_buf = torch.empty(b, hq, head_dim, dtype=torch.bfloat16, device=DEV) if use_buffers else None
+    lse_buf = torch.empty(b, hq, dtype=torch.float32, device=DEV) if use_buffers else None
+    fn = fsa.flash_dense_attn_with_kvcache_func if kind == "dense" else fsa.flash_sparse_attn_with_kvcache_func
+    kw = {} if kind == "dense" else {"softmax_threshold": -128.0}
+    out, lse = fn(q.to(DEV), k.to(DEV), v.to(DEV), window_sizes=ws.to(DEV) if local else None, out=out_buf,
+                  lse=lse_buf, return_lse=True, **kw)
+    _sync()
+    if use_buffers:
+        assert out.data_ptr() == out_buf.data_ptr() and lse.data_ptr() == lse_buf.data_ptr()
+    assert_close("decode", out, ref)
+    assert torch.allclose(lse.cpu(), ref_lse, rtol=0, atol=2e-3)
+
+
+@pytest.mark.parametrize("page_size", [32, 64, 128, 256])
+@pytest.mark.parametrize("with_gather", [False, True])
+def test_paged_and_gathered_decode(page_size, with_gather):
+    """Permuted page table (tests/test_paged_kv.py) and random top-k lists with masked entries
+    (tests/test_topk_gather_decode.py:36-52), alone and combined."""
+    fsa = _ops()
+    b, hq, hkv, d = 3, 16, 2, 128
+    max_pages = 2048 // page_size
+    num_pages = b * max_pages + 7
+    g = torch.Generator().manual_seed(page_size)
+    q = torch.randn(b, hq, d, generator=g).to(torch.bfloat16)
+    kc = torch.randn(num_pages, page_size, hkv, d, generator=g).to(torch.bfloat16)
+    vc = torch.randn(num_pages, page_size, hkv, d, generator=g).to(torch.bfloat16)
+    table = torch.randperm(num_pages, generator=g)[: b * max_pages].reshape(b, max_pages).to(torch.int32)
+    used = torch.tensor([2048, 1111, 300], dtype=torch.int32)
+    kl, vl = eager.unpage(kc, table), eager.unpage(vc, table)
+    if with_gather:
+        topk = 256
+        idx = torch.full((b, topk), -1, dtype=torch.int32)
+        for i in range(b):
+            n = min(topk, int(used[i]))
+            idx[i, :n] = torch.randperm(int(used[i]), generator=g)[:n].to(torch.int32)
+            idx[i, i::23] = -1
+        ref = eager.gather_decode(q, kl, vl, idx)
+        out = fsa.flash_sparse_attn_with_kvcache_func(q.to(DEV), kc.to(DEV), vc.to(DEV), page_table=table.to(DEV),
+                                                      gather_kv_indices=idx.to(DEV), softmax_threshold=-128.0)
+    else:
+        ref = eager.decode(q, kl, vl, seqused_k=used)
+        out = fsa.flash_sparse_attn_with_kvcache_func(q.to(DEV), kc.to(DEV), vc.to(DEV), page_table=table.to(DEV),
+                                                      seqused_k=used.to(DEV), softmax_threshold=-128.0)
+    _sync()
+    assert_close("paged", out, ref, rtol=2.5e-2, atol=2.5e-2)
+
+
+def test_contiguous_topk_equals_regular_decode():
+    """Gathering positions 0..Sk-1 in order is the plain decode (tests/test_topk_gather_decode.py:321-397)."""
+    fsa = _ops()
+    q, k, v = _qkv(3, 2, 777, 8, 2, 128)
+    idx = torch.arange(777, dtype=torch.int32).repeat(2, 1)
+    a = fsa.flash_dense_attn_with_kvcache_func(q.to(DEV), k.to(DEV), v.to(DEV), num_splits=1)
+    b_ = fsa.flash_dense_attn_with_kvcache_func(q.to(DEV), k.to(DEV), v.to(DEV), gather_kv_indices=idx.to(DEV),
+                                                num_splits=1)
+    _sync()
+    assert torch.equal(a, b_)
+
+
+def test_decode_is_graph_capturable():
+    """The decode call does no host synchronisation or allocation once buffers are supplied, so it
+    can be captured and replayed (the usage README.md:136-164 of the reference describes)."""
+    fsa = _ops()
+    q, k, v = _qkv(4, 4, 2048, 16, 2, 128)
+    q, k, v = q.to(DEV), k.to(DEV), v.to(DEV)
+    out = torch.empty_like(q)
+    lse = torch.empty(4, 16, dtype=torch.float32, device=DEV)
+    fsa.flash_sparse_attn_with_kvcache_func(q, k, v, out=out, lse=lse, num_splits=1)  # warm-up outside capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fsa.flash_sparse_attn_with_kvcache_func(q, k, v, out=out, lse=lse, num_splits=1)
+    out.zero_()
+    graph.replay()
+    _sync()
+    ref = eager.decode(q.cpu(), k.cpu(), v.cpu())
+    assert_close("graph", out, ref)
+
+
+def test_decode_skip_map():
+    """Peaked scores trigger the skip rule per 16-key warp tile; the result stays within tolerance."""
+    from flash_sparse_attn.ops.triton.flash_dec import attn_decode
+
+    g = torch.Generator().manual_seed(7)
+    b, sk, hq, hkv, d = 2, 4096, 16, 2, 128
+    k = torch.randn(b, sk, hkv, d, generator=g)
+    q = (k[:, -1].repeat_interleave(hq // hkv, dim=1) * 3).to(torch.bfloat16)
+    k = k.to(torch.bfloat16)
+    v = torch.randn(b, sk, hkv, d, generator=g).to(torch.bfloat16)
+    tmap = torch.zeros(b * hkv * (sk // 16), dtype=torch.uint8, device=DEV)
+    out, _ = attn_decode("sparse", q.to(DEV), k.to(DEV), v.to(DEV), softmax_threshold=1.0, num_splits=2, tile_map=tmap)
+    _sync()
+    assert (tmap == 2).sum().item() > 0 and (tmap != 0).all()
+    ref = eager.decode(q, k, v)
+    assert_close("skip", out, ref, rtol=3e-2, atol=3e-2)

@@ -99,6 +99,32 @@ def test_bwd_exact_cover(local, ns):
         assert all(v == 1 for v in seen.values())
 
 
+def _decode_cover(sk, window, tn, nsub, gpack, cover):
+    seen = {}
+    for sp in range(nsub):
+        sc = S.fwd_schedule(1, sk, 0, sp, window, nsub, tn, 16, False, True, True, gpack, cover_single_query=cover)
+        if sc.is_empty():
+            continue
+        for n, mode in S.fwd_tiles(sc, True, True):
+            for kk in range(n * tn, min((n + 1) * tn, sk)):
+                if S.visible(0, kk, 1, sk, window, mode):
+                    seen[kk] = seen.get(kk, 0) + 1
+    exp = {kk for kk in range(sk) if S.allowed(0, kk, 1, sk, window, False, True)}
+    return seen, exp
+
+
+def test_decode_schedule_cover():
+    """Single query position + local window + split-KV. With the reference's rounding the first partial
+    tile of the near band is not visited when the band is not tile aligned (a property of the reference,
+    recorded here); the decode kernel's variant covers the mask exactly once."""
+    for window in ([32, 200, 100, 160], [0, 300, 0, 64], [64, 128, 256, 1024]):
+        for tn, nsub, gpack in itertools.product((16, 64), (1, 4, 12), (1, 16)):
+            seen, exp = _decode_cover(1500, window, tn, nsub, gpack, cover=True)
+            assert set(seen) == exp and all(v == 1 for v in seen.values()), (window, tn, nsub, gpack)
+    seen, exp = _decode_cover(1500, [32, 200, 100, 160], 16, 4, 16, cover=False)
+    assert sorted(exp - set(seen)) == [1340, 1341, 1342, 1343]
+
+
 def test_c_schedule_matches_oracle():
     from flash_sparse_attn import _lib
 
@@ -115,9 +141,10 @@ def test_c_schedule_matches_oracle():
         gpack = rng.choice([1, 1, 2, 4, 8])
         mb = rng.randint(0, max(0, -(-sq * gpack // tm) - 1))
         sp = rng.randint(0, ns - 1)
-        ref = S.fwd_schedule(sq, sk, mb, sp, window, ns, tn, tm, causal, local, split, gpack).as_list()
-        got = _lib.debug_fwd_schedule(sq, sk, mb, sp, window, ns, tn, tm, causal, local, split, gpack)
-        assert got == ref, ("fwd", sq, sk, mb, sp, window, ns, tn, tm, causal, local, split, gpack)
+        cover = rng.random() < 0.3
+        ref = S.fwd_schedule(sq, sk, mb, sp, window, ns, tn, tm, causal, local, split, gpack, cover).as_list()
+        got = _lib.debug_fwd_schedule(sq, sk, mb, sp, window, ns, tn, tm, causal, local, split, gpack, cover)
+        assert got == ref, ("fwd", sq, sk, mb, sp, window, ns, tn, tm, causal, local, split, gpack, cover)
         nb = rng.randint(0, max(0, -(-sk // tn) - 1))
         ref = S.bwd_schedule(sq, sk, nb, sp, window, ns, tn, tm, causal, local, split).as_list()
         got = _lib.debug_bwd_schedule(sq, sk, nb, sp, window, ns, tn, tm, causal, local, split)
