@@ -21,18 +21,15 @@ WARPS = 4
 
 
 def decode_num_splits(batch: int, num_heads_kv: int, keys: int, num_sms: int) -> int:
-    """Number of KV splits when the caller gives none: one CTA serves (sequence, KV head, split) and two
-    CTAs share an SM; pick the split count that fills whole waves best, while every warp keeps at
-    least 128 keys."""
+    """Number of KV splits when the caller gives none. One CTA serves (sequence, KV head, split) and two
+    CTAs share an SM. Splitting costs a second (combine) launch and per-CTA set-up, so it is only used to
+    fill an otherwise under-occupied GPU, and never below 512 keys per CTA (128 per warp)."""
     slots = 2 * max(num_sms, 1)
+    ctas = batch * num_heads_kv
+    if ctas >= slots:
+        return 1
     max_ns = max(1, min(32, keys // (WARPS * 128)))
-    best, best_eff = 1, -1.0
-    for ns in range(1, max_ns + 1):
-        ctas = batch * num_heads_kv * ns
-        eff = ctas / (-(-ctas // slots) * slots)
-        if eff > best_eff + 1e-9:
-            best, best_eff = ns, eff
-    return best
+    return max(1, min(max_ns, -(-slots // ctas)))
 
 
 def attn_decode(
