@@ -21,6 +21,7 @@ SOURCES = [
     "fsa_fwd_sm100.cu",
     "fsa_bwd_sm100.cu",
     "fsa_dec_sm100.cu",
+    "fsa_static_scratch.cu",
 ]
 
 NVCC_FLAGS = [

@@ -100,6 +100,9 @@ const char* fsa_status_string(int code) {
     case FSA_ERR_UNSUPPORTED: return "unsupported combination (head_dim must be 64 or 128, dtype bf16/fp16, ...)";
     case FSA_ERR_LAUNCH: return "CUDA error at launch or tensor-map creation";
     case FSA_ERR_NO_DRIVER: return "CUDA driver entry point cuTensorMapEncodeTiled unavailable";
+    case FSA_ERR_SCRATCH_TOO_SMALL:
+      return "request does not fit the built-in workspace: num_splits * batch * heads_q * (head_dim + 1) floats "
+             "must be at most 16 MiB";
     default: return "unknown status";
   }
 }

@@ -27,7 +27,8 @@ enum {
   FSA_ERR_INVALID_ARG = -1, /* null pointer, bad size, misaligned stride */
   FSA_ERR_UNSUPPORTED = -2, /* valid request outside what the kernels implement */
   FSA_ERR_LAUNCH = -3,      /* CUDA reported an error at launch / descriptor creation */
-  FSA_ERR_NO_DRIVER = -4    /* cuTensorMapEncodeTiled could not be resolved (no CUDA driver) */
+  FSA_ERR_NO_DRIVER = -4,   /* cuTensorMapEncodeTiled could not be resolved (no CUDA driver) */
+  FSA_ERR_SCRATCH_TOO_SMALL = -5 /* fsa_decode_static_scratch: the partials exceed the built-in workspace */
 };
 
 enum { FSA_KIND_DENSE = 0, FSA_KIND_SPARSE = 1, FSA_KIND_GATED = 2 };
@@ -225,6 +226,29 @@ int fsa_decode(const FsaDecArgs* args, void* stream);
  */
 int fsa_combine(const float* out_partial, const float* lse_partial, void* out, float* lse, int num_partials,
                 int rows, int heads, int head_dim, int dtype, void* stream);
+
+/*
+ * Split-KV decode without any caller-provided (or freshly allocated) workspace. This entry point has
+ * no counterpart in the reference, whose launcher allocates its partial buffers with torch.empty on
+ * every call (flash_sparse_attn/ops/triton/flash_sparse_dec.py:637-646).
+ *
+ * It is fsa_decode with the split workspace taken from a fixed array of FSA_STATIC_SCRATCH_BYTES that
+ * is part of the library image on every GPU: meant for callers that cannot obtain device memory at
+ * call time (all memory already owned by a serving pool, a frozen memory plan, no tolerance for the
+ * implicit synchronisation of cudaMalloc / cudaFree). args->out_partial / lse_partial are ignored and
+ * partial_only must be 0; everything else means what it means for fsa_decode.
+ *   - num_splits * batch * heads_q * (head_dim + 1) floats must fit in the array, otherwise the call
+ *     returns FSA_ERR_SCRATCH_TOO_SMALL and launches nothing.
+ *   - The array is shared by all calls and keeps the previous call's contents; the kernels overwrite
+ *     every slot they later read, so nothing has to be cleared. Calls that may run concurrently on
+ *     one GPU race on it: order them.
+ *   - The first call on each device resolves the array's address with cudaGetSymbolAddress; make that
+ *     first call before starting any stream capture.
+ * It calls no cudaMalloc, cudaFree or other allocating routine.
+ */
+#define FSA_STATIC_SCRATCH_BYTES (16u * 1024u * 1024u)
+int fsa_decode_static_scratch(const FsaDecArgs* args, void* stream);
+size_t fsa_static_scratch_bytes(void);
 
 /* Integer schedule of one forward query tile, for checking against the reference's
  * AttnFwdBlockScheduler.create (flash_sparse_attn/ops/triton/scheduler.py:836-948). out9 receives
