@@ -168,7 +168,8 @@ int fsa_fwd(const FsaFwdArgs* a, void* stream_) {
   if (a->batch <= 0 || a->heads_q <= 0 || a->head_dim <= 0) return FSA_ERR_INVALID_ARG;
   if (a->head_dim != 64 && a->head_dim != 128) return FSA_ERR_UNSUPPORTED;
   if (a->dtype != FSA_DT_BF16 && a->dtype != FSA_DT_FP16) return FSA_ERR_UNSUPPORTED;
-  if (a->kind != FSA_KIND_DENSE && a->kind != FSA_KIND_SPARSE) return FSA_ERR_UNSUPPORTED;
+  if (a->kind != FSA_KIND_DENSE && a->kind != FSA_KIND_SPARSE && a->kind != FSA_KIND_GATED) return FSA_ERR_UNSUPPORTED;
+  if (a->kind == FSA_KIND_GATED && (!a->alpha || !a->delta)) return FSA_ERR_INVALID_ARG;
   if ((a->tile_m && a->tile_m != 128) || (a->tile_n && a->tile_n != 128)) return FSA_ERR_UNSUPPORTED;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   const bool varlen_q = a->cu_seqlens_q != nullptr, varlen_k = a->cu_seqlens_k != nullptr;
@@ -236,6 +237,10 @@ int fsa_fwd(const FsaFwdArgs* a, void* stream_) {
   p.windows = a->window_sizes;
   p.alpha = a->alpha;
   p.delta = a->delta;
+  p.a_sb = a->alpha_stride_b;
+  p.a_sh = a->alpha_stride_h;
+  p.d_sb = a->delta_stride_b;
+  p.d_sh = a->delta_stride_h;
   p.status = a->status;
   p.tile_map = a->tile_map;
   if (split) {

@@ -42,7 +42,7 @@ struct FwdSmem {
   static constexpr int kK = kQ + 2 * kTileBytes;
   static constexpr int kV = kK + KSTAGES * kTileBytes;
   static constexpr int kBar = kV + VSTAGES * kTileBytes;
-  static constexpr int kTotal = kBar + 512 + 1024;  // barriers/flags + alignment slack
+  static constexpr int kTotal = kBar + 2048 + 1024;  // barriers/flags/delta ring + alignment slack
 };
 
 struct FwdBars {
@@ -50,10 +50,13 @@ struct FwdBars {
   uint64_t k_full[KSTAGES], k_empty[KSTAGES];
   uint64_t v_full[VSTAGES], v_empty[VSTAGES];
   uint64_t s_full[2], p_full[2], o_final[2], vote[2], wg_sync[2];
+  uint64_t d_full[2], d_empty[2], a_sync[2];  // gated: delta ring (stager warp -> softmax warps), alpha exchange
   uint32_t tmem_base;
   int abort_flag;
   int skip_flag[2][2];   // [group][parity of the group's tile counter]
   int vote_any[2][2][4]; // [group][parity][warp]: bit0 = some row wants the tile, bit1 = some row votes skip
+  float a_ext[2][4][2];  // gated: per group, per warp (max, min) of alpha
+  float dl[2][TN + 4];   // gated: delta of the key tile as fp32, then its max and min
 };
 
 struct SeqInfo {
@@ -203,6 +206,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       mbar_init(&bars->o_final[q], 1);
       mbar_init(&bars->vote[q], 1);
       mbar_init(&bars->wg_sync[q], 4);
+      mbar_init(&bars->d_full[q], 1);
+      mbar_init(&bars->d_empty[q], 8);
+      mbar_init(&bars->a_sync[q], 4);
     }
     bars->abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
     mbar_fence_init();
@@ -318,6 +324,53 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       }
     }
     __syncwarp();
+  } else if (warp == 10) {
+    // =============================== delta stager (gated only) ================================
+    // delta of every visited key tile as fp32 in a 2-slot ring, with the tile's max / min for the
+    // gate bound (flash_sparse_attn/ops/triton/flash_gated_fwd.py:100-115). Keys past the sequence
+    // read as 0, like the reference's masked load (scheduler.py:1674-1691).
+    if (KIND == KIND_GATED) {
+      bool ok = !*abort_flag;
+      const T* dbase = reinterpret_cast<const T*>(p.delta);
+      int t = 0;
+      for (int n = first_tile(); n >= 0 && ok; n = next_tile(n), ++t) {
+        const int s = t & 1, use = t >> 1;
+        if (use > 0) ok = mbar_wait(&bars->d_empty[s], (use - 1) & 1, abort_flag);
+        if (!ok) break;
+        float dv[4];
+        float dmax = -INFINITY, dmin = INFINITY;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int k = n * TN + lane * 4 + j;
+          float v = 0.f;
+          if (k < si.sk) {
+            long long e;
+            if (p.flags & F_PAGED) {
+              const int page = p.page_table[(long long)si.b * p.pt_stride + k / p.page_size];
+              e = (long long)page * p.d_sb + (long long)si.hkv * p.d_sh + (k % p.page_size);
+            } else {
+              e = (long long)((p.flags & F_VARLEN_K) ? 0 : si.b) * p.d_sb + (long long)si.hkv * p.d_sh + si.off_k + k;
+            }
+            v = float(dbase[e]);
+          }
+          dv[j] = v;
+          dmax = fmaxf(dmax, v);
+          dmin = fminf(dmin, v);
+        }
+#pragma unroll
+        for (int sft = 16; sft > 0; sft >>= 1) {
+          dmax = fmaxf(dmax, __shfl_xor_sync(0xffffffffu, dmax, sft));
+          dmin = fminf(dmin, __shfl_xor_sync(0xffffffffu, dmin, sft));
+        }
+        *reinterpret_cast<float4*>(&bars->dl[s][lane * 4]) = make_float4(dv[0], dv[1], dv[2], dv[3]);
+        if (lane == 0) {
+          bars->dl[s][TN] = dmax;
+          bars->dl[s][TN + 1] = dmin;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->d_full[s]);
+      }
+    }
   } else if (warp == 9) {
     // =============================== MMA issuer ==============================================
     constexpr uint32_t idesc_s = umma_idesc_f16(TM, TN, IS_BF16, false, false);
@@ -467,21 +520,114 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     bool ok = !*abort_flag;
     const bool has_work = q_valid[q] && !fsa_fwd_sched_empty(my);
 
-    for (int n = fsa_fwd_next_tile_below(my, 1 << 28, local); n >= 0 && ok && has_work;
-         n = fsa_fwd_next_tile_below(my, n, local)) {
-      const int mode = fsa_fwd_tile_mode(my, n, causal, local);
+    // ---- gated: alpha of this row, its extremes over the tile, the gate threshold ------------------
+    float alpha = 0.f, a_max = 0.f, a_min = 0.f, gate_max = -INFINITY, gate_thr_log2 = 0.f;
+    if (KIND == KIND_GATED) {
+      if (rm.row_ok && q_valid[q]) {
+        const T* ab = reinterpret_cast<const T*>(p.alpha);
+        alpha = float(ab[(long long)((p.flags & F_VARLEN_Q) ? 0 : si.b) * p.a_sb + (long long)q_head * p.a_sh +
+                         si.off_q + q_idx]);
+      }
+      float mx = alpha, mn = alpha;
+#pragma unroll
+      for (int sft = 16; sft > 0; sft >>= 1) {
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sft));
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, sft));
+      }
+      if (lane == 0) {
+        bars->a_ext[q][wq][0] = mx;
+        bars->a_ext[q][wq][1] = mn;
+        mbar_arrive(&bars->a_sync[q]);
+      }
+      ok = ok && mbar_wait(&bars->a_sync[q], 0, abort_flag);
+      a_max = fmaxf(fmaxf(bars->a_ext[q][0][0], bars->a_ext[q][1][0]), fmaxf(bars->a_ext[q][2][0], bars->a_ext[q][3][0]));
+      a_min = fminf(fminf(bars->a_ext[q][0][1], bars->a_ext[q][1][1]), fminf(bars->a_ext[q][2][1], bars->a_ext[q][3][1]));
+      // flash_sparse_attn/ops/triton/seqlen_info.py:156-191: the adaptive bound is smallest at the tile's first row
+      float g_thr = p.gate_thr;
+      if (causal && (p.flags & F_ADAPT_GATE))
+        g_thr = p.gate_thr * (float((mb * TM) / gpack + (si.sk - si.sq)) + 1.0f) / float(si.sk);
+      gate_thr_log2 = log2f(g_thr);
+    }
+
+    int t_merged = -1;
+    for (int n = (KIND == KIND_GATED || has_work) ? first_tile() : -1; n >= 0 && ok; n = next_tile(n)) {
+      ++t_merged;
+      const int mode = has_work ? fsa_fwd_tile_mode(my, n, causal, local) : -1;
+      const int ds = t_merged & 1;
+      if (KIND == KIND_GATED) {
+        ok = mbar_wait(&bars->d_full[ds], (t_merged >> 1) & 1, abort_flag);
+        if (!ok) break;
+      }
+      if (mode < 0) {
+        if (KIND == KIND_GATED) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->d_empty[ds]);
+        }
+        continue;
+      }
+      // gate bound of the tile (flash_sparse_attn/ops/triton/activations.py:265-299): a running scalar
+      bool gate_skip = false;
+      if (KIND == KIND_GATED) {
+        const float dmax = bars->dl[ds][TN], dmin = bars->dl[ds][TN + 1];
+        const float gmc = fmaxf(fmaxf(a_max * dmax, a_max * dmin), fmaxf(a_min * dmax, a_min * dmin));
+        gate_skip = (gmc - gate_max) * c < gate_thr_log2;
+        if (!gate_skip) gate_max = fmaxf(gmc, gate_max);
+      }
       ok = mbar_wait(&bars->s_full[q], cnt_s & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
       const int par = cnt_s & 1;
       cnt_s++;
       const int k0 = n * TN;
+      if (gate_skip) {
+        // the tile contributes nothing: publish "skipped" to the producer and the MMA warp
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->d_empty[ds]);
+        if (wq == 0 && lane == 0) {
+          bars->skip_flag[q][par] = 1;
+          if (p.tile_map) {
+            const long long idx =
+                ((((long long)si.b * p.hgrid + si.head) * p.num_m_blocks + mb) * p.num_splits + si.split) *
+                    p.n_tiles_k + n;
+            p.tile_map[idx] = 3;
+          }
+          __threadfence_block();
+          mbar_arrive(&bars->vote[q]);
+        }
+        // keep the group's vote barrier in step with the tile counter
+        if (lane == 0) mbar_arrive(&bars->wg_sync[q]);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->p_full[q]);
+        continue;
+      }
 
       // ---- scores of this row: TMEM -> registers (warp-collective loads, one wait) ---------------
       uint32_t sr[TN];
 #pragma unroll
       for (int ch = 0; ch < TN / 32; ++ch) tmem_ld32(tS + ch * 32, &sr[ch * 32]);
       tmem_ld_wait();
+      if (KIND == KIND_GATED) {
+        // logits = (q.k + g(alpha * delta_j)) * scale, g = logsigmoid or identity
+        // (flash_sparse_attn/ops/triton/flash_gated_fwd.py:104-122, activations.py:245-262)
+        const float4* d4 = reinterpret_cast<const float4*>(&bars->dl[ds][0]);
+        const bool logsig = p.flags & F_LOGSIGMOID;
+#pragma unroll
+        for (int i = 0; i < TN; i += 4) {
+          const float4 dd = d4[i >> 2];
+          const float dv[4] = {dd.x, dd.y, dd.z, dd.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float x = alpha * dv[j];
+            float gte = x;
+            if (logsig)
+              gte = fminf(x, 0.f) - 0.6931471805599453f * lg2_approx(1.0f + ex2_approx(-fabsf(x) * 1.4426950408889634f));
+            sr[i + j] = __float_as_uint(__uint_as_float(sr[i + j]) + gte);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->d_empty[ds]);
+      }
       if (mode != FSA_MASK_NONE) {
         const TileMask tm = make_tile_mask(rm, mode, k0);
 #pragma unroll
@@ -685,6 +831,7 @@ cudaError_t launch_fwd(const FwdKernelParams& p, int kind, int dtype, int head_d
   if (head_dim == HD_ && dtype == DT_) {                                            \
     if (kind == KIND_DENSE) return launch_one<HD_, T_, KIND_DENSE>(p, stream);      \
     if (kind == KIND_SPARSE) return launch_one<HD_, T_, KIND_SPARSE>(p, stream);    \
+    if (kind == KIND_GATED) return launch_one<HD_, T_, KIND_GATED>(p, stream);      \
   }
   FSA_FWD_CASE(128, __nv_bfloat16, DT_BF16)
   FSA_FWD_CASE(128, __half, DT_FP16)

@@ -63,6 +63,10 @@ class FsaFwdArgs(ctypes.Structure):
         ("o_stride_h", c_int64),
         ("lse_stride_b", c_int64),
         ("lse_stride_h", c_int64),
+        ("alpha_stride_b", c_int64),
+        ("alpha_stride_h", c_int64),
+        ("delta_stride_b", c_int64),
+        ("delta_stride_h", c_int64),
         ("batch", c_int32),
         ("seqlen_q", c_int32),
         ("seqlen_k", c_int32),

@@ -163,6 +163,13 @@ def attn_forward(
         a.v_stride_b, a.v_stride_s, a.v_stride_h = value.stride(0), value.stride(1), value.stride(2)
         a.o_stride_b, a.o_stride_s, a.o_stride_h = out.stride(0), out.stride(1), out.stride(2)
         a.lse_stride_b, a.lse_stride_h = lse.stride(0), lse.stride(1)
+    if kind == "gated":
+        # alpha [B, Hq, Sq] / [Hq, Tq], delta [B, Hkv, Sk] / [Hkv, Tk] / paged [pages, Hkv, page] (position contiguous)
+        if alpha.dtype != query.dtype or delta.dtype != query.dtype:
+            alpha, delta = alpha.to(query.dtype), delta.to(query.dtype)
+            a.alpha, a.delta = alpha.data_ptr(), delta.data_ptr()
+        a.alpha_stride_b, a.alpha_stride_h = (0, alpha.stride(0)) if varlen else (alpha.stride(0), alpha.stride(1))
+        a.delta_stride_b, a.delta_stride_h = (0, delta.stride(0)) if varlen else (delta.stride(0), delta.stride(1))
     a.batch, a.seqlen_q, a.seqlen_k = batch, seqlen_q, seqlen_k
     a.total_q, a.total_k = total_q, total_k
     a.heads_q, a.heads_kv, a.head_dim = num_heads_q, num_heads_kv, head_dim

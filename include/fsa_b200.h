@@ -87,6 +87,8 @@ typedef struct FsaFwdArgs {
   int64_t v_stride_b, v_stride_s, v_stride_h;
   int64_t o_stride_b, o_stride_s, o_stride_h;
   int64_t lse_stride_b, lse_stride_h;
+  int64_t alpha_stride_b, alpha_stride_h; /* gated: alpha[b, h, position] (position stride 1) */
+  int64_t delta_stride_b, delta_stride_h; /* gated: delta[b, h_kv, position]; paged: delta[page, h_kv, row] */
   int32_t batch, seqlen_q, seqlen_k; /* varlen: max_seqlen_q / max_seqlen_k */
   int32_t total_q, total_k;          /* varlen: rows of the packed tensors */
   int32_t heads_q, heads_kv, head_dim;

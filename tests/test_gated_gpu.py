@@ -1,0 +1,101 @@
+"""GPU parity of the gated operators against the golden fixtures (reference's eager gated forward) and
+the CPU oracle: logits = (q.k + g(alpha_i * delta_j)) * scale, g = logsigmoid or identity."""
+
+import pytest
+import torch
+
+from fixtures import assert_close, load, seeded_qkv
+from oracle import eager
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _ops():
+    import flash_sparse_attn as fsa
+
+    return fsa
+
+
+def _sync():
+    torch.cuda.synchronize()
+    _ops().check_status()
+
+
+def _gates(seed, b, sq, sk, hq, hkv, dtype=torch.bfloat16):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(b, sq, hq, generator=g).to(dtype), torch.randn(b, sk, hkv, generator=g).to(dtype)
+
+
+@pytest.mark.parametrize("name", ["fwd_nc", "fwd_causal", "fwd_causal_sq_lt_sk"])
+def test_golden_gated_forward(name):
+    fsa = _ops()
+    g = load(name)
+    q, k, v, a, d = (g[n].to(DEV) for n in ("q", "k", "v", "alpha", "delta"))
+    causal = bool(g["causal"])
+    out, lse = fsa.flash_gated_attn_func(q, k, v, a, d, is_causal=causal, softmax_threshold=-128.0,
+                                         gate_threshold=-128.0, return_lse=True)
+    _sync()
+    assert_close(name + "-gated", out, g["out_gated"])
+    assert torch.allclose(lse.cpu(), g["lse_gated"], rtol=0, atol=2e-3)
+    out = fsa.flash_gated_attn_func(q, k, v, a, d, is_causal=causal, softmax_threshold=-128.0, gate_threshold=-128.0,
+                                    is_logsigmoid_gate=False)
+    _sync()
+    assert_close(name + "-gated-linear", out, g["out_gated_lin"])
+
+
+def test_golden_gated_varlen():
+    fsa = _ops()
+    g = load("fwd_varlen")
+    q, k, v, a, d = (g[n].to(DEV) for n in ("q", "k", "v", "alpha", "delta"))
+    cu = g["cu_seqlens"].to(torch.int32).to(DEV)
+    out = fsa.flash_gated_attn_varlen_func(q, k, v, a, d, cu, cu, 160, 160, is_causal=True, softmax_threshold=-128.0,
+                                           gate_threshold=-128.0)
+    _sync()
+    assert_close("gated-varlen", out, g["out_gated"])
+
+
+# the reference's gated forward grid (tests/test_gated_base_forward.py) adds is_logsigmoid_gate
+@pytest.mark.parametrize("causal,local", [(False, False), (True, False), (True, True)])
+@pytest.mark.parametrize("split", [False, True])
+@pytest.mark.parametrize("head_dim", [64, 128])
+@pytest.mark.parametrize("pack_gqa", [False, True])
+@pytest.mark.parametrize("logsig", [True, False])
+def test_gated_forward_grid(causal, local, split, head_dim, pack_gqa, logsig):
+    fsa = _ops()
+    b, s, hq, hkv = 2, 1024, 8, 2
+    q, k, v = seeded_qkv(0, b, s, s, hq, hkv, head_dim)
+    a, d = _gates(1, b, s, s, hq, hkv)
+    ws = torch.tensor([[32, 200, 100, 160], [0, 300, 0, 64]], dtype=torch.int32) if local else None
+    ref = eager.forward(q, k, v, None, causal, is_local=local, window_sizes=ws, alpha=a, delta=d,
+                        is_logsigmoid_gate=logsig)
+    out = fsa.flash_gated_attn_func(q.to(DEV), k.to(DEV), v.to(DEV), a.to(DEV), d.to(DEV), is_causal=causal,
+                                    window_sizes=ws.to(DEV) if local else None, softmax_threshold=-128.0,
+                                    gate_threshold=-128.0, is_logsigmoid_gate=logsig, is_split_kv=split,
+                                    num_splits=3 if split else None, pack_gqa=pack_gqa)
+    _sync()
+    assert_close("gated-fwd", out, ref)
+
+
+def test_gate_skip_triggers_and_stays_close():
+    """With the default gate threshold, tiles whose gate bound is far below the running maximum are
+    skipped (map value 3); their weight is bounded by the threshold, so the output stays close."""
+    from flash_sparse_attn.ops.triton.flash_fwd import attn_forward, tile_map_numel
+
+    b, s, hq, hkv, d = 1, 2048, 2, 2, 128
+    q, k, v = seeded_qkv(3, b, s, s, hq, hkv, d)
+    g = torch.Generator().manual_seed(4)
+    alpha = torch.full((b, s, hq), 4.0)
+    # keys of the last 256 positions carry a large positive delta, everything else strongly negative
+    delta = torch.full((b, s, hkv), -32.0)
+    delta[:, -256:] = 6.0
+    alpha, delta = alpha.to(torch.bfloat16), delta.to(torch.bfloat16)
+    ref = eager.forward(q, k, v, None, True, alpha=alpha, delta=delta, is_logsigmoid_gate=False)
+    tmap = torch.zeros(tile_map_numel(b, s, s, hq, hkv), dtype=torch.uint8, device=DEV)
+    out, *_ = attn_forward("gated", q.to(DEV), k.to(DEV), v.to(DEV), alpha=alpha.transpose(1, 2).contiguous().to(DEV),
+                           delta=delta.transpose(1, 2).contiguous().to(DEV), is_causal=True, softmax_threshold=0.0,
+                           gate_threshold=None, is_logsigmoid_gate=False, is_adapt_gate=True, tile_map=tmap)
+    _sync()
+    assert (tmap == 3).sum().item() > 0
+    # rows in the last 256 positions see the boosted keys: everything else is negligible there
+    assert_close("gate-skip", out[:, -200:], ref[:, -200:], rtol=3e-2, atol=3e-2)
