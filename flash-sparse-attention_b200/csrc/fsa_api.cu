@@ -536,7 +536,8 @@ int fsa_decode(const FsaDecArgs* a, void* stream_) {
   if (a->batch <= 0 || a->heads_q <= 0 || a->heads_kv <= 0 || a->heads_q % a->heads_kv) return FSA_ERR_INVALID_ARG;
   if (a->head_dim != 64 && a->head_dim != 128) return FSA_ERR_UNSUPPORTED;
   if (a->dtype != FSA_DT_BF16 && a->dtype != FSA_DT_FP16) return FSA_ERR_UNSUPPORTED;
-  if (a->kind != FSA_KIND_DENSE && a->kind != FSA_KIND_SPARSE) return FSA_ERR_UNSUPPORTED;
+  if (a->kind != FSA_KIND_DENSE && a->kind != FSA_KIND_SPARSE && a->kind != FSA_KIND_GATED) return FSA_ERR_UNSUPPORTED;
+  if (a->kind == FSA_KIND_GATED && (!a->alpha || !a->delta)) return FSA_ERR_INVALID_ARG;
   if ((a->flags & FSA_F_LOCAL) && !a->window_sizes) return FSA_ERR_INVALID_ARG;
   const bool paged = a->page_table != nullptr, gather = a->gather_kv_indices != nullptr;
   const bool varlen_k = a->cu_seqlens_k != nullptr;
@@ -565,6 +566,13 @@ int fsa_decode(const FsaDecArgs* a, void* stream_) {
   p.page_table = a->page_table;
   p.gather_idx = a->gather_kv_indices;
   p.windows = a->window_sizes;
+  p.alpha = a->alpha;
+  p.delta = a->delta;
+  p.a_sb = a->alpha_stride_b;
+  p.a_sh = a->alpha_stride_h;
+  p.d_sb = a->delta_stride_b;
+  p.d_sh = a->delta_stride_h;
+  p.gate_thr = a->gate_threshold;
   p.tile_map = a->tile_map;
   p.q_sb = a->q_stride_b;
   p.q_sh = a->q_stride_h;
@@ -597,6 +605,7 @@ int fsa_decode(const FsaDecArgs* a, void* stream_) {
   if (paged) f |= fsa::F_PAGED;
   if (gather) f |= fsa::F_GATHER;
   if (a->seqused_k) f |= fsa::F_USED_K;
+  if (a->flags & FSA_F_LOGSIGMOID) f |= fsa::F_LOGSIGMOID;
   p.flags = f;
   mark_before(stream);
   cudaError_t e = fsa::launch_dec(p, a->kind, a->dtype, a->head_dim, stream);

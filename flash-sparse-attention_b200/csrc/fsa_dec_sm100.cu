@@ -131,7 +131,8 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
   };
 
   // Issue the copies of tile n into ring slot `slot`; returns the bitmask of keys that exist.
-  auto issue_tile = [&](int n, int slot) -> unsigned {
+  // Gated kernels also fetch delta of key (lane & 15) into *dval (0 for keys that do not exist).
+  auto issue_tile = [&](int n, int slot, float* dval) -> unsigned {
     long long e = -1;
     int pos = -1;
     if (lane < DTN) {
@@ -141,6 +142,16 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
       else
         pos = (i < sk) ? i : -1;
       e = row_elem(pos);
+    }
+    if (KIND == KIND_GATED) {
+      float dv = 0.f;
+      if (lane < DTN && e >= 0) {
+        const long long de = paged ? (long long)ptab[pos / p.page_size] * p.d_sb + (long long)hkv * p.d_sh +
+                                         (pos % p.page_size)
+                                   : (long long)bk * p.d_sb + (long long)hkv * p.d_sh + off_k + pos;
+        dv = float(reinterpret_cast<const T*>(p.delta)[de]);
+      }
+      *dval = __shfl_sync(0xffffffffu, dv, lane & 15);
     }
     const unsigned present = __ballot_sync(0xffffffffu, e >= 0) & 0xffffu;
     uint8_t* kt = ring + slot * 2 * SM::kTile;
@@ -176,6 +187,22 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
       }
     }
     const bool row0_ok = mt * 16 + g < p.G, row1_ok = mt * 16 + g + 8 < p.G;
+    // ---- gated: alpha of the two rows, its extremes over the real rows, the running gate bound ----
+    float al0 = 0.f, al1 = 0.f, a_max = 0.f, a_min = 0.f, gate_max = -INFINITY;
+    float dl0 = 0.f, dl1 = 0.f, dl2 = 0.f;
+    const float gate_thr_log2 = (KIND == KIND_GATED) ? log2f(p.gate_thr) : 0.f;
+    if (KIND == KIND_GATED) {
+      const T* ab = reinterpret_cast<const T*>(p.alpha) + (long long)b * p.a_sb;
+      if (row0_ok) al0 = float(ab[(long long)(hkv * p.G + mt * 16 + g) * p.a_sh]);
+      if (row1_ok) al1 = float(ab[(long long)(hkv * p.G + mt * 16 + g + 8) * p.a_sh]);
+      a_max = fmaxf(row0_ok ? al0 : -INFINITY, row1_ok ? al1 : -INFINITY);
+      a_min = fminf(row0_ok ? al0 : INFINITY, row1_ok ? al1 : INFINITY);
+#pragma unroll
+      for (int sft = 16; sft > 0; sft >>= 1) {
+        a_max = fmaxf(a_max, __shfl_xor_sync(0xffffffffu, a_max, sft));
+        a_min = fminf(a_min, __shfl_xor_sync(0xffffffffu, a_min, sft));
+      }
+    }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float o[HD / 8][4];
 #pragma unroll
@@ -189,7 +216,7 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
     for (int s = 0; s < DSTAGES - 1; ++s) {
       present_q[s] = 0;
       if (n_load >= 0) {
-        present_q[s] = issue_tile(n_load, s);
+        present_q[s] = issue_tile(n_load, s, s == 0 ? &dl0 : &dl1);
         n_load = fsa_fwd_next_tile_below(sched, n_load, loc_sched);
       }
       cp_async_commit();
@@ -202,7 +229,7 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
       // keep the ring full, then wait for the oldest tile
       unsigned pres_new = 0;
       if (n_load >= 0) {
-        pres_new = issue_tile(n_load, slot_load);
+        pres_new = issue_tile(n_load, slot_load, &dl2);
         n_load = fsa_fwd_next_tile_below(sched, n_load, loc_sched);
       }
       cp_async_commit();
@@ -233,6 +260,28 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
         }
       }
 
+      // ---- gated: bound of the gate over the tile, running maximum, skip
+      // (flash_sparse_attn/ops/triton/activations.py:265-299) ------------------------------------------
+      if (KIND == KIND_GATED) {
+        float dmax = dl0, dmin = dl0;
+#pragma unroll
+        for (int sft = 8; sft > 0; sft >>= 1) {
+          dmax = fmaxf(dmax, __shfl_xor_sync(0xffffffffu, dmax, sft));
+          dmin = fminf(dmin, __shfl_xor_sync(0xffffffffu, dmin, sft));
+        }
+        const float gmc = fmaxf(fmaxf(a_max * dmax, a_max * dmin), fmaxf(a_min * dmax, a_min * dmin));
+        const bool gate_skip = (gmc - gate_max) * c < gate_thr_log2;
+        if (!gate_skip) gate_max = fmaxf(gmc, gate_max);
+        if (gate_skip) {
+          if (p.tile_map && lane == 0 && mt == 0) p.tile_map[((long long)b * p.Hkv + hkv) * p.n_tiles + n] = 3;
+          __syncwarp();
+          slot = (slot + 1) % DSTAGES;
+          dl0 = dl1;
+          dl1 = dl2;
+          continue;
+        }
+      }
+
       // ---- S = Q K^T over this tile: 2 key groups of 8 ------------------------------------------------
       float s[2][4];
 #pragma unroll
@@ -248,6 +297,21 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
           mma16816<T>(s[j], qa[kk], b0, b1);
           mma16816<T>(s[j], qa[kk + 1], b2, b3);
         }
+      }
+      if (KIND == KIND_GATED) {
+        // logits = (q.k + g(alpha * delta)) * scale (flash_sparse_attn/ops/triton/flash_gated_dec.py)
+        const bool logsig = p.flags & F_LOGSIGMOID;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float dk = __shfl_sync(0xffffffffu, dl0, 8 * j + 2 * t + (e & 1));
+            const float x = (e < 2 ? al0 : al1) * dk;
+            float gte = x;
+            if (logsig)
+              gte = fminf(x, 0.f) - 0.6931471805599453f * lg2_approx(1.0f + ex2_approx(-fabsf(x) * 1.4426950408889634f));
+            s[j][e] += gte;
+          }
       }
       // mask: element (j, e) is key 8j + 2t + (e & 1)
 #pragma unroll
@@ -325,6 +389,8 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
       }
       __syncwarp();
       slot = (slot + 1) % DSTAGES;
+      dl0 = dl1;
+      dl1 = dl2;
     }
     cp_async_wait<0>();
     __syncthreads();  // every warp is done with its ring: the space becomes the merge buffer
@@ -413,6 +479,7 @@ cudaError_t launch_dec(const DecKernelParams& p, int kind, int dtype, int head_d
   if (head_dim == HD_ && dtype == DT_) {                                         \
     if (kind == KIND_DENSE) return launch_one<HD_, T_, KIND_DENSE>(p, stream);   \
     if (kind == KIND_SPARSE) return launch_one<HD_, T_, KIND_SPARSE>(p, stream); \
+    if (kind == KIND_GATED) return launch_one<HD_, T_, KIND_GATED>(p, stream);   \
   }
   FSA_DEC_CASE(128, __nv_bfloat16, DT_BF16)
   FSA_DEC_CASE(128, __half, DT_FP16)

@@ -86,12 +86,14 @@ struct DecKernelParams {
   const int* page_table;
   const int* gather_idx;
   const int* windows;
+  const void* alpha;  // gated: [B, Hq]
+  const void* delta;  // gated: [B, Hkv, Sk] | [Hkv, Tk] | paged [pages, Hkv, page]
   uint8_t* tile_map;  // optional [B, Hkv, n_tiles] over 16-key tiles
-  long long q_sb, q_sh, k_sb, k_sn, k_sh, o_sb, o_sh, l_sb, l_sh;
+  long long q_sb, q_sh, k_sb, k_sn, k_sh, o_sb, o_sh, l_sb, l_sh, a_sb, a_sh, d_sb, d_sh;
   int B, Hq, Hkv, G;
   int sk, sk_capacity, topk;
   int num_splits, page_size, pt_stride, gi_stride, win_stride, n_tiles;
-  float scale_log2, softmax_thr;
+  float scale_log2, softmax_thr, gate_thr;
   unsigned flags;
 };
 

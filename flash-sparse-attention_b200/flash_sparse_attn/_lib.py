@@ -172,6 +172,8 @@ class FsaDecArgs(ctypes.Structure):
         ("page_table", c_void_p),
         ("gather_kv_indices", c_void_p),
         ("window_sizes", c_void_p),
+        ("alpha", c_void_p),
+        ("delta", c_void_p),
         ("status", c_void_p),
         ("tile_map", c_void_p),
         ("q_stride_b", c_int64),
@@ -183,6 +185,10 @@ class FsaDecArgs(ctypes.Structure):
         ("o_stride_h", c_int64),
         ("lse_stride_b", c_int64),
         ("lse_stride_h", c_int64),
+        ("alpha_stride_b", c_int64),
+        ("alpha_stride_h", c_int64),
+        ("delta_stride_b", c_int64),
+        ("delta_stride_h", c_int64),
         ("batch", c_int32),
         ("seqlen_k", c_int32),
         ("total_k", c_int32),

@@ -67,8 +67,6 @@ def attn_decode(
     """Returns ``(out, lse)``; with ``partial_only`` returns ``(out_partial [ns,B,Hq,D] fp32,
     lse_partial [ns,Hq,B] fp32 base-2)`` instead (used by context-parallel decode).
     ``workspace`` optionally supplies the two partial buffers so that no allocation happens."""
-    if kind == "gated":
-        raise NotImplementedError("the gated decode kernel is not built yet")
     if is_quant:
         raise NotImplementedError("FP8 KV-cache decode is not built yet")
     if not query.is_cuda:
@@ -89,6 +87,10 @@ def attn_decode(
         total_k = 0
     softmax_scale = softmax_scale if softmax_scale is not None else 1.0 / (head_dim**0.5)
     softmax_threshold = softmax_threshold if softmax_threshold is not None else 1.0
+    if kind == "gated":
+        gate_threshold = gate_threshold if gate_threshold is not None else 1.0 / max(seqlen_k, 1)
+    else:
+        gate_threshold = 0.0
     is_gather = gather_kv_indices is not None
     if is_local and window_sizes is None:
         window_sizes = utils.window_sizes_heuristic(seqlen_k, num_heads_kv, device)
@@ -148,10 +150,17 @@ def attn_decode(
     a.partial_only = int(partial_only)
     a.kind = _KIND[kind]
     a.dtype = _lib.dtype_code(query.dtype)
-    a.flags = _lib.F_LOCAL if is_local else 0
+    a.flags = (_lib.F_LOCAL if is_local else 0) | (_lib.F_LOGSIGMOID if is_logsigmoid_gate else 0)
+    if kind == "gated":
+        # alpha [B, Hq]; delta [B, Hkv, Sk] / [Hkv, Tk] / paged [pages, Hkv, page] (positions contiguous)
+        alpha, delta = alpha.to(query.dtype).contiguous(), delta.to(query.dtype).contiguous()
+        keep_alive = (alpha, delta)  # noqa: F841  (the launch below is asynchronous)
+        a.alpha, a.delta = alpha.data_ptr(), delta.data_ptr()
+        a.alpha_stride_b, a.alpha_stride_h = alpha.stride(0), alpha.stride(1)
+        a.delta_stride_b, a.delta_stride_h = (0, delta.stride(0)) if varlen else (delta.stride(0), delta.stride(1))
     a.softmax_scale = float(softmax_scale)
     a.softmax_threshold = float(softmax_threshold)
-    a.gate_threshold = 0.0
+    a.gate_threshold = float(gate_threshold)
 
     with torch.cuda.device(device):
         rc = _lib.load().fsa_decode(ctypes.byref(a), _lib.current_stream_ptr(device))

@@ -199,12 +199,16 @@ typedef struct FsaDecArgs {
   const int32_t* page_table;
   const int32_t* gather_kv_indices;
   const int32_t* window_sizes;
+  const void* alpha; /* gated: [batch, heads_q], dtype of q */
+  const void* delta; /* gated: [batch, heads_kv, seqlen_k] | [heads_kv, total_k] | paged [num_pages, heads_kv, page_size] */
   int32_t* status;
   uint8_t* tile_map; /* optional [batch, heads_kv, 16-key tiles]; may be null */
   int64_t q_stride_b, q_stride_h;
   int64_t k_stride_b, k_stride_s, k_stride_h; /* v must share k's strides */
   int64_t o_stride_b, o_stride_h;
   int64_t lse_stride_b, lse_stride_h;
+  int64_t alpha_stride_b, alpha_stride_h;
+  int64_t delta_stride_b, delta_stride_h;
   int32_t batch, seqlen_k, total_k;
   int32_t heads_q, heads_kv, head_dim;
   int32_t topk, gather_stride;

@@ -99,3 +99,66 @@ def test_gate_skip_triggers_and_stays_close():
     assert (tmap == 3).sum().item() > 0
     # rows in the last 256 positions see the boosted keys: everything else is negligible there
     assert_close("gate-skip", out[:, -200:], ref[:, -200:], rtol=3e-2, atol=3e-2)
+
+
+# ---------------------------------------------------------------------------------------------------
+# gated decode
+# ---------------------------------------------------------------------------------------------------
+def test_golden_gated_decode():
+    fsa = _ops()
+    g = load("decode")
+    q, k, v, a, d = (g[n].to(DEV) for n in ("q", "k", "v", "alpha", "delta"))
+    out = fsa.flash_gated_attn_with_kvcache_func(q, k, v, a, d, softmax_threshold=-128.0, gate_threshold=-128.0)
+    _sync()
+    assert_close("gated-decode", out, g["out_gated"])
+
+
+@pytest.mark.parametrize("logsig", [True, False])
+@pytest.mark.parametrize("local", [False, True])
+@pytest.mark.parametrize("head_dim", [64, 128])
+@pytest.mark.parametrize("mode", ["plain", "gather", "paged", "varlen"])
+def test_gated_decode_grid(logsig, local, head_dim, mode):
+    fsa = _ops()
+    b, sk, hq, hkv = 2, 1024, 16, 2
+    g = torch.Generator().manual_seed(11)
+    mk = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16)  # noqa: E731
+    q, k, v, a, d = mk(b, hq, head_dim), mk(b, sk, hkv, head_dim), mk(b, sk, hkv, head_dim), mk(b, hq), mk(b, sk, hkv)
+    ws = torch.tensor([[32, 200, 100, 160], [0, 300, 0, 64]], dtype=torch.int32) if local else None
+    kw = dict(softmax_threshold=-128.0, gate_threshold=-128.0, is_logsigmoid_gate=logsig)
+    if mode == "gather":
+        if local:
+            pytest.skip("windows do not apply to gathered keys")
+        idx = torch.stack([torch.randperm(sk, generator=g)[:128] for _ in range(b)]).to(torch.int32)
+        idx[:, 2::13] = -1
+        ref = eager.gather_decode(q, k, v, idx, alpha=a, delta=d, is_logsigmoid_gate=logsig)
+        out = fsa.flash_gated_attn_with_kvcache_func(q.to(DEV), k.to(DEV), v.to(DEV), a.to(DEV), d.to(DEV),
+                                                     gather_kv_indices=idx.to(DEV), **kw)
+    elif mode == "paged":
+        page = 64
+        kc, vc, dc = k.reshape(b * sk // page, page, hkv, head_dim), v.reshape(b * sk // page, page, hkv, head_dim), \
+            d.reshape(b * sk // page, page, hkv)
+        perm = torch.randperm(b * sk // page, generator=g)
+        table = torch.empty(b * sk // page, dtype=torch.int32)
+        table[perm] = torch.arange(b * sk // page, dtype=torch.int32)   # logical page i lives at physical perm^-1
+        kp, vp, dp = torch.empty_like(kc), torch.empty_like(vc), torch.empty_like(dc)
+        kp[table.long()], vp[table.long()], dp[table.long()] = kc, vc, dc
+        table = table.reshape(b, sk // page)
+        ref = eager.decode(q, k, v, is_local=local, window_sizes=ws, alpha=a, delta=d, is_logsigmoid_gate=logsig)
+        out = fsa.flash_gated_attn_with_kvcache_func(q.to(DEV), kp.to(DEV), vp.to(DEV), a.to(DEV), dp.to(DEV),
+                                                     page_table=table.to(DEV),
+                                                     window_sizes=ws.to(DEV) if local else None, **kw)
+    elif mode == "varlen":
+        lens = [1024, 700]
+        cu = torch.tensor([0, 1024, 1724], dtype=torch.int32)
+        kp, vp, dp = mk(1724, hkv, head_dim), mk(1724, hkv, head_dim), mk(1724, hkv)
+        ref = eager.varlen_decode(q, kp, vp, cu, is_local=local, window_sizes=ws, alpha=a, delta=dp,
+                                  is_logsigmoid_gate=logsig)
+        out = fsa.flash_gated_attn_varlen_with_kvcache_func(q.to(DEV), kp.to(DEV), vp.to(DEV), a.to(DEV), dp.to(DEV),
+                                                            cu.to(DEV), max(lens),
+                                                            window_sizes=ws.to(DEV) if local else None, **kw)
+    else:
+        ref = eager.decode(q, k, v, is_local=local, window_sizes=ws, alpha=a, delta=d, is_logsigmoid_gate=logsig)
+        out = fsa.flash_gated_attn_with_kvcache_func(q.to(DEV), k.to(DEV), v.to(DEV), a.to(DEV), d.to(DEV),
+                                                     window_sizes=ws.to(DEV) if local else None, **kw)
+    _sync()
+    assert_close(f"gated-decode-{mode}", out, ref, rtol=2.5e-2, atol=2.5e-2)
