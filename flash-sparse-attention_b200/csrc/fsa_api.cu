@@ -343,7 +343,11 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
   if (a->batch <= 0 || a->heads_q <= 0 || a->heads_kv <= 0 || a->heads_q % a->heads_kv) return FSA_ERR_INVALID_ARG;
   if (a->head_dim != 64 && a->head_dim != 128) return FSA_ERR_UNSUPPORTED;
   if (a->dtype != FSA_DT_BF16 && a->dtype != FSA_DT_FP16) return FSA_ERR_UNSUPPORTED;
-  if (a->kind != FSA_KIND_DENSE && a->kind != FSA_KIND_SPARSE) return FSA_ERR_UNSUPPORTED;
+  if (a->kind != FSA_KIND_DENSE && a->kind != FSA_KIND_SPARSE && a->kind != FSA_KIND_GATED)
+    return FSA_ERR_UNSUPPORTED;
+  const bool gated = a->kind == FSA_KIND_GATED;
+  if (gated && (!a->alpha || !a->delta || !a->dalpha || !a->ddelta || !a->alpha_ws || !a->da_accum))
+    return FSA_ERR_INVALID_ARG;
   if ((a->tile_m && a->tile_m != 128) || (a->tile_n && a->tile_n != 128)) return FSA_ERR_UNSUPPORTED;
   if ((a->flags & FSA_F_LOCAL) && !a->window_sizes) return FSA_ERR_INVALID_ARG;
   if (a->dk_stride_b % 8 || a->dk_stride_s % 8 || a->dk_stride_h % 8) return FSA_ERR_INVALID_ARG;
@@ -353,6 +357,7 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
   if (ns <= 0) return FSA_ERR_INVALID_ARG;
   const bool split = ns > 1;
   if (split && (!a->dk_partial || !a->dv_partial)) return FSA_ERR_INVALID_ARG;
+  if (split && gated && (!a->dd_partial || a->delta_numel <= 0)) return FSA_ERR_INVALID_ARG;
   if (a->seqlen_q <= 0 || a->seqlen_k <= 0) return FSA_OK;
   const int64_t R = fsa_bwd_padded_rows(a->batch, a->seqlen_q, a->total_q, varlen_q);
   const long long rows_k = varlen_k ? a->total_k : (long long)a->batch * a->seqlen_k;
@@ -381,6 +386,15 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
   pre.heads = a->heads_q;
   pre.head_dim = a->head_dim;
   pre.varlen = varlen_q;
+  if (gated) {
+    if (cudaMemsetAsync(a->alpha_ws, 0, 2 * (size_t)a->heads_q * R, stream) != cudaSuccess) return FSA_ERR_LAUNCH;
+    if (cudaMemsetAsync(a->da_accum, 0, sizeof(float) * (size_t)a->heads_q * R, stream) != cudaSuccess)
+      return FSA_ERR_LAUNCH;
+    pre.alpha = a->alpha;
+    pre.alpha_ws = a->alpha_ws;
+    pre.a_sb = a->alpha_stride_b;
+    pre.a_sh = a->alpha_stride_h;
+  }
   if (fsa::launch_bwd_pre(pre, a->dtype, stream) != cudaSuccess) return FSA_ERR_LAUNCH;
   if (cudaMemsetAsync(a->dq_accum, 0, sizeof(float) * (size_t)a->heads_q * R * a->head_dim, stream) != cudaSuccess)
     return FSA_ERR_LAUNCH;
@@ -449,6 +463,18 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
   p.softmax_scale = a->softmax_scale;
   p.softmax_thr = a->softmax_threshold;
   unsigned f = 0;
+  if (gated) {
+    p.alpha_ws = a->alpha_ws;
+    p.delta = a->delta;
+    p.da_accum = a->da_accum;
+    p.dd_out = split ? (void*)a->dd_partial : a->ddelta;
+    p.d_sb = a->delta_stride_b;
+    p.d_sh = a->delta_stride_h;
+    p.dd_ss = a->delta_numel;
+    p.gate_thr = a->gate_threshold;
+    if (a->flags & FSA_F_LOGSIGMOID) f |= fsa::F_LOGSIGMOID;
+    if (a->flags & FSA_F_ADAPT_GATE) f |= fsa::F_ADAPT_GATE;
+  }
   if (a->flags & FSA_F_CAUSAL) f |= fsa::F_CAUSAL;
   if (a->flags & FSA_F_LOCAL) f |= fsa::F_LOCAL;
   if (split) f |= fsa::F_SPLIT;
@@ -479,7 +505,23 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
   post.head_dim = a->head_dim;
   post.varlen = varlen_q;
   post.scale = a->softmax_scale;
+  if (gated) {
+    post.da_accum = a->da_accum;
+    post.da = a->dalpha;
+    post.da_sb = a->alpha_stride_b;
+    post.da_sh = a->alpha_stride_h;
+  }
   if (fsa::launch_bwd_post(post, a->dtype, stream) != cudaSuccess) return FSA_ERR_LAUNCH;
+  if (split && gated) {
+    fsa::FlatSumParams fs;
+    memset(&fs, 0, sizeof(fs));
+    fs.partial = a->dd_partial;
+    fs.out = a->ddelta;
+    fs.part_ss = a->delta_numel;
+    fs.n = a->delta_numel;
+    fs.num_splits = ns;
+    if (fsa::launch_flat_sum(fs, a->dtype, stream) != cudaSuccess) return FSA_ERR_LAUNCH;
+  }
 
   if (split) {
     for (int which = 0; which < 2; ++which) {

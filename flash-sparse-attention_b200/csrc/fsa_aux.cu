@@ -119,6 +119,9 @@ __global__ void __launch_bounds__(256) bwd_pre_kernel(BwdPreParams p) {
     const long long w = (long long)h * p.ws_sh + padded_row(p.varlen, p.cu_q, b, p.sq, q);
     p.lse2_ws[w] = l2;
     p.dpsum_ws[w] = acc;
+    if (p.alpha_ws)
+      reinterpret_cast<T*>(p.alpha_ws)[w] =
+          reinterpret_cast<const T*>(p.alpha)[(p.varlen ? 0 : (long long)b * p.a_sb) + (long long)h * p.a_sh + tok];
   }
 }
 
@@ -152,6 +155,18 @@ __global__ void __launch_bounds__(256) bwd_post_kernel(BwdPostParams p) {
     o.y = pack2<T>(v.z * p.scale, v.w * p.scale);
     *reinterpret_cast<uint2*>(dst + i) = o;
   }
+  if (p.da && lane == 0)
+    reinterpret_cast<T*>(p.da)[(p.varlen ? 0 : (long long)b * p.da_sb) + (long long)h * p.da_sh + tok] =
+        T(p.da_accum[(long long)h * p.ws_sh + padded_row(p.varlen, p.cu_q, b, p.sq, q)] * p.scale);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) flat_sum_kernel(FlatSumParams p) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= p.n) return;
+  float acc = 0.f;
+  for (int s = 0; s < p.num_splits; ++s) acc += p.partial[(long long)s * p.part_ss + i];
+  reinterpret_cast<T*>(p.out)[i] = T(acc);
 }
 
 // One warp per (key row, head): sum the split partials in split order (fixed order, deterministic).
@@ -205,6 +220,16 @@ cudaError_t launch_bwd_post(const BwdPostParams& p, int dtype, cudaStream_t stre
     bwd_post_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
   else
     bwd_post_kernel<__half><<<grid, 256, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_flat_sum(const FlatSumParams& p, int dtype, cudaStream_t stream) {
+  if (p.n <= 0) return cudaSuccess;
+  const unsigned grid = (unsigned)((p.n + 255) / 256);
+  if (dtype == DT_BF16)
+    flat_sum_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
+  else
+    flat_sum_kernel<__half><<<grid, 256, 0, stream>>>(p);
   return cudaGetLastError();
 }
 

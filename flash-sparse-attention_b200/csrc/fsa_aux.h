@@ -29,14 +29,21 @@ struct BwdPreParams {
   float* lse2_ws;
   float* dpsum_ws;
   const int* cu_q;
+  const void* alpha;  // optional (gated): T [B, heads, sq] | [heads, total_q]
+  void* alpha_ws;     // optional (gated): T [heads, ws_sh], pre-zeroed; receives alpha at the padded rows
+  long long a_sb, a_sh;
   long long o_sb, o_sm, o_sh, do_sb, do_sm, do_sh, l_sb, l_sh, ws_sh;
   int B, sq, total_q, heads, head_dim, varlen;
 };
-// Backward post-pass: dq = dq_accum * scale in the 16-bit type.
+// Backward post-pass: dq = dq_accum * scale in the 16-bit type (and dalpha = da_accum * scale when given,
+// flash_sparse_attn/ops/triton/flash_bwd_postprocess.py:106-148).
 struct BwdPostParams {
   const float* dq_accum;  // [Hq, ws_sh, D]
   void* dq;
   const int* cu_q;
+  const float* da_accum;  // optional [Hq, ws_sh]
+  void* da;               // optional T, laid out like alpha
+  long long da_sb, da_sh;
   long long dq_sb, dq_sm, dq_sh, ws_sh;
   int B, sq, total_q, heads, head_dim, varlen;
   float scale;
@@ -50,6 +57,15 @@ struct SplitSumParams {
   int rows, rows_per_batch, heads, head_dim, num_splits;
 };
 
+// out[i] = sum over splits of partial[split * part_ss + i] for i < n, in split order (16-bit out).
+struct FlatSumParams {
+  const float* partial;
+  void* out;
+  long long part_ss, n;
+  int num_splits;
+};
+
+cudaError_t launch_flat_sum(const FlatSumParams& p, int dtype, cudaStream_t stream);
 cudaError_t launch_bwd_pre(const BwdPreParams& p, int dtype, cudaStream_t stream);
 cudaError_t launch_bwd_post(const BwdPostParams& p, int dtype, cudaStream_t stream);
 cudaError_t launch_split_sum(const SplitSumParams& p, int dtype, cudaStream_t stream);

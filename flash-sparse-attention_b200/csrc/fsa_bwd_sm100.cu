@@ -45,14 +45,15 @@ struct BwdSmem {
   static constexpr int kQ = kV + kTile;        // 2 stages
   static constexpr int kDO = kQ + 2 * kTile;   // 2 stages
   static constexpr int kDS = kDO + 2 * kTile;  // dS^T (16-bit, 128 x 128) / dQ staging (8 warps x 4 KB)
-  static constexpr int kAux = kDS + 32768;     // lse2[2][128], dpsum[2][128]
-  static constexpr int kBar = kAux + 2048;
+  static constexpr int kAux = kDS + 32768;     // lse2[2][128], dpsum[2][128] fp32, alpha[2][128] 16-bit (gated)
+  static constexpr int kBar = kAux + 2560;
   static constexpr int kTotal = kBar + 256;
 };
 
 struct BwdBars {
   uint64_t kv_full, qdo_full[2], qdo_empty[2];
   uint64_t s_full, p_full, dp_full, ds_full, dq_full, dq_empty, ds_free, vote_sync, acc_full;
+  uint64_t dd_sync;  // gated: second column group -> first, partial ddelta handed over in shared memory
   uint32_t tmem_base;
   int abort_flag;
   int skip_flag[2];
@@ -145,6 +146,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
   volatile int* abort_flag = &bars->abort_flag;
   float* s_lse = reinterpret_cast<float*>(smem + SM::kAux);          // [2][128]
   float* s_dps = reinterpret_cast<float*>(smem + SM::kAux + 1024);   // [2][128]
+  T* s_alpha = reinterpret_cast<T*>(smem + SM::kAux + 2048);         // [2][128] (gated)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool causal = p.flags & F_CAUSAL, local = p.flags & F_LOCAL, split_qo = p.flags & F_SPLIT;
@@ -197,6 +199,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
     mbar_init(&bars->ds_free, 8);
     mbar_init(&bars->vote_sync, 8);
     mbar_init(&bars->acc_full, 1);
+    mbar_init(&bars->dd_sync, 4);
     bars->abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
     mbar_fence_init();
   }
@@ -234,7 +237,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
           int m, mode;
           seg_at(segs, it - g * NT, &m, &mode);
           const int head = hkv * p.G + g;
-          mbar_arrive_expect_tx(&bars->qdo_full[st], 2 * SM::kTile + 1024);
+          mbar_arrive_expect_tx(&bars->qdo_full[st], 2 * SM::kTile + 1024 + (KIND == KIND_GATED ? 256 : 0));
           for (int d = 0; d < HD; d += 64) {
             tma_load_4d(smem + SM::kQ + st * SM::kTile + (d / 64) * (TM * 128), &p.map_q, &bars->qdo_full[st], d, head,
                         off_q + m * TM, bq);
@@ -244,6 +247,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
           const long long wrow = (long long)head * p.ws_sh + pad_off + (long long)m * TM;
           bulk_load_1d(s_lse + st * 128, p.lse2_ws + wrow, 512, &bars->qdo_full[st]);
           bulk_load_1d(s_dps + st * 128, p.dpsum_ws + wrow, 512, &bars->qdo_full[st]);
+          if (KIND == KIND_GATED)
+            bulk_load_1d(s_alpha + st * 128, reinterpret_cast<const T*>(p.alpha_ws) + wrow, 256, &bars->qdo_full[st]);
         }
       }
       __syncwarp();
@@ -358,6 +363,40 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
     int n_live = 0, n_staged = 0;
     bool skip_cur = false;
 
+    // ---- gated: delta of this key row, its extremes over the key tile, running gate bound --------
+    // (flash_sparse_attn/ops/triton/flash_gated_bwd.py:406-421; keys past the sequence read as zero)
+    float dlt = 0.f, d_max = 0.f, d_min = 0.f, dd_acc = 0.f, gate_max = -INFINITY;
+    const bool logsig = p.flags & F_LOGSIGMOID;
+    if (KIND == KIND_GATED) {
+      const T* dp = reinterpret_cast<const T*>(p.delta) + (long long)bk * p.d_sb + (long long)hkv * p.d_sh + off_k;
+      float mx = -INFINITY, mn = INFINITY;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int kj = n_block * TN + j * 32 + lane;
+        const float v = kj < sk ? float(dp[kj]) : 0.f;
+        if (j == wq) dlt = v;
+        mx = fmaxf(mx, v);
+        mn = fminf(mn, v);
+      }
+#pragma unroll
+      for (int sft = 16; sft > 0; sft >>= 1) {
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sft));
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, sft));
+      }
+      d_max = mx;
+      d_min = mn;
+    }
+    auto unpack16 = [&](uint32_t v, float& lo, float& hi) {
+      if (IS_BF16) {
+        lo = __uint_as_float(v << 16);
+        hi = __uint_as_float(v & 0xffff0000u);
+      } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v));
+        lo = f.x;
+        hi = f.y;
+      }
+    };
+
     auto col_mask = [&](int mode, int m) {
       ColMask cm;
       const int q0 = m * TM;
@@ -409,6 +448,33 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         return true;
       }
       tc_fence_after();
+      bool gate_skip = false;
+      if (KIND == KIND_GATED) {
+        // bound of the gate over the tile against a running maximum that restarts with every query head
+        // (flash_gated_bwd.py:61-79, activations.py:265-299, seqlen_info.py:156-191)
+        if (it == g * NT) gate_max = -INFINITY;
+        const uint2 av = *reinterpret_cast<const uint2*>(s_alpha + st * 128 + lane * 4);
+        float a4[4];
+        unpack16(av.x, a4[0], a4[1]);
+        unpack16(av.y, a4[2], a4[3]);
+        float mx = -INFINITY, mn = INFINITY;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float v = (m * TM + lane * 4 + j < sq) ? a4[j] : 0.f;
+          mx = fmaxf(mx, v);
+          mn = fminf(mn, v);
+        }
+#pragma unroll
+        for (int sft = 16; sft > 0; sft >>= 1) {
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sft));
+          mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, sft));
+        }
+        float g_thr = p.gate_thr;
+        if (causal && (p.flags & F_ADAPT_GATE)) g_thr = p.gate_thr * (float(m * TM + off) + 1.0f) / float(sk);
+        const float gmc = fmaxf(fmaxf(mx * d_max, mx * d_min), fmaxf(mn * d_max, mn * d_min));
+        gate_skip = (gmc - gate_max) * c < log2f(g_thr);
+        if (!gate_skip) gate_max = fmaxf(gmc, gate_max);
+      }
       uint32_t sr[64];
       tmem_ld32(tmem_base + lane_addr + TMEM_S + wg * 64, &sr[0]);
       tmem_ld32(tmem_base + lane_addr + TMEM_S + wg * 64 + 32, &sr[32]);
@@ -418,6 +484,27 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       const ColMask cm = col_mask(mode, m);
       const float4* lse4 = reinterpret_cast<const float4*>(s_lse + st * 128 + wg * 64);
       float x[64];  // log2 of the probabilities
+      if (KIND == KIND_GATED) {
+        // logits = (q.k + g(alpha_q * delta_k)) * scale, g = logsigmoid or identity (flash_gated_bwd.py:81-98)
+        const uint4* al4 = reinterpret_cast<const uint4*>(s_alpha + st * 128 + wg * 64);
+#pragma unroll
+        for (int i = 0; i < 64; i += 8) {
+          const uint4 av = al4[i >> 3];
+          float a8[8];
+          unpack16(av.x, a8[0], a8[1]);
+          unpack16(av.y, a8[2], a8[3]);
+          unpack16(av.z, a8[4], a8[5]);
+          unpack16(av.w, a8[6], a8[7]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float gx = a8[j] * dlt;
+            float gte = gx;
+            if (logsig)
+              gte = fminf(gx, 0.f) - 0.6931471805599453f * lg2_approx(1.0f + ex2_approx(-fabsf(gx) * 1.4426950408889634f));
+            sr[i + j] = __float_as_uint(__uint_as_float(sr[i + j]) + gte);
+          }
+        }
+      }
 #pragma unroll
       for (int i = 0; i < 64; i += 4) {
         const float4 l = lse4[i >> 2];
@@ -448,6 +535,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
           want |= (v >= 0.0f);
           drop |= (v < 0.0f);
         }
+        if (KIND == KIND_GATED && gate_skip) {
+          want = false;
+          drop = true;
+        }
         const unsigned w_any = __ballot_sync(0xffffffffu, want);
         const unsigned d_any = __ballot_sync(0xffffffffu, drop);
         if (lane == 0) {
@@ -467,7 +558,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
           if (p.tile_map) {
             const int head = hkv * p.G + g;
             p.tile_map[((((long long)b * p.Hq + head) * p.n_tiles_k + n_block) * p.num_splits + split) *
-                           p.num_m_blocks + m] = skip ? 2 : 1;
+                           p.num_m_blocks + m] = skip ? (gate_skip ? 3 : 2) : 1;
           }
           __threadfence_block();
         }
@@ -504,7 +595,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         return;
       }
       const float4* dps4 = reinterpret_cast<const float4*>(s_dps + st * 128 + wg * 64);
+      const uint4* al4 = reinterpret_cast<const uint4*>(s_alpha + st * 128 + wg * 64);
       uint8_t* slab = ds_buf + wg * (128 * 128);
+      float da_r[8];  // gated: per chunk, one column's dalpha summed over 8 lanes
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
         const float4 d0 = dps4[ch * 2], d1 = dps4[ch * 2 + 1];
@@ -538,6 +631,58 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
           o[j >> 1] = pack2<T>(p0 == 0.f ? 0.f : p0 * t0, p1 == 0.f ? 0.f : p1 * t1);
         }
         *reinterpret_cast<uint4*>(slab + sw128_offset(row, ch)) = make_uint4(o[0], o[1], o[2], o[3]);
+        if (KIND == KIND_GATED) {
+          // dalpha[q] += sum_k dS g'(alpha_q delta_k) delta_k, ddelta[k] += sum_q dS g'(alpha_q delta_k) alpha_q,
+          // g' = sigmoid(-x) for the logsigmoid gate, 1 for the identity (flash_gated_bwd.py:84-88, :152-160)
+          const uint4 av = al4[ch];
+          float a8[8], v[8];
+          unpack16(av.x, a8[0], a8[1]);
+          unpack16(av.y, a8[2], a8[3]);
+          unpack16(av.z, a8[4], a8[5]);
+          unpack16(av.w, a8[6], a8[7]);
+#pragma unroll
+          for (int j = 0; j < 8; j += 2) {
+            float e0, e1;
+            unpack16(o[j >> 1], e0, e1);
+            if (logsig) {
+              e0 *= __fdividef(1.0f, 1.0f + ex2_approx(a8[j] * dlt * 1.4426950408889634f));
+              e1 *= __fdividef(1.0f, 1.0f + ex2_approx(a8[j + 1] * dlt * 1.4426950408889634f));
+            }
+            dd_acc = fmaf(e0, a8[j], dd_acc);
+            dd_acc = fmaf(e1, a8[j + 1], dd_acc);
+            v[j] = e0 * dlt;
+            v[j + 1] = e1 * dlt;
+          }
+          // three butterfly steps fold the 8 columns onto lane bits 4, 3, 2: one column per lane, summed over 8 lanes
+          const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
+          float u[4], t2[2];
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            u[j] = (b4 ? v[j + 4] : v[j]) + __shfl_xor_sync(0xffffffffu, b4 ? v[j] : v[j + 4], 16);
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+            t2[j] = (b3 ? u[j + 2] : u[j]) + __shfl_xor_sync(0xffffffffu, b3 ? u[j] : u[j + 2], 8);
+          da_r[ch] = (b2 ? t2[1] : t2[0]) + __shfl_xor_sync(0xffffffffu, b2 ? t2[0] : t2[1], 4);
+        }
+      }
+      if (KIND == KIND_GATED) {
+        // two more steps fold the 8 chunks onto lane bits 1, 0: each lane ends with two complete column sums
+        const bool b1 = lane & 2, b0 = lane & 1;
+        float u[4], z[2];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          u[j] = (b1 ? da_r[j + 4] : da_r[j]) + __shfl_xor_sync(0xffffffffu, b1 ? da_r[j] : da_r[j + 4], 2);
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+          z[j] = (b0 ? u[j + 2] : u[j]) + __shfl_xor_sync(0xffffffffu, b0 ? u[j] : u[j + 2], 1);
+        const int g = it / NT;
+        int m, mode;
+        seg_at(segs, it - g * NT, &m, &mode);
+        const int chunk0 = (b1 ? 4 : 0) + (b0 ? 2 : 0);
+        const int cin = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+        float* dst = p.da_accum + (long long)(hkv * p.G + g) * p.ws_sh + pad_off + (long long)m * TM + wg * 64 + cin;
+        atomicAdd(dst + chunk0 * 8, z[0]);
+        atomicAdd(dst + (chunk0 + 1) * 8, z[1]);
       }
       fence_proxy_async_smem();
       tc_fence_before();
@@ -654,6 +799,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         }
       }
     }
+    // ---- gated epilogue: ddelta of this key row = (columns 0-63) + (columns 64-127), scaled -------------
+    if (KIND == KIND_GATED && ok) {
+      float* tmp = s_lse;  // every load of the ring has been consumed by now
+      if (wg == 1) {
+        tmp[row] = dd_acc;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->dd_sync);
+      } else {
+        ok = mbar_wait(&bars->dd_sync, 0, abort_flag);
+        if (ok && row_ok) {
+          const float val = (dd_acc + tmp[row]) * p.softmax_scale;
+          const long long at = (long long)bk * p.d_sb + (long long)hkv * p.d_sh + off_k + k_idx;
+          if (p.flags & F_SPLIT)
+            reinterpret_cast<float*>(p.dd_out)[(long long)split * p.dd_ss + at] = val;
+          else
+            reinterpret_cast<T*>(p.dd_out)[at] = T(val);
+        }
+      }
+    }
     if (lane == 0) bulk_wait0();
     __syncwarp();
   }
@@ -691,6 +855,7 @@ cudaError_t launch_bwd(const BwdKernelParams& p, int kind, int dtype, int head_d
   if (head_dim == HD_ && dtype == DT_) {                                         \
     if (kind == KIND_DENSE) return launch_one<HD_, T_, KIND_DENSE>(p, stream);   \
     if (kind == KIND_SPARSE) return launch_one<HD_, T_, KIND_SPARSE>(p, stream); \
+    if (kind == KIND_GATED) return launch_one<HD_, T_, KIND_GATED>(p, stream);   \
   }
   FSA_BWD_CASE(128, __nv_bfloat16, DT_BF16)
   FSA_BWD_CASE(128, __half, DT_FP16)

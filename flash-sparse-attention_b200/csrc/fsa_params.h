@@ -64,12 +64,17 @@ struct alignas(64) BwdKernelParams {
   const int* windows;
   int* status;
   uint8_t* tile_map;  // optional [B, Hq, n_tiles_k, num_splits, num_m_blocks]
+  const void* alpha_ws;  // gated: T [Hq, ws_sh], tile-padded rows, zero outside the sequences
+  const void* delta;     // gated: T [B, Hkv, Sk] | [Hkv, Tk]
+  float* da_accum;       // gated: [Hq, ws_sh] fp32, zeroed; receives atomic adds
+  void* dd_out;          // gated: T* laid out like delta, or float partial [splits, ...] when F_SPLIT
+  long long d_sb, d_sh, dd_ss;
   long long dkv_sb, dkv_sn, dkv_sh, dkv_ss;
   long long ws_sh;
   int B, Hq, Hkv, G;
   int sq, sk;
   int num_splits, n_tiles_k, num_m_blocks, win_stride;
-  float scale_log2, softmax_scale, softmax_thr;
+  float scale_log2, softmax_scale, softmax_thr, gate_thr;
   unsigned flags;
 };
 

@@ -155,6 +155,18 @@ class FsaBwdArgs(ctypes.Structure):
         ("softmax_scale", c_float),
         ("softmax_threshold", c_float),
         ("gate_threshold", c_float),
+        ("alpha", c_void_p),
+        ("delta", c_void_p),
+        ("dalpha", c_void_p),
+        ("ddelta", c_void_p),
+        ("alpha_ws", c_void_p),
+        ("da_accum", c_void_p),
+        ("dd_partial", c_void_p),
+        ("alpha_stride_b", c_int64),
+        ("alpha_stride_h", c_int64),
+        ("delta_stride_b", c_int64),
+        ("delta_stride_h", c_int64),
+        ("delta_numel", c_int64),
     ]
 
 

@@ -1,8 +1,9 @@
 """Host launcher of the backward pass.
 
-Serves the dense and sparse operators, batched and packed; it plays the role of
-``_flash_{dense,sparse}_attn_backward`` / ``..._varlen_backward`` of the reference
-(flash_sparse_attn/ops/triton/flash_sparse_bwd.py:491-748, :751-1026): resolve defaults, pick the
+Serves the dense, sparse and gated operators, batched and packed; it plays the role of
+``_flash_{dense,sparse,gated}_attn_backward`` / ``..._varlen_backward`` of the reference
+(flash_sparse_attn/ops/triton/flash_sparse_bwd.py:491-748, :751-1026, flash_gated_bwd.py:682-1298):
+resolve defaults, pick the
 number of QO splits, allocate gradients and fp32 workspaces with PyTorch and make ONE call into the C
 ABI (``fsa_bwd``), which runs the pre-pass, the sm_100a main kernel, the dQ post-pass and the
 reduction over splits. No host synchronisation happens here.
@@ -63,8 +64,6 @@ def attn_backward(
     tile_map: Optional[torch.Tensor] = None,
 ):
     """Returns ``(dq, dk, dv)`` (plus ``(dalpha, ddelta)`` for the gated kind) in ``dout.dtype``."""
-    if kind == "gated":
-        raise NotImplementedError("the gated backward kernel is not built yet")
     if not query.is_cuda:
         raise RuntimeError("flash_sparse_attn (B200 build) only runs on CUDA tensors; there is no CPU path")
     device = query.device
@@ -80,6 +79,8 @@ def attn_backward(
         total_q = total_k = 0
     softmax_scale = softmax_scale if softmax_scale is not None else 1.0 / (head_dim**0.5)
     softmax_threshold = softmax_threshold if softmax_threshold is not None else 1.0
+    if kind == "gated":
+        gate_threshold = gate_threshold if gate_threshold is not None else 1.0 / max(seqlen_k, 1)
     if is_local and window_sizes is None:
         window_sizes = utils.window_sizes_heuristic(seqlen_k, num_heads_kv, device)
 
@@ -123,11 +124,27 @@ def attn_backward(
         rows_k = total_k if varlen else batch * seqlen_k
         dk_partial = torch.empty((num_splits, rows_k, num_heads_kv, head_dim), dtype=torch.float32, device=device)
         dv_partial = torch.empty((num_splits, rows_k, num_heads_kv, head_dim), dtype=torch.float32, device=device)
+    da = dd = alpha_ws = da_accum = dd_partial = None
+    if kind == "gated":
+        # alpha [B, Hq, Sq] / [Hq, Tq], delta [B, Hkv, Sk] / [Hkv, Tk] (position contiguous), 16-bit like dout
+        alpha = alpha.to(dout.dtype).contiguous()
+        delta = delta.to(dout.dtype).contiguous()
+        da = torch.empty_like(alpha)
+        dd = torch.empty_like(delta)
+        alpha_ws = torch.empty((num_heads_q, rows_pad), dtype=dout.dtype, device=device)
+        da_accum = torch.empty((num_heads_q, rows_pad), dtype=torch.float32, device=device)
+        if use_split:
+            dd_partial = torch.empty((num_splits, delta.numel()), dtype=torch.float32, device=device)
     if seqused_k is not None or seqused_q is not None:
         # rows outside the used part of a sequence receive no gradient
         dq.zero_()
         dk.zero_()
         dv.zero_()
+        if kind == "gated":
+            da.zero_()
+            dd.zero_()
+            if use_split:
+                dd_partial.zero_()
         if use_split:
             dk_partial.zero_()
             dv_partial.zero_()
@@ -177,10 +194,22 @@ def attn_backward(
     a.softmax_scale = float(softmax_scale)
     a.softmax_threshold = float(softmax_threshold)
     a.gate_threshold = float(gate_threshold) if gate_threshold is not None else 0.0
+    if kind == "gated":
+        a.alpha, a.delta, a.dalpha, a.ddelta = alpha.data_ptr(), delta.data_ptr(), da.data_ptr(), dd.data_ptr()
+        a.alpha_ws, a.da_accum, a.dd_partial = alpha_ws.data_ptr(), da_accum.data_ptr(), _lib.ptr(dd_partial)
+        a.alpha_stride_b, a.alpha_stride_h = (0, alpha.stride(0)) if varlen else (alpha.stride(0), alpha.stride(1))
+        a.delta_stride_b, a.delta_stride_h = (0, delta.stride(0)) if varlen else (delta.stride(0), delta.stride(1))
+        a.delta_numel = delta.numel()
+        if is_logsigmoid_gate:
+            a.flags |= _lib.F_LOGSIGMOID
+        if is_adapt_gate:
+            a.flags |= _lib.F_ADAPT_GATE
 
     with torch.cuda.device(device):
         rc = lib.fsa_bwd(ctypes.byref(a), _lib.current_stream_ptr(device))
     _lib.check(rc, f"fsa_bwd[{kind}]")
+    if kind == "gated":
+        return dq, dk, dv, da, dd
     return dq, dk, dv
 
 

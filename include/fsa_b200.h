@@ -121,6 +121,9 @@ size_t fsa_fwd_tile_map_bytes(const FsaFwdArgs* args);
  *   num_splits > 1 (rows_k = batch*seqlen_k or total_k); otherwise null.
  * dq is accumulated with TMA reduce-adds in fp32 (summation order across key tiles is not fixed,
  * like the reference's atomics); dk and dv are reduced inside one CTA per key tile in a fixed order.
+ * FSA_KIND_GATED additionally returns dalpha (fp32 atomics into da_accum, then scaled and rounded) and
+ * ddelta (reduced inside the CTA over the query heads of the group, fixed order); flags
+ * FSA_F_LOGSIGMOID / FSA_F_ADAPT_GATE as in the forward.
  */
 typedef struct FsaBwdArgs {
   const void* q;
@@ -161,6 +164,17 @@ typedef struct FsaBwdArgs {
   int32_t kind, dtype;
   uint32_t flags;
   float softmax_scale, softmax_threshold, gate_threshold;
+  /* gated kind only (flash_sparse_attn/ops/triton/flash_gated_bwd.py:682-981); null otherwise */
+  const void* alpha;  /* [batch, heads_q, seqlen_q] | packed [heads_q, total_q]; 16-bit like q */
+  const void* delta;  /* [batch, heads_kv, seqlen_k] | packed [heads_kv, total_k]; position stride 1 */
+  void* dalpha;       /* laid out like alpha */
+  void* ddelta;       /* laid out like delta */
+  void* alpha_ws;     /* workspace, 16-bit [heads_q, R] (zeroed by this call) */
+  float* da_accum;    /* workspace, fp32 [heads_q, R] (zeroed by this call) */
+  float* dd_partial;  /* [num_splits, numel(delta)] fp32, only when FSA_F_SPLIT and num_splits > 1 */
+  int64_t alpha_stride_b, alpha_stride_h;
+  int64_t delta_stride_b, delta_stride_h;
+  int64_t delta_numel; /* elements of delta / ddelta (contiguous) */
 } FsaBwdArgs;
 
 int fsa_bwd(const FsaBwdArgs* args, void* stream);

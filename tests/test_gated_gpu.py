@@ -162,3 +162,113 @@ def test_gated_decode_grid(logsig, local, head_dim, mode):
                                                      window_sizes=ws.to(DEV) if local else None, **kw)
     _sync()
     assert_close(f"gated-decode-{mode}", out, ref, rtol=2.5e-2, atol=2.5e-2)
+
+
+# ---------------------------------------------------------------------------------------------------
+# gated backward: dq, dk, dv, dalpha, ddelta
+# ---------------------------------------------------------------------------------------------------
+def _run_gated_bwd(fn, q, k, v, a, d, do, *extra, **kw):
+    leaves = [t.to(DEV).requires_grad_(True) for t in (q, k, v, a, d)]
+    kw = {n: (t.to(DEV) if isinstance(t, torch.Tensor) else t) for n, t in kw.items()}
+    extra = [t.to(DEV) if isinstance(t, torch.Tensor) else t for t in extra]
+    out = fn(*leaves, *extra, softmax_threshold=-128.0, gate_threshold=-128.0, **kw)
+    out.backward(do.to(DEV))
+    _sync()
+    return [t.grad for t in leaves]
+
+
+_GNAMES = ("dq", "dk", "dv", "dalpha", "ddelta")
+
+
+def test_golden_gated_backward():
+    fsa = _ops()
+    g = load("bwd_causal")
+    got = _run_gated_bwd(fsa.flash_gated_attn_func, g["q"], g["k"], g["v"], g["alpha"], g["delta"], g["dout"],
+                         is_causal=True)
+    for name, t, key in zip(_GNAMES, got, ("dq_gated", "dk_gated", "dv_gated", "da_gated", "dd_gated")):
+        assert_close("golden-gated-" + name, t, g[key])
+
+
+# the reference's gated backward grid (tests/test_gated_base_backward.py): causal x local x split_qo x gate form
+@pytest.mark.parametrize("causal,local", [(False, False), (True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("split", [False, True])
+@pytest.mark.parametrize("logsig", [True, False])
+@pytest.mark.parametrize("head_dim", [64, 128])
+def test_gated_backward_grid(causal, local, split, logsig, head_dim):
+    fsa = _ops()
+    b, s, hq, hkv = 2, 640, 8, 2
+    q, k, v = seeded_qkv(0, b, s, s, hq, hkv, head_dim)
+    a, d = _gates(5, b, s, s, hq, hkv)
+    do = torch.randn(b, s, hq, head_dim, generator=torch.Generator().manual_seed(9)).to(torch.bfloat16)
+    ws = torch.tensor([[32, 200, 100, 160], [0, 300, 0, 64]], dtype=torch.int32) if local else None
+    ref = eager.backward(q, k, v, do, None, causal, is_local=local, window_sizes=ws, alpha=a, delta=d,
+                         is_logsigmoid_gate=logsig)
+    got = _run_gated_bwd(fsa.flash_gated_attn_func, q, k, v, a, d, do, is_causal=causal, window_sizes=ws,
+                         is_split_qo=split, num_splits=3 if split else None, is_logsigmoid_gate=logsig)
+    for name, t, r in zip(_GNAMES, got, ref):
+        assert_close("gated-" + name, t, r, rtol=2.5e-2, atol=2.5e-2)
+
+
+@pytest.mark.parametrize("sq,sk", [(77, 300), (300, 300), (129, 1000)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_gated_backward_ragged(sq, sk, causal):
+    fsa = _ops()
+    q, k, v = seeded_qkv(1, 2, sq, sk, 4, 2, 128, torch.float16)
+    a, d = _gates(6, 2, sq, sk, 4, 2, torch.float16)
+    do = torch.randn(2, sq, 4, 128, generator=torch.Generator().manual_seed(3)).to(torch.float16)
+    ref = eager.backward(q, k, v, do, None, causal, alpha=a, delta=d)
+    got = _run_gated_bwd(fsa.flash_gated_attn_func, q, k, v, a, d, do, is_causal=causal)
+    for name, t, r in zip(_GNAMES, got, ref):
+        assert_close("gated-ragged-" + name, t, r, rtol=2.5e-2, atol=2.5e-2)
+
+
+def test_gated_backward_varlen():
+    import itertools
+
+    fsa = _ops()
+    lens_q, lens_k = [5, 130, 257, 64], [70, 130, 300, 64]
+    cq = torch.tensor([0] + list(itertools.accumulate(lens_q)), dtype=torch.int32)
+    ck = torch.tensor([0] + list(itertools.accumulate(lens_k)), dtype=torch.int32)
+    g = torch.Generator().manual_seed(3)
+    mk = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16)  # noqa: E731
+    q, k, v, do = mk(sum(lens_q), 4, 128), mk(sum(lens_k), 2, 128), mk(sum(lens_k), 2, 128), mk(sum(lens_q), 4, 128)
+    a, d = mk(sum(lens_q), 4), mk(sum(lens_k), 2)
+    ref = eager.varlen_backward(q, k, v, do, cq, ck, None, True, alpha=a, delta=d)
+    got = _run_gated_bwd(fsa.flash_gated_attn_varlen_func, q, k, v, a, d, do, cq, ck, max(lens_q), max(lens_k),
+                         is_causal=True)
+    for name, t, r in zip(_GNAMES, got, ref):
+        assert_close("gated-varlen-" + name, t, r, rtol=2.5e-2, atol=2.5e-2)
+
+
+def test_gated_backward_gate_skip_is_recorded():
+    """Keys whose delta pushes the gate far below the running bound are skipped (tile map value 3) and
+    the gradients stay close to the exact ones."""
+    from flash_sparse_attn.ops.triton import flash_bwd, flash_fwd
+
+    b, s, hq, hkv, hd = 1, 1024, 4, 2, 128
+    q, k, v = seeded_qkv(2, b, s, s, hq, hkv, hd)
+    # The bound runs over the query tiles of ONE key tile (flash_gated_bwd.py:406-432): the first query
+    # tile (alpha = 0, gate bound 0) sets it, the others (alpha = 4 against delta = -64) fall far below.
+    a = torch.full((b, s, hq), 4.0)
+    a[:, :128] = 0.0
+    a = a.to(torch.bfloat16)
+    d = torch.zeros(b, s, hkv)
+    d[:, 256:512] = -64.0
+    d = d.to(torch.bfloat16)
+    do = torch.randn(b, s, hq, hd, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16)
+    ref = eager.backward(q, k, v, do, None, False, alpha=a, delta=d)
+    at, dt = a.transpose(1, 2).contiguous().to(DEV), d.transpose(1, 2).contiguous().to(DEV)
+    qd, kd, vd, dod = (t.to(DEV) for t in (q, k, v, do))
+    out, lse, *_ = flash_fwd.attn_forward("gated", qd, kd, vd, alpha=at, delta=dt, softmax_threshold=-128.0,
+                                          gate_threshold=-128.0)
+    tmap = torch.zeros(flash_bwd.tile_map_numel(b, s, s, hq), dtype=torch.uint8, device=DEV)
+    got = flash_bwd.attn_backward("gated", qd, kd, vd, out, dod, lse, alpha=at, delta=dt, softmax_threshold=-128.0,
+                                  gate_threshold=1e-6, tile_map=tmap)
+    _sync()
+    tm = tmap.cpu().reshape(b, hq, 8, 1, 8)
+    assert (tm[:, :, 2:4, :, 1:] == 3).all(), "key tiles 2 and 3 are gate-skipped after their first query tile"
+    assert (tm[:, :, 2:4, :, 0] == 1).all() and (tm[:, :, :2] == 1).all() and (tm[:, :, 4:] == 1).all()
+    got = list(got)
+    got[3], got[4] = got[3].transpose(1, 2), got[4].transpose(1, 2)
+    for name, t, r in zip(_GNAMES, got, ref):
+        assert_close("gated-skip-" + name, t, r, rtol=2.5e-2, atol=2.5e-2)
