@@ -22,6 +22,7 @@ SOURCES = [
     "fsa_bwd_sm100.cu",
     "fsa_dec_sm100.cu",
     "fsa_static_scratch.cu",
+    "fsa_quant.cu",
 ]
 
 NVCC_FLAGS = [

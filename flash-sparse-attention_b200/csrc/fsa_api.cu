@@ -284,6 +284,7 @@ int fsa_fwd(const FsaFwdArgs* a, void* stream_) {
   p.softmax_thr = a->softmax_threshold;
   p.gate_thr = a->gate_threshold;
   p.v_scale = 1.0f;
+  p.qkv_scale = a->qkv_scale;
   unsigned f = 0;
   if (a->flags & FSA_F_CAUSAL) f |= fsa::F_CAUSAL;
   if (a->flags & FSA_F_LOCAL) f |= fsa::F_LOCAL;
@@ -615,6 +616,7 @@ int fsa_decode(const FsaDecArgs* a, void* stream_) {
   p.d_sb = a->delta_stride_b;
   p.d_sh = a->delta_stride_h;
   p.gate_thr = a->gate_threshold;
+  p.qkv_scale = a->qkv_scale;
   p.tile_map = a->tile_map;
   p.q_sb = a->q_stride_b;
   p.q_sh = a->q_stride_h;

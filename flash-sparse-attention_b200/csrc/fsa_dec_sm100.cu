@@ -109,7 +109,8 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
                                    : fsa_fwd_schedule(1, sk, 0, sub, w, nsub, DTN, 16, false, local, true, p.G,
                                                       /*cover_single_query=*/true);
   const bool loc_sched = local && !gather;
-  const float c = p.scale_log2;
+  const float c = p.qkv_scale ? p.scale_log2 * p.qkv_scale[0] * p.qkv_scale[1] : p.scale_log2;
+  const float v_scale = p.qkv_scale ? p.qkv_scale[2] : 1.0f;
   const float thr_log2 = (KIND != KIND_DENSE) ? log2f(fmaxf(fminf(p.softmax_thr / float(sk), 1.0f), 0.0f)) : 0.f;
   const int* gidx = gather ? p.gather_idx + (long long)b * p.gi_stride : nullptr;
   const int* ptab = paged ? p.page_table + (long long)b * p.pt_stride : nullptr;
@@ -434,7 +435,7 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
         acc.w += ov.w * wgt;
       }
       const bool dead = (l_tot == 0.f) || (l_tot != l_tot);
-      const float inv = dead ? 1.f : 1.f / l_tot;
+      const float inv = dead ? 1.f : v_scale / l_tot;
       const int head = hkv * p.G + row;
       if (p.flags & F_SPLIT) {
         float* dst = p.out_partial + (((long long)split * p.B + b) * p.Hq + head) * HD + d0;

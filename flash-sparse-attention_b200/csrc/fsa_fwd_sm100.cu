@@ -512,7 +512,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       const float visible = causal ? float(q_idx + (si.sk - si.sq) + 1) : float(si.sk);
       thr_log2 = log2f(fmaxf(fminf(p.softmax_thr / visible, 1.0f), 0.0f));
     }
-    const float c = p.scale_log2;
+    const float c = p.qkv_scale ? p.scale_log2 * p.qkv_scale[0] * p.qkv_scale[1] : p.scale_log2;
+    const float v_scale = p.qkv_scale ? p.qkv_scale[2] : p.v_scale;
     float m_ref = -INFINITY;  // reference maximum all stored exponentials are relative to
     float l_ref = 0.f;        // sum of exp2((s - m_ref) * c)
     bool have_o = false;      // some P V has been issued for this tile
@@ -752,7 +753,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     }
     if (ok && q_valid[q]) {
       const bool dead = (l_ref == 0.0f) || (l_ref != l_ref);
-      const float inv = dead ? 1.0f : p.v_scale / l_ref;
+      const float inv = dead ? 1.0f : v_scale / l_ref;
       float lse = dead ? -INFINITY : m_ref * c + log2f(l_ref);
       if (!(p.flags & F_LSE_LOG2)) lse *= 0.6931471805599453f;
       const long long tok = si.off_q + q_idx;

@@ -48,6 +48,7 @@ struct alignas(64) FwdKernelParams {
   int num_splits, num_m_blocks, num_pairs, hgrid;
   int page_size, pt_stride, win_stride, n_tiles_k;
   float scale_log2, softmax_thr, gate_thr, v_scale;
+  const float* qkv_scale;  // optional device fp32 [3]: de-quantisation scales of q, k, v
   unsigned flags;
 };
 
@@ -99,6 +100,7 @@ struct DecKernelParams {
   int sk, sk_capacity, topk;
   int num_splits, page_size, pt_stride, gi_stride, win_stride, n_tiles;
   float scale_log2, softmax_thr, gate_thr;
+  const float* qkv_scale;  // optional device fp32 [3]
   unsigned flags;
 };
 

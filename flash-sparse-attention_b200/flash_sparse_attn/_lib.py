@@ -88,6 +88,7 @@ class FsaFwdArgs(ctypes.Structure):
         ("softmax_scale", c_float),
         ("softmax_threshold", c_float),
         ("gate_threshold", c_float),
+        ("qkv_scale", c_void_p),
     ]
 
 
@@ -221,6 +222,7 @@ class FsaDecArgs(ctypes.Structure):
         ("softmax_scale", c_float),
         ("softmax_threshold", c_float),
         ("gate_threshold", c_float),
+        ("qkv_scale", c_void_p),
     ]
 
 
@@ -257,6 +259,10 @@ def load():
     lib.fsa_decode.argtypes = [POINTER(FsaDecArgs), c_void_p]
     lib.fsa_combine.restype = c_int
     lib.fsa_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+    lib.fsa_quantize_fp8.restype = c_int
+    lib.fsa_quantize_fp8.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
+    lib.fsa_fp8_widen.restype = c_int
+    lib.fsa_fp8_widen.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
     lib.fsa_set_profile_events.restype = None
     lib.fsa_set_profile_events.argtypes = [c_void_p, c_void_p]
     lib.fsa_debug_fwd_schedule.restype = None

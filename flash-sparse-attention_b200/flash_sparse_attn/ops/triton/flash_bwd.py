@@ -15,7 +15,7 @@ from typing import Optional, Tuple
 import torch
 
 from flash_sparse_attn import _lib
-from flash_sparse_attn.ops.triton import assert_inputs, utils
+from flash_sparse_attn.ops.triton import assert_inputs, quant, utils
 
 TILE_M = 128
 TILE_N = 128
@@ -25,7 +25,7 @@ _KIND = {"dense": _lib.KIND_DENSE, "sparse": _lib.KIND_SPARSE, "gated": _lib.KIN
 def _dequantize(x: torch.Tensor, scale: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     # saved tensors of a quantised forward are FP8; the backward runs on their de-quantised values in
     # the gradient dtype (flash_sparse_attn/ops/triton/scheduler.py:2133-2148)
-    return (x.to(torch.float32) * scale.to(torch.float32)).to(dtype)
+    return quant.widen_fp8(x, dtype, scale)
 
 
 def attn_backward(

@@ -13,7 +13,7 @@ from typing import Optional, Tuple
 import torch
 
 from flash_sparse_attn import _lib
-from flash_sparse_attn.ops.triton import assert_inputs, utils
+from flash_sparse_attn.ops.triton import assert_inputs, quant, utils
 
 _KIND = {"dense": _lib.KIND_DENSE, "sparse": _lib.KIND_SPARSE, "gated": _lib.KIND_GATED}
 KEYS_PER_WARP_TILE = 16
@@ -67,8 +67,6 @@ def attn_decode(
     """Returns ``(out, lse)``; with ``partial_only`` returns ``(out_partial [ns,B,Hq,D] fp32,
     lse_partial [ns,Hq,B] fp32 base-2)`` instead (used by context-parallel decode).
     ``workspace`` optionally supplies the two partial buffers so that no allocation happens."""
-    if is_quant:
-        raise NotImplementedError("FP8 KV-cache decode is not built yet")
     if not query.is_cuda:
         raise RuntimeError("flash_sparse_attn (B200 build) only runs on CUDA tensors; there is no CPU path")
     device = query.device
@@ -102,6 +100,12 @@ def attn_decode(
             page_table=page_table, gather_kv_indices=gather_kv_indices, num_heads_q=num_heads_q,
             num_heads_kv=num_heads_kv, head_dim=head_dim, page_size=page_size, is_quant=is_quant, device=device,
         )
+
+    qkv_scale = None
+    if is_quant:
+        # FP8 query and cache: widened (exactly) to bf16 before the kernel; scales as in the forward
+        qkv_scale = quant.scales_f32(query_scale, key_scale, value_scale, device)
+        query, key, value = (quant.widen_fp8(t, torch.bfloat16) for t in (query, key, value))
 
     keys = gather_kv_indices.shape[-1] if is_gather else seqlen_k
     if num_splits is None:
@@ -161,6 +165,7 @@ def attn_decode(
     a.softmax_scale = float(softmax_scale)
     a.softmax_threshold = float(softmax_threshold)
     a.gate_threshold = float(gate_threshold)
+    a.qkv_scale = _lib.ptr(qkv_scale)
 
     with torch.cuda.device(device):
         rc = _lib.load().fsa_decode(ctypes.byref(a), _lib.current_stream_ptr(device))

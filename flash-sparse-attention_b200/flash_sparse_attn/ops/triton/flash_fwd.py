@@ -14,7 +14,7 @@ from typing import Optional, Tuple
 import torch
 
 from flash_sparse_attn import _lib
-from flash_sparse_attn.ops.triton import assert_inputs, utils
+from flash_sparse_attn.ops.triton import assert_inputs, quant, utils
 
 TILE_M = 128
 TILE_N = 128
@@ -108,6 +108,13 @@ def attn_forward(
             device=device,
         )
 
+    qkv_scale = None
+    if is_quant:
+        # FP8 inputs: widened (exactly) to bf16 in one pass; the per-tensor scales stay on the device and
+        # enter the kernel as in scheduler.py:298-307 (logit scale *= q_scale * k_scale, out *= v_scale)
+        qkv_scale = quant.scales_f32(query_scale, key_scale, value_scale, device)
+        query, key, value = (quant.widen_fp8(t, torch.bfloat16) for t in (query, key, value))
+
     if is_split_kv and num_splits is None:
         num_splits = utils.num_splits_heuristic(
             seqlen_q=seqlen_q * group_packed, seqlen_k=seqlen_k, num_SMs=utils.device_num_sms(device),
@@ -151,6 +158,7 @@ def attn_forward(
     a.page_table, a.window_sizes = _lib.ptr(page_table), _lib.ptr(window_sizes)
     a.status = _lib.status_word(device).data_ptr()
     a.tile_map = _lib.ptr(tile_map)
+    a.qkv_scale = _lib.ptr(qkv_scale)
     if varlen:
         a.q_stride_b, a.q_stride_s, a.q_stride_h = 0, query.stride(0), query.stride(1)
         a.k_stride_b, a.k_stride_s, a.k_stride_h = 0, key.stride(0), key.stride(1)

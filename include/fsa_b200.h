@@ -98,6 +98,9 @@ typedef struct FsaFwdArgs {
   int32_t kind, dtype;
   uint32_t flags;
   float softmax_scale, softmax_threshold, gate_threshold;
+  /* optional: three fp32 values on the device, the per-tensor de-quantisation scales of q, k, v
+   * (scheduler.py:298-307: logits scale *= q_scale * k_scale; out *= v_scale). Null = all 1. */
+  const float* qkv_scale;
 } FsaFwdArgs;
 
 int fsa_fwd(const FsaFwdArgs* args, void* stream);
@@ -232,6 +235,7 @@ typedef struct FsaDecArgs {
   int32_t kind, dtype;
   uint32_t flags;
   float softmax_scale, softmax_threshold, gate_threshold;
+  const float* qkv_scale; /* optional, as in FsaFwdArgs */
 } FsaDecArgs;
 
 int fsa_decode(const FsaDecArgs* args, void* stream);
@@ -295,6 +299,24 @@ void fsa_debug_bwd_schedule(int seqlen_q, int seqlen_k, int n_block, int split_i
 void fsa_set_profile_events(void* before, void* after);
 
 const char* fsa_status_string(int code);
+/*
+ * Per-tensor FP8 quantisation, the contract of flash_sparse_attn/ops/triton/quant.py:42-64:
+ * scale = FP8_MAX / max|x|, x_fp8 = rne(x * scale), *scale_out = max|x| / FP8_MAX in x's type
+ * (FSA_DT_E5M2: 57344, FSA_DT_E4M3: 448). x: n contiguous elements of x_dtype (bf16 / fp16 / fp32,
+ * 16-byte aligned); amax_ws: caller-owned 4-byte device workspace (zeroed by this call). Two kernels,
+ * no host synchronisation.
+ */
+int fsa_quantize_fp8(const void* x, void* x_fp8, void* scale_out, float* amax_ws, int64_t n, int x_dtype,
+                     int fp8_dtype, void* stream);
+
+/*
+ * out[i] = (out_dtype)(float(x_fp8[i]) * *scale), scale optional (one element of out_dtype on the
+ * device; null = 1). The load-time de-quantisation of scheduler.py:2133-2148 as one pass; with a null
+ * scale the widening is exact. Both pointers 16-byte aligned.
+ */
+int fsa_fp8_widen(const void* x_fp8, void* out, const void* scale, int64_t n, int fp8_dtype, int out_dtype,
+                  void* stream);
+
 int fsa_abi_version(void);
 
 #ifdef __cplusplus

@@ -23,7 +23,7 @@ def test_library_exports_declared_symbols():
 
     lib = _lib.load()
     names = _declared_symbols()
-    assert {"fsa_fwd", "fsa_abi_version", "fsa_status_string"} <= names
+    assert {"fsa_fwd", "fsa_abi_version", "fsa_status_string", "fsa_quantize_fp8", "fsa_fp8_widen"} <= names
     for n in sorted(names):
         assert hasattr(lib, n), f"libfsa_b200.so does not export {n}"
     assert lib.fsa_abi_version() == _lib.ABI_VERSION
@@ -36,7 +36,8 @@ def test_struct_layout_matches_header():
     from flash_sparse_attn import _lib
 
     text = open(os.path.join(ROOT, "include", "fsa_b200.h")).read()
-    for cname, cls in (("FsaFwdArgs", _lib.FsaFwdArgs),):
+    for cname, cls in (("FsaFwdArgs", _lib.FsaFwdArgs), ("FsaBwdArgs", _lib.FsaBwdArgs),
+                       ("FsaDecArgs", _lib.FsaDecArgs)):
         body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), text, flags=re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         fields = []

@@ -1,0 +1,127 @@
+"""GPU parity of the FP8 path: quantize_fp8 bit-exact against the CPU restatement of
+flash_sparse_attn/ops/triton/quant.py:42-64, and the quantised operators against the reference's own
+check (tests/test_utils.py:1133-1138, :1246-1249, :1383-1384): de-quantise, run the eager oracle,
+compare with rtol = atol = 1.5e-1."""
+
+import pytest
+import torch
+
+from fixtures import assert_close, seeded_qkv
+from oracle import eager
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+QTOL = dict(rtol=1.5e-1, atol=1.5e-1)
+
+
+def _ops():
+    import flash_sparse_attn as fsa
+
+    return fsa
+
+
+def _sync():
+    torch.cuda.synchronize()
+    _ops().check_status()
+
+
+@pytest.mark.parametrize("src", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("fp8", [torch.float8_e5m2, torch.float8_e4m3fn])
+@pytest.mark.parametrize("n", [1, 7, 4096, 1000003])
+def test_quantize_fp8_is_bit_exact(src, fp8, n):
+    from flash_sparse_attn.ops.triton.quant import quantize_fp8, widen_fp8
+
+    x = (torch.randn(n, generator=torch.Generator().manual_seed(n)) * 3.0).to(src)
+    ref_q, ref_s = eager.quantize_fp8(x, fp8)
+    got_q, got_s = quantize_fp8(x.to(DEV), fp8)
+    _sync()
+    assert got_q.dtype == fp8 and got_s.dtype == src and got_s.shape == (1,)
+    assert torch.equal(got_q.cpu().view(torch.uint8), ref_q.view(torch.uint8))
+    assert torch.equal(got_s.cpu(), ref_s)
+    if src != torch.float32:
+        # widening: exact without a scale, (x * scale) rounded once with one
+        wide = widen_fp8(got_q, src)
+        scaled = widen_fp8(got_q, src, got_s)
+        _sync()
+        assert torch.equal(wide.cpu(), ref_q.to(src))
+        assert torch.equal(scaled.cpu(), (ref_q.float() * ref_s.float()).to(src))
+
+
+def _quantized(seed, b, sq, sk, hq, hkv, d):
+    q, k, v = seeded_qkv(seed, b, sq, sk, hq, hkv, d)
+    qs = [eager.quantize_fp8(t) for t in (q, k, v)]
+    deq = [(t.float() * s.float()).to(torch.bfloat16) for t, s in qs]
+    return qs, deq
+
+
+@pytest.mark.parametrize("kind", ["dense", "sparse", "gated"])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("auto", [False, True])
+def test_quant_forward(kind, causal, auto):
+    """``auto``: bf16 inputs with is_quant=True are quantised by the operator itself (interface.py:83-86)."""
+    fsa = _ops()
+    b, s, hq, hkv, d = 2, 512, 8, 2, 128
+    (q8, k8, v8), (qd, kd, vd) = _quantized(3, b, s, s, hq, hkv, d)
+    g = torch.Generator().manual_seed(8)
+    a, dl = torch.randn(b, s, hq, generator=g).to(torch.bfloat16), torch.randn(b, s, hkv, generator=g).to(torch.bfloat16)
+    # Under quantisation the reference adds the gate to the RAW fp8 dot product and scales the sum by
+    # q_scale * k_scale (flash_gated_fwd.py:104-122 with scheduler.py:307): the gate is shrunk by that
+    # factor. With the identity gate this equals alpha * q_scale * k_scale in the eager oracle.
+    sc = q8[1].float() * k8[1].float()
+    gate = dict(alpha=a.float() * sc, delta=dl.float(), is_logsigmoid_gate=False) if kind == "gated" else {}
+    ref = eager.forward(qd, kd, vd, None, causal, **gate)
+    kw = {}
+    if kind != "dense":
+        kw["softmax_threshold"] = -128.0
+    if kind == "gated":
+        kw["gate_threshold"] = -128.0
+        kw["is_logsigmoid_gate"] = False
+    fn = {"dense": fsa.flash_dense_attn_func, "sparse": fsa.flash_sparse_attn_func,
+          "gated": fsa.flash_gated_attn_func}[kind]
+    extra = [a.to(DEV), dl.to(DEV)] if kind == "gated" else []
+    if auto:
+        out = fn(qd.to(DEV), kd.to(DEV), vd.to(DEV), *extra, is_causal=causal, is_quant=True, **kw)
+    else:
+        out = fn(q8[0].to(DEV), k8[0].to(DEV), v8[0].to(DEV), *extra, is_causal=causal, is_quant=True,
+                 query_scale=q8[1].to(DEV), key_scale=k8[1].to(DEV), value_scale=v8[1].to(DEV), **kw)
+    _sync()
+    assert out.dtype == torch.bfloat16
+    assert_close(f"quant-{kind}", out, ref, **QTOL)
+
+
+def test_quant_backward_runs_on_dequantised_inputs():
+    fsa = _ops()
+    b, s, hq, hkv, d = 1, 384, 4, 2, 128
+    (q8, k8, v8), (qd, kd, vd) = _quantized(4, b, s, s, hq, hkv, d)
+    do = torch.randn(b, s, hq, d, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16)
+    ref = eager.backward(qd, kd, vd, do, None, True)
+    leaves = [t.to(DEV).requires_grad_(True) for t in (qd, kd, vd)]
+    out = fsa.flash_sparse_attn_func(*leaves, is_causal=True, is_quant=True, softmax_threshold=-128.0)
+    out.backward(do.to(DEV))
+    _sync()
+    for name, t, r in zip(("dq", "dk", "dv"), leaves, ref):
+        assert_close("quant-" + name, t.grad, r, **QTOL)
+
+
+@pytest.mark.parametrize("mode", ["plain", "gather"])
+def test_quant_decode(mode):
+    fsa = _ops()
+    b, sk, hq, hkv, d = 2, 1024, 16, 2, 128
+    g = torch.Generator().manual_seed(12)
+    mk = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16)  # noqa: E731
+    q, k, v = mk(b, hq, d), mk(b, sk, hkv, d), mk(b, sk, hkv, d)
+    q8, k8, v8 = (eager.quantize_fp8(t) for t in (q, k, v))
+    qd, kd, vd = ((t.float() * s.float()).to(torch.bfloat16) for t, s in (q8, k8, v8))
+    kw = dict(is_quant=True, query_scale=q8[1].to(DEV), key_scale=k8[1].to(DEV), value_scale=v8[1].to(DEV),
+              softmax_threshold=-128.0)
+    if mode == "gather":
+        idx = torch.stack([torch.randperm(sk, generator=g)[:256] for _ in range(b)]).to(torch.int32)
+        ref = eager.gather_decode(qd, kd, vd, idx)
+        out = fsa.flash_sparse_attn_with_kvcache_func(q8[0].to(DEV), k8[0].to(DEV), v8[0].to(DEV),
+                                                      gather_kv_indices=idx.to(DEV), **kw)
+    else:
+        ref = eager.decode(qd, kd, vd)
+        out = fsa.flash_sparse_attn_with_kvcache_func(q8[0].to(DEV), k8[0].to(DEV), v8[0].to(DEV), **kw)
+    _sync()
+    assert out.dtype == torch.bfloat16
+    assert_close("quant-decode-" + mode, out, ref, **QTOL)
