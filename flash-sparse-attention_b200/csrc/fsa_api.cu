@@ -396,6 +396,9 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
     pre.a_sb = a->alpha_stride_b;
     pre.a_sh = a->alpha_stride_h;
   }
+  // padding rows of dpsum must hold finite values (they meet zero probabilities in a packed product)
+  if (cudaMemsetAsync(a->dpsum_ws, 0, sizeof(float) * (size_t)a->heads_q * R, stream) != cudaSuccess)
+    return FSA_ERR_LAUNCH;
   if (fsa::launch_bwd_pre(pre, a->dtype, stream) != cudaSuccess) return FSA_ERR_LAUNCH;
   if (cudaMemsetAsync(a->dq_accum, 0, sizeof(float) * (size_t)a->heads_q * R * a->head_dim, stream) != cudaSuccess)
     return FSA_ERR_LAUNCH;

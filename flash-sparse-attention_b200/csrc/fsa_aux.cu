@@ -117,8 +117,9 @@ __global__ void __launch_bounds__(256) bwd_pre_kernel(BwdPreParams p) {
     float l2 = (lse == lse) ? lse * 1.4426950408889634f : 1e6f;
     l2 = fmaxf(l2, -1e6f);
     const long long w = (long long)h * p.ws_sh + padded_row(p.varlen, p.cu_q, b, p.sq, q);
-    p.lse2_ws[w] = l2;
-    p.dpsum_ws[w] = acc;
+    // both are stored negated: the main kernel then needs one packed fma / add per pair of entries
+    p.lse2_ws[w] = -l2;
+    p.dpsum_ws[w] = -acc;
     if (p.alpha_ws)
       reinterpret_cast<T*>(p.alpha_ws)[w] =
           reinterpret_cast<const T*>(p.alpha)[(p.varlen ? 0 : (long long)b * p.a_sb) + (long long)h * p.a_sh + tok];

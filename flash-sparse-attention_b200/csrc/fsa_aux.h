@@ -21,7 +21,7 @@ struct CombineParams {
 };
 
 // Backward pre-pass over every (query row, head): dpsum = sum_d O*dO, lse2 = lse * log2(e) (NaN -> 1e6,
-// clamped at -1e6), both written at tile-padded row positions.
+// clamped at -1e6), both written NEGATED at tile-padded row positions.
 struct BwdPreParams {
   const void* out;
   const void* dout;

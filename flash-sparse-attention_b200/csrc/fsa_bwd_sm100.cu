@@ -29,6 +29,29 @@
 #include "fsa_schedule.h"
 #include "fsa_aux.h"
 
+// Development aid: with -DFSA_PHASE_TIMING one lane of a compute warp and of the MMA warp add up the
+// clock cycles they spend in each wait / phase; fsa_debug_bwd_ticks() reads the totals over all CTAs.
+#ifdef FSA_PHASE_TIMING
+__device__ unsigned long long g_bwd_ticks[16];
+#define FSA_TICK_DECL long long tk_[16] = {0}; long long tk_t_ = clock64(); const bool tk_on_ = (lane == 0) && (warp == 0 || warp == 9)
+#define FSA_TICK(i)                          \
+  do {                                       \
+    const long long now_ = clock64();        \
+    tk_[i] += now_ - tk_t_;                  \
+    tk_t_ = now_;                            \
+  } while (0)
+#define FSA_TICK_FLUSH                                                                      \
+  do {                                                                                      \
+    if (tk_on_)                                                                             \
+      for (int i_ = 0; i_ < 16; ++i_)                                                       \
+        if (tk_[i_]) atomicAdd(&g_bwd_ticks[i_], (unsigned long long)tk_[i_]);               \
+  } while (0)
+#else
+#define FSA_TICK_DECL
+#define FSA_TICK(i)
+#define FSA_TICK_FLUSH
+#endif
+
 namespace fsa {
 
 namespace {
@@ -43,16 +66,17 @@ struct BwdSmem {
   static constexpr int kK = 0;
   static constexpr int kV = kK + kTile;
   static constexpr int kQ = kV + kTile;        // 2 stages
-  static constexpr int kDO = kQ + 2 * kTile;   // 2 stages
-  static constexpr int kDS = kDO + 2 * kTile;  // dS^T (16-bit, 128 x 128) / dQ staging (8 warps x 4 KB)
-  static constexpr int kAux = kDS + 32768;     // lse2[2][128], dpsum[2][128] fp32, alpha[2][128] 16-bit (gated)
+  static constexpr int kDO = kQ + 2 * kTile;   // 1 stage: dO lives only from dP^T to dV of its step
+  static constexpr int kDS = kDO + kTile;      // dS^T (16-bit, 128 x 128)
+  static constexpr int kStage = kDS + 32768;   // dQ staging for the TMA reduce-add: 8 warps x 4 KB
+  static constexpr int kAux = kStage + 32768;  // lse2[2][128], dpsum[2][128] fp32, alpha[2][128] 16-bit (gated)
   static constexpr int kBar = kAux + 2560;
   static constexpr int kTotal = kBar + 256;
 };
 
 struct BwdBars {
-  uint64_t kv_full, qdo_full[2], qdo_empty[2];
-  uint64_t s_full, p_full, dp_full, ds_full, dq_full, dq_empty, ds_free, vote_sync, acc_full;
+  uint64_t kv_full, q_full[2], q_empty[2], do_full, do_empty;
+  uint64_t s_full, p_full, dp_full, ds_full, dq_full, dq_empty, vote_sync, acc_full;
   uint64_t dd_sync;  // gated: second column group -> first, partial ddelta handed over in shared memory
   uint32_t tmem_base;
   int abort_flag;
@@ -99,19 +123,31 @@ __device__ __forceinline__ SegList make_segments(const FsaBwdSched& s, bool caus
   }
   return l;
 }
-__device__ __forceinline__ void seg_at(const SegList& l, int j, int* m, int* mode) {
-  *m = 0;
-  *mode = FSA_MASK_NONE;
+// Walks the query tiles of a SegList in order without searching: (m, mode) of the current step.
+struct SegIter {
+  int seg, m, mode;
+};
+__device__ __forceinline__ SegIter seg_begin(const SegList& l) {
+  SegIter s;
+  s.seg = 0;
+  s.m = l.n > 0 ? l.beg[0] : 0;
+  s.mode = l.n > 0 ? l.mode[0] : FSA_MASK_NONE;
+  return s;
+}
+__device__ __forceinline__ void seg_next(const SegList& l, SegIter& s) {
+  s.m++;
+  bool wrap = false;
 #pragma unroll
-  for (int i = 0; i < 6; ++i) {
-    if (i < l.n) {
-      const int len = l.end[i] - l.beg[i];
-      if (j >= 0 && j < len) {
-        *m = l.beg[i] + j;
-        *mode = l.mode[i];
+  for (int i = 0; i < 6; ++i)
+    if (i == s.seg && i < l.n && s.m >= l.end[i]) wrap = true;
+  if (wrap) {
+    s.seg++;
+#pragma unroll
+    for (int i = 1; i < 6; ++i)
+      if (i == s.seg && i < l.n) {
+        s.m = l.beg[i];
+        s.mode = l.mode[i];
       }
-      j -= len;
-    }
   }
 }
 
@@ -187,8 +223,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
   if (tid == 0) {
     mbar_init(&bars->kv_full, 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&bars->qdo_full[s], 1);
-      mbar_init(&bars->qdo_empty[s], 1);
+      mbar_init(&bars->q_full[s], 1);
+      mbar_init(&bars->q_empty[s], 1);
     }
     mbar_init(&bars->s_full, 1);
     mbar_init(&bars->p_full, 8);
@@ -196,7 +232,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
     mbar_init(&bars->ds_full, 8);
     mbar_init(&bars->dq_full, 1);
     mbar_init(&bars->dq_empty, 8);
-    mbar_init(&bars->ds_free, 8);
+    mbar_init(&bars->do_full, 1);
+    mbar_init(&bars->do_empty, 1);
     mbar_init(&bars->vote_sync, 8);
     mbar_init(&bars->acc_full, 1);
     mbar_init(&bars->dd_sync, 4);
@@ -228,27 +265,33 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
           tma_load_4d(smem + SM::kK + (d / 64) * (TN * 128), &p.map_k, &bars->kv_full, d, hkv, off_k + n_block * TN, bk);
           tma_load_4d(smem + SM::kV + (d / 64) * (TN * 128), &p.map_v, &bars->kv_full, d, hkv, off_k + n_block * TN, bk);
         }
+        // Q (with the row statistics of its tile) runs two steps ahead in a 2-stage ring; dO has one
+        // buffer and is reloaded as soon as dV of the previous step has consumed it.
         bool ok = true;
+        SegIter si_q = seg_begin(segs);
         for (int it = 0; it < N_IT && ok; ++it) {
           const int st = it & 1, use = it >> 1;
-          if (use > 0) ok = mbar_wait(&bars->qdo_empty[st], (use - 1) & 1, abort_flag);
-          if (!ok) break;
           const int g = it / NT;
-          int m, mode;
-          seg_at(segs, it - g * NT, &m, &mode);
+          if (it == g * NT) si_q = seg_begin(segs);
+          const int m = si_q.m;
+          seg_next(segs, si_q);
           const int head = hkv * p.G + g;
-          mbar_arrive_expect_tx(&bars->qdo_full[st], 2 * SM::kTile + 1024 + (KIND == KIND_GATED ? 256 : 0));
-          for (int d = 0; d < HD; d += 64) {
-            tma_load_4d(smem + SM::kQ + st * SM::kTile + (d / 64) * (TM * 128), &p.map_q, &bars->qdo_full[st], d, head,
+          if (use > 0) ok = mbar_wait(&bars->q_empty[st], (use - 1) & 1, abort_flag);
+          if (!ok) break;
+          mbar_arrive_expect_tx(&bars->q_full[st], SM::kTile + 1024 + (KIND == KIND_GATED ? 256 : 0));
+          for (int d = 0; d < HD; d += 64)
+            tma_load_4d(smem + SM::kQ + st * SM::kTile + (d / 64) * (TM * 128), &p.map_q, &bars->q_full[st], d, head,
                         off_q + m * TM, bq);
-            tma_load_4d(smem + SM::kDO + st * SM::kTile + (d / 64) * (TM * 128), &p.map_do, &bars->qdo_full[st], d,
-                        head, off_q + m * TM, bq);
-          }
           const long long wrow = (long long)head * p.ws_sh + pad_off + (long long)m * TM;
-          bulk_load_1d(s_lse + st * 128, p.lse2_ws + wrow, 512, &bars->qdo_full[st]);
-          bulk_load_1d(s_dps + st * 128, p.dpsum_ws + wrow, 512, &bars->qdo_full[st]);
+          bulk_load_1d(s_lse + st * 128, p.lse2_ws + wrow, 512, &bars->q_full[st]);
+          bulk_load_1d(s_dps + st * 128, p.dpsum_ws + wrow, 512, &bars->q_full[st]);
           if (KIND == KIND_GATED)
-            bulk_load_1d(s_alpha + st * 128, reinterpret_cast<const T*>(p.alpha_ws) + wrow, 256, &bars->qdo_full[st]);
+            bulk_load_1d(s_alpha + st * 128, reinterpret_cast<const T*>(p.alpha_ws) + wrow, 256, &bars->q_full[st]);
+          if (it > 0) ok = mbar_wait(&bars->do_empty, (it - 1) & 1, abort_flag);
+          if (!ok) break;
+          mbar_arrive_expect_tx(&bars->do_full, SM::kTile);
+          for (int d = 0; d < HD; d += 64)
+            tma_load_4d(smem + SM::kDO + (d / 64) * (TM * 128), &p.map_do, &bars->do_full, d, head, off_q + m * TM, bq);
         }
       }
       __syncwarp();
@@ -275,20 +318,26 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       };
       if (ok) {
         ok = mbar_wait(&bars->kv_full, 0, abort_flag);
-        ok = ok && mbar_wait(&bars->qdo_full[0], 0, abort_flag);
+        ok = ok && mbar_wait(&bars->q_full[0], 0, abort_flag);
         tc_fence_after();
         if (ok) issue_st(0);
       }
       int n_live = 0;  // steps that were not skipped so far
       bool acc_started = false;
+      FSA_TICK_DECL;
       for (int it = 0; it < N_IT && ok; ++it) {
         const int st = it & 1;
+        FSA_TICK(15);
         ok = mbar_wait(&bars->p_full, it & 1, abort_flag);
+        FSA_TICK(10);
         if (!ok) break;
         const bool skip = (KIND != KIND_DENSE) && bars->skip_flag[it & 1];
+        ok = mbar_wait(&bars->do_full, it & 1, abort_flag);  // every phase is observed, skipped step or not
+        if (!ok) break;
         tc_fence_after();
         if (!skip) {
           if (n_live > 0) ok = mbar_wait(&bars->dq_empty, (n_live - 1) & 1, abort_flag);
+          FSA_TICK(11);
           if (!ok) break;
           tc_fence_after();
           if (lane == 0) {
@@ -296,27 +345,33 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
             for (int kk = 0; kk < KK_D; ++kk) {
               const uint32_t koff = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
               umma_ss(tmem_base + TMEM_DP, umma_smem_desc(sV + koff, 16, 1024),
-                      umma_smem_desc(sDO + st * SM::kTile + koff, 16, 1024), idesc_s, kk > 0);
+                      umma_smem_desc(sDO + koff, 16, 1024), idesc_s, kk > 0);
             }
             umma_commit(&bars->dp_full);
 #pragma unroll
             for (int kk = 0; kk < KK_M; ++kk) {
               const uint32_t a_col = (kk < 4) ? kk * 8 : 96 + (kk - 4) * 8;
               umma_ts(tmem_base + TMEM_DV, tmem_base + TMEM_S + a_col,
-                      umma_smem_desc(sDO + st * SM::kTile + kk * 2048, TM * 128, 1024), idesc_dv,
+                      umma_smem_desc(sDO + kk * 2048, TM * 128, 1024), idesc_dv,
                       (kk > 0 || acc_started) ? 1u : 0u);
             }
           }
           __syncwarp();
         }
+        if (lane == 0) umma_commit(&bars->do_empty);  // dO may be overwritten once dV has read it
+        __syncwarp();
         if (it + 1 < N_IT) {
-          ok = mbar_wait(&bars->qdo_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_flag);
+          FSA_TICK(15);
+          ok = mbar_wait(&bars->q_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_flag);
+          FSA_TICK(12);
           if (!ok) break;
           tc_fence_after();
           issue_st((it + 1) & 1);
         }
         if (!skip) {
+          FSA_TICK(15);
           ok = mbar_wait(&bars->ds_full, n_live & 1, abort_flag);
+          FSA_TICK(13);
           if (!ok) break;
           tc_fence_after();
           if (lane == 0) {
@@ -337,11 +392,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
           acc_started = true;
           n_live++;
         }
-        if (lane == 0) umma_commit(&bars->qdo_empty[st]);
+        if (lane == 0) umma_commit(&bars->q_empty[st]);
         __syncwarp();
       }
       if (lane == 0) umma_commit(&bars->acc_full);
       __syncwarp();
+      FSA_TICK(15);
+      FSA_TICK_FLUSH;
     }
   } else {
     // =============================== compute warps ===========================================
@@ -356,12 +413,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
     const int off = sk - sq;
     const float c = p.scale_log2;
     uint8_t* ds_buf = smem + SM::kDS;
-    uint8_t* stage = ds_buf + cw * 4096;
+    uint8_t* stage = smem + SM::kStage + cw * 4096;
 
+    FSA_TICK_DECL;
     bool ok = !*abort_flag;
     uint32_t pk[32];  // P^T of the step in flight, packed pairs (this thread's 64 query columns)
-    int n_live = 0, n_staged = 0;
+    int n_live = 0;
     bool skip_cur = false;
+    // dQ leaves in 32-column chunks through this warp's 4 KB staging buffer; a second chunk waits in
+    // registers until the TMA engine has read the first one out of the buffer
+    constexpr int NCH = HALF / 32;
+    uint32_t dq_hold[32];
+    bool dq_pending = false;
+    int dq_row = 0, dq_head = 0;
+    int m_cur = 0, g_cur = 0;  // query tile / head of the step whose dS and dQ are being handled
 
     // ---- gated: delta of this key row, its extremes over the key tile, running gate bound --------
     // (flash_sparse_attn/ops/triton/flash_gated_bwd.py:406-421; keys past the sequence read as zero)
@@ -433,26 +498,36 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
     };
 
     // ---- P step: scores -> probabilities (and the skip vote) ------------------------------------
-    auto p_step = [&](int it) -> bool {  // returns the skip decision
+    SegIter si_p = seg_begin(segs);
+    int m_p = 0, g_p = 0, it_head = 0;  // query tile and head (within the group) of the step p_step just handled
+    auto p_step = [&](int it) -> bool {  // returns the skip decision; steps are visited in order
       const int st = it & 1, par = it & 1;
-      const int g = it / NT;
-      int m, mode;
-      seg_at(segs, it - g * NT, &m, &mode);
+      if (it - it_head == NT) {
+        it_head = it;
+        g_p++;
+        si_p = seg_begin(segs);
+      }
+      const int g = g_p;
+      const int m = si_p.m, mode = si_p.mode;
+      m_p = m;
+      seg_next(segs, si_p);
+      FSA_TICK(9);
       if (!mbar_wait(&bars->s_full, par, abort_flag)) {
         ok = false;
         return true;
       }
       // lse2 / dpsum arrived with the Q tile; observing the barrier makes them visible here
-      if (!mbar_wait(&bars->qdo_full[st], (it >> 1) & 1, abort_flag)) {
+      if (!mbar_wait(&bars->q_full[st], (it >> 1) & 1, abort_flag)) {
         ok = false;
         return true;
       }
+      FSA_TICK(0);
       tc_fence_after();
       bool gate_skip = false;
       if (KIND == KIND_GATED) {
         // bound of the gate over the tile against a running maximum that restarts with every query head
         // (flash_gated_bwd.py:61-79, activations.py:265-299, seqlen_info.py:156-191)
-        if (it == g * NT) gate_max = -INFINITY;
+        if (it == it_head) gate_max = -INFINITY;
         const uint2 av = *reinterpret_cast<const uint2*>(s_alpha + st * 128 + lane * 4);
         float a4[4];
         unpack16(av.x, a4[0], a4[1]);
@@ -505,13 +580,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
           }
         }
       }
+      const float2 c2 = make_float2(c, c);
 #pragma unroll
       for (int i = 0; i < 64; i += 4) {
-        const float4 l = lse4[i >> 2];
-        x[i] = fmaf(__uint_as_float(sr[i]), c, -l.x);
-        x[i + 1] = fmaf(__uint_as_float(sr[i + 1]), c, -l.y);
-        x[i + 2] = fmaf(__uint_as_float(sr[i + 2]), c, -l.z);
-        x[i + 3] = fmaf(__uint_as_float(sr[i + 3]), c, -l.w);
+        const float4 l = lse4[i >> 2];  // minus lse2
+        const float2 xa = fma2(make_float2(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])), c2, make_float2(l.x, l.y));
+        const float2 xb =
+            fma2(make_float2(__uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3])), c2, make_float2(l.z, l.w));
+        x[i] = xa.x;
+        x[i + 1] = xa.y;
+        x[i + 2] = xb.x;
+        x[i + 3] = xb.y;
       }
       if (masked) {
 #pragma unroll
@@ -522,18 +601,34 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       if (KIND != KIND_DENSE) {
         // skip iff max over the tile of (log2 p - thr_log2[q]) < 0 (flash_sparse_bwd.py:61-79);
         // thresholds of this group's 64 query columns live two per lane and travel by shuffle
-        const int q_a = m * TM + wg * 64 + lane, q_b = q_a + 32;
-        const float vis_a = causal ? float(q_a + off + 1) : float(sk);
-        const float vis_b = causal ? float(q_b + off + 1) : float(sk);
-        const float thr_a = log2f(fmaxf(fminf(p.softmax_thr / vis_a, 1.0f), 0.0f));
-        const float thr_b = log2f(fmaxf(fminf(p.softmax_thr / vis_b, 1.0f), 0.0f));
-        bool want = false, drop = false;
+        // The threshold falls as the query index grows (causal) or is one number (otherwise): the row
+        // maximum against the thresholds of the group's first and last column settles most votes at
+        // once; only a warp with a lane in between compares entry by entry.
+        const int q_first = m * TM + wg * 64;
+        const float vis_first = causal ? float(q_first + off + 1) : float(sk);
+        const float vis_last = causal ? float(q_first + 63 + off + 1) : float(sk);
+        const float thr_hi = log2f(fmaxf(fminf(p.softmax_thr / vis_first, 1.0f), 0.0f));
+        const float thr_lo = log2f(fmaxf(fminf(p.softmax_thr / vis_last, 1.0f), 0.0f));
+        float mx = fmaxf(x[0], x[1]);
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          const float t = __shfl_sync(0xffffffffu, i < 32 ? thr_a : thr_b, i & 31);
-          const float v = x[i] - t;
-          want |= (v >= 0.0f);
-          drop |= (v < 0.0f);
+        for (int i = 2; i < 64; i += 2) mx = max3(mx, x[i], x[i + 1]);
+        bool want = mx >= thr_hi, drop = mx < thr_lo;
+        const bool unsure = (vis_first < 1.0f) || (!want && !drop);
+        if (__any_sync(0xffffffffu, unsure)) {
+          const int q_a = q_first + lane, q_b = q_a + 32;
+          const float vis_a = causal ? float(q_a + off + 1) : float(sk);
+          const float vis_b = causal ? float(q_b + off + 1) : float(sk);
+          const float thr_a = log2f(fmaxf(fminf(p.softmax_thr / vis_a, 1.0f), 0.0f));
+          const float thr_b = log2f(fmaxf(fminf(p.softmax_thr / vis_b, 1.0f), 0.0f));
+          want = false;
+          drop = false;
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const float t = __shfl_sync(0xffffffffu, i < 32 ? thr_a : thr_b, i & 31);
+            const float v = x[i] - t;
+            want |= (v >= 0.0f);
+            drop |= (v < 0.0f);
+          }
         }
         if (KIND == KIND_GATED && gate_skip) {
           want = false;
@@ -545,10 +640,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
           bars->vote_any[par][cw] = (w_any ? 1 : 0) | (d_any ? 2 : 0);
           mbar_arrive(&bars->vote_sync);
         }
+        FSA_TICK(1);
         if (!mbar_wait(&bars->vote_sync, par, abort_flag)) {
           ok = false;
           return true;
         }
+        FSA_TICK(2);
         int v = 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) v |= bars->vote_any[par][i];
@@ -574,61 +671,41 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_full);
+      FSA_TICK(1);
       return skip;
     };
 
     // ---- dS step: dS^T = P^T o (dP^T - dpsum) into shared memory ------------------------------------
     auto ds_step = [&](int it) {
       const int st = it & 1;
+      FSA_TICK(9);
       if (!mbar_wait(&bars->dp_full, n_live & 1, abort_flag)) {
         ok = false;
         return;
       }
+      FSA_TICK(3);
       tc_fence_after();
       uint32_t dr[64];
       tmem_ld32(tmem_base + lane_addr + TMEM_DP + wg * 64, &dr[0]);
       tmem_ld32(tmem_base + lane_addr + TMEM_DP + wg * 64 + 32, &dr[32]);
       tmem_ld_wait();
-      // the dS buffer doubles as dQ staging: all warps must be done with the previous staging reads
-      if (n_staged > 0 && !mbar_wait(&bars->ds_free, (n_staged - 1) & 1, abort_flag)) {
-        ok = false;
-        return;
-      }
       const float4* dps4 = reinterpret_cast<const float4*>(s_dps + st * 128 + wg * 64);
       const uint4* al4 = reinterpret_cast<const uint4*>(s_alpha + st * 128 + wg * 64);
       uint8_t* slab = ds_buf + wg * (128 * 128);
       float da_r[8];  // gated: per chunk, one column's dalpha summed over 8 lanes
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
-        const float4 d0 = dps4[ch * 2], d1 = dps4[ch * 2 + 1];
-        const float dps[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+        const float4 d0 = dps4[ch * 2], d1 = dps4[ch * 2 + 1];  // minus dpsum
+        const float nd[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
         uint32_t o[4];
 #pragma unroll
         for (int j = 0; j < 8; j += 2) {
-          const uint32_t pp = pk[(ch * 8 + j) >> 1];
-          float p0, p1;
-          if (IS_BF16) {
-            p0 = __uint_as_float(pp << 16);
-            p1 = __uint_as_float(pp & 0xffff0000u);
-          } else {
-            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pp));
-            p0 = f.x;
-            p1 = f.y;
-          }
-          // both factors are rounded to the 16-bit type before the product, like the reference
-          const uint32_t tt = pack2<T>(__uint_as_float(dr[ch * 8 + j]) - dps[j],
-                                       __uint_as_float(dr[ch * 8 + j + 1]) - dps[j + 1]);
-          float t0, t1;
-          if (IS_BF16) {
-            t0 = __uint_as_float(tt << 16);
-            t1 = __uint_as_float(tt & 0xffff0000u);
-          } else {
-            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&tt));
-            t0 = f.x;
-            t1 = f.y;
-          }
-          // p == 0 marks masked entries: keep them exactly zero whatever sits in the other factor
-          o[j >> 1] = pack2<T>(p0 == 0.f ? 0.f : p0 * t0, p1 == 0.f ? 0.f : p1 * t1);
+          // both factors are rounded to the 16-bit type and so is their product, like the reference
+          // (flash_sparse_bwd.py:93-96). Masked entries carry p = 0 and the other factor is always finite
+          // (out-of-range rows of V and dO load as zeros, padding rows of dpsum are zero), so they stay 0.
+          const float2 t = add2(make_float2(__uint_as_float(dr[ch * 8 + j]), __uint_as_float(dr[ch * 8 + j + 1])),
+                                make_float2(nd[j], nd[j + 1]));
+          o[j >> 1] = hmul2<T>(pk[(ch * 8 + j) >> 1], pack2_sat<T>(t.x, t.y));
         }
         *reinterpret_cast<uint4*>(slab + sw128_offset(row, ch)) = make_uint4(o[0], o[1], o[2], o[3]);
         if (KIND == KIND_GATED) {
@@ -675,9 +752,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
 #pragma unroll
         for (int j = 0; j < 2; ++j)
           z[j] = (b0 ? u[j + 2] : u[j]) + __shfl_xor_sync(0xffffffffu, b0 ? u[j] : u[j + 2], 1);
-        const int g = it / NT;
-        int m, mode;
-        seg_at(segs, it - g * NT, &m, &mode);
+        const int g = g_cur, m = m_cur;
         const int chunk0 = (b1 ? 4 : 0) + (b0 ? 2 : 0);
         const int cin = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
         float* dst = p.da_accum + (long long)(hkv * p.G + g) * p.ws_sh + pad_off + (long long)m * TM + wg * 64 + cin;
@@ -688,56 +763,75 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->ds_full);
+      FSA_TICK(5);
     };
 
-    // ---- dQ step: TMEM -> shared staging -> TMA reduce-add into the fp32 accumulator ----------------
+    // ---- dQ step: TMEM -> registers -> shared staging -> TMA reduce-add into the fp32 accumulator -------
+    // The path from an SM to L2 moves about 21 bytes per clock, so the 64 KB of a dQ tile take as long as
+    // the five MMAs of a step: nobody waits for it. The first 32 columns go out at once, the second 32
+    // stay in registers until the next phase has passed (dq_flush) and the engine has drained the buffer.
+    auto stage_store = [&](const uint32_t* r) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+            make_uint4(r[j * 4], r[j * 4 + 1], r[j * 4 + 2], r[j * 4 + 3]);
+      fence_proxy_async_smem();
+      __syncwarp();
+    };
+    auto dq_flush = [&]() {
+      if (NCH > 1 && dq_pending) {
+        FSA_TICK(9);
+        if (lane == 0) bulk_wait_read0();
+        __syncwarp();
+        FSA_TICK(8);
+        stage_store(dq_hold);
+        if (lane == 0) {
+          tma_reduce_add_3d(&p.map_dq, stage, wg * HALF + 32, dq_row, dq_head);
+          bulk_commit();
+        }
+        dq_pending = false;
+        FSA_TICK(7);
+      }
+    };
     auto dq_step = [&](int it) {
-      const int g = it / NT;
-      int m, mode;
-      seg_at(segs, it - g * NT, &m, &mode);
-      const int head = hkv * p.G + g;
+      FSA_TICK(9);
       if (!mbar_wait(&bars->dq_full, n_live & 1, abort_flag)) {
         ok = false;
         return;
       }
+      FSA_TICK(6);
       tc_fence_after();
-#pragma unroll
-      for (int ch = 0; ch < HALF / 32; ++ch) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + lane_addr + TMEM_DP + wg * HALF + ch * 32, r);
-        tmem_ld_wait();
-        if (ch == HALF / 32 - 1) {
-          // all of this warp's dQ values are in registers: the TMEM block may be overwritten
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bars->dq_empty);
-        }
-        if (ch > 0) {
-          if (lane == 0) bulk_wait_read0();
-          __syncwarp();
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) =
-              make_uint4(r[j * 4], r[j * 4 + 1], r[j * 4 + 2], r[j * 4 + 3]);
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          tma_reduce_add_3d(&p.map_dq, stage, wg * HALF + ch * 32, (int)(pad_off + (long long)m * TM + wq * 32), head);
-          bulk_commit();
-        }
-      }
-      if (lane == 0) {
-        bulk_wait_read0();
-        mbar_arrive(&bars->ds_free);
-      }
+      uint32_t r[32];
+      tmem_ld32(tmem_base + lane_addr + TMEM_DP + wg * HALF, r);
+      if (NCH > 1) tmem_ld32(tmem_base + lane_addr + TMEM_DP + wg * HALF + 32, dq_hold);
+      tmem_ld_wait();
+      // all of this warp's dQ values are in registers: the TMEM block may be overwritten
+      tc_fence_before();
       __syncwarp();
-      n_staged++;
+      if (lane == 0) mbar_arrive(&bars->dq_empty);
+      FSA_TICK(7);
+      if (lane == 0) bulk_wait_read0();  // the buffer went to the engine a whole phase ago
+      __syncwarp();
+      FSA_TICK(14);
+      stage_store(r);
+      dq_row = (int)(pad_off + (long long)m_cur * TM + wq * 32);
+      dq_head = hkv * p.G + g_cur;
+      if (lane == 0) {
+        tma_reduce_add_3d(&p.map_dq, stage, wg * HALF, dq_row, dq_head);
+        bulk_commit();
+      }
+      dq_pending = NCH > 1;
+      FSA_TICK(7);
     };
 
-    if (ok && N_IT > 0) skip_cur = p_step(0);
+    if (ok && N_IT > 0) {
+      skip_cur = p_step(0);
+      m_cur = m_p;
+      g_cur = g_p;
+    }
     for (int it = 0; it < N_IT && ok; ++it) {
       if (!skip_cur) ds_step(it);
+      dq_flush();
       bool skip_next = false;
       if (ok && it + 1 < N_IT) skip_next = p_step(it + 1);
       if (ok && !skip_cur) {
@@ -745,8 +839,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         n_live++;
       }
       skip_cur = skip_next;
+      m_cur = m_p;
+      g_cur = g_p;
     }
+    dq_flush();
 
+    FSA_TICK(9);
+    FSA_TICK_FLUSH;
     // ---- epilogue: dK (scaled) and dV of this key tile ------------------------------------------------
     if (ok) {
       bool have = false;
@@ -849,6 +948,17 @@ cudaError_t launch_one(const BwdKernelParams& p, cudaStream_t stream) {
 }
 
 }  // namespace
+
+#ifdef FSA_PHASE_TIMING
+extern "C" void fsa_debug_bwd_ticks(unsigned long long* out16, int reset) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out16, g_bwd_ticks, sizeof(unsigned long long) * 16);
+  if (reset) {
+    unsigned long long z[16] = {0};
+    cudaMemcpyToSymbol(g_bwd_ticks, z, sizeof(z));
+  }
+}
+#endif
 
 cudaError_t launch_bwd(const BwdKernelParams& p, int kind, int dtype, int head_dim, cudaStream_t stream) {
 #define FSA_BWD_CASE(HD_, T_, DT_)                                               \

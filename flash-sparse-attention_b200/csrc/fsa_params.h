@@ -54,8 +54,8 @@ struct alignas(64) FwdKernelParams {
 
 struct alignas(64) BwdKernelParams {
   CUtensorMap map_q, map_k, map_v, map_do, map_dq;
-  const float* lse2_ws;   // [Hq, ws_sh] base-2 log-sum-exp, tile-padded rows
-  const float* dpsum_ws;  // [Hq, ws_sh] rowsum(O * dO)
+  const float* lse2_ws;   // [Hq, ws_sh] minus the base-2 log-sum-exp, tile-padded rows
+  const float* dpsum_ws;  // [Hq, ws_sh] minus rowsum(O * dO); zero at padding rows
   void* dk_out;           // T* [rows_k, Hkv, D] (strided) or float partial [splits, ...] when F_SPLIT
   void* dv_out;
   const int* cu_q;

@@ -317,6 +317,35 @@ __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
   return r;
 }
 
+// Conversion that clamps to the largest finite value (matters for fp16 only), and the packed product
+// rounded once to the 16-bit type.
+template <typename T>
+__device__ __forceinline__ uint32_t pack2_sat(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2_sat<__nv_bfloat16>(float lo, float hi) {
+  return pack2<__nv_bfloat16>(lo, hi);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2_sat<__half>(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+template <typename T>
+__device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b);
+template <>
+__device__ __forceinline__ uint32_t hmul2<__nv_bfloat16>(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+template <>
+__device__ __forceinline__ uint32_t hmul2<__half>(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
 // Byte offset of 16-byte chunk `chunk` (0..7) of row `row` inside a [rows x 128 B] tile with the
 // 128-byte swizzle (tile base 1024-byte aligned).
 __device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t chunk) {
