@@ -32,8 +32,8 @@
 // Development aid: with -DFSA_PHASE_TIMING one lane of a compute warp and of the MMA warp add up the
 // clock cycles they spend in each wait / phase; fsa_debug_bwd_ticks() reads the totals over all CTAs.
 #ifdef FSA_PHASE_TIMING
-__device__ unsigned long long g_bwd_ticks[16];
-#define FSA_TICK_DECL long long tk_[16] = {0}; long long tk_t_ = clock64(); const bool tk_on_ = (lane == 0) && (warp == 0 || warp == 9)
+__device__ unsigned long long g_bwd_ticks[24];
+#define FSA_TICK_DECL long long tk_[24] = {0}; long long tk_t_ = clock64(); const bool tk_on_ = (lane == 0) && (warp == 0 || warp == 9)
 #define FSA_TICK(i)                          \
   do {                                       \
     const long long now_ = clock64();        \
@@ -43,7 +43,7 @@ __device__ unsigned long long g_bwd_ticks[16];
 #define FSA_TICK_FLUSH                                                                      \
   do {                                                                                      \
     if (tk_on_)                                                                             \
-      for (int i_ = 0; i_ < 16; ++i_)                                                       \
+      for (int i_ = 0; i_ < 24; ++i_)                                                       \
         if (tk_[i_]) atomicAdd(&g_bwd_ticks[i_], (unsigned long long)tk_[i_]);               \
   } while (0)
 #else
@@ -660,6 +660,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
           __threadfence_block();
         }
       }
+      FSA_TICK(18);
       if (!skip) {
 #pragma unroll
         for (int i = 0; i < 64; i += 2) pk[i >> 1] = pack2<T>(ex2_approx(x[i]), ex2_approx(x[i + 1]));
@@ -689,6 +690,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       tmem_ld32(tmem_base + lane_addr + TMEM_DP + wg * 64, &dr[0]);
       tmem_ld32(tmem_base + lane_addr + TMEM_DP + wg * 64 + 32, &dr[32]);
       tmem_ld_wait();
+      FSA_TICK(19);
       const float4* dps4 = reinterpret_cast<const float4*>(s_dps + st * 128 + wg * 64);
       const uint4* al4 = reinterpret_cast<const uint4*>(s_alpha + st * 128 + wg * 64);
       uint8_t* slab = ds_buf + wg * (128 * 128);
@@ -785,12 +787,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         __syncwarp();
         FSA_TICK(8);
         stage_store(dq_hold);
+        FSA_TICK(16);
         if (lane == 0) {
           tma_reduce_add_3d(&p.map_dq, stage, wg * HALF + 32, dq_row, dq_head);
           bulk_commit();
         }
         dq_pending = false;
-        FSA_TICK(7);
+        FSA_TICK(17);
       }
     };
     auto dq_step = [&](int it) {
@@ -814,6 +817,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       __syncwarp();
       FSA_TICK(14);
       stage_store(r);
+      FSA_TICK(16);
       dq_row = (int)(pad_off + (long long)m_cur * TM + wq * 32);
       dq_head = hkv * p.G + g_cur;
       if (lane == 0) {
@@ -821,7 +825,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         bulk_commit();
       }
       dq_pending = NCH > 1;
-      FSA_TICK(7);
+      FSA_TICK(17);
     };
 
     if (ok && N_IT > 0) {
@@ -952,9 +956,9 @@ cudaError_t launch_one(const BwdKernelParams& p, cudaStream_t stream) {
 #ifdef FSA_PHASE_TIMING
 extern "C" void fsa_debug_bwd_ticks(unsigned long long* out16, int reset) {
   cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out16, g_bwd_ticks, sizeof(unsigned long long) * 16);
+  cudaMemcpyFromSymbol(out16, g_bwd_ticks, sizeof(unsigned long long) * 24);
   if (reset) {
-    unsigned long long z[16] = {0};
+    unsigned long long z[24] = {0};
     cudaMemcpyToSymbol(g_bwd_ticks, z, sizeof(z));
   }
 }

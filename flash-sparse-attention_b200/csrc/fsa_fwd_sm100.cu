@@ -281,7 +281,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
         }
       };
       int t = 0;
-      int cnt[2] = {0, 0};
       bool ok = true;
       int n = first_tile();
       if (n >= 0) {
@@ -296,19 +295,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
           if (!ok) break;
           load_kv(&p.map_k, smem + SM::kK + s * SM::kTileBytes, &bars->k_full[s], n_next);
         }
-        bool need_v = false;
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          if (fsa_fwd_tile_mode(sched[q], n, causal, local) < 0) continue;
-          if (KIND != KIND_DENSE) {
-            ok = ok && mbar_wait(&bars->vote[q], cnt[q] & 1, abort_flag);
-            if (ok && !bars->skip_flag[q][cnt[q] & 1]) need_v = true;
-          } else {
-            need_v = true;
-          }
-          cnt[q]++;
-        }
-        if (!ok) break;
+        // V is prefetched like K, before the softmax groups have voted on the tile: waiting for the vote
+        // would put a full load latency between every S tile and its P V product, and in this
+        // tensor-bound kernel a V tile that ends up unused only costs an L2 read. (The reference skips
+        // the load, flash_sparse_fwd.py:60-88; it matters there because its tiles are loaded by the same
+        // warps that compute.) A skipped tile still skips the softmax work and the P V product.
+        const bool need_v = true;
         {
           const int s = t % VSTAGES;
           const int use = t / VSTAGES;
