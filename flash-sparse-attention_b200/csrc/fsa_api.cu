@@ -352,6 +352,9 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
   if ((a->tile_m && a->tile_m != 128) || (a->tile_n && a->tile_n != 128)) return FSA_ERR_UNSUPPORTED;
   if ((a->flags & FSA_F_LOCAL) && !a->window_sizes) return FSA_ERR_INVALID_ARG;
   if (a->dk_stride_b % 8 || a->dk_stride_s % 8 || a->dk_stride_h % 8) return FSA_ERR_INVALID_ARG;
+  if (a->o_stride_b % 8 || a->o_stride_s % 8 || a->o_stride_h % 8 || a->do_stride_b % 8 || a->do_stride_s % 8 ||
+      a->do_stride_h % 8 || a->dq_stride_b % 8 || a->dq_stride_s % 8 || a->dq_stride_h % 8)
+    return FSA_ERR_INVALID_ARG;  // rows are moved in 16-byte pieces
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   const bool varlen_q = a->cu_seqlens_q != nullptr, varlen_k = a->cu_seqlens_k != nullptr;
   const int ns = (a->flags & FSA_F_SPLIT) ? a->num_splits : 1;

@@ -80,85 +80,93 @@ __device__ __forceinline__ long long padded_row(int varlen, const int* cu_q, int
   return (long long)b * ((sq_static + 127) / 128) * 128 + q;
 }
 
-// One warp per (query row, head). flash_sparse_attn/ops/triton/flash_bwd_preprocess.py:170-195.
+// Locates one (query row, head) item: batch, position inside the sequence, row in the packed tensor.
+struct RowPos {
+  int b, q, h;
+  long long tok;
+};
+__device__ __forceinline__ RowPos locate_row(long long item, int heads, int varlen, const int* cu_q, int B, int sq) {
+  RowPos r;
+  r.h = (int)(item % heads);
+  const long long row = item / heads;
+  if (varlen) {
+    // B is small: linear scan over the sequence starts
+    int b = 0;
+    while (b + 1 < B && cu_q[b + 1] <= row) ++b;
+    r.b = b;
+    r.q = (int)(row - cu_q[b]);
+    r.tok = row;
+  } else {
+    r.b = (int)(row / sq);
+    r.q = (int)(row - (long long)r.b * sq);
+    r.tok = r.q;
+  }
+  return r;
+}
+
+// head_dim / 8 lanes per (query row, head), 16-byte loads. flash_sparse_attn/ops/triton/flash_bwd_preprocess.py:170-195.
 template <typename T>
 __global__ void __launch_bounds__(256) bwd_pre_kernel(BwdPreParams p) {
-  const int lane = threadIdx.x & 31;
-  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lpr = p.head_dim >> 3;  // lanes per row (8 or 16)
+  const int lane = threadIdx.x & 31, sub = lane % lpr;
+  const long long item = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (32 / lpr) + lane / lpr;
   const long long rows = p.varlen ? p.total_q : (long long)p.B * p.sq;
-  if (item >= rows * p.heads) return;
-  const int h = (int)(item % p.heads);
-  const long long row = item / p.heads;
-  int b, q;
-  long long tok;
-  if (p.varlen) {
-    // locate the sequence of this packed row (B is small: linear scan)
-    b = 0;
-    while (b + 1 < p.B && p.cu_q[b + 1] <= row) ++b;
-    q = (int)(row - p.cu_q[b]);
-    tok = row;
-  } else {
-    b = (int)(row / p.sq);
-    q = (int)(row - (long long)b * p.sq);
-    tok = q;
-  }
-  const T* o = reinterpret_cast<const T*>(p.out) + (p.varlen ? 0 : (long long)b * p.o_sb) + tok * p.o_sm + (long long)h * p.o_sh;
-  const T* d = reinterpret_cast<const T*>(p.dout) + (p.varlen ? 0 : (long long)b * p.do_sb) + tok * p.do_sm + (long long)h * p.do_sh;
+  const bool live = item < rows * p.heads;
   float acc = 0.f;
-  for (int i = lane * 2; i < p.head_dim; i += 64) {
-    const float2 a = unpack2<T>(*reinterpret_cast<const uint32_t*>(o + i));
-    const float2 g = unpack2<T>(*reinterpret_cast<const uint32_t*>(d + i));
-    acc += a.x * g.x + a.y * g.y;
-  }
+  RowPos r = {0, 0, 0, 0};
+  if (live) {
+    r = locate_row(item, p.heads, p.varlen, p.cu_q, p.B, p.sq);
+    const T* o = reinterpret_cast<const T*>(p.out) + (p.varlen ? 0 : (long long)r.b * p.o_sb) + r.tok * p.o_sm +
+                 (long long)r.h * p.o_sh + sub * 8;
+    const T* d = reinterpret_cast<const T*>(p.dout) + (p.varlen ? 0 : (long long)r.b * p.do_sb) + r.tok * p.do_sm +
+                 (long long)r.h * p.do_sh + sub * 8;
+    const uint4 a = *reinterpret_cast<const uint4*>(o);
+    const uint4 g = *reinterpret_cast<const uint4*>(d);
+    const uint32_t av[4] = {a.x, a.y, a.z, a.w}, gv[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
-  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-  if (lane == 0) {
-    const float lse = p.lse[(p.varlen ? 0 : (long long)b * p.l_sb) + (long long)h * p.l_sh + tok];
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = unpack2<T>(av[i]), y = unpack2<T>(gv[i]);
+      acc += x.x * y.x + x.y * y.y;
+    }
+  }
+  for (int s = lpr >> 1; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (live && sub == 0) {
+    const float lse = p.lse[(p.varlen ? 0 : (long long)r.b * p.l_sb) + (long long)r.h * p.l_sh + r.tok];
     float l2 = (lse == lse) ? lse * 1.4426950408889634f : 1e6f;
     l2 = fmaxf(l2, -1e6f);
-    const long long w = (long long)h * p.ws_sh + padded_row(p.varlen, p.cu_q, b, p.sq, q);
+    const long long w = (long long)r.h * p.ws_sh + padded_row(p.varlen, p.cu_q, r.b, p.sq, r.q);
     // both are stored negated: the main kernel then needs one packed fma / add per pair of entries
     p.lse2_ws[w] = -l2;
     p.dpsum_ws[w] = -acc;
     if (p.alpha_ws)
-      reinterpret_cast<T*>(p.alpha_ws)[w] =
-          reinterpret_cast<const T*>(p.alpha)[(p.varlen ? 0 : (long long)b * p.a_sb) + (long long)h * p.a_sh + tok];
+      reinterpret_cast<T*>(p.alpha_ws)[w] = reinterpret_cast<const T*>(
+          p.alpha)[(p.varlen ? 0 : (long long)r.b * p.a_sb) + (long long)r.h * p.a_sh + r.tok];
   }
 }
 
-// One warp per (query row, head). flash_sparse_attn/ops/triton/flash_bwd_postprocess.py:60-105.
+// head_dim / 8 lanes per (query row, head). flash_sparse_attn/ops/triton/flash_bwd_postprocess.py:60-148.
 template <typename T>
 __global__ void __launch_bounds__(256) bwd_post_kernel(BwdPostParams p) {
-  const int lane = threadIdx.x & 31;
-  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lpr = p.head_dim >> 3;
+  const int lane = threadIdx.x & 31, sub = lane % lpr;
+  const long long item = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (32 / lpr) + lane / lpr;
   const long long rows = p.varlen ? p.total_q : (long long)p.B * p.sq;
   if (item >= rows * p.heads) return;
-  const int h = (int)(item % p.heads);
-  const long long row = item / p.heads;
-  int b, q;
-  long long tok;
-  if (p.varlen) {
-    b = 0;
-    while (b + 1 < p.B && p.cu_q[b + 1] <= row) ++b;
-    q = (int)(row - p.cu_q[b]);
-    tok = row;
-  } else {
-    b = (int)(row / p.sq);
-    q = (int)(row - (long long)b * p.sq);
-    tok = q;
-  }
-  const float* src = p.dq_accum + ((long long)h * p.ws_sh + padded_row(p.varlen, p.cu_q, b, p.sq, q)) * p.head_dim;
-  T* dst = reinterpret_cast<T*>(p.dq) + (p.varlen ? 0 : (long long)b * p.dq_sb) + tok * p.dq_sm + (long long)h * p.dq_sh;
-  for (int i = lane * 4; i < p.head_dim; i += 128) {
-    const float4 v = *reinterpret_cast<const float4*>(src + i);
-    uint2 o;
-    o.x = pack2<T>(v.x * p.scale, v.y * p.scale);
-    o.y = pack2<T>(v.z * p.scale, v.w * p.scale);
-    *reinterpret_cast<uint2*>(dst + i) = o;
-  }
-  if (p.da && lane == 0)
-    reinterpret_cast<T*>(p.da)[(p.varlen ? 0 : (long long)b * p.da_sb) + (long long)h * p.da_sh + tok] =
-        T(p.da_accum[(long long)h * p.ws_sh + padded_row(p.varlen, p.cu_q, b, p.sq, q)] * p.scale);
+  const RowPos r = locate_row(item, p.heads, p.varlen, p.cu_q, p.B, p.sq);
+  const long long wrow = (long long)r.h * p.ws_sh + padded_row(p.varlen, p.cu_q, r.b, p.sq, r.q);
+  const float4* src = reinterpret_cast<const float4*>(p.dq_accum + wrow * p.head_dim + sub * 8);
+  const float4 v0 = __ldcs(src), v1 = __ldcs(src + 1);  // read once: do not keep in cache
+  uint4 o;
+  o.x = pack2<T>(v0.x * p.scale, v0.y * p.scale);
+  o.y = pack2<T>(v0.z * p.scale, v0.w * p.scale);
+  o.z = pack2<T>(v1.x * p.scale, v1.y * p.scale);
+  o.w = pack2<T>(v1.z * p.scale, v1.w * p.scale);
+  T* dst = reinterpret_cast<T*>(p.dq) + (p.varlen ? 0 : (long long)r.b * p.dq_sb) + r.tok * p.dq_sm +
+           (long long)r.h * p.dq_sh + sub * 8;
+  *reinterpret_cast<uint4*>(dst) = o;
+  if (p.da && sub == 0)
+    reinterpret_cast<T*>(p.da)[(p.varlen ? 0 : (long long)r.b * p.da_sb) + (long long)r.h * p.da_sh + r.tok] =
+        T(p.da_accum[wrow] * p.scale);
 }
 
 template <typename T>
@@ -204,7 +212,9 @@ cudaError_t launch_bwd_pre(const BwdPreParams& p, int dtype, cudaStream_t stream
   const long long rows = p.varlen ? p.total_q : (long long)p.B * p.sq;
   const long long items = rows * p.heads;
   if (items <= 0) return cudaSuccess;
-  const unsigned grid = (unsigned)((items + 7) / 8);
+  if (p.head_dim != 64 && p.head_dim != 128) return cudaErrorInvalidValue;
+  const int per_block = 8 * (32 / (p.head_dim >> 3));
+  const unsigned grid = (unsigned)((items + per_block - 1) / per_block);
   if (dtype == DT_BF16)
     bwd_pre_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
   else
@@ -216,7 +226,9 @@ cudaError_t launch_bwd_post(const BwdPostParams& p, int dtype, cudaStream_t stre
   const long long rows = p.varlen ? p.total_q : (long long)p.B * p.sq;
   const long long items = rows * p.heads;
   if (items <= 0) return cudaSuccess;
-  const unsigned grid = (unsigned)((items + 7) / 8);
+  if (p.head_dim != 64 && p.head_dim != 128) return cudaErrorInvalidValue;
+  const int per_block = 8 * (32 / (p.head_dim >> 3));
+  const unsigned grid = (unsigned)((items + per_block - 1) / per_block);
   if (dtype == DT_BF16)
     bwd_post_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
   else
