@@ -362,6 +362,8 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
   const bool split = ns > 1;
   if (split && (!a->dk_partial || !a->dv_partial)) return FSA_ERR_INVALID_ARG;
   if (split && gated && (!a->dd_partial || a->delta_numel <= 0)) return FSA_ERR_INVALID_ARG;
+  const bool det = a->flags & FSA_F_DETERMINISTIC;
+  if (det && (!a->dq_order || !a->dq_turn)) return FSA_ERR_INVALID_ARG;
   if (a->seqlen_q <= 0 || a->seqlen_k <= 0) return FSA_OK;
   const int64_t R = fsa_bwd_padded_rows(a->batch, a->seqlen_q, a->total_q, varlen_q);
   const long long rows_k = varlen_k ? a->total_k : (long long)a->batch * a->seqlen_k;
@@ -490,6 +492,32 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
   if (a->seqused_q) f |= fsa::F_USED_Q;
   if (a->seqused_k) f |= fsa::F_USED_K;
   p.flags = f;
+  if (det) {
+    fsa::DqOrderParams op;
+    memset(&op, 0, sizeof(op));
+    op.order = a->dq_order;
+    op.cu_q = a->cu_seqlens_q;
+    op.cu_k = a->cu_seqlens_k;
+    op.used_q = a->seqused_q;
+    op.used_k = a->seqused_k;
+    op.windows = a->window_sizes;
+    op.B = a->batch;
+    op.Hkv = a->heads_kv;
+    op.sq = a->seqlen_q;
+    op.sk = a->seqlen_k;
+    op.num_splits = ns;
+    op.n_tiles_k = p.n_tiles_k;
+    op.num_m_blocks = p.num_m_blocks;
+    op.win_stride = a->window_stride;
+    op.flags = f;
+    if (fsa::launch_dq_order(op, stream) != cudaSuccess) return FSA_ERR_LAUNCH;
+    if (cudaMemsetAsync(a->dq_turn, 0, sizeof(int32_t) * (size_t)a->batch * a->heads_q * p.num_m_blocks, stream) !=
+        cudaSuccess)
+      return FSA_ERR_LAUNCH;
+    p.dq_order = a->dq_order;
+    p.dq_turn = a->dq_turn;
+    p.flags |= fsa::F_DETERMINISTIC;
+  }
   mark_before(stream);
   cudaError_t e = fsa::launch_bwd(p, a->kind, a->dtype, a->head_dim, stream);
   mark_after(stream);

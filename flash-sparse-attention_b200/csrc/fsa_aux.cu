@@ -2,6 +2,7 @@
 #include "fsa_ptx.cuh"
 #include "fsa_params.h"
 #include "fsa_aux.h"
+#include "fsa_schedule.h"
 
 namespace fsa {
 
@@ -169,6 +170,36 @@ __global__ void __launch_bounds__(256) bwd_post_kernel(BwdPostParams p) {
         T(p.da_accum[wrow] * p.scale);
 }
 
+__global__ void __launch_bounds__(128) dq_order_kernel(DqOrderParams p) {
+  const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (item >= (long long)p.B * p.Hkv * p.num_m_blocks) return;
+  const int m = (int)(item % p.num_m_blocks);
+  const int hkv = (int)((item / p.num_m_blocks) % p.Hkv);
+  const int b = (int)(item / ((long long)p.num_m_blocks * p.Hkv));
+  const int off_q = (p.flags & F_VARLEN_Q) ? p.cu_q[b] : 0;
+  const int off_k = (p.flags & F_VARLEN_K) ? p.cu_k[b] : 0;
+  const int sq = (p.flags & F_USED_Q) ? p.used_q[b] : ((p.flags & F_VARLEN_Q) ? p.cu_q[b + 1] - off_q : p.sq);
+  const int sk = (p.flags & F_USED_K) ? p.used_k[b] : ((p.flags & F_VARLEN_K) ? p.cu_k[b + 1] - off_k : p.sk);
+  const bool causal = p.flags & F_CAUSAL, local = p.flags & F_LOCAL, split_qo = p.flags & F_SPLIT;
+  FsaWindow w = {0, 0, 0, 0};
+  if (local) {
+    const int* wp = p.windows + (long long)hkv * p.win_stride;
+    w.sink = wp[0];
+    w.left = wp[1];
+    w.right = wp[2];
+    w.near_ = wp[3];
+  }
+  unsigned short count = 0;
+  for (int n = p.n_tiles_k - 1; n >= 0; --n) {
+    if (n * 128 >= sk) continue;
+    bool visits = false;
+    for (int s = 0; s < p.num_splits && !visits; ++s)
+      visits = fsa_bwd_visits(fsa_bwd_schedule(sq, sk, n, s, w, p.num_splits, 128, 128, causal, local, split_qo), m,
+                              causal, local);
+    if (visits) p.order[(((long long)b * p.Hkv + hkv) * p.n_tiles_k + n) * p.num_m_blocks + m] = count++;
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) flat_sum_kernel(FlatSumParams p) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -233,6 +264,13 @@ cudaError_t launch_bwd_post(const BwdPostParams& p, int dtype, cudaStream_t stre
     bwd_post_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
   else
     bwd_post_kernel<__half><<<grid, 256, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_dq_order(const DqOrderParams& p, cudaStream_t stream) {
+  const long long items = (long long)p.B * p.Hkv * p.num_m_blocks;
+  if (items <= 0) return cudaSuccess;
+  dq_order_kernel<<<(unsigned)((items + 127) / 128), 128, 0, stream>>>(p);
   return cudaGetLastError();
 }
 

@@ -65,6 +65,19 @@ struct FlatSumParams {
   int num_splits;
 };
 
+// Deterministic dQ: for every (batch, KV head, query tile) number the key tiles that visit it, highest
+// key tile first; the main kernel adds its dQ tiles in that order.
+struct DqOrderParams {
+  unsigned short* order;  // [B, Hkv, n_tiles_k, num_m_blocks]
+  const int* cu_q;
+  const int* cu_k;
+  const int* used_q;
+  const int* used_k;
+  const int* windows;
+  int B, Hkv, sq, sk, num_splits, n_tiles_k, num_m_blocks, win_stride;
+  unsigned flags;  // F_CAUSAL | F_LOCAL | F_SPLIT | F_VARLEN_* | F_USED_*
+};
+cudaError_t launch_dq_order(const DqOrderParams& p, cudaStream_t stream);
 cudaError_t launch_flat_sum(const FlatSumParams& p, int dtype, cudaStream_t stream);
 cudaError_t launch_bwd_pre(const BwdPreParams& p, int dtype, cudaStream_t stream);
 cudaError_t launch_bwd_post(const BwdPostParams& p, int dtype, cudaStream_t stream);

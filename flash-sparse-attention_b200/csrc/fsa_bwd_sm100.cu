@@ -189,8 +189,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
 
   // ---- work decode ------------------------------------------------------------------------------
   int idx = blockIdx.x;
-  const int n_block = idx % p.n_tiles_k;
-  idx /= p.n_tiles_k;
+  int n_block;
+  if (p.flags & F_DETERMINISTIC) {
+    // key tiles in descending order, slowest index: a CTA only ever waits for CTAs launched before it
+    const int per_tile = p.Hkv * p.B * p.num_splits;
+    n_block = p.n_tiles_k - 1 - idx / per_tile;
+    idx %= per_tile;
+  } else {
+    n_block = idx % p.n_tiles_k;
+    idx /= p.n_tiles_k;
+  }
   const int hkv = idx % p.Hkv;
   idx /= p.Hkv;
   const int b = idx / p.num_splits;
@@ -427,6 +435,38 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
     bool dq_pending = false;
     int dq_row = 0, dq_head = 0;
     int m_cur = 0, g_cur = 0;  // query tile / head of the step whose dS and dQ are being handled
+    // Deterministic mode: the key tiles that add into one dQ tile do so in descending key order. A
+    // counter per (head, query tile) advances by one per warp (8 per key tile) once that warp's adds
+    // have completed; a warp adds only when the counter shows 8 x its key tile's rank (bounded wait).
+    const bool det = p.flags & F_DETERMINISTIC;
+    int* turn_prev = nullptr;  // counter of the tile whose adds are still in flight
+    auto turn_of = [&](int head, int m) { return p.dq_turn + ((long long)b * p.Hq + head) * p.num_m_blocks + m; };
+    auto turn_wait = [&](int head, int m) {
+      if (lane == 0) {
+        const int target =
+            8 * (int)p.dq_order[(((long long)b * p.Hkv + hkv) * p.n_tiles_k + n_block) * p.num_m_blocks + m];
+        const int* tp = turn_of(head, m);
+        const long long t_end = clock64() + FSA_WAIT_CYCLES;
+        int seen;
+        for (;;) {
+          asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(tp) : "memory");
+          if (seen == target || *abort_flag) break;
+          if (clock64() > t_end) {
+            *abort_flag = 1;
+            break;
+          }
+          __nanosleep(64);
+        }
+      }
+      __syncwarp();
+      if (*abort_flag) ok = false;
+    };
+    auto turn_done = [&](int* tp) {
+      if (lane == 0 && tp) {
+        __threadfence();
+        atomicAdd(tp, 1);
+      }
+    };
 
     // ---- gated: delta of this key row, its extremes over the key tile, running gate bound --------
     // (flash_sparse_attn/ops/triton/flash_gated_bwd.py:406-421; keys past the sequence read as zero)
@@ -813,8 +853,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->dq_empty);
       FSA_TICK(7);
-      if (lane == 0) bulk_wait_read0();  // the buffer went to the engine a whole phase ago
-      __syncwarp();
+      if (det) {
+        // the previous tile's adds must have landed before its counter moves; then take this tile's turn
+        if (lane == 0) bulk_wait0();
+        turn_done(turn_prev);
+        turn_prev = turn_of(hkv * p.G + g_cur, m_cur);
+        turn_wait(hkv * p.G + g_cur, m_cur);
+        if (!ok) return;
+      } else {
+        if (lane == 0) bulk_wait_read0();  // the buffer went to the engine a whole phase ago
+        __syncwarp();
+      }
       FSA_TICK(14);
       stage_store(r);
       FSA_TICK(16);
@@ -841,12 +890,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       if (ok && !skip_cur) {
         dq_step(it);
         n_live++;
+      } else if (ok && det) {
+        // a skipped tile adds nothing but still takes (and passes on) its turn
+        turn_wait(hkv * p.G + g_cur, m_cur);
+        turn_done(ok ? turn_of(hkv * p.G + g_cur, m_cur) : nullptr);
       }
       skip_cur = skip_next;
       m_cur = m_p;
       g_cur = g_p;
     }
     dq_flush();
+    if (det) {
+      if (lane == 0) bulk_wait0();
+      turn_done(turn_prev);
+    }
 
     FSA_TICK(9);
     FSA_TICK_FLUSH;

@@ -21,6 +21,7 @@ enum : unsigned {
   F_GATHER = 1u << 11,
   F_LSE_LOG2 = 1u << 12,   // store lse in base 2 (split partials), else natural log
   F_KV_RAGGED = 1u << 13,  // rows past the key length may hold foreign data: zero V tails in smem
+  F_DETERMINISTIC = 1u << 14,  // backward: dQ contributions of the key tiles are added in a fixed order
 };
 
 enum { KIND_DENSE = 0, KIND_SPARSE = 1, KIND_GATED = 2 };
@@ -68,6 +69,9 @@ struct alignas(64) BwdKernelParams {
   const void* alpha_ws;  // gated: T [Hq, ws_sh], tile-padded rows, zero outside the sequences
   const void* delta;     // gated: T [B, Hkv, Sk] | [Hkv, Tk]
   float* da_accum;       // gated: [Hq, ws_sh] fp32, zeroed; receives atomic adds
+  const unsigned short* dq_order;  // deterministic: [B, Hkv, n_tiles_k, num_m_blocks] rank of a key tile among
+                                   // the key tiles that add into a query tile (descending key index)
+  int* dq_turn;                    // deterministic: [B, Hq, num_m_blocks] zeroed; 8 ticks per finished key tile
   void* dd_out;          // gated: T* laid out like delta, or float partial [splits, ...] when F_SPLIT
   long long d_sb, d_sh, dd_ss;
   long long dkv_sb, dkv_sn, dkv_sh, dkv_ss;

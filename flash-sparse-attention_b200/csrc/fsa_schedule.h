@@ -374,6 +374,21 @@ FSA_HD FsaBwdSched fsa_bwd_schedule(int sq, int sk, int n_block, int split_idx, 
   return s;
 }
 
+// Whether query tile `m` is one of the tiles this schedule walks (the union of the phases of
+// flash_sparse_attn/ops/triton/flash_sparse_bwd.py:315-464).
+FSA_HD bool fsa_bwd_visits(const FsaBwdSched& s, int m, bool causal, bool local) {
+  bool in = false;
+  if (causal || local) in |= (m >= s.m_min && m < s.m_min_no_mask);
+  if (!local) in |= (m >= ((causal || local) ? s.m_min_no_mask : s.m_min) && m < s.m_max);
+  if (local) {
+    in |= (m >= s.win_min && m < s.win_min_no_mask);
+    in |= (m >= s.win_min_no_mask && m < s.win_max_no_mask);
+    in |= (m >= s.win_max_no_mask && m < s.win_max);
+    in |= (m >= s.sink_min && m < s.sink_max);
+  }
+  return in;
+}
+
 FSA_HD bool fsa_bwd_sched_empty(const FsaBwdSched& s) {
   return (s.m_max <= s.m_min) && (s.win_max <= s.win_min) && (s.sink_max <= s.sink_min);
 }

@@ -21,3 +21,4 @@ from flash_sparse_attn.ops.triton.interface import (  # noqa: F401
     flash_sparse_attn_with_kvcache_func,
 )
 from flash_sparse_attn._lib import check_status  # noqa: F401
+from flash_sparse_attn.ops.triton.utils import deterministic_enabled, set_deterministic  # noqa: F401

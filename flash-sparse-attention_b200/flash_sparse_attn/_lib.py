@@ -25,6 +25,7 @@ F_SPLIT = 1 << 2
 F_PACK_GQA = 1 << 3
 F_LOGSIGMOID = 1 << 4
 F_ADAPT_GATE = 1 << 5
+F_DETERMINISTIC = 1 << 6
 
 
 class FsaFwdArgs(ctypes.Structure):
@@ -168,6 +169,8 @@ class FsaBwdArgs(ctypes.Structure):
         ("delta_stride_b", c_int64),
         ("delta_stride_h", c_int64),
         ("delta_numel", c_int64),
+        ("dq_order", c_void_p),
+        ("dq_turn", c_void_p),
     ]
 
 

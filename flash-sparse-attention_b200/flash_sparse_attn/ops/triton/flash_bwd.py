@@ -62,8 +62,15 @@ def attn_backward(
     tile_mn: Optional[Tuple[int, int]] = None,
     skip_checks: bool = False,
     tile_map: Optional[torch.Tensor] = None,
+    deterministic: Optional[bool] = None,
 ):
-    """Returns ``(dq, dk, dv)`` (plus ``(dalpha, ddelta)`` for the gated kind) in ``dout.dtype``."""
+    """Returns ``(dq, dk, dv)`` (plus ``(dalpha, ddelta)`` for the gated kind) in ``dout.dtype``.
+
+    ``deterministic`` (default: the package-wide switch ``flash_sparse_attn.set_deterministic``) makes dQ
+    bitwise reproducible: the key tiles add their dQ tiles in a fixed order instead of in the order the
+    CTAs happen to run (dK and dV always are; for the gated kind dalpha keeps its fp32 atomics)."""
+    if deterministic is None:
+        deterministic = utils.deterministic_enabled()
     if not query.is_cuda:
         raise RuntimeError("flash_sparse_attn (B200 build) only runs on CUDA tensors; there is no CPU path")
     device = query.device
@@ -194,6 +201,12 @@ def attn_backward(
     a.softmax_scale = float(softmax_scale)
     a.softmax_threshold = float(softmax_threshold)
     a.gate_threshold = float(gate_threshold) if gate_threshold is not None else 0.0
+    if deterministic:
+        n_tiles_k, n_tiles_q = -(-seqlen_k // TILE_N), -(-seqlen_q // TILE_M)
+        dq_order = torch.empty((batch, num_heads_kv, n_tiles_k, n_tiles_q), dtype=torch.int16, device=device)
+        dq_turn = torch.empty((batch, num_heads_q, n_tiles_q), dtype=torch.int32, device=device)
+        a.dq_order, a.dq_turn = dq_order.data_ptr(), dq_turn.data_ptr()
+        a.flags |= _lib.F_DETERMINISTIC
     if kind == "gated":
         a.alpha, a.delta, a.dalpha, a.ddelta = alpha.data_ptr(), delta.data_ptr(), da.data_ptr(), dd.data_ptr()
         a.alpha_ws, a.da_accum, a.dd_partial = alpha_ws.data_ptr(), da_accum.data_ptr(), _lib.ptr(dd_partial)

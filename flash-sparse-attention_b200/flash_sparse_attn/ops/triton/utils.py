@@ -1,6 +1,7 @@
 """Host-side helpers with the behaviour of flash_sparse_attn/ops/triton/utils.py."""
 
 import functools
+import os
 from typing import Optional
 
 import torch
@@ -96,3 +97,18 @@ def num_splits_heuristic(
 @functools.lru_cache(maxsize=16)
 def device_num_sms(device: torch.device) -> int:
     return torch.cuda.get_device_properties(device).multi_processor_count
+
+
+_DETERMINISTIC = os.environ.get("FSA_DETERMINISTIC", "0") not in ("", "0", "false", "False")
+
+
+def set_deterministic(enabled: bool) -> None:
+    """Package-wide default of the backward's deterministic dQ accumulation (also set by the
+    environment variable ``FSA_DETERMINISTIC=1``). The reference has no such switch: its dQ is summed
+    with atomics in arrival order (flash_sparse_attn/ops/triton/scheduler.py:2190-2192)."""
+    global _DETERMINISTIC
+    _DETERMINISTIC = bool(enabled)
+
+
+def deterministic_enabled() -> bool:
+    return _DETERMINISTIC

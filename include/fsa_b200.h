@@ -41,7 +41,8 @@ enum {
   FSA_F_SPLIT = 1u << 2,      /* split-KV (forward, decode) / split-QO (backward) */
   FSA_F_PACK_GQA = 1u << 3,   /* rows of one query tile interleave the G heads of a KV head */
   FSA_F_LOGSIGMOID = 1u << 4, /* gated: gate = logsigmoid(alpha*delta), else alpha*delta */
-  FSA_F_ADAPT_GATE = 1u << 5
+  FSA_F_ADAPT_GATE = 1u << 5,
+  FSA_F_DETERMINISTIC = 1u << 6 /* backward: add the dQ tiles of the key tiles in a fixed order */
 };
 
 /*
@@ -178,6 +179,13 @@ typedef struct FsaBwdArgs {
   int64_t alpha_stride_b, alpha_stride_h;
   int64_t delta_stride_b, delta_stride_h;
   int64_t delta_numel; /* elements of delta / ddelta (contiguous) */
+  /* FSA_F_DETERMINISTIC only: workspaces (both written by this call)
+   *   dq_order uint16 [batch, heads_kv, ceil(seqlen_k/128), ceil(seqlen_q/128)]
+   *   dq_turn  int32  [batch, heads_q, ceil(seqlen_q/128)]
+   * dQ then no longer depends on the order in which CTAs happen to run: every key tile waits (bounded) for
+   * the key tiles above it before its reduce-add into a query tile; results are bitwise reproducible. */
+  uint16_t* dq_order;
+  int32_t* dq_turn;
 } FsaBwdArgs;
 
 int fsa_bwd(const FsaBwdArgs* args, void* stream);

@@ -159,3 +159,62 @@ def test_c2_full_size_backward_properties():
     assert_close("c2-dq", a[0][:1, :, 4:8], ref[0])
     assert_close("c2-dk", a[1][:1, :, 1:2], ref[1])
     assert_close("c2-dv", a[2][:1, :, 1:2], ref[2])
+
+
+# ---------------------------------------------------------------------------------------------------
+# deterministic dQ: key tiles add their dQ tiles in a fixed (descending) order
+# ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("case", ["causal", "noncausal", "local_split", "gqa_hd64"])
+def test_deterministic_dq_is_bitwise_reproducible(case):
+    fsa = _ops()
+    hd = 64 if case == "gqa_hd64" else 128
+    b, s, hq, hkv = 2, 2048, 8, 2
+    q, k, v = seeded_qkv(5, b, s, s, hq, hkv, hd)
+    do = torch.randn(b, s, hq, hd, generator=torch.Generator().manual_seed(6)).to(torch.bfloat16)
+    kw = dict(is_causal=case != "noncausal", softmax_threshold=-128.0)
+    ws = None
+    if case == "local_split":
+        ws = torch.tensor([[32, 200, 100, 160], [0, 300, 0, 64]], dtype=torch.int32)
+        kw.update(window_sizes=ws, is_split_qo=True, num_splits=3)
+    ref = eager.backward(q, k, v, do, None, kw["is_causal"], is_local=ws is not None, window_sizes=ws)
+    fsa.set_deterministic(True)
+    try:
+        runs = [_run(fsa.flash_sparse_attn_func, q, k, v, do, **kw) for _ in range(3)]
+    finally:
+        fsa.set_deterministic(False)
+    for name, a, r in zip(("dq", "dk", "dv"), runs[0], ref):
+        assert_close(f"det-{case}-{name}", a, r)
+    for other in runs[1:]:
+        for name, a, o in zip(("dq", "dk", "dv"), runs[0], other):
+            assert torch.equal(a, o), f"{case}: {name} differs between two deterministic runs"
+
+
+def test_deterministic_dq_varlen_and_skipped_tiles():
+    """Packed sequences of different lengths, and a run in which tiles are skipped (a skipped tile still
+    has to pass its turn on)."""
+    fsa = _ops()
+    lens = [300, 1000, 129, 2048]
+    cu = torch.tensor([0] + list(itertools.accumulate(lens)), dtype=torch.int32)
+    g = torch.Generator().manual_seed(8)
+    q = (torch.randn(sum(lens), 8, 128, generator=g) * 2.5).to(torch.bfloat16)
+    k = (torch.randn(sum(lens), 2, 128, generator=g) * 2.5).to(torch.bfloat16)
+    v = torch.randn(sum(lens), 2, 128, generator=g).to(torch.bfloat16)
+    do = torch.randn(sum(lens), 8, 128, generator=g).to(torch.bfloat16)
+    fsa.set_deterministic(True)
+    try:
+        outs = []
+        for _ in range(2):
+            qg, kg, vg = (t.to(DEV).requires_grad_(True) for t in (q, k, v))
+            out = fsa.flash_sparse_attn_varlen_func(qg, kg, vg, cu.to(DEV), cu.to(DEV), max(lens), max(lens),
+                                                    is_causal=True, softmax_threshold=1.0)
+            out.backward(do.to(DEV))
+            torch.cuda.synchronize()
+            fsa.check_status()
+            outs.append((qg.grad, kg.grad, vg.grad))
+    finally:
+        fsa.set_deterministic(False)
+    for a, o in zip(outs[0], outs[1]):
+        assert torch.equal(a, o)
+    ref = eager.varlen_backward(q, k, v, do, cu, cu, None, True)
+    for name, a, r in zip(("dq", "dk", "dv"), outs[0], ref):
+        assert_close("det-varlen-" + name, a, r, rtol=5e-2, atol=5e-2)
