@@ -821,6 +821,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       __syncwarp();
     };
     auto dq_flush = [&]() {
+      if (det && turn_prev) {
+        // both halves went out in dq_step: once they have landed the next key tile may add
+        if (lane == 0) bulk_wait0();
+        turn_done(turn_prev);
+        turn_prev = nullptr;
+      }
       if (NCH > 1 && dq_pending) {
         FSA_TICK(9);
         if (lane == 0) bulk_wait_read0();
@@ -854,9 +860,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       if (lane == 0) mbar_arrive(&bars->dq_empty);
       FSA_TICK(7);
       if (det) {
-        // the previous tile's adds must have landed before its counter moves; then take this tile's turn
-        if (lane == 0) bulk_wait0();
-        turn_done(turn_prev);
+        if (lane == 0) bulk_wait_read0();
         turn_prev = turn_of(hkv * p.G + g_cur, m_cur);
         turn_wait(hkv * p.G + g_cur, m_cur);
         if (!ok) return;
@@ -874,6 +878,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         bulk_commit();
       }
       dq_pending = NCH > 1;
+      if (det && NCH > 1) {
+        // keep the turn short: the second half follows as soon as the engine has read the first
+        if (lane == 0) bulk_wait_read0();
+        __syncwarp();
+        stage_store(dq_hold);
+        if (lane == 0) {
+          tma_reduce_add_3d(&p.map_dq, stage, wg * HALF + 32, dq_row, dq_head);
+          bulk_commit();
+        }
+        dq_pending = false;
+      }
       FSA_TICK(17);
     };
 
@@ -900,10 +915,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       g_cur = g_p;
     }
     dq_flush();
-    if (det) {
-      if (lane == 0) bulk_wait0();
-      turn_done(turn_prev);
-    }
 
     FSA_TICK(9);
     FSA_TICK_FLUSH;
