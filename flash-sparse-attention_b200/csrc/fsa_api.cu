@@ -167,7 +167,11 @@ int fsa_fwd(const FsaFwdArgs* a, void* stream_) {
   if (!a || !a->q || !a->k || !a->v || !a->out || !a->lse || !a->status) return FSA_ERR_INVALID_ARG;
   if (a->batch <= 0 || a->heads_q <= 0 || a->head_dim <= 0) return FSA_ERR_INVALID_ARG;
   if (a->head_dim != 64 && a->head_dim != 128) return FSA_ERR_UNSUPPORTED;
-  if (a->dtype != FSA_DT_BF16 && a->dtype != FSA_DT_FP16) return FSA_ERR_UNSUPPORTED;
+  const bool fp8 = a->dtype == FSA_DT_E4M3 || a->dtype == FSA_DT_E5M2;
+  if (a->dtype != FSA_DT_BF16 && a->dtype != FSA_DT_FP16 && !fp8) return FSA_ERR_UNSUPPORTED;
+  if (fp8 && a->head_dim != 128) return FSA_ERR_UNSUPPORTED;  // FP8 tiles: one 128-byte swizzle row per head row
+  const int out_dtype = fp8 ? FSA_DT_BF16 : a->dtype;        // flash_sparse_fwd.py:634
+  const uint32_t box0 = fp8 ? 128 : 64;                       // elements in a 128-byte row
   if (a->kind != FSA_KIND_DENSE && a->kind != FSA_KIND_SPARSE && a->kind != FSA_KIND_GATED) return FSA_ERR_UNSUPPORTED;
   if (a->kind == FSA_KIND_GATED && (!a->alpha || !a->delta)) return FSA_ERR_INVALID_ARG;
   if ((a->tile_m && a->tile_m != 128) || (a->tile_n && a->tile_n != 128)) return FSA_ERR_UNSUPPORTED;
@@ -197,7 +201,7 @@ int fsa_fwd(const FsaFwdArgs* a, void* stream_) {
     const uint64_t d_b = varlen_q ? 1 : (uint64_t)a->batch;
     const int64_t s_b = varlen_q ? a->q_stride_s * (int64_t)a->total_q : a->q_stride_b;
     rc = make_map4(&p.map_q, a->dtype, a->q, a->head_dim, a->heads_q, a->q_stride_h, d_rows, a->q_stride_s, d_b, s_b,
-                   64, gpack, 128 / gpack);
+                   box0, gpack, 128 / gpack);
     if (rc != FSA_OK) return rc;
   }
   {
@@ -223,10 +227,10 @@ int fsa_fwd(const FsaFwdArgs* a, void* stream_) {
     }
     if (d_rows == 0) return FSA_ERR_INVALID_ARG;
     rc = make_map4(&p.map_k, a->dtype, a->k, a->head_dim, a->heads_kv, a->k_stride_h, d_rows, a->k_stride_s, d_b, ks_b,
-                   64, 1, box_rows);
+                   box0, 1, box_rows);
     if (rc != FSA_OK) return rc;
     rc = make_map4(&p.map_v, a->dtype, a->v, a->head_dim, a->heads_kv, a->v_stride_h, d_rows, a->v_stride_s, d_b, vs_b,
-                   64, 1, box_rows);
+                   box0, 1, box_rows);
     if (rc != FSA_OK) return rc;
   }
   p.cu_q = a->cu_seqlens_q;
@@ -326,7 +330,7 @@ int fsa_fwd(const FsaFwdArgs* a, void* stream_) {
     c.heads = a->heads_q;
     c.head_dim = a->head_dim;
     c.num_splits = ns;
-    e = fsa::launch_combine(c, a->dtype, stream);
+    e = fsa::launch_combine(c, out_dtype, stream);
     if (e != cudaSuccess) return FSA_ERR_LAUNCH;
   }
   return FSA_OK;

@@ -35,14 +35,28 @@ constexpr int NTHREADS = 384;  // three warpgroups: softmax 0, softmax 1, {produ
 constexpr int KSTAGES = 2;
 constexpr int VSTAGES = 2;
 
-template <int HD>
+template <int HD, int ES = 2>
 struct FwdSmem {
-  static constexpr int kTileBytes = TM * HD * 2;  // one Q / K / V tile of 16-bit elements
+  static constexpr int kTileBytes = TM * HD * ES;  // one Q / K / V tile of ES-byte elements
   static constexpr int kQ = 0;
   static constexpr int kK = kQ + 2 * kTileBytes;
   static constexpr int kV = kK + KSTAGES * kTileBytes;
   static constexpr int kBar = kV + VSTAGES * kTileBytes;
   static constexpr int kTotal = kBar + 2048 + 1024;  // barriers/flags/delta ring + alignment slack
+};
+
+// Output / gate element type that goes with an input element type.
+template <typename T>
+struct OutType {
+  using type = T;
+};
+template <>
+struct OutType<__nv_fp8_e4m3> {
+  using type = __nv_bfloat16;
+};
+template <>
+struct OutType<__nv_fp8_e5m2> {
+  using type = __nv_bfloat16;
 };
 
 struct FwdBars {
@@ -117,11 +131,19 @@ __device__ __forceinline__ bool tile_col_visible(const TileMask& tm, int i) {
 
 template <int HD, typename T, int KIND>
 __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant__ FwdKernelParams p) {
-  using SM = FwdSmem<HD>;
-  constexpr int KK_QK = HD / 16;      // MMAs (K = 16) per S tile
-  constexpr int KK_PV = TN / 16;      // MMAs per P V tile
+  // T is the element type of Q, K, V and of P: bf16 / fp16 (kind::f16) or FP8 e4m3 / e5m2 (kind::f8f6f4,
+  // flash_sparse_attn/ops/triton/flash_sparse_fwd.py:49, :84-86 under IS_QUANT). Outputs and the gate
+  // vectors are 16-bit (bf16 for FP8 inputs, flash_sparse_fwd.py:634).
+  constexpr int ES = sizeof(T);
+  constexpr bool F8 = ES == 1;
+  constexpr int SLAB = 128 / ES;      // elements per 128-byte swizzle row
+  using TO = typename OutType<T>::type;
+  using SM = FwdSmem<HD, ES>;
+  constexpr int KK_QK = HD * ES / 32;  // MMAs per S tile: every MMA consumes 32 bytes of the head dimension
+  constexpr int KK_PV = TN * ES / 32;  // MMAs per P V tile: 32 bytes of the key dimension each
   constexpr int OCH = HD / 32;        // 32-column chunks of an O tile
   constexpr bool IS_BF16 = (sizeof(T) == 2) && !__is_same(T, __half);
+  static_assert(!F8 || HD == 128, "FP8 tiles are one 128-byte swizzle row wide");
   constexpr uint32_t TMEM_S0 = 0, TMEM_O0 = 256;
 
   extern __shared__ uint8_t smem_raw[];
@@ -249,8 +271,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
             const int row0 = (mb * TM) / gpack;  // token index of the tile's first row
             const int head0 = (p.flags & F_PACK_GQA) ? si.hkv * p.G : si.head;
             const int bq = (p.flags & F_VARLEN_Q) ? 0 : si.b;
-            for (int d = 0; d < HD; d += 64)
-              tma_load_4d(dst + (d / 64) * (TM * 128), &p.map_q, &bars->q_full, d, head0, si.off_q + row0, bq);
+            for (int d = 0; d < HD; d += SLAB)
+              tma_load_4d(dst + (d / SLAB) * (TM * 128), &p.map_q, &bars->q_full, d, head0, si.off_q + row0, bq);
           }
         }
       }
@@ -264,20 +286,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
           for (int i = 0; i < nbox; ++i) {
             const int r0 = n * TN + i * rows_per_box;
             pages[i] = (r0 < si.sk) ? p.page_table[(long long)si.b * p.pt_stride + r0 / p.page_size] : -1;
-            if (pages[i] >= 0) bytes += rows_per_box * HD * 2;
+            if (pages[i] >= 0) bytes += rows_per_box * HD * ES;
           }
           mbar_arrive_expect_tx(bar, bytes);
           for (int i = 0; i < nbox; ++i) {
             if (pages[i] < 0) continue;
             const int r0 = n * TN + i * rows_per_box;
-            for (int d = 0; d < HD; d += 64)
-              tma_load_4d(dst + (d / 64) * (TN * 128) + i * rows_per_box * 128, map, bar, d, si.hkv,
+            for (int d = 0; d < HD; d += SLAB)
+              tma_load_4d(dst + (d / SLAB) * (TN * 128) + i * rows_per_box * 128, map, bar, d, si.hkv,
                           r0 % p.page_size, pages[i]);
           }
         } else {
           mbar_arrive_expect_tx(bar, SM::kTileBytes);
-          for (int d = 0; d < HD; d += 64)
-            tma_load_4d(dst + (d / 64) * (TN * 128), map, bar, d, si.hkv, si.off_k + n * TN, kv_row_coord_b);
+          for (int d = 0; d < HD; d += SLAB)
+            tma_load_4d(dst + (d / SLAB) * (TN * 128), map, bar, d, si.hkv, si.off_k + n * TN, kv_row_coord_b);
         }
       };
       int t = 0;
@@ -323,7 +345,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     // read as 0, like the reference's masked load (scheduler.py:1674-1691).
     if (KIND == KIND_GATED) {
       bool ok = !*abort_flag;
-      const T* dbase = reinterpret_cast<const T*>(p.delta);
+      const TO* dbase = reinterpret_cast<const TO*>(p.delta);
       int t = 0;
       for (int n = first_tile(); n >= 0 && ok; n = next_tile(n), ++t) {
         const int s = t & 1, use = t >> 1;
@@ -365,8 +387,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     }
   } else if (warp == 9) {
     // =============================== MMA issuer ==============================================
-    constexpr uint32_t idesc_s = umma_idesc_f16(TM, TN, IS_BF16, false, false);
-    constexpr uint32_t idesc_o = umma_idesc_f16(TM, HD, IS_BF16, false, true);
+    constexpr int F8_FMT = __is_same(T, __nv_fp8_e5m2) ? 1 : 0;
+    constexpr uint32_t idesc_s = F8 ? umma_idesc_f8(TM, TN, F8_FMT, F8_FMT, false, false)
+                                    : umma_idesc_f16(TM, TN, IS_BF16, false, false);
+    constexpr uint32_t idesc_o = F8 ? umma_idesc_f8(TM, HD, F8_FMT, F8_FMT, false, true)
+                                    : umma_idesc_f16(TM, HD, IS_BF16, false, true);
     const uint32_t sQ = smem_u32(smem + SM::kQ), sK = smem_u32(smem + SM::kK), sV = smem_u32(smem + SM::kV);
     bool ok = !*abort_flag;
     int cnt[2] = {0, 0};
@@ -377,8 +402,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
 #pragma unroll
         for (int kk = 0; kk < KK_QK; ++kk) {
           const uint32_t koff = (kk >> 2) * (TM * 128) + (kk & 3) * 32;
-          umma_ss(tmem_base + TMEM_S0 + q * 128, umma_smem_desc(sQ + q * SM::kTileBytes + koff, 16, 1024),
-                  umma_smem_desc(sK + ks * SM::kTileBytes + koff, 16, 1024), idesc_s, kk > 0);
+          if (F8)
+            umma_f8_ss(tmem_base + TMEM_S0 + q * 128, umma_smem_desc(sQ + q * SM::kTileBytes + koff, 16, 1024),
+                       umma_smem_desc(sK + ks * SM::kTileBytes + koff, 16, 1024), idesc_s, kk > 0);
+          else
+            umma_ss(tmem_base + TMEM_S0 + q * 128, umma_smem_desc(sQ + q * SM::kTileBytes + koff, 16, 1024),
+                    umma_smem_desc(sK + ks * SM::kTileBytes + koff, 16, 1024), idesc_s, kk > 0);
         }
         umma_commit(&bars->s_full[q]);
       }
@@ -417,8 +446,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
               // anything: clear them so that 0 * garbage cannot produce NaN
               const int r0 = si.sk - n * TN;
               uint8_t* vt = smem + SM::kV + vs * SM::kTileBytes;
-              for (int i = lane; i < (TN - r0) * (HD / 8); i += 32) {
-                const int r = r0 + i / (HD / 8), c = i % (HD / 8);
+              constexpr int CPR = HD * ES / 16;  // 16-byte chunks per row
+              for (int i = lane; i < (TN - r0) * CPR; i += 32) {
+                const int r = r0 + i / CPR, c = i % CPR;
                 *reinterpret_cast<uint4*>(vt + (c >> 3) * (TN * 128) + sw128_offset(r, c & 7)) =
                     make_uint4(0, 0, 0, 0);
               }
@@ -431,9 +461,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
             if (lane == 0) {
 #pragma unroll
               for (int kk = 0; kk < KK_PV; ++kk) {
-                umma_ts(tmem_base + TMEM_O0 + q * 128, tmem_base + TMEM_S0 + q * 128 + kk * 8,
-                        umma_smem_desc(sV + vs * SM::kTileBytes + kk * 2048, TN * 128, 1024), idesc_o,
-                        (kk > 0 || o_started[q]) ? 1u : 0u);
+                if (F8)
+                  umma_f8_ts(tmem_base + TMEM_O0 + q * 128, tmem_base + TMEM_S0 + q * 128 + kk * 8,
+                             umma_smem_desc(sV + vs * SM::kTileBytes + kk * 4096, TN * 128, 1024), idesc_o,
+                             (kk > 0 || o_started[q]) ? 1u : 0u);
+                else
+                  umma_ts(tmem_base + TMEM_O0 + q * 128, tmem_base + TMEM_S0 + q * 128 + kk * 8,
+                          umma_smem_desc(sV + vs * SM::kTileBytes + kk * 2048, TN * 128, 1024), idesc_o,
+                          (kk > 0 || o_started[q]) ? 1u : 0u);
               }
             }
             __syncwarp();
@@ -517,7 +552,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     float alpha = 0.f, a_max = 0.f, a_min = 0.f, gate_max = -INFINITY, gate_thr_log2 = 0.f;
     if (KIND == KIND_GATED) {
       if (rm.row_ok && q_valid[q]) {
-        const T* ab = reinterpret_cast<const T*>(p.alpha);
+        const TO* ab = reinterpret_cast<const TO*>(p.alpha);
         alpha = float(ab[(long long)((p.flags & F_VARLEN_Q) ? 0 : si.b) * p.a_sb + (long long)q_head * p.a_sh +
                          si.off_q + q_idx]);
       }
@@ -719,16 +754,29 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       for (int ch = 0; ch < TN / 32; ++ch) {
         uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float2 t = fma2(make_float2(__uint_as_float(sr[ch * 32 + i]), __uint_as_float(sr[ch * 32 + i + 1])),
-                                c2, nm2);
-          float2 e;
-          e.x = ex2_approx(t.x);
-          e.y = ex2_approx(t.y);
-          sum2[(i >> 1) & 1] = add2(sum2[(i >> 1) & 1], e);
-          pk[i >> 1] = pack2<T>(e.x, e.y);
+        for (int i = 0; i < 32; i += 4) {
+          const float2 ta = fma2(make_float2(__uint_as_float(sr[ch * 32 + i]), __uint_as_float(sr[ch * 32 + i + 1])),
+                                 c2, nm2);
+          const float2 tb =
+              fma2(make_float2(__uint_as_float(sr[ch * 32 + i + 2]), __uint_as_float(sr[ch * 32 + i + 3])), c2, nm2);
+          float2 ea, eb;
+          ea.x = ex2_approx(ta.x);
+          ea.y = ex2_approx(ta.y);
+          eb.x = ex2_approx(tb.x);
+          eb.y = ex2_approx(tb.y);
+          sum2[0] = add2(sum2[0], ea);
+          sum2[1] = add2(sum2[1], eb);
+          if constexpr (F8) {
+            pk[i >> 2] = pack4_fp8<T>(ea.x, ea.y, eb.x, eb.y);
+          } else {
+            pk[i >> 1] = pack2<T>(ea.x, ea.y);
+            pk[(i >> 1) + 1] = pack2<T>(eb.x, eb.y);
+          }
         }
-        tmem_st16(tS + ch * 16, pk);
+        if constexpr (F8)
+          tmem_st8(tS + ch * 8, pk);
+        else
+          tmem_st16(tS + ch * 16, pk);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -773,14 +821,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
                   make_float4(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv,
                               __uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
           } else {
-            T* dst = reinterpret_cast<T*>(p.out) + obase + ch * 32;
+            TO* dst = reinterpret_cast<TO*>(p.out) + obase + ch * 32;
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
               uint4 v;
-              v.x = pack2<T>(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
-              v.y = pack2<T>(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
-              v.z = pack2<T>(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
-              v.w = pack2<T>(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+              v.x = pack2<TO>(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+              v.y = pack2<TO>(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+              v.z = pack2<TO>(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+              v.w = pack2<TO>(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
               *reinterpret_cast<uint4*>(dst + i) = v;
             }
           }
@@ -802,7 +850,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
 template <int HD, typename T, int KIND>
 cudaError_t launch_one(const FwdKernelParams& p, cudaStream_t stream) {
   auto kern = fwd_kernel<HD, T, KIND>;
-  constexpr int smem = FwdSmem<HD>::kTotal;
+  constexpr int smem = FwdSmem<HD, sizeof(T)>::kTotal;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -830,6 +878,8 @@ cudaError_t launch_fwd(const FwdKernelParams& p, int kind, int dtype, int head_d
   FSA_FWD_CASE(128, __half, DT_FP16)
   FSA_FWD_CASE(64, __nv_bfloat16, DT_BF16)
   FSA_FWD_CASE(64, __half, DT_FP16)
+  FSA_FWD_CASE(128, __nv_fp8_e4m3, DT_E4M3)
+  FSA_FWD_CASE(128, __nv_fp8_e5m2, DT_E5M2)
 #undef FSA_FWD_CASE
   return cudaErrorInvalidValue;
 }

@@ -113,7 +113,9 @@ def attn_forward(
         # FP8 inputs: widened (exactly) to bf16 in one pass; the per-tensor scales stay on the device and
         # enter the kernel as in scheduler.py:298-307 (logit scale *= q_scale * k_scale, out *= v_scale)
         qkv_scale = quant.scales_f32(query_scale, key_scale, value_scale, device)
-        query, key, value = (quant.widen_fp8(t, torch.bfloat16) for t in (query, key, value))
+        native = head_dim == 128 and query.dtype == key.dtype == value.dtype
+        if not native:  # other head sizes / mixed formats: widen (exactly) to bf16 and use the 16-bit kernel
+            query, key, value = (quant.widen_fp8(t, torch.bfloat16) for t in (query, key, value))
 
     if is_split_kv and num_splits is None:
         num_splits = utils.num_splits_heuristic(
@@ -173,8 +175,8 @@ def attn_forward(
         a.lse_stride_b, a.lse_stride_h = lse.stride(0), lse.stride(1)
     if kind == "gated":
         # alpha [B, Hq, Sq] / [Hq, Tq], delta [B, Hkv, Sk] / [Hkv, Tk] / paged [pages, Hkv, page] (position contiguous)
-        if alpha.dtype != query.dtype or delta.dtype != query.dtype:
-            alpha, delta = alpha.to(query.dtype), delta.to(query.dtype)
+        if alpha.dtype != out_dtype or delta.dtype != out_dtype:
+            alpha, delta = alpha.to(out_dtype), delta.to(out_dtype)
             a.alpha, a.delta = alpha.data_ptr(), delta.data_ptr()
         a.alpha_stride_b, a.alpha_stride_h = (0, alpha.stride(0)) if varlen else (alpha.stride(0), alpha.stride(1))
         a.delta_stride_b, a.delta_stride_h = (0, delta.stride(0)) if varlen else (delta.stride(0), delta.stride(1))

@@ -100,7 +100,9 @@ typedef struct FsaFwdArgs {
   uint32_t flags;
   float softmax_scale, softmax_threshold, gate_threshold;
   /* optional: three fp32 values on the device, the per-tensor de-quantisation scales of q, k, v
-   * (scheduler.py:298-307: logits scale *= q_scale * k_scale; out *= v_scale). Null = all 1. */
+   * (scheduler.py:298-307: logits scale *= q_scale * k_scale; out *= v_scale). Null = all 1.
+   * With dtype FSA_DT_E4M3 / FSA_DT_E5M2 (head_dim 128) q, k, v are FP8, both GEMMs run as
+   * tcgen05 kind::f8f6f4 with P rounded to the same FP8 format, out / alpha / delta are bf16. */
   const float* qkv_scale;
 } FsaFwdArgs;
 

@@ -125,3 +125,40 @@ def test_quant_decode(mode):
     _sync()
     assert out.dtype == torch.bfloat16
     assert_close("quant-decode-" + mode, out, ref, **QTOL)
+
+
+def test_quant_forward_e4m3_varlen_split():
+    """Packed sequences, e4m3 inputs, split-KV with combine: the shape of the varlen + fused-quant config."""
+    import itertools
+
+    fsa = _ops()
+    lens = [256, 777, 1300, 129]
+    cu = torch.tensor([0] + list(itertools.accumulate(lens)), dtype=torch.int32)
+    g = torch.Generator().manual_seed(21)
+    mk = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16)  # noqa: E731
+    q, k, v = mk(sum(lens), 8, 128), mk(sum(lens), 2, 128), mk(sum(lens), 2, 128)
+    q8, k8, v8 = (eager.quantize_fp8(t, torch.float8_e4m3fn) for t in (q, k, v))
+    qd, kd, vd = ((t.float() * s.float()).to(torch.bfloat16) for t, s in (q8, k8, v8))
+    ref = eager.varlen_forward(qd, kd, vd, cu, cu, None, True)
+    for split in (False, True):
+        out = fsa.flash_sparse_attn_varlen_func(
+            q8[0].to(DEV), k8[0].to(DEV), v8[0].to(DEV), cu.to(DEV), cu.to(DEV), max(lens), max(lens), is_causal=True,
+            softmax_threshold=-128.0, is_quant=True, query_scale=q8[1].to(DEV), key_scale=k8[1].to(DEV),
+            value_scale=v8[1].to(DEV), is_split_kv=split, num_splits=3 if split else None)
+        _sync()
+        assert out.dtype == torch.bfloat16
+        assert_close(f"quant-e4m3-varlen-split{int(split)}", out, ref, **QTOL)
+
+
+@pytest.mark.parametrize("head_dim,pack", [(64, False), (128, True)])
+def test_quant_forward_other_shapes(head_dim, pack):
+    """head_dim 64 takes the widening route, head_dim 128 with packed GQA rows the native FP8 kernel."""
+    fsa = _ops()
+    b, s, hq, hkv = 1, 640, 8, 2
+    (q8, k8, v8), (qd, kd, vd) = _quantized(7, b, s, s, hq, hkv, head_dim)
+    ref = eager.forward(qd, kd, vd, None, True)
+    out = fsa.flash_dense_attn_func(q8[0].to(DEV), k8[0].to(DEV), v8[0].to(DEV), is_causal=True, is_quant=True,
+                                    query_scale=q8[1].to(DEV), key_scale=k8[1].to(DEV), value_scale=v8[1].to(DEV),
+                                    pack_gqa=pack)
+    _sync()
+    assert_close(f"quant-hd{head_dim}-pack{int(pack)}", out, ref, **QTOL)
