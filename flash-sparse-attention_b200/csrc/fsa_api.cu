@@ -74,6 +74,11 @@ int make_map4(CUtensorMap* map, int dt, const void* base, uint64_t head_dim, uin
 
 int cdiv(int a, int b) { return (a + b - 1) / b; }
 
+// Head sizes that are a multiple of 8 up to 128 run on the 64- or 128-wide kernels: TMA fills the missing
+// columns of every row with zeros (they add nothing to any dot product) and the epilogues do not write them.
+bool head_dim_ok(int d) { return d >= 8 && d <= 128 && d % 8 == 0; }
+int head_dim_kernel(int d) { return d <= 64 ? 64 : 128; }
+
 cudaEvent_t g_ev_before = nullptr, g_ev_after = nullptr;
 void mark_before(cudaStream_t s) {
   if (g_ev_before) cudaEventRecord(g_ev_before, s);
@@ -97,7 +102,7 @@ const char* fsa_status_string(int code) {
   switch (code) {
     case FSA_OK: return "ok";
     case FSA_ERR_INVALID_ARG: return "invalid argument (null pointer, bad size, or stride/base not 16-byte aligned)";
-    case FSA_ERR_UNSUPPORTED: return "unsupported combination (head_dim must be 64 or 128, dtype bf16/fp16, ...)";
+    case FSA_ERR_UNSUPPORTED: return "unsupported combination (head_dim must be a multiple of 8 up to 128, dtype bf16/fp16/fp8, ...)";
     case FSA_ERR_LAUNCH: return "CUDA error at launch or tensor-map creation";
     case FSA_ERR_NO_DRIVER: return "CUDA driver entry point cuTensorMapEncodeTiled unavailable";
     case FSA_ERR_SCRATCH_TOO_SMALL:
@@ -166,7 +171,7 @@ size_t fsa_fwd_tile_map_bytes(const FsaFwdArgs* a) {
 int fsa_fwd(const FsaFwdArgs* a, void* stream_) {
   if (!a || !a->q || !a->k || !a->v || !a->out || !a->lse || !a->status) return FSA_ERR_INVALID_ARG;
   if (a->batch <= 0 || a->heads_q <= 0 || a->head_dim <= 0) return FSA_ERR_INVALID_ARG;
-  if (a->head_dim != 64 && a->head_dim != 128) return FSA_ERR_UNSUPPORTED;
+  if (!head_dim_ok(a->head_dim)) return FSA_ERR_UNSUPPORTED;
   const bool fp8 = a->dtype == FSA_DT_E4M3 || a->dtype == FSA_DT_E5M2;
   if (a->dtype != FSA_DT_BF16 && a->dtype != FSA_DT_FP16 && !fp8) return FSA_ERR_UNSUPPORTED;
   if (fp8 && a->head_dim != 128) return FSA_ERR_UNSUPPORTED;  // FP8 tiles: one 128-byte swizzle row per head row
@@ -305,7 +310,8 @@ int fsa_fwd(const FsaFwdArgs* a, void* stream_) {
   p.flags = f;
 
   mark_before(stream);
-  cudaError_t e = fsa::launch_fwd(p, a->kind, a->dtype, a->head_dim, stream);
+  p.D = a->head_dim;
+  cudaError_t e = fsa::launch_fwd(p, a->kind, a->dtype, head_dim_kernel(a->head_dim), stream);
   mark_after(stream);
   if (e == cudaErrorInvalidValue) return FSA_ERR_UNSUPPORTED;
   if (e != cudaSuccess) return FSA_ERR_LAUNCH;
@@ -346,7 +352,8 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
     return FSA_ERR_INVALID_ARG;
   if (!a->lse2_ws || !a->dpsum_ws || !a->dq_accum) return FSA_ERR_INVALID_ARG;
   if (a->batch <= 0 || a->heads_q <= 0 || a->heads_kv <= 0 || a->heads_q % a->heads_kv) return FSA_ERR_INVALID_ARG;
-  if (a->head_dim != 64 && a->head_dim != 128) return FSA_ERR_UNSUPPORTED;
+  if (!head_dim_ok(a->head_dim)) return FSA_ERR_UNSUPPORTED;
+  const int hdk = head_dim_kernel(a->head_dim);  // also the row pitch of dq_accum
   if (a->dtype != FSA_DT_BF16 && a->dtype != FSA_DT_FP16) return FSA_ERR_UNSUPPORTED;
   if (a->kind != FSA_KIND_DENSE && a->kind != FSA_KIND_SPARSE && a->kind != FSA_KIND_GATED)
     return FSA_ERR_UNSUPPORTED;
@@ -395,6 +402,7 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
   pre.total_q = a->total_q;
   pre.heads = a->heads_q;
   pre.head_dim = a->head_dim;
+  pre.head_dim_pad = hdk;
   pre.varlen = varlen_q;
   if (gated) {
     if (cudaMemsetAsync(a->alpha_ws, 0, 2 * (size_t)a->heads_q * R, stream) != cudaSuccess) return FSA_ERR_LAUNCH;
@@ -409,7 +417,7 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
   if (cudaMemsetAsync(a->dpsum_ws, 0, sizeof(float) * (size_t)a->heads_q * R, stream) != cudaSuccess)
     return FSA_ERR_LAUNCH;
   if (fsa::launch_bwd_pre(pre, a->dtype, stream) != cudaSuccess) return FSA_ERR_LAUNCH;
-  if (cudaMemsetAsync(a->dq_accum, 0, sizeof(float) * (size_t)a->heads_q * R * a->head_dim, stream) != cudaSuccess)
+  if (cudaMemsetAsync(a->dq_accum, 0, sizeof(float) * (size_t)a->heads_q * R * hdk, stream) != cudaSuccess)
     return FSA_ERR_LAUNCH;
 
   fsa::BwdKernelParams p;
@@ -435,7 +443,7 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
                    varlen_k ? a->v_stride_s * (int64_t)a->total_k : a->v_stride_b, 64, 1, 128);
     if (rc != FSA_OK) return rc;
   }
-  rc = make_map_dq(&p.map_dq, a->dq_accum, a->head_dim, R, a->heads_q);
+  rc = make_map_dq(&p.map_dq, a->dq_accum, hdk, R, a->heads_q);
   if (rc != FSA_OK) return rc;
   p.lse2_ws = a->lse2_ws;
   p.dpsum_ws = a->dpsum_ws;
@@ -523,7 +531,8 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
     p.flags |= fsa::F_DETERMINISTIC;
   }
   mark_before(stream);
-  cudaError_t e = fsa::launch_bwd(p, a->kind, a->dtype, a->head_dim, stream);
+  p.D = a->head_dim;
+  cudaError_t e = fsa::launch_bwd(p, a->kind, a->dtype, hdk, stream);
   mark_after(stream);
   if (e == cudaErrorInvalidValue) return FSA_ERR_UNSUPPORTED;
   if (e != cudaSuccess) return FSA_ERR_LAUNCH;
@@ -542,6 +551,7 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
   post.total_q = a->total_q;
   post.heads = a->heads_q;
   post.head_dim = a->head_dim;
+  post.head_dim_pad = hdk;
   post.varlen = varlen_q;
   post.scale = a->softmax_scale;
   if (gated) {
@@ -615,7 +625,7 @@ int fsa_combine(const float* out_partial, const float* lse_partial, void* out, f
 int fsa_decode(const FsaDecArgs* a, void* stream_) {
   if (!a || !a->q || !a->k || !a->v || !a->status) return FSA_ERR_INVALID_ARG;
   if (a->batch <= 0 || a->heads_q <= 0 || a->heads_kv <= 0 || a->heads_q % a->heads_kv) return FSA_ERR_INVALID_ARG;
-  if (a->head_dim != 64 && a->head_dim != 128) return FSA_ERR_UNSUPPORTED;
+  if (!head_dim_ok(a->head_dim)) return FSA_ERR_UNSUPPORTED;
   if (a->dtype != FSA_DT_BF16 && a->dtype != FSA_DT_FP16) return FSA_ERR_UNSUPPORTED;
   if (a->kind != FSA_KIND_DENSE && a->kind != FSA_KIND_SPARSE && a->kind != FSA_KIND_GATED) return FSA_ERR_UNSUPPORTED;
   if (a->kind == FSA_KIND_GATED && (!a->alpha || !a->delta)) return FSA_ERR_INVALID_ARG;
@@ -690,7 +700,8 @@ int fsa_decode(const FsaDecArgs* a, void* stream_) {
   if (a->flags & FSA_F_LOGSIGMOID) f |= fsa::F_LOGSIGMOID;
   p.flags = f;
   mark_before(stream);
-  cudaError_t e = fsa::launch_dec(p, a->kind, a->dtype, a->head_dim, stream);
+  p.D = a->head_dim;
+  cudaError_t e = fsa::launch_dec(p, a->kind, a->dtype, head_dim_kernel(a->head_dim), stream);
   mark_after(stream);
   if (e == cudaErrorInvalidValue) return FSA_ERR_UNSUPPORTED;
   if (e != cudaSuccess) return FSA_ERR_LAUNCH;

@@ -108,15 +108,15 @@ __device__ __forceinline__ RowPos locate_row(long long item, int heads, int varl
 // head_dim / 8 lanes per (query row, head), 16-byte loads. flash_sparse_attn/ops/triton/flash_bwd_preprocess.py:170-195.
 template <typename T>
 __global__ void __launch_bounds__(256) bwd_pre_kernel(BwdPreParams p) {
-  const int lpr = p.head_dim >> 3;  // lanes per row (8 or 16)
+  const int lpr = p.head_dim_pad >> 3;  // lanes per row (8 or 16); lanes past the real head size idle
   const int lane = threadIdx.x & 31, sub = lane % lpr;
   const long long item = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (32 / lpr) + lane / lpr;
   const long long rows = p.varlen ? p.total_q : (long long)p.B * p.sq;
   const bool live = item < rows * p.heads;
   float acc = 0.f;
   RowPos r = {0, 0, 0, 0};
-  if (live) {
-    r = locate_row(item, p.heads, p.varlen, p.cu_q, p.B, p.sq);
+  if (live) r = locate_row(item, p.heads, p.varlen, p.cu_q, p.B, p.sq);
+  if (live && sub * 8 < p.head_dim) {
     const T* o = reinterpret_cast<const T*>(p.out) + (p.varlen ? 0 : (long long)r.b * p.o_sb) + r.tok * p.o_sm +
                  (long long)r.h * p.o_sh + sub * 8;
     const T* d = reinterpret_cast<const T*>(p.dout) + (p.varlen ? 0 : (long long)r.b * p.do_sb) + r.tok * p.do_sm +
@@ -148,14 +148,18 @@ __global__ void __launch_bounds__(256) bwd_pre_kernel(BwdPreParams p) {
 // head_dim / 8 lanes per (query row, head). flash_sparse_attn/ops/triton/flash_bwd_postprocess.py:60-148.
 template <typename T>
 __global__ void __launch_bounds__(256) bwd_post_kernel(BwdPostParams p) {
-  const int lpr = p.head_dim >> 3;
+  const int lpr = p.head_dim_pad >> 3;
   const int lane = threadIdx.x & 31, sub = lane % lpr;
   const long long item = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (32 / lpr) + lane / lpr;
   const long long rows = p.varlen ? p.total_q : (long long)p.B * p.sq;
   if (item >= rows * p.heads) return;
   const RowPos r = locate_row(item, p.heads, p.varlen, p.cu_q, p.B, p.sq);
   const long long wrow = (long long)r.h * p.ws_sh + padded_row(p.varlen, p.cu_q, r.b, p.sq, r.q);
-  const float4* src = reinterpret_cast<const float4*>(p.dq_accum + wrow * p.head_dim + sub * 8);
+  if (p.da && sub == 0)
+    reinterpret_cast<T*>(p.da)[(p.varlen ? 0 : (long long)r.b * p.da_sb) + (long long)r.h * p.da_sh + r.tok] =
+        T(p.da_accum[wrow] * p.scale);
+  if (sub * 8 >= p.head_dim) return;
+  const float4* src = reinterpret_cast<const float4*>(p.dq_accum + wrow * p.head_dim_pad + sub * 8);
   const float4 v0 = __ldcs(src), v1 = __ldcs(src + 1);  // read once: do not keep in cache
   uint4 o;
   o.x = pack2<T>(v0.x * p.scale, v0.y * p.scale);
@@ -165,9 +169,6 @@ __global__ void __launch_bounds__(256) bwd_post_kernel(BwdPostParams p) {
   T* dst = reinterpret_cast<T*>(p.dq) + (p.varlen ? 0 : (long long)r.b * p.dq_sb) + r.tok * p.dq_sm +
            (long long)r.h * p.dq_sh + sub * 8;
   *reinterpret_cast<uint4*>(dst) = o;
-  if (p.da && sub == 0)
-    reinterpret_cast<T*>(p.da)[(p.varlen ? 0 : (long long)r.b * p.da_sb) + (long long)r.h * p.da_sh + r.tok] =
-        T(p.da_accum[wrow] * p.scale);
 }
 
 __global__ void __launch_bounds__(128) dq_order_kernel(DqOrderParams p) {
@@ -243,8 +244,8 @@ cudaError_t launch_bwd_pre(const BwdPreParams& p, int dtype, cudaStream_t stream
   const long long rows = p.varlen ? p.total_q : (long long)p.B * p.sq;
   const long long items = rows * p.heads;
   if (items <= 0) return cudaSuccess;
-  if (p.head_dim != 64 && p.head_dim != 128) return cudaErrorInvalidValue;
-  const int per_block = 8 * (32 / (p.head_dim >> 3));
+  if (p.head_dim_pad != 64 && p.head_dim_pad != 128) return cudaErrorInvalidValue;
+  const int per_block = 8 * (32 / (p.head_dim_pad >> 3));
   const unsigned grid = (unsigned)((items + per_block - 1) / per_block);
   if (dtype == DT_BF16)
     bwd_pre_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
@@ -257,8 +258,8 @@ cudaError_t launch_bwd_post(const BwdPostParams& p, int dtype, cudaStream_t stre
   const long long rows = p.varlen ? p.total_q : (long long)p.B * p.sq;
   const long long items = rows * p.heads;
   if (items <= 0) return cudaSuccess;
-  if (p.head_dim != 64 && p.head_dim != 128) return cudaErrorInvalidValue;
-  const int per_block = 8 * (32 / (p.head_dim >> 3));
+  if (p.head_dim_pad != 64 && p.head_dim_pad != 128) return cudaErrorInvalidValue;
+  const int per_block = 8 * (32 / (p.head_dim_pad >> 3));
   const unsigned grid = (unsigned)((items + per_block - 1) / per_block);
   if (dtype == DT_BF16)
     bwd_post_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);

@@ -34,6 +34,7 @@ struct BwdPreParams {
   long long a_sb, a_sh;
   long long o_sb, o_sm, o_sh, do_sb, do_sm, do_sh, l_sb, l_sh, ws_sh;
   int B, sq, total_q, heads, head_dim, varlen;
+  int head_dim_pad;  // 64 or 128: lanes per row = head_dim_pad / 8
 };
 // Backward post-pass: dq = dq_accum * scale in the 16-bit type (and dalpha = da_accum * scale when given,
 // flash_sparse_attn/ops/triton/flash_bwd_postprocess.py:106-148).
@@ -46,6 +47,7 @@ struct BwdPostParams {
   long long da_sb, da_sh;
   long long dq_sb, dq_sm, dq_sh, ws_sh;
   int B, sq, total_q, heads, head_dim, varlen;
+  int head_dim_pad;  // row pitch of dq_accum (64 or 128)
   float scale;
 };
 // Sum of per-split fp32 partials [splits, n] into a strided 16-bit tensor of rows x heads x head_dim.

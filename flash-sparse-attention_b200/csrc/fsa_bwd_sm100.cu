@@ -950,9 +950,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
                 float* dst = reinterpret_cast<float*>(outp) + base + ch * 32;
 #pragma unroll
                 for (int i = 0; i < 32; i += 4)
-                  *reinterpret_cast<float4*>(dst + i) =
-                      make_float4(__uint_as_float(r[i]) * mul, __uint_as_float(r[i + 1]) * mul,
-                                  __uint_as_float(r[i + 2]) * mul, __uint_as_float(r[i + 3]) * mul);
+                  if (wg * HALF + ch * 32 + i < p.D)
+                    *reinterpret_cast<float4*>(dst + i) =
+                        make_float4(__uint_as_float(r[i]) * mul, __uint_as_float(r[i + 1]) * mul,
+                                    __uint_as_float(r[i + 2]) * mul, __uint_as_float(r[i + 3]) * mul);
               } else {
                 T* dst = reinterpret_cast<T*>(outp) + base + ch * 32;
 #pragma unroll
@@ -962,7 +963,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
                   v.y = pack2<T>(__uint_as_float(r[i + 2]) * mul, __uint_as_float(r[i + 3]) * mul);
                   v.z = pack2<T>(__uint_as_float(r[i + 4]) * mul, __uint_as_float(r[i + 5]) * mul);
                   v.w = pack2<T>(__uint_as_float(r[i + 6]) * mul, __uint_as_float(r[i + 7]) * mul);
-                  *reinterpret_cast<uint4*>(dst + i) = v;
+                  if (wg * HALF + ch * 32 + i < p.D) *reinterpret_cast<uint4*>(dst + i) = v;
                 }
               }
             }

@@ -162,7 +162,7 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
       const int item = it * 32 + lane;
       const int r = item / CH, ch = item % CH;
       const long long er = __shfl_sync(0xffffffffu, e, r);
-      const bool ok = er >= 0;
+      const bool ok = er >= 0 && ch * 8 < p.D;  // columns past the real head size read as zeros
       const long long src = ok ? (er + ch * 8) * 2 : 0;
       const uint32_t dsto = r * SM::kRow + ((ch ^ (r & 7)) << 4);
       cp_async16(kt + dsto, kbase + src, ok);
@@ -181,10 +181,11 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
       const T* q1 = reinterpret_cast<const T*>(p.q) + (long long)b * p.q_sb + (long long)(hkv * p.G + r1) * p.q_sh;
 #pragma unroll
       for (int kk = 0; kk < HD / 16; ++kk) {
-        qa[kk][0] = (r0 < p.G) ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 2 * t) : 0u;
-        qa[kk][1] = (r1 < p.G) ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 2 * t) : 0u;
-        qa[kk][2] = (r0 < p.G) ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 8 + 2 * t) : 0u;
-        qa[kk][3] = (r1 < p.G) ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 8 + 2 * t) : 0u;
+        const bool lo = kk * 16 + 2 * t < p.D, hi = kk * 16 + 8 + 2 * t < p.D;
+        qa[kk][0] = (r0 < p.G && lo) ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 2 * t) : 0u;
+        qa[kk][1] = (r1 < p.G && lo) ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 2 * t) : 0u;
+        qa[kk][2] = (r0 < p.G && hi) ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 8 + 2 * t) : 0u;
+        qa[kk][3] = (r1 < p.G && hi) ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 8 + 2 * t) : 0u;
       }
     }
     const bool row0_ok = mt * 16 + g < p.G, row1_ok = mt * 16 + g + 8 < p.G;
@@ -416,7 +417,7 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
     for (int item = tid; item < 16 * (HD / 4); item += DWARPS * 32) {
       const int r = item / (HD / 4), d0 = (item % (HD / 4)) * 4;
       const int row = mt * 16 + r;
-      if (row >= p.G) continue;
+      if (row >= p.G || d0 >= p.D) continue;
       float m_tot = -INFINITY;
 #pragma unroll
       for (int ww = 0; ww < DWARPS; ++ww) m_tot = fmaxf(m_tot, all[ww * (16 * HD + 32) + 16 * HD + r]);
@@ -438,7 +439,7 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
       const float inv = dead ? 1.f : v_scale / l_tot;
       const int head = hkv * p.G + row;
       if (p.flags & F_SPLIT) {
-        float* dst = p.out_partial + (((long long)split * p.B + b) * p.Hq + head) * HD + d0;
+        float* dst = p.out_partial + (((long long)split * p.B + b) * p.Hq + head) * p.D + d0;
         *reinterpret_cast<float4*>(dst) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
         if (d0 == 0)
           p.lse_partial[((long long)split * p.Hq + head) * p.B + b] = dead ? -INFINITY : m_tot * c + log2f(l_tot);

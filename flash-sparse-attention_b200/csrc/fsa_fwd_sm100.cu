@@ -817,9 +817,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
             float* dst = reinterpret_cast<float*>(p.out) + obase + ch * 32;
 #pragma unroll
             for (int i = 0; i < 32; i += 4)
-              *reinterpret_cast<float4*>(dst + i) =
-                  make_float4(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv,
-                              __uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+              if (ch * 32 + i < p.D)
+                *reinterpret_cast<float4*>(dst + i) =
+                    make_float4(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv,
+                                __uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
           } else {
             TO* dst = reinterpret_cast<TO*>(p.out) + obase + ch * 32;
 #pragma unroll
@@ -829,7 +830,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
               v.y = pack2<TO>(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
               v.z = pack2<TO>(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
               v.w = pack2<TO>(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
-              *reinterpret_cast<uint4*>(dst + i) = v;
+              if (ch * 32 + i < p.D) *reinterpret_cast<uint4*>(dst + i) = v;
             }
           }
         }

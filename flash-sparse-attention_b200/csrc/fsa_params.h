@@ -45,6 +45,7 @@ struct alignas(64) FwdKernelParams {
   long long l_sb, l_sh, l_ss;
   long long a_sb, a_sh, d_sb, d_sh;
   int B, Hq, Hkv, G, gpack;
+  int D;       // real head size (<= the kernel's HD; the tail loads as zeros and is not written)
   int sq, sk;  // static lengths (max lengths for varlen)
   int num_splits, num_m_blocks, num_pairs, hgrid;
   int page_size, pt_stride, win_stride, n_tiles_k;
@@ -76,6 +77,7 @@ struct alignas(64) BwdKernelParams {
   long long d_sb, d_sh, dd_ss;
   long long dkv_sb, dkv_sn, dkv_sh, dkv_ss;
   long long ws_sh;
+  int D;  // real head size (<= the kernel's HD)
   int B, Hq, Hkv, G;
   int sq, sk;
   int num_splits, n_tiles_k, num_m_blocks, win_stride;
@@ -105,6 +107,7 @@ struct DecKernelParams {
   int num_splits, page_size, pt_stride, gi_stride, win_stride, n_tiles;
   float scale_log2, softmax_thr, gate_thr;
   const float* qkv_scale;  // optional device fp32 [3]
+  int D;  // real head size (<= the kernel's HD)
   unsigned flags;
 };
 

@@ -125,7 +125,8 @@ def attn_backward(
     rows_pad = lib.fsa_bwd_padded_rows(batch, seqlen_q, total_q, int(varlen))
     lse2_ws = torch.empty((num_heads_q, rows_pad), dtype=torch.float32, device=device)
     dpsum_ws = torch.empty((num_heads_q, rows_pad), dtype=torch.float32, device=device)
-    dq_accum = torch.empty((num_heads_q, rows_pad, head_dim), dtype=torch.float32, device=device)
+    # rows of the accumulator are as wide as the kernel's head tile (64 or 128 columns)
+    dq_accum = torch.empty((num_heads_q, rows_pad, 64 if head_dim <= 64 else 128), dtype=torch.float32, device=device)
     dk_partial = dv_partial = None
     if use_split:
         rows_k = total_k if varlen else batch * seqlen_k

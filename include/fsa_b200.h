@@ -122,7 +122,7 @@ size_t fsa_fwd_tile_map_bytes(const FsaFwdArgs* args);
  * q/k/v/out/dout/dq/dk/dv use the forward layouts (dout, dq like q; dk, dv like k). lse is the forward
  * output (natural log). Caller-owned fp32 workspaces, all sized with R = fsa_bwd_padded_rows():
  *   lse2_ws  [heads_q, R]            dpsum_ws [heads_q, R]
- *   dq_accum [heads_q, R, head_dim]  (zeroed by this call)
+ *   dq_accum [heads_q, R, head_dim rounded up to 64 or 128]  (zeroed by this call)
  *   dk_partial, dv_partial [num_splits, rows_k, heads_kv, head_dim] only when FSA_F_SPLIT and
  *   num_splits > 1 (rows_k = batch*seqlen_k or total_k); otherwise null.
  * dq is accumulated with TMA reduce-adds in fp32 (summation order across key tiles is not fixed,

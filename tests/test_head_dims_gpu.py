@@ -1,0 +1,89 @@
+"""Head sizes other than 64 / 128 (any multiple of 16 up to 128, the reference's contract
+`assert_inputs.py:39-40` up to that size): forward, backward and decode run on the 64- or 128-wide kernels
+with the missing columns loaded as zeros; results are compared with the eager oracle."""
+
+import pytest
+import torch
+
+from fixtures import assert_close, seeded_qkv
+from oracle import eager
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _ops():
+    import flash_sparse_attn as fsa
+
+    return fsa
+
+
+@pytest.mark.parametrize("head_dim", [16, 32, 48, 80, 96, 112])
+@pytest.mark.parametrize("kind", ["dense", "sparse", "gated"])
+def test_forward_backward_other_head_dims(head_dim, kind):
+    fsa = _ops()
+    b, s, hq, hkv = 2, 384, 4, 2
+    q, k, v = seeded_qkv(head_dim, b, s, s, hq, hkv, head_dim)
+    g = torch.Generator().manual_seed(3)
+    do = torch.randn(b, s, hq, head_dim, generator=g).to(torch.bfloat16)
+    a, d = torch.randn(b, s, hq, generator=g).to(torch.bfloat16), torch.randn(b, s, hkv, generator=g).to(torch.bfloat16)
+    gate = dict(alpha=a, delta=d) if kind == "gated" else {}
+    ref_out = eager.forward(q, k, v, None, True, **gate)
+    ref_grads = eager.backward(q, k, v, do, None, True, **gate)
+    leaves = [t.to(DEV).requires_grad_(True) for t in ((q, k, v, a, d) if kind == "gated" else (q, k, v))]
+    kw = {}
+    if kind != "dense":
+        kw["softmax_threshold"] = -128.0
+    if kind == "gated":
+        kw["gate_threshold"] = -128.0
+    fn = {"dense": fsa.flash_dense_attn_func, "sparse": fsa.flash_sparse_attn_func,
+          "gated": fsa.flash_gated_attn_func}[kind]
+    out = fn(*leaves, is_causal=True, **kw)
+    out.backward(do.to(DEV))
+    torch.cuda.synchronize()
+    fsa.check_status()
+    assert out.shape == (b, s, hq, head_dim)
+    assert_close(f"hd{head_dim}-{kind}-out", out, ref_out)
+    for name, t, r in zip(("dq", "dk", "dv", "dalpha", "ddelta"), leaves, ref_grads):
+        assert_close(f"hd{head_dim}-{kind}-{name}", t.grad, r, rtol=2.5e-2, atol=2.5e-2)
+
+
+@pytest.mark.parametrize("head_dim", [32, 96])
+def test_split_paths_other_head_dims(head_dim):
+    """Split-KV forward (fp32 partials + combine) and split-QO backward (fp32 dK/dV partials)."""
+    fsa = _ops()
+    b, s, hq, hkv = 1, 1024, 4, 2
+    q, k, v = seeded_qkv(head_dim + 1, b, s, s, hq, hkv, head_dim)
+    do = torch.randn(b, s, hq, head_dim, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16)
+    ref_out = eager.forward(q, k, v, None, True)
+    ref = eager.backward(q, k, v, do, None, True)
+    leaves = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    out = fsa.flash_sparse_attn_func(*leaves, is_causal=True, softmax_threshold=-128.0, is_split_kv=True,
+                                     is_split_qo=True, num_splits=3)
+    out.backward(do.to(DEV))
+    torch.cuda.synchronize()
+    fsa.check_status()
+    assert_close(f"hd{head_dim}-split-out", out, ref_out)
+    for name, t, r in zip(("dq", "dk", "dv"), leaves, ref):
+        assert_close(f"hd{head_dim}-split-{name}", t.grad, r, rtol=2.5e-2, atol=2.5e-2)
+
+
+@pytest.mark.parametrize("head_dim", [32, 80, 96])
+@pytest.mark.parametrize("mode", ["plain", "gather_split"])
+def test_decode_other_head_dims(head_dim, mode):
+    fsa = _ops()
+    b, sk, hq, hkv = 2, 1024, 16, 2
+    g = torch.Generator().manual_seed(head_dim)
+    mk = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16)  # noqa: E731
+    q, k, v = mk(b, hq, head_dim), mk(b, sk, hkv, head_dim), mk(b, sk, hkv, head_dim)
+    if mode == "plain":
+        ref = eager.decode(q, k, v)
+        out = fsa.flash_sparse_attn_with_kvcache_func(q.to(DEV), k.to(DEV), v.to(DEV), softmax_threshold=-128.0)
+    else:
+        idx = torch.stack([torch.randperm(sk, generator=g)[:512] for _ in range(b)]).to(torch.int32)
+        ref = eager.gather_decode(q, k, v, idx)
+        out = fsa.flash_sparse_attn_with_kvcache_func(q.to(DEV), k.to(DEV), v.to(DEV), gather_kv_indices=idx.to(DEV),
+                                                      softmax_threshold=-128.0, num_splits=4)
+    torch.cuda.synchronize()
+    fsa.check_status()
+    assert_close(f"hd{head_dim}-decode-{mode}", out, ref, rtol=2.5e-2, atol=2.5e-2)
