@@ -626,7 +626,9 @@ int fsa_decode(const FsaDecArgs* a, void* stream_) {
   if (!a || !a->q || !a->k || !a->v || !a->status) return FSA_ERR_INVALID_ARG;
   if (a->batch <= 0 || a->heads_q <= 0 || a->heads_kv <= 0 || a->heads_q % a->heads_kv) return FSA_ERR_INVALID_ARG;
   if (!head_dim_ok(a->head_dim)) return FSA_ERR_UNSUPPORTED;
-  if (a->dtype != FSA_DT_BF16 && a->dtype != FSA_DT_FP16) return FSA_ERR_UNSUPPORTED;
+  const bool fp8 = a->dtype == FSA_DT_E4M3 || a->dtype == FSA_DT_E5M2;  // q, k, v in FP8; out / alpha / delta bf16
+  if (a->dtype != FSA_DT_BF16 && a->dtype != FSA_DT_FP16 && !fp8) return FSA_ERR_UNSUPPORTED;
+  if (fp8 && a->head_dim != 128) return FSA_ERR_UNSUPPORTED;
   if (a->kind != FSA_KIND_DENSE && a->kind != FSA_KIND_SPARSE && a->kind != FSA_KIND_GATED) return FSA_ERR_UNSUPPORTED;
   if (a->kind == FSA_KIND_GATED && (!a->alpha || !a->delta)) return FSA_ERR_INVALID_ARG;
   if ((a->flags & FSA_F_LOCAL) && !a->window_sizes) return FSA_ERR_INVALID_ARG;
@@ -725,7 +727,7 @@ int fsa_decode(const FsaDecArgs* a, void* stream_) {
     c.heads = a->heads_q;
     c.head_dim = a->head_dim;
     c.num_splits = ns;
-    e = fsa::launch_combine(c, a->dtype, stream);
+    e = fsa::launch_combine(c, fp8 ? FSA_DT_BF16 : a->dtype, stream);
     if (e != cudaSuccess) return FSA_ERR_LAUNCH;
   }
   return FSA_OK;

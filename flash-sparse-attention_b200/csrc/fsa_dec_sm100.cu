@@ -31,9 +31,9 @@ constexpr int DTN = 16;      // keys per warp tile
 constexpr int DSTAGES = 3;   // cp.async ring depth per warp
 constexpr int DWARPS = 4;
 
-template <int HD>
+template <int HD, int ES = 2>
 struct DecSmem {
-  static constexpr int kRow = HD * 2;                 // bytes per key row
+  static constexpr int kRow = HD * ES;                // bytes per key row
   static constexpr int kTile = DTN * kRow;            // one K or V tile
   static constexpr int kWarp = DSTAGES * 2 * kTile;   // ring of one warp
   static constexpr int kMerge = DWARPS * (16 * HD * 4 + 16 * 8);  // O, m, l of every warp
@@ -59,6 +59,41 @@ __device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t&
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
                : "r"(addr));
 }
+// FP8 -> fp16 pairs (exact). `w` holds four FP8 bytes b0..b3; SEL picks two of them:
+// 0 -> (b0, b1), 1 -> (b2, b3), 2 -> (b0, b2), 3 -> (b1, b3).
+template <typename T, int SEL>
+__device__ __forceinline__ uint32_t fp8x2_to_f16x2(uint32_t w) {
+  constexpr int first = SEL == 0 ? 0 : (SEL == 1 ? 2 : (SEL == 2 ? 0 : 1));
+  constexpr int second = SEL == 0 ? 1 : (SEL == 1 ? 3 : (SEL == 2 ? 2 : 3));
+  uint32_t r;
+  if (__is_same(T, __nv_fp8_e5m2)) {
+    // e5m2 is the upper byte of an fp16: place the bytes at positions 1 and 3
+    asm("prmt.b32 %0, %1, 0, %2;" : "=r"(r) : "r"(w), "n"(0x0404 | (first << 4) | (second << 12)));
+  } else {
+    uint32_t pair;
+    asm("prmt.b32 %0, %1, 0, %2;" : "=r"(pair) : "r"(w), "n"(0x4400 | first | (second << 4)));
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, lo;\n\t}" : "=r"(r) : "r"(pair));
+  }
+  return r;
+}
+
+// Input element type -> type of the mma.sync operands / of the outputs and gate vectors.
+template <typename T>
+struct DecTypes {
+  using mma = T;
+  using out = T;
+};
+template <>
+struct DecTypes<__nv_fp8_e4m3> {
+  using mma = __half;
+  using out = __nv_bfloat16;
+};
+template <>
+struct DecTypes<__nv_fp8_e5m2> {
+  using mma = __half;
+  using out = __nv_bfloat16;
+};
+
 template <typename T>
 __device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1);
 template <>
@@ -80,8 +115,16 @@ __device__ __forceinline__ void mma16816<__half>(float* c, const uint32_t* a, ui
 
 template <int HD, typename T, int KIND>
 __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelParams p) {
-  using SM = DecSmem<HD>;
-  constexpr int CH = HD / 8;  // 16-byte chunks per key row
+  // T: element type of q, k, v. FP8 (e4m3 / e5m2, head size 128) tiles are copied as bytes and widened
+  // exactly to fp16 in registers in front of the fp16 mma.sync; a 16-byte chunk of a key row then holds
+  // 16 head columns, used in the order the fragments deliver them (q follows the same order).
+  constexpr int ES = sizeof(T);
+  constexpr bool F8 = ES == 1;
+  using TM = typename DecTypes<T>::mma;   // mma.sync operand type
+  using TO = typename DecTypes<T>::out;   // outputs, alpha, delta
+  using SM = DecSmem<HD, ES>;
+  constexpr int CH = HD * ES / 16;  // 16-byte chunks per key row
+  static_assert(!F8 || HD == 128, "FP8 rows are 128 bytes: eight chunks, as the swizzle assumes");
   extern __shared__ __align__(128) uint8_t dsm[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -150,7 +193,7 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
         const long long de = paged ? (long long)ptab[pos / p.page_size] * p.d_sb + (long long)hkv * p.d_sh +
                                          (pos % p.page_size)
                                    : (long long)bk * p.d_sb + (long long)hkv * p.d_sh + off_k + pos;
-        dv = float(reinterpret_cast<const T*>(p.delta)[de]);
+        dv = float(reinterpret_cast<const TO*>(p.delta)[de]);
       }
       *dval = __shfl_sync(0xffffffffu, dv, lane & 15);
     }
@@ -162,8 +205,8 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
       const int item = it * 32 + lane;
       const int r = item / CH, ch = item % CH;
       const long long er = __shfl_sync(0xffffffffu, e, r);
-      const bool ok = er >= 0 && ch * 8 < p.D;  // columns past the real head size read as zeros
-      const long long src = ok ? (er + ch * 8) * 2 : 0;
+      const bool ok = er >= 0 && ch * (16 / ES) < p.D;  // columns past the real head size read as zeros
+      const long long src = ok ? (er + ch * (16 / ES)) * ES : 0;
       const uint32_t dsto = r * SM::kRow + ((ch ^ (r & 7)) << 4);
       cp_async16(kt + dsto, kbase + src, ok);
       cp_async16(vt + dsto, vbase + src, ok);
@@ -179,13 +222,26 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
       const int r0 = mt * 16 + g, r1 = r0 + 8;
       const T* q0 = reinterpret_cast<const T*>(p.q) + (long long)b * p.q_sb + (long long)(hkv * p.G + r0) * p.q_sh;
       const T* q1 = reinterpret_cast<const T*>(p.q) + (long long)b * p.q_sb + (long long)(hkv * p.G + r1) * p.q_sh;
+      if constexpr (F8) {
+        // step kk uses head columns 16 kk + 4t .. +3: the first two as k = 2t, 2t+1, the others as k = 2t+8, 2t+9
 #pragma unroll
-      for (int kk = 0; kk < HD / 16; ++kk) {
-        const bool lo = kk * 16 + 2 * t < p.D, hi = kk * 16 + 8 + 2 * t < p.D;
-        qa[kk][0] = (r0 < p.G && lo) ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 2 * t) : 0u;
-        qa[kk][1] = (r1 < p.G && lo) ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 2 * t) : 0u;
-        qa[kk][2] = (r0 < p.G && hi) ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 8 + 2 * t) : 0u;
-        qa[kk][3] = (r1 < p.G && hi) ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 8 + 2 * t) : 0u;
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t w0 = (r0 < p.G) ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 4 * t) : 0u;
+          const uint32_t w1 = (r1 < p.G) ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 4 * t) : 0u;
+          qa[kk][0] = fp8x2_to_f16x2<T, 0>(w0);
+          qa[kk][1] = fp8x2_to_f16x2<T, 0>(w1);
+          qa[kk][2] = fp8x2_to_f16x2<T, 1>(w0);
+          qa[kk][3] = fp8x2_to_f16x2<T, 1>(w1);
+        }
+      } else {
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const bool lo = kk * 16 + 2 * t < p.D, hi = kk * 16 + 8 + 2 * t < p.D;
+          qa[kk][0] = (r0 < p.G && lo) ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 2 * t) : 0u;
+          qa[kk][1] = (r1 < p.G && lo) ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 2 * t) : 0u;
+          qa[kk][2] = (r0 < p.G && hi) ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 8 + 2 * t) : 0u;
+          qa[kk][3] = (r1 < p.G && hi) ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 8 + 2 * t) : 0u;
+        }
       }
     }
     const bool row0_ok = mt * 16 + g < p.G, row1_ok = mt * 16 + g + 8 < p.G;
@@ -194,7 +250,7 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
     float dl0 = 0.f, dl1 = 0.f, dl2 = 0.f;
     const float gate_thr_log2 = (KIND == KIND_GATED) ? log2f(p.gate_thr) : 0.f;
     if (KIND == KIND_GATED) {
-      const T* ab = reinterpret_cast<const T*>(p.alpha) + (long long)b * p.a_sb;
+      const TO* ab = reinterpret_cast<const TO*>(p.alpha) + (long long)b * p.a_sb;
       if (row0_ok) al0 = float(ab[(long long)(hkv * p.G + mt * 16 + g) * p.a_sh]);
       if (row1_ok) al1 = float(ab[(long long)(hkv * p.G + mt * 16 + g + 8) * p.a_sh]);
       a_max = fmaxf(row0_ok ? al0 : -INFINITY, row1_ok ? al1 : -INFINITY);
@@ -288,16 +344,34 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
       float s[2][4];
 #pragma unroll
       for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+      if constexpr (F8) {
+        // one ldmatrix.x4 = four 16-byte chunks = four k-steps; every register carries the four head
+        // columns 4t .. 4t+3 of its chunk for key row g
 #pragma unroll
-      for (int kk = 0; kk < HD / 16; kk += 2) {
+        for (int kk = 0; kk < HD / 16; kk += 4) {
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int r = 8 * j + (lane & 7);
-          const int ch = 2 * kk + (lane >> 3);
-          uint32_t b0, b1, b2, b3;
-          ldsm_x4(kt + r * SM::kRow + ((ch ^ (r & 7)) << 4), b0, b1, b2, b3);
-          mma16816<T>(s[j], qa[kk], b0, b1);
-          mma16816<T>(s[j], qa[kk + 1], b2, b3);
+          for (int j = 0; j < 2; ++j) {
+            const int r = 8 * j + (lane & 7);
+            const int ch = kk + (lane >> 3);
+            uint32_t w[4];
+            ldsm_x4(kt + r * SM::kRow + ((ch ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              mma16816<TM>(s[j], qa[kk + i], fp8x2_to_f16x2<T, 0>(w[i]), fp8x2_to_f16x2<T, 1>(w[i]));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; kk += 2) {
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int r = 8 * j + (lane & 7);
+            const int ch = 2 * kk + (lane >> 3);
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4(kt + r * SM::kRow + ((ch ^ (r & 7)) << 4), b0, b1, b2, b3);
+            mma16816<TM>(s[j], qa[kk], b0, b1);
+            mma16816<TM>(s[j], qa[kk + 1], b2, b3);
+          }
         }
       }
       if (KIND == KIND_GATED) {
@@ -360,8 +434,8 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
           const float p2 = ex2_approx(fmaf(s[j][2], c, -mc1)), p3 = ex2_approx(fmaf(s[j][3], c, -mc1));
           sum0 += p0 + p1;
           sum1 += p2 + p3;
-          pa[2 * j] = pack2<T>(p0, p1);
-          pa[2 * j + 1] = pack2<T>(p2, p3);
+          pa[2 * j] = pack2<TM>(p0, p1);
+          pa[2 * j + 1] = pack2<TM>(p2, p3);
         }
         sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
         sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
@@ -379,14 +453,31 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
           }
         }
         // ---- O += P V -----------------------------------------------------------------------------------
+        if constexpr (F8) {
+          // The transposing ldmatrix moves byte PAIRS: a register holds head columns (2g, 2g+1) of its
+          // chunk for keys 2t and 2t+1. Even and odd columns are split into two MMAs, whose accumulators
+          // o[2c] / o[2c+1] then stand for head columns 16c + 4t + {0, 2} / {1, 3}.
 #pragma unroll
-        for (int jd = 0; jd < HD / 16; ++jd) {
-          const int r = (lane & 7) + 8 * ((lane >> 3) & 1);
-          const int ch = 2 * jd + (lane >> 4);
-          uint32_t b0, b1, b2, b3;
-          ldsm_x4_t(vt + r * SM::kRow + ((ch ^ (r & 7)) << 4), b0, b1, b2, b3);
-          mma16816<T>(o[2 * jd], pa, b0, b1);
-          mma16816<T>(o[2 * jd + 1], pa, b2, b3);
+          for (int jd = 0; jd < HD / 32; ++jd) {
+            const int r = (lane & 7) + 8 * ((lane >> 3) & 1);
+            const int ch = 2 * jd + (lane >> 4);
+            uint32_t w0, w1, w2, w3;  // chunk 2jd: keys 0-7, keys 8-15; chunk 2jd+1: keys 0-7, keys 8-15
+            ldsm_x4_t(vt + r * SM::kRow + ((ch ^ (r & 7)) << 4), w0, w1, w2, w3);
+            mma16816<TM>(o[4 * jd], pa, fp8x2_to_f16x2<T, 2>(w0), fp8x2_to_f16x2<T, 2>(w1));
+            mma16816<TM>(o[4 * jd + 1], pa, fp8x2_to_f16x2<T, 3>(w0), fp8x2_to_f16x2<T, 3>(w1));
+            mma16816<TM>(o[4 * jd + 2], pa, fp8x2_to_f16x2<T, 2>(w2), fp8x2_to_f16x2<T, 2>(w3));
+            mma16816<TM>(o[4 * jd + 3], pa, fp8x2_to_f16x2<T, 3>(w2), fp8x2_to_f16x2<T, 3>(w3));
+          }
+        } else {
+#pragma unroll
+          for (int jd = 0; jd < HD / 16; ++jd) {
+            const int r = (lane & 7) + 8 * ((lane >> 3) & 1);
+            const int ch = 2 * jd + (lane >> 4);
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4_t(vt + r * SM::kRow + ((ch ^ (r & 7)) << 4), b0, b1, b2, b3);
+            mma16816<TM>(o[2 * jd], pa, b0, b1);
+            mma16816<TM>(o[2 * jd + 1], pa, b2, b3);
+          }
         }
       }
       __syncwarp();
@@ -401,10 +492,20 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
     float* mo = reinterpret_cast<float*>(dsm) + warp * (16 * HD + 32);
     float* mm = mo + 16 * HD;
     float* ml = mm + 16;
+    if constexpr (F8) {
 #pragma unroll
-    for (int j = 0; j < HD / 8; ++j) {
-      *reinterpret_cast<float2*>(mo + g * HD + 8 * j + 2 * t) = make_float2(o[j][0], o[j][1]);
-      *reinterpret_cast<float2*>(mo + (g + 8) * HD + 8 * j + 2 * t) = make_float2(o[j][2], o[j][3]);
+      for (int cch = 0; cch < HD / 16; ++cch) {
+        *reinterpret_cast<float4*>(mo + g * HD + 16 * cch + 4 * t) =
+            make_float4(o[2 * cch][0], o[2 * cch + 1][0], o[2 * cch][1], o[2 * cch + 1][1]);
+        *reinterpret_cast<float4*>(mo + (g + 8) * HD + 16 * cch + 4 * t) =
+            make_float4(o[2 * cch][2], o[2 * cch + 1][2], o[2 * cch][3], o[2 * cch + 1][3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < HD / 8; ++j) {
+        *reinterpret_cast<float2*>(mo + g * HD + 8 * j + 2 * t) = make_float2(o[j][0], o[j][1]);
+        *reinterpret_cast<float2*>(mo + (g + 8) * HD + 8 * j + 2 * t) = make_float2(o[j][2], o[j][3]);
+      }
     }
     if (t == 0) {
       mm[g] = m_run[0];
@@ -444,10 +545,10 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
         if (d0 == 0)
           p.lse_partial[((long long)split * p.Hq + head) * p.B + b] = dead ? -INFINITY : m_tot * c + log2f(l_tot);
       } else {
-        T* dst = reinterpret_cast<T*>(p.out) + (long long)b * p.o_sb + (long long)head * p.o_sh + d0;
+        TO* dst = reinterpret_cast<TO*>(p.out) + (long long)b * p.o_sb + (long long)head * p.o_sh + d0;
         uint2 v;
-        v.x = pack2<T>(acc.x * inv, acc.y * inv);
-        v.y = pack2<T>(acc.z * inv, acc.w * inv);
+        v.x = pack2<TO>(acc.x * inv, acc.y * inv);
+        v.y = pack2<TO>(acc.z * inv, acc.w * inv);
         *reinterpret_cast<uint2*>(dst) = v;
         if (d0 == 0)
           p.lse[(long long)b * p.l_sb + (long long)head * p.l_sh] =
@@ -461,7 +562,7 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
 template <int HD, typename T, int KIND>
 cudaError_t launch_one(const DecKernelParams& p, cudaStream_t stream) {
   auto kern = dec_kernel<HD, T, KIND>;
-  constexpr int smem = DecSmem<HD>::kTotal;
+  constexpr int smem = DecSmem<HD, sizeof(T)>::kTotal;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -487,6 +588,8 @@ cudaError_t launch_dec(const DecKernelParams& p, int kind, int dtype, int head_d
   FSA_DEC_CASE(128, __half, DT_FP16)
   FSA_DEC_CASE(64, __nv_bfloat16, DT_BF16)
   FSA_DEC_CASE(64, __half, DT_FP16)
+  FSA_DEC_CASE(128, __nv_fp8_e4m3, DT_E4M3)
+  FSA_DEC_CASE(128, __nv_fp8_e5m2, DT_E5M2)
 #undef FSA_DEC_CASE
   return cudaErrorInvalidValue;
 }

@@ -105,15 +105,18 @@ def attn_decode(
     if is_quant:
         # FP8 query and cache: widened (exactly) to bf16 before the kernel; scales as in the forward
         qkv_scale = quant.scales_f32(query_scale, key_scale, value_scale, device)
-        query, key, value = (quant.widen_fp8(t, torch.bfloat16) for t in (query, key, value))
+        native = head_dim == 128 and query.dtype == key.dtype == value.dtype
+        if not native:  # other head sizes / mixed formats: widen the tensors and run the 16-bit kernel
+            query, key, value = (quant.widen_fp8(t, torch.bfloat16) for t in (query, key, value))
 
+    out_dtype = torch.bfloat16 if is_quant else query.dtype
     keys = gather_kv_indices.shape[-1] if is_gather else seqlen_k
     if num_splits is None:
         num_splits = decode_num_splits(batch, num_heads_kv, keys, utils.device_num_sms(device))
     num_splits = max(1, int(num_splits))
 
     if out is None and not partial_only:
-        out = torch.empty(query.shape, dtype=query.dtype, device=device)
+        out = torch.empty(query.shape, dtype=out_dtype, device=device)
     if lse is None and not partial_only:
         lse = torch.empty((batch, num_heads_q), dtype=torch.float32, device=device)
     out_partial = lse_partial = None
@@ -157,7 +160,7 @@ def attn_decode(
     a.flags = (_lib.F_LOCAL if is_local else 0) | (_lib.F_LOGSIGMOID if is_logsigmoid_gate else 0)
     if kind == "gated":
         # alpha [B, Hq]; delta [B, Hkv, Sk] / [Hkv, Tk] / paged [pages, Hkv, page] (positions contiguous)
-        alpha, delta = alpha.to(query.dtype).contiguous(), delta.to(query.dtype).contiguous()
+        alpha, delta = alpha.to(out_dtype).contiguous(), delta.to(out_dtype).contiguous()
         keep_alive = (alpha, delta)  # noqa: F841  (the launch below is asynchronous)
         a.alpha, a.delta = alpha.data_ptr(), delta.data_ptr()
         a.alpha_stride_b, a.alpha_stride_h = alpha.stride(0), alpha.stride(1)

@@ -162,3 +162,35 @@ def test_quant_forward_other_shapes(head_dim, pack):
                                     pack_gqa=pack)
     _sync()
     assert_close(f"quant-hd{head_dim}-pack{int(pack)}", out, ref, **QTOL)
+
+
+@pytest.mark.parametrize("fp8", [torch.float8_e5m2, torch.float8_e4m3fn])
+def test_quant_decode_paged_gather_split(fp8):
+    """FP8 pages read by the decode kernel itself: paged cache, top-k gather through the page table, split-KV."""
+    fsa = _ops()
+    b, sk, hq, hkv, d, page = 2, 2048, 16, 2, 128, 64
+    g = torch.Generator().manual_seed(31)
+    mk = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16)  # noqa: E731
+    q, k, v = mk(b, hq, d), mk(b, sk, hkv, d), mk(b, sk, hkv, d)
+    q8, k8, v8 = (eager.quantize_fp8(t, fp8) for t in (q, k, v))
+    qd, kd, vd = ((t.float() * s.float()).to(torch.bfloat16) for t, s in (q8, k8, v8))
+    n_pages = b * sk // page
+    perm = torch.randperm(n_pages, generator=g)
+    table = torch.empty(n_pages, dtype=torch.int32)
+    table[perm] = torch.arange(n_pages, dtype=torch.int32)
+    kp = torch.empty(n_pages, page, hkv, d, dtype=fp8)
+    vp = torch.empty(n_pages, page, hkv, d, dtype=fp8)
+    kp.view(torch.uint8)[table.long()] = k8[0].reshape(n_pages, page, hkv, d).view(torch.uint8)
+    vp.view(torch.uint8)[table.long()] = v8[0].reshape(n_pages, page, hkv, d).view(torch.uint8)
+    table = table.reshape(b, sk // page)
+    idx = torch.stack([torch.randperm(sk, generator=g)[:512] for _ in range(b)]).to(torch.int32)
+    idx[:, 5::17] = -1
+    kw = dict(is_quant=True, query_scale=q8[1].to(DEV), key_scale=k8[1].to(DEV), value_scale=v8[1].to(DEV),
+              softmax_threshold=-128.0, page_table=table.to(DEV))
+    out = fsa.flash_sparse_attn_with_kvcache_func(q8[0].to(DEV), kp.to(DEV), vp.to(DEV), **kw)
+    _sync()
+    assert_close("quant-paged-decode", out, eager.decode(qd, kd, vd), **QTOL)
+    out = fsa.flash_sparse_attn_with_kvcache_func(q8[0].to(DEV), kp.to(DEV), vp.to(DEV), gather_kv_indices=idx.to(DEV),
+                                                  num_splits=4, **kw)
+    _sync()
+    assert_close("quant-paged-gather-decode", out, eager.gather_decode(qd, kd, vd, idx), **QTOL)
