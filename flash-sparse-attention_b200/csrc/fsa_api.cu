@@ -635,7 +635,7 @@ int fsa_decode(const FsaDecArgs* a, void* stream_) {
   const bool paged = a->page_table != nullptr, gather = a->gather_kv_indices != nullptr;
   const bool varlen_k = a->cu_seqlens_k != nullptr;
   if (paged && varlen_k) return FSA_ERR_UNSUPPORTED;
-  if (paged && a->page_size <= 0) return FSA_ERR_INVALID_ARG;
+  if (paged && (a->page_size <= 0 || (a->page_size & (a->page_size - 1)))) return FSA_ERR_INVALID_ARG;  // power of two
   const int ns = a->num_splits > 0 ? a->num_splits : 1;
   const bool partial = ns > 1 || a->partial_only;
   if (partial && (!a->out_partial || !a->lse_partial)) return FSA_ERR_INVALID_ARG;

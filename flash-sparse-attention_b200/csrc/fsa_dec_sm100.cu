@@ -28,14 +28,25 @@ namespace fsa {
 namespace {
 
 constexpr int DTN = 16;      // keys per warp tile
-constexpr int DSTAGES = 3;   // cp.async ring depth per warp
+// cp.async ring depth per warp: 3 tiles of 16-bit rows, 6 of FP8 rows (same shared memory, twice as
+// many row fetches in flight: the loaded latency of scattered rows, not bandwidth, bounds the kernel)
+#ifndef FSA_DEC_STAGES16
+#define FSA_DEC_STAGES16 3
+#endif
+#ifndef FSA_DEC_MINBLOCKS
+#define FSA_DEC_MINBLOCKS 2
+#endif
+template <int ES>
+struct DecStages {
+  static constexpr int value = ES == 1 ? 2 * FSA_DEC_STAGES16 : FSA_DEC_STAGES16;
+};
 constexpr int DWARPS = 4;
 
 template <int HD, int ES = 2>
 struct DecSmem {
   static constexpr int kRow = HD * ES;                // bytes per key row
   static constexpr int kTile = DTN * kRow;            // one K or V tile
-  static constexpr int kWarp = DSTAGES * 2 * kTile;   // ring of one warp
+  static constexpr int kWarp = DecStages<ES>::value * 2 * kTile;   // ring of one warp
   static constexpr int kMerge = DWARPS * (16 * HD * 4 + 16 * 8);  // O, m, l of every warp
   static constexpr int kTotal = (DWARPS * kWarp > kMerge ? DWARPS * kWarp : kMerge);
 };
@@ -114,7 +125,7 @@ __device__ __forceinline__ void mma16816<__half>(float* c, const uint32_t* a, ui
 }
 
 template <int HD, typename T, int KIND>
-__global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelParams p) {
+__global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(const DecKernelParams p) {
   // T: element type of q, k, v. FP8 (e4m3 / e5m2, head size 128) tiles are copied as bytes and widened
   // exactly to fp16 in registers in front of the fp16 mma.sync; a 16-byte chunk of a key row then holds
   // 16 head columns, used in the order the fragments deliver them (q follows the same order).
@@ -124,6 +135,7 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
   using TO = typename DecTypes<T>::out;   // outputs, alpha, delta
   using SM = DecSmem<HD, ES>;
   constexpr int CH = HD * ES / 16;  // 16-byte chunks per key row
+  constexpr int DSTAGES = DecStages<ES>::value;
   static_assert(!F8 || HD == 128, "FP8 rows are 128 bytes: eight chunks, as the swizzle assumes");
   extern __shared__ __align__(128) uint8_t dsm[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -160,6 +172,9 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
   const int capacity = paged ? p.pt_stride * p.page_size
                              : ((p.flags & F_VARLEN_K) ? p.cu_k[b + 1] - off_k : p.sk_capacity);
 
+  // page sizes are powers of two (checked on the host): positions split into page / row by shift and mask
+  const int page_shift = paged ? (31 - __clz(p.page_size)) : 0;
+  const int page_mask = paged ? (p.page_size - 1) : 0;
   uint8_t* ring = dsm + warp * SM::kWarp;
   const char* kbase = reinterpret_cast<const char*>(p.k);
   const char* vbase = reinterpret_cast<const char*>(p.v);
@@ -168,8 +183,8 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
   auto row_elem = [&](int pos) -> long long {
     if (pos < 0 || pos >= capacity) return -1;
     if (paged) {
-      const int page = ptab[pos / p.page_size];
-      return (long long)page * p.k_sb + (long long)(pos % p.page_size) * p.k_sn + (long long)hkv * p.k_sh;
+      const int page = ptab[pos >> page_shift];
+      return (long long)page * p.k_sb + (long long)(pos & page_mask) * p.k_sn + (long long)hkv * p.k_sh;
     }
     return (long long)bk * p.k_sb + (long long)(off_k + pos) * p.k_sn + (long long)hkv * p.k_sh;
   };
@@ -190,8 +205,8 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
     if (KIND == KIND_GATED) {
       float dv = 0.f;
       if (lane < DTN && e >= 0) {
-        const long long de = paged ? (long long)ptab[pos / p.page_size] * p.d_sb + (long long)hkv * p.d_sh +
-                                         (pos % p.page_size)
+        const long long de = paged ? (long long)ptab[pos >> page_shift] * p.d_sb + (long long)hkv * p.d_sh +
+                                         (pos & page_mask)
                                    : (long long)bk * p.d_sb + (long long)hkv * p.d_sh + off_k + pos;
         dv = float(reinterpret_cast<const TO*>(p.delta)[de]);
       }
@@ -247,7 +262,9 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
     const bool row0_ok = mt * 16 + g < p.G, row1_ok = mt * 16 + g + 8 < p.G;
     // ---- gated: alpha of the two rows, its extremes over the real rows, the running gate bound ----
     float al0 = 0.f, al1 = 0.f, a_max = 0.f, a_min = 0.f, gate_max = -INFINITY;
-    float dl0 = 0.f, dl1 = 0.f, dl2 = 0.f;
+    float dlq[DSTAGES];  // gated: delta of key (lane & 15) of the tiles in the ring, oldest first
+#pragma unroll
+    for (int i = 0; i < DSTAGES; ++i) dlq[i] = 0.f;
     const float gate_thr_log2 = (KIND == KIND_GATED) ? log2f(p.gate_thr) : 0.f;
     if (KIND == KIND_GATED) {
       const TO* ab = reinterpret_cast<const TO*>(p.alpha) + (long long)b * p.a_sb;
@@ -267,35 +284,41 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
     for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
 
     // ---- ring prologue ----------------------------------------------------------------------------
-    int n_load = fsa_fwd_next_tile_below(sched, 1 << 28, loc_sched);
-    unsigned present_q[DSTAGES];
+    // without local windows the visited tiles are one descending range
+    auto tile_below = [&](int n) {
+      return loc_sched ? fsa_fwd_next_tile_below(sched, n, true) : (n - 1 >= sched.n_min ? n - 1 : -1);
+    };
+    const int n_first = fsa_fwd_next_tile_below(sched, 1 << 28, loc_sched);
+    int n_load = n_first;
+    unsigned present_q[DSTAGES];  // presence masks of the tiles in the ring, oldest first
     int slot_load = 0;
 #pragma unroll
     for (int s = 0; s < DSTAGES - 1; ++s) {
       present_q[s] = 0;
       if (n_load >= 0) {
-        present_q[s] = issue_tile(n_load, s, s == 0 ? &dl0 : &dl1);
-        n_load = fsa_fwd_next_tile_below(sched, n_load, loc_sched);
+        present_q[s] = issue_tile(n_load, s, &dlq[s]);
+        n_load = tile_below(n_load);
       }
       cp_async_commit();
     }
     present_q[DSTAGES - 1] = 0;
     slot_load = DSTAGES - 1;
     int slot = 0;
-    for (int n = fsa_fwd_next_tile_below(sched, 1 << 28, loc_sched); n >= 0;
-         n = fsa_fwd_next_tile_below(sched, n, loc_sched)) {
+    for (int n = n_first; n >= 0; n = tile_below(n)) {
       // keep the ring full, then wait for the oldest tile
       unsigned pres_new = 0;
       if (n_load >= 0) {
-        pres_new = issue_tile(n_load, slot_load, &dl2);
-        n_load = fsa_fwd_next_tile_below(sched, n_load, loc_sched);
+        pres_new = issue_tile(n_load, slot_load, &dlq[DSTAGES - 1]);
+        n_load = tile_below(n_load);
       }
       cp_async_commit();
-      present_q[slot_load] = pres_new;
+      present_q[DSTAGES - 1] = pres_new;
       slot_load = (slot_load + 1) % DSTAGES;
       cp_async_wait<DSTAGES - 1>();
       __syncwarp();
-      const unsigned present = present_q[slot];
+      const unsigned present = present_q[0];
+#pragma unroll
+      for (int i = 0; i + 1 < DSTAGES; ++i) present_q[i] = present_q[i + 1];
       const uint32_t kt = smem_u32(ring + slot * 2 * SM::kTile);
       const uint32_t vt = kt + SM::kTile;
 
@@ -321,7 +344,7 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
       // ---- gated: bound of the gate over the tile, running maximum, skip
       // (flash_sparse_attn/ops/triton/activations.py:265-299) ------------------------------------------
       if (KIND == KIND_GATED) {
-        float dmax = dl0, dmin = dl0;
+        float dmax = dlq[0], dmin = dlq[0];
 #pragma unroll
         for (int sft = 8; sft > 0; sft >>= 1) {
           dmax = fmaxf(dmax, __shfl_xor_sync(0xffffffffu, dmax, sft));
@@ -334,16 +357,19 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
           if (p.tile_map && lane == 0 && mt == 0) p.tile_map[((long long)b * p.Hkv + hkv) * p.n_tiles + n] = 3;
           __syncwarp();
           slot = (slot + 1) % DSTAGES;
-          dl0 = dl1;
-          dl1 = dl2;
+#pragma unroll
+          for (int i = 0; i + 1 < DSTAGES; ++i) dlq[i] = dlq[i + 1];
           continue;
         }
       }
 
       // ---- S = Q K^T over this tile: 2 key groups of 8 ------------------------------------------------
-      float s[2][4];
+      float s[2][4], s_alt[2][4];  // two accumulators per key group: half as long a chain of dependent MMAs
 #pragma unroll
-      for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+      for (int j = 0; j < 2; ++j) {
+        s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+        s_alt[j][0] = s_alt[j][1] = s_alt[j][2] = s_alt[j][3] = 0.f;
+      }
       if constexpr (F8) {
         // one ldmatrix.x4 = four 16-byte chunks = four k-steps; every register carries the four head
         // columns 4t .. 4t+3 of its chunk for key row g
@@ -357,7 +383,7 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
             ldsm_x4(kt + r * SM::kRow + ((ch ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-              mma16816<TM>(s[j], qa[kk + i], fp8x2_to_f16x2<T, 0>(w[i]), fp8x2_to_f16x2<T, 1>(w[i]));
+              mma16816<TM>((i & 1) ? s_alt[j] : s[j], qa[kk + i], fp8x2_to_f16x2<T, 0>(w[i]), fp8x2_to_f16x2<T, 1>(w[i]));
           }
         }
       } else {
@@ -370,10 +396,14 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
             uint32_t b0, b1, b2, b3;
             ldsm_x4(kt + r * SM::kRow + ((ch ^ (r & 7)) << 4), b0, b1, b2, b3);
             mma16816<TM>(s[j], qa[kk], b0, b1);
-            mma16816<TM>(s[j], qa[kk + 1], b2, b3);
+            mma16816<TM>(s_alt[j], qa[kk + 1], b2, b3);
           }
         }
       }
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[j][e] += s_alt[j][e];
       if (KIND == KIND_GATED) {
         // logits = (q.k + g(alpha * delta)) * scale (flash_sparse_attn/ops/triton/flash_gated_dec.py)
         const bool logsig = p.flags & F_LOGSIGMOID;
@@ -381,7 +411,7 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
         for (int j = 0; j < 2; ++j)
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float dk = __shfl_sync(0xffffffffu, dl0, 8 * j + 2 * t + (e & 1));
+            const float dk = __shfl_sync(0xffffffffu, dlq[0], 8 * j + 2 * t + (e & 1));
             const float x = (e < 2 ? al0 : al1) * dk;
             float gte = x;
             if (logsig)
@@ -390,11 +420,13 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
           }
       }
       // mask: element (j, e) is key 8j + 2t + (e & 1)
+      if (vis != 0xffffu) {
 #pragma unroll
-      for (int j = 0; j < 2; ++j)
+        for (int j = 0; j < 2; ++j)
 #pragma unroll
-        for (int e = 0; e < 4; ++e)
-          if (!((vis >> (8 * j + 2 * t + (e & 1))) & 1u)) s[j][e] = -INFINITY;
+          for (int e = 0; e < 4; ++e)
+            if (!((vis >> (8 * j + 2 * t + (e & 1))) & 1u)) s[j][e] = -INFINITY;
+      }
 
       float m_cur[2];
       m_cur[0] = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
@@ -482,8 +514,8 @@ __global__ void __launch_bounds__(DWARPS * 32, 2) dec_kernel(const DecKernelPara
       }
       __syncwarp();
       slot = (slot + 1) % DSTAGES;
-      dl0 = dl1;
-      dl1 = dl2;
+#pragma unroll
+      for (int i = 0; i + 1 < DSTAGES; ++i) dlq[i] = dlq[i + 1];
     }
     cp_async_wait<0>();
     __syncthreads();  // every warp is done with its ring: the space becomes the merge buffer
