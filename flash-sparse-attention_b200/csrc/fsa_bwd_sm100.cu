@@ -633,9 +633,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         x[i + 3] = xb.y;
       }
       if (masked) {
+        const int n_iv = (cm.len[0] != 0u) + (cm.len[1] != 0u) + (cm.len[2] != 0u);
+        if (__all_sync(0xffffffffu, n_iv <= 1)) {  // at most one interval per key row: one compare per entry
+          const int which = cm.len[1] != 0u ? 1 : (cm.len[2] != 0u ? 2 : 0);
+          const int nlo = wg * 64 - (which == 1 ? cm.lo[1] : (which == 2 ? cm.lo[2] : cm.lo[0]));
+          const unsigned len = which == 1 ? cm.len[1] : (which == 2 ? cm.len[2] : cm.len[0]);
 #pragma unroll
-        for (int i = 0; i < 64; ++i)
-          if (!visible(cm, wg * 64 + i)) x[i] = -INFINITY;
+          for (int i = 0; i < 64; ++i)
+            if (unsigned(i + nlo) >= len) x[i] = -INFINITY;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; ++i)
+            if (!visible(cm, wg * 64 + i)) x[i] = -INFINITY;
+        }
       }
       bool skip = false;
       if (KIND != KIND_DENSE) {

@@ -658,9 +658,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       }
       if (mode != FSA_MASK_NONE) {
         const TileMask tm = make_tile_mask(rm, mode, k0);
+        // most masked tiles leave every row one interval (causal diagonal, one window band, key tail):
+        // one compare per entry instead of three
+        const int n_iv = (tm.len[0] != 0u) + (tm.len[1] != 0u) + (tm.len[2] != 0u);
+        if (__all_sync(0xffffffffu, n_iv <= 1)) {
+          const int which = tm.len[1] != 0u ? 1 : (tm.len[2] != 0u ? 2 : 0);
+          const int nlo = -(which == 1 ? tm.lo[1] : (which == 2 ? tm.lo[2] : tm.lo[0]));
+          const unsigned len = which == 1 ? tm.len[1] : (which == 2 ? tm.len[2] : tm.len[0]);
 #pragma unroll
-        for (int i = 0; i < TN; ++i)
-          if (!tile_col_visible(tm, i)) sr[i] = 0xff800000u;  // -inf
+          for (int i = 0; i < TN; ++i)
+            if (unsigned(i + nlo) >= len) sr[i] = 0xff800000u;  // -inf
+        } else {
+#pragma unroll
+          for (int i = 0; i < TN; ++i)
+            if (!tile_col_visible(tm, i)) sr[i] = 0xff800000u;  // -inf
+        }
       } else if (!rm.row_ok) {
         // rows past the query length read as zero scores in fully visible tiles
 #pragma unroll
