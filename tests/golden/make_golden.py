@@ -1,9 +1,8 @@
 """Generate the golden fixtures in this directory from the REFERENCE's own eager functions.
 
-Run once, in a container that has the reference checked out (read-only) at REF (default
-/root/reference):
+Run once, on a machine that has the reference repository checked out (read-only) at REF:
 
-    python tests/golden/make_golden.py [REF]
+    python tests/golden/make_golden.py REF      (or set FSA_REFERENCE_DIR)
 
 It imports the reference's tests/test_utils.py (eager fp32 oracles), tests/test_topk_gather_decode.py
 (gathered-decode oracle) and flash_sparse_attn/ops/triton/utils.py (window / split heuristics), feeds
@@ -17,7 +16,7 @@ import sys
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FSA_REFERENCE_DIR", "reference")
 sys.path.insert(0, os.path.join(REF, "tests"))
 sys.path.insert(0, REF)
 
