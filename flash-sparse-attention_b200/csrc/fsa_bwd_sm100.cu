@@ -21,7 +21,8 @@
 //   dQ   = dS K        (A = dS^T from shared memory, read MN-major)
 //
 // Roles (384 threads): warps 0-7 compute (warps 0-3 own query columns 0-63 of the tile, warps 4-7
-// columns 64-127; both cover all 128 key lanes), warp 8 producer (TMA), warp 9 MMA issuer.
+// columns 64-127; both cover all 128 key lanes), warp 8 producer (TMA), warp 9 MMA issuer, warp 10 dQ
+// drain (deterministic mode only: takes the turns and issues the TMA reduce-adds of the staged dQ tiles).
 // TMEM columns: [0,128) S^T, then P^T packed into [0,32) and [96,128) | [128,256) dP^T, later dQ |
 // [256,384) dV | [384,512) dK.
 #include "fsa_ptx.cuh"
@@ -78,6 +79,8 @@ struct BwdBars {
   uint64_t kv_full, q_full[2], q_empty[2], do_full, do_empty;
   uint64_t s_full, p_full, dp_full, ds_full, dq_full, dq_empty, vote_sync, acc_full;
   uint64_t dd_sync;  // gated: second column group -> first, partial ddelta handed over in shared memory
+  uint64_t stg_full, stg_free;  // dQ staging: compute warps -> drain warp (job posted) and back (buffers read)
+  int job[2][4];                // job descriptors {first row, head, query tile, code}, slot = job index & 1
   uint32_t tmem_base;
   int abort_flag;
   int skip_flag[2];
@@ -245,6 +248,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
     mbar_init(&bars->vote_sync, 8);
     mbar_init(&bars->acc_full, 1);
     mbar_init(&bars->dd_sync, 4);
+    mbar_init(&bars->stg_full, 8);
+    mbar_init(&bars->stg_free, 1);
     bars->abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
     mbar_fence_init();
   }
@@ -407,6 +412,74 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       __syncwarp();
       FSA_TICK(15);
       FSA_TICK_FLUSH;
+    } else if (warp == 10) {
+      // =============================== dQ drain =================================================
+      // Deterministic mode only (otherwise every compute warp issues the reduce-add of its own buffer, which
+      // measured 3 % faster). Jobs arrive in order: a 32-column chunk of a dQ tile staged by the eight
+      // compute warps (lane i issues the reduce-add of warp i's 4 KB buffer), "pass" for a skipped tile and
+      // "exit". This warp waits for the tile's turn before the first chunk and passes it on when the adds
+      // of the last chunk have completed (one tick of the per-(head, query tile) counter per key tile), so
+      // the compute warps never wait for a turn or for the completion of an add.
+      constexpr int HALF_ = HD / 2;
+      const bool det = p.flags & F_DETERMINISTIC;
+      bool ok = det && !*abort_flag;  // without deterministic mode the compute warps issue their own reduce-adds
+      // one counter per (head, query tile); a link of the chain costs the issue-to-completion latency of the
+      // tile's reduce-adds (per-chunk chains were tried: the drain warp then blocks on every completion
+      // and the whole pipeline slows down)
+      auto turn_ptr = [&](int head, int m) { return p.dq_turn + ((long long)b * p.Hq + head) * p.num_m_blocks + m; };
+      auto turn_wait = [&](int head, int m) {
+        if (lane == 0) {
+          const int target =
+              (int)p.dq_order[(((long long)b * p.Hkv + hkv) * p.n_tiles_k + n_block) * p.num_m_blocks + m];
+          const int* tp = turn_ptr(head, m);
+          const long long t_end = clock64() + FSA_WAIT_CYCLES;
+          int seen;
+          for (;;) {
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(tp) : "memory");
+            if (seen == target || *abort_flag) break;
+            if (clock64() > t_end) {
+              *abort_flag = 1;
+              break;
+            }
+            __nanosleep(64);
+          }
+        }
+        __syncwarp();
+      };
+      auto turn_pass = [&](int head, int m) {
+        if (lane == 0) {
+          __threadfence();
+          atomicAdd(turn_ptr(head, m), 1);
+        }
+      };
+      for (int j = 0; ok; ++j) {
+        ok = mbar_wait(&bars->stg_full, j & 1, abort_flag);
+        if (!ok) break;
+        const volatile int* jd = bars->job[j & 1];
+        const int row0 = jd[0], head = jd[1], m = jd[2], code = jd[3];
+        const int kind = code & 3, chunk = (code >> 4) & 1;
+        const bool last = (code >> 8) & 1;
+        if (kind == 2) break;
+        if (det && (kind == 1 || chunk == 0)) {
+          turn_wait(head, m);
+          if (*abort_flag) break;
+        }
+        if (kind == 0 && lane < 8) {
+          tma_reduce_add_3d(&p.map_dq, smem + SM::kStage + lane * 4096, (lane >> 2) * HALF_ + chunk * 32,
+                            row0 + (lane & 3) * 32, head);
+          bulk_commit();
+          bulk_wait_read0();
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->stg_free);
+        if (det && (kind == 1 || last)) {
+          if (kind == 0 && lane < 8) bulk_wait0();  // the adds have landed: the next key tile may add
+          __syncwarp();
+          turn_pass(head, m);
+        }
+      }
+      if (lane < 8) bulk_wait0();
+      __syncwarp();
     }
   } else {
     // =============================== compute warps ===========================================
@@ -433,39 +506,27 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
     constexpr int NCH = HALF / 32;
     uint32_t dq_hold[32];
     bool dq_pending = false;
-    int dq_row = 0, dq_head = 0;
+    int dq_row = 0, dq_head = 0, dq_m = 0;
     int m_cur = 0, g_cur = 0;  // query tile / head of the step whose dS and dQ are being handled
-    // Deterministic mode: the key tiles that add into one dQ tile do so in descending key order. A
-    // counter per (head, query tile) advances by one per warp (8 per key tile) once that warp's adds
-    // have completed; a warp adds only when the counter shows 8 x its key tile's rank (bounded wait).
     const bool det = p.flags & F_DETERMINISTIC;
-    int* turn_prev = nullptr;  // counter of the tile whose adds are still in flight
-    auto turn_of = [&](int head, int m) { return p.dq_turn + ((long long)b * p.Hq + head) * p.num_m_blocks + m; };
-    auto turn_wait = [&](int head, int m) {
-      if (lane == 0) {
-        const int target =
-            8 * (int)p.dq_order[(((long long)b * p.Hkv + hkv) * p.n_tiles_k + n_block) * p.num_m_blocks + m];
-        const int* tp = turn_of(head, m);
-        const long long t_end = clock64() + FSA_WAIT_CYCLES;
-        int seen;
-        for (;;) {
-          asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(tp) : "memory");
-          if (seen == target || *abort_flag) break;
-          if (clock64() > t_end) {
-            *abort_flag = 1;
-            break;
-          }
-          __nanosleep(64);
-        }
+    int jobs = 0;  // staging jobs handed to the drain warp so far (same count in every compute warp)
+    // wait until the drain warp's TMA reads of the previous job have left the staging buffers
+    auto stage_wait_free = [&]() {
+      if (jobs > 0 && !mbar_wait(&bars->stg_free, (jobs - 1) & 1, abort_flag)) ok = false;
+    };
+    // hand a job to the drain warp: {first row of the tile, head, query tile, code}
+    // code = kind (0 chunk, 1 pass, 2 exit) | chunk << 4 | last chunk of the tile << 8
+    auto stage_post = [&](int row0, int head, int m, int code) {
+      if (cw == 0 && lane == 0) {
+        volatile int* jd = bars->job[jobs & 1];
+        jd[0] = row0;
+        jd[1] = head;
+        jd[2] = m;
+        jd[3] = code;
       }
       __syncwarp();
-      if (*abort_flag) ok = false;
-    };
-    auto turn_done = [&](int* tp) {
-      if (lane == 0 && tp) {
-        __threadfence();
-        atomicAdd(tp, 1);
-      }
+      if (lane == 0) mbar_arrive(&bars->stg_full);
+      jobs++;
     };
 
     // ---- gated: delta of this key row, its extremes over the key tile, running gate bound --------
@@ -818,10 +879,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       FSA_TICK(5);
     };
 
-    // ---- dQ step: TMEM -> registers -> shared staging -> TMA reduce-add into the fp32 accumulator -------
+    // ---- dQ step: TMEM -> registers -> shared staging; the drain warp issues the TMA reduce-adds -------
     // The path from an SM to L2 moves about 21 bytes per clock, so the 64 KB of a dQ tile take as long as
-    // the five MMAs of a step: nobody waits for it. The first 32 columns go out at once, the second 32
-    // stay in registers until the next phase has passed (dq_flush) and the engine has drained the buffer.
+    // the five MMAs of a step: nobody waits for it. The first 32 columns are staged at once, the second 32
+    // stay in registers until the next phase has passed (dq_flush) and the engine has drained the buffers.
     auto stage_store = [&](const uint32_t* r) {
 #pragma unroll
       for (int j = 0; j < 8; ++j)
@@ -831,25 +892,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       __syncwarp();
     };
     auto dq_flush = [&]() {
-      if (det && turn_prev) {
-        // both halves went out in dq_step: once they have landed the next key tile may add
-        if (lane == 0) bulk_wait0();
-        turn_done(turn_prev);
-        turn_prev = nullptr;
-      }
       if (NCH > 1 && dq_pending) {
         FSA_TICK(9);
-        if (lane == 0) bulk_wait_read0();
-        __syncwarp();
-        FSA_TICK(8);
-        stage_store(dq_hold);
-        FSA_TICK(16);
-        if (lane == 0) {
-          tma_reduce_add_3d(&p.map_dq, stage, wg * HALF + 32, dq_row, dq_head);
-          bulk_commit();
+        if (det) {
+          stage_wait_free();
+          if (!ok) return;
+          stage_store(dq_hold);
+          stage_post(dq_row, dq_head, dq_m, 0 | (1 << 4) | (1 << 8));
+        } else {
+          if (lane == 0) bulk_wait_read0();
+          __syncwarp();
+          FSA_TICK(8);
+          stage_store(dq_hold);
+          if (lane == 0) {
+            tma_reduce_add_3d(&p.map_dq, stage, wg * HALF + 32, dq_row + wq * 32, dq_head);
+            bulk_commit();
+          }
         }
         dq_pending = false;
-        FSA_TICK(17);
+        FSA_TICK(7);
       }
     };
     auto dq_step = [&](int it) {
@@ -869,37 +930,26 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->dq_empty);
       FSA_TICK(7);
+      dq_row = (int)(pad_off + (long long)m_cur * TM);
+      dq_head = hkv * p.G + g_cur;
+      dq_m = m_cur;
       if (det) {
-        if (lane == 0) bulk_wait_read0();
-        turn_prev = turn_of(hkv * p.G + g_cur, m_cur);
-        turn_wait(hkv * p.G + g_cur, m_cur);
+        stage_wait_free();
         if (!ok) return;
+        stage_store(r);
+        stage_post(dq_row, dq_head, dq_m, 0 | (0 << 4) | ((NCH == 1 ? 1 : 0) << 8));
       } else {
         if (lane == 0) bulk_wait_read0();  // the buffer went to the engine a whole phase ago
         __syncwarp();
-      }
-      FSA_TICK(14);
-      stage_store(r);
-      FSA_TICK(16);
-      dq_row = (int)(pad_off + (long long)m_cur * TM + wq * 32);
-      dq_head = hkv * p.G + g_cur;
-      if (lane == 0) {
-        tma_reduce_add_3d(&p.map_dq, stage, wg * HALF, dq_row, dq_head);
-        bulk_commit();
-      }
-      dq_pending = NCH > 1;
-      if (det && NCH > 1) {
-        // keep the turn short: the second half follows as soon as the engine has read the first
-        if (lane == 0) bulk_wait_read0();
-        __syncwarp();
-        stage_store(dq_hold);
+        FSA_TICK(14);
+        stage_store(r);
         if (lane == 0) {
-          tma_reduce_add_3d(&p.map_dq, stage, wg * HALF + 32, dq_row, dq_head);
+          tma_reduce_add_3d(&p.map_dq, stage, wg * HALF, dq_row + wq * 32, dq_head);
           bulk_commit();
         }
-        dq_pending = false;
       }
-      FSA_TICK(17);
+      dq_pending = NCH > 1;
+      FSA_TICK(7);
     };
 
     if (ok && N_IT > 0) {
@@ -917,14 +967,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         n_live++;
       } else if (ok && det) {
         // a skipped tile adds nothing but still takes (and passes on) its turn
-        turn_wait(hkv * p.G + g_cur, m_cur);
-        turn_done(ok ? turn_of(hkv * p.G + g_cur, m_cur) : nullptr);
+        stage_wait_free();
+        if (ok) stage_post(0, hkv * p.G + g_cur, m_cur, 1);
       }
       skip_cur = skip_next;
       m_cur = m_p;
       g_cur = g_p;
     }
     dq_flush();
+    if (det) {
+      stage_wait_free();
+      stage_post(0, 0, 0, 2);  // the drain warp leaves (also when this warp is bailing out: it must not be left waiting)
+    }
 
     FSA_TICK(9);
     FSA_TICK_FLUSH;

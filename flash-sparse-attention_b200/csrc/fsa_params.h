@@ -72,7 +72,7 @@ struct alignas(64) BwdKernelParams {
   float* da_accum;       // gated: [Hq, ws_sh] fp32, zeroed; receives atomic adds
   const unsigned short* dq_order;  // deterministic: [B, Hkv, n_tiles_k, num_m_blocks] rank of a key tile among
                                    // the key tiles that add into a query tile (descending key index)
-  int* dq_turn;                    // deterministic: [B, Hq, num_m_blocks] zeroed; 8 ticks per finished key tile
+  int* dq_turn;                    // deterministic: [B, Hq, num_m_blocks] zeroed; one tick per finished key tile
   void* dd_out;          // gated: T* laid out like delta, or float partial [splits, ...] when F_SPLIT
   long long d_sb, d_sh, dd_ss;
   long long dkv_sb, dkv_sn, dkv_sh, dkv_ss;
