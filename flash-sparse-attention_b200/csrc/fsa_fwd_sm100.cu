@@ -25,6 +25,29 @@
 #include "fsa_params.h"
 #include "fsa_schedule.h"
 
+// Development aid: with -DFSA_PHASE_TIMING lane 0 of softmax warp 0 adds up the clock cycles of its phases;
+// fsa_debug_fwd_ticks() reads the totals over all CTAs.
+#ifdef FSA_PHASE_TIMING
+__device__ unsigned long long g_fwd_ticks[16];
+#define FWD_TICK_DECL long long ftk_[16] = {0}; long long ftk_t_ = clock64(); const bool ftk_on_ = (lane == 0) && (warp == 0)
+#define FWD_TICK(i)                          \
+  do {                                       \
+    const long long now_ = clock64();        \
+    ftk_[i] += now_ - ftk_t_;                \
+    ftk_t_ = now_;                           \
+  } while (0)
+#define FWD_TICK_FLUSH                                                                      \
+  do {                                                                                      \
+    if (ftk_on_)                                                                            \
+      for (int i_ = 0; i_ < 16; ++i_)                                                       \
+        if (ftk_[i_]) atomicAdd(&g_fwd_ticks[i_], (unsigned long long)ftk_[i_]);             \
+  } while (0)
+#else
+#define FWD_TICK_DECL
+#define FWD_TICK(i)
+#define FWD_TICK_FLUSH
+#endif
+
 namespace fsa {
 
 namespace {
@@ -206,6 +229,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     return fsa_imax(a, b);
   };
   auto next_tile = [&](int n) {
+    // common case first: the tile just below is visited by one of the two groups
+    const int c = n - 1;
+    if (!local && ((c >= sched[0].n_min && c < sched[0].n_max) || (c >= sched[1].n_min && c < sched[1].n_max))) return c;
     const int a = fsa_fwd_next_tile_below(sched[0], n, local);
     const int b = fsa_fwd_next_tile_below(sched[1], n, local);
     return fsa_imax(a, b);
@@ -545,6 +571,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     float l_ref = 0.f;        // sum of exp2((s - m_ref) * c)
     bool have_o = false;      // some P V has been issued for this tile
     int cnt_s = 0;
+    FWD_TICK_DECL;
     bool ok = !*abort_flag;
     const bool has_work = q_valid[q] && !fsa_fwd_sched_empty(my);
 
@@ -601,7 +628,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
         gate_skip = (gmc - gate_max) * c < gate_thr_log2;
         if (!gate_skip) gate_max = fmaxf(gmc, gate_max);
       }
+      FWD_TICK(9);
       ok = mbar_wait(&bars->s_full[q], cnt_s & 1, abort_flag);
+      FWD_TICK(0);
       if (!ok) break;
       tc_fence_after();
       const int par = cnt_s & 1;
@@ -635,6 +664,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
 #pragma unroll
       for (int ch = 0; ch < TN / 32; ++ch) tmem_ld32(tS + ch * 32, &sr[ch * 32]);
       tmem_ld_wait();
+      FWD_TICK(1);
       if (KIND == KIND_GATED) {
         // logits = (q.k + g(alpha * delta_j)) * scale, g = logsigmoid or identity
         // (flash_sparse_attn/ops/triton/flash_gated_fwd.py:104-122, activations.py:245-262)
@@ -690,6 +720,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       }
       const float m_cur = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
 
+      FWD_TICK(2);
       // ---- tile skip vote (flash_sparse_attn/ops/triton/activations.py:129-138) -----------------
       bool skip = false;
       if (KIND != KIND_DENSE) {
@@ -734,6 +765,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
         continue;
       }
 
+      FWD_TICK(3);
       // ---- move the reference maximum only when it lags by more than 2^8 -------------------------
       float m_cand = fmaxf(m_cur, m_ref);
       if (mode != FSA_MASK_NONE) m_cand = fmaxf(m_cand, -1e6f);
@@ -757,6 +789,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
         }
       }
 
+      FWD_TICK(4);
       // ---- P = exp2(S*c - m*c), row sum, publish P (16-bit pairs) over the S columns -----------------
       const float2 c2 = make_float2(c, c);
       const float neg_mc = -(m_ref * c);
@@ -790,13 +823,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
         else
           tmem_st16(tS + ch * 16, pk);
       }
+      FWD_TICK(5);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_full[q]);
       l_ref += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
       have_o = true;
+      FWD_TICK(6);
     }
+    FWD_TICK(9);
+    FWD_TICK_FLUSH;
 
     // ---- epilogue (flash_sparse_attn/ops/triton/activations.py:169-203) ---------------------------
     if (ok && have_o) {
@@ -880,6 +917,17 @@ cudaError_t launch_one(const FwdKernelParams& p, cudaStream_t stream) {
 
 // kind: KIND_*, dtype: DT_BF16 / DT_FP16, head_dim: 64 or 128. Returns cudaErrorInvalidValue for
 // unsupported combinations.
+#ifdef FSA_PHASE_TIMING
+extern "C" void fsa_debug_fwd_ticks(unsigned long long* out16, int reset) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out16, g_fwd_ticks, sizeof(unsigned long long) * 16);
+  if (reset) {
+    unsigned long long z[16] = {0};
+    cudaMemcpyToSymbol(g_fwd_ticks, z, sizeof(z));
+  }
+}
+#endif
+
 cudaError_t launch_fwd(const FwdKernelParams& p, int kind, int dtype, int head_dim, cudaStream_t stream) {
 #define FSA_FWD_CASE(HD_, T_, DT_)                                                  \
   if (head_dim == HD_ && dtype == DT_) {                                            \
