@@ -23,6 +23,7 @@ SOURCES = [
     "fsa_dec_sm100.cu",
     "fsa_static_scratch.cu",
     "fsa_quant.cu",
+    "fsa_topk.cu",
 ]
 
 NVCC_FLAGS = [

@@ -266,6 +266,8 @@ def load():
     lib.fsa_quantize_fp8.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
     lib.fsa_fp8_widen.restype = c_int
     lib.fsa_fp8_widen.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
+    lib.fsa_topk_indices.restype = c_int
+    lib.fsa_topk_indices.argtypes = [c_void_p, c_int, c_int, c_int, c_int64, c_int, c_void_p, c_int, c_void_p]
     lib.fsa_set_profile_events.restype = None
     lib.fsa_set_profile_events.argtypes = [c_void_p, c_void_p]
     lib.fsa_debug_fwd_schedule.restype = None

@@ -327,6 +327,17 @@ int fsa_quantize_fp8(const void* x, void* x_fp8, void* scale_out, float* amax_ws
 int fsa_fp8_widen(const void* x_fp8, void* out, const void* scale, int64_t n, int fp8_dtype, int out_dtype,
                   void* stream);
 
+/*
+ * Top-k position selection in front of the gathered decode: for every row of `scores`
+ * [rows, n] (bf16 / fp16 / fp32, `row_stride` elements between rows) the positions of the k largest
+ * entries in ascending order, int32 or int64 [rows, k]. Same contract as
+ * flash_sparse_attn/utils/mask.py:20-44 (torch.topk + sort of the indices); among equal scores at the
+ * threshold the lowest positions are taken, NaN orders above +inf. One CTA per row: four-pass radix
+ * select, then an ordered compaction (no sort).
+ */
+int fsa_topk_indices(const void* scores, int dtype, int rows, int n, int64_t row_stride, int k, void* out,
+                     int out_is_int64, void* stream);
+
 int fsa_abi_version(void);
 
 #ifdef __cplusplus

@@ -16,7 +16,7 @@ import sys
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FSA_REFERENCE_DIR", "reference")
+REF = sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("--") else os.environ.get("FSA_REFERENCE_DIR", "reference")
 sys.path.insert(0, os.path.join(REF, "tests"))
 sys.path.insert(0, REF)
 
@@ -157,8 +157,38 @@ def heuristics():
     save("heuristics", windows=np.array(rows, dtype=np.int64), splits=np.array(splits, dtype=np.int64))
 
 
+def topk_cases():
+    """flash_sparse_attn/utils/mask.py:20-44 on rows WITHOUT equal scores (torch does not define which of
+    several equal entries at the threshold it returns)."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("ref_mask", os.path.join(REF, "flash_sparse_attn", "utils", "mask.py"))
+    ref_mask = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref_mask)
+    g = torch.Generator().manual_seed(11)
+    res = {}
+    for name, shape, k, dt in [("a", (2, 3, 1000), 37, torch.float32), ("b", (1, 2, 4096), 512, torch.float32),
+                               ("c", (2, 2, 200), 200, torch.float32), ("d", (1, 4, 250), 16, torch.bfloat16)]:
+        n = shape[-1]
+        rows = int(np.prod(shape[:-1]))
+        if dt == torch.bfloat16:
+            # distinct values that bf16 represents exactly
+            base = torch.arange(n, dtype=torch.float32) - 100.0
+        else:
+            base = torch.randn(n * 4, generator=g).unique()[:n] * 3.0
+        x = torch.stack([base[torch.randperm(n, generator=g)] for _ in range(rows)]).reshape(shape).to(dt)
+        idx = ref_mask.topk_indices(x, k)
+        res[f"{name}_scores"] = x
+        res[f"{name}_k"] = torch.tensor(k)
+        res[f"{name}_idx"] = idx
+    save("topk", **res)
+
+
 if __name__ == "__main__":
     torch.set_num_threads(8)
+    topk_cases()
+    if "--only-topk" in sys.argv:
+        sys.exit(0)
     forward_cases()
     local_case()
     varlen_case()
