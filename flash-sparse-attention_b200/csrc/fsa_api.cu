@@ -416,9 +416,8 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
   // padding rows of dpsum must hold finite values (they meet zero probabilities in a packed product)
   if (cudaMemsetAsync(a->dpsum_ws, 0, sizeof(float) * (size_t)a->heads_q * R, stream) != cudaSuccess)
     return FSA_ERR_LAUNCH;
+  pre.dq_accum = a->dq_accum;  // the pre-pass clears the accumulator rows it visits (padding rows are never read)
   if (fsa::launch_bwd_pre(pre, a->dtype, stream) != cudaSuccess) return FSA_ERR_LAUNCH;
-  if (cudaMemsetAsync(a->dq_accum, 0, sizeof(float) * (size_t)a->heads_q * R * hdk, stream) != cudaSuccess)
-    return FSA_ERR_LAUNCH;
 
   fsa::BwdKernelParams p;
   memset(&p, 0, sizeof(p));

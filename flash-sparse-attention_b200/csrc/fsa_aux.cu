@@ -105,43 +105,67 @@ __device__ __forceinline__ RowPos locate_row(long long item, int heads, int varl
   return r;
 }
 
-// head_dim / 8 lanes per (query row, head), 16-byte loads. flash_sparse_attn/ops/triton/flash_bwd_preprocess.py:170-195.
+constexpr int PP_ITEMS = 4;  // (row, head) items per lane group in the pre / post passes: more loads in flight
+
+// head_dim / 8 lanes per (query row, head), 16-byte loads; also clears the row of the fp32 dQ accumulator.
+// flash_sparse_attn/ops/triton/flash_bwd_preprocess.py:170-195.
 template <typename T>
 __global__ void __launch_bounds__(256) bwd_pre_kernel(BwdPreParams p) {
   const int lpr = p.head_dim_pad >> 3;  // lanes per row (8 or 16); lanes past the real head size idle
   const int lane = threadIdx.x & 31, sub = lane % lpr;
-  const long long item = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (32 / lpr) + lane / lpr;
+  const int groups = 32 / lpr;
+  const long long first =
+      (((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * groups + lane / lpr) * PP_ITEMS;
   const long long rows = p.varlen ? p.total_q : (long long)p.B * p.sq;
-  const bool live = item < rows * p.heads;
-  float acc = 0.f;
-  RowPos r = {0, 0, 0, 0};
-  if (live) r = locate_row(item, p.heads, p.varlen, p.cu_q, p.B, p.sq);
-  if (live && sub * 8 < p.head_dim) {
-    const T* o = reinterpret_cast<const T*>(p.out) + (p.varlen ? 0 : (long long)r.b * p.o_sb) + r.tok * p.o_sm +
-                 (long long)r.h * p.o_sh + sub * 8;
-    const T* d = reinterpret_cast<const T*>(p.dout) + (p.varlen ? 0 : (long long)r.b * p.do_sb) + r.tok * p.do_sm +
-                 (long long)r.h * p.do_sh + sub * 8;
-    const uint4 a = *reinterpret_cast<const uint4*>(o);
-    const uint4 g = *reinterpret_cast<const uint4*>(d);
-    const uint32_t av[4] = {a.x, a.y, a.z, a.w}, gv[4] = {g.x, g.y, g.z, g.w};
+  const long long n_items = rows * p.heads;
+  RowPos r[PP_ITEMS];
+  uint4 a[PP_ITEMS], g[PP_ITEMS];
+  bool live[PP_ITEMS];
+#pragma unroll
+  for (int u = 0; u < PP_ITEMS; ++u) {
+    live[u] = first + u < n_items;
+    r[u] = RowPos{0, 0, 0, 0};
+    a[u] = g[u] = make_uint4(0, 0, 0, 0);
+    if (live[u]) {
+      r[u] = locate_row(first + u, p.heads, p.varlen, p.cu_q, p.B, p.sq);
+      if (sub * 8 < p.head_dim) {
+        const T* o = reinterpret_cast<const T*>(p.out) + (p.varlen ? 0 : (long long)r[u].b * p.o_sb) + r[u].tok * p.o_sm +
+                     (long long)r[u].h * p.o_sh + sub * 8;
+        const T* d = reinterpret_cast<const T*>(p.dout) + (p.varlen ? 0 : (long long)r[u].b * p.do_sb) +
+                     r[u].tok * p.do_sm + (long long)r[u].h * p.do_sh + sub * 8;
+        a[u] = *reinterpret_cast<const uint4*>(o);
+        g[u] = *reinterpret_cast<const uint4*>(d);
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < PP_ITEMS; ++u) {
+    const uint32_t av[4] = {a[u].x, a[u].y, a[u].z, a[u].w}, gv[4] = {g[u].x, g[u].y, g[u].z, g[u].w};
+    float acc = 0.f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float2 x = unpack2<T>(av[i]), y = unpack2<T>(gv[i]);
       acc += x.x * y.x + x.y * y.y;
     }
-  }
-  for (int s = lpr >> 1; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-  if (live && sub == 0) {
-    const float lse = p.lse[(p.varlen ? 0 : (long long)r.b * p.l_sb) + (long long)r.h * p.l_sh + r.tok];
-    float l2 = (lse == lse) ? lse * 1.4426950408889634f : 1e6f;
-    l2 = fmaxf(l2, -1e6f);
-    const long long w = (long long)r.h * p.ws_sh + padded_row(p.varlen, p.cu_q, r.b, p.sq, r.q);
-    // both are stored negated: the main kernel then needs one packed fma / add per pair of entries
-    p.lse2_ws[w] = -l2;
-    p.dpsum_ws[w] = -acc;
-    if (p.alpha_ws)
-      reinterpret_cast<T*>(p.alpha_ws)[w] = reinterpret_cast<const T*>(
-          p.alpha)[(p.varlen ? 0 : (long long)r.b * p.a_sb) + (long long)r.h * p.a_sh + r.tok];
+    for (int s = lpr >> 1; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+    if (!live[u]) continue;
+    const long long w = (long long)r[u].h * p.ws_sh + padded_row(p.varlen, p.cu_q, r[u].b, p.sq, r[u].q);
+    if (p.dq_accum) {
+      float4* z = reinterpret_cast<float4*>(p.dq_accum + w * p.head_dim_pad + sub * 8);
+      z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+      z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (sub == 0) {
+      const float lse = p.lse[(p.varlen ? 0 : (long long)r[u].b * p.l_sb) + (long long)r[u].h * p.l_sh + r[u].tok];
+      float l2 = (lse == lse) ? lse * 1.4426950408889634f : 1e6f;
+      l2 = fmaxf(l2, -1e6f);
+      // both are stored negated: the main kernel then needs one packed fma / add per pair of entries
+      p.lse2_ws[w] = -l2;
+      p.dpsum_ws[w] = -acc;
+      if (p.alpha_ws)
+        reinterpret_cast<T*>(p.alpha_ws)[w] = reinterpret_cast<const T*>(
+            p.alpha)[(p.varlen ? 0 : (long long)r[u].b * p.a_sb) + (long long)r[u].h * p.a_sh + r[u].tok];
+    }
   }
 }
 
@@ -150,25 +174,47 @@ template <typename T>
 __global__ void __launch_bounds__(256) bwd_post_kernel(BwdPostParams p) {
   const int lpr = p.head_dim_pad >> 3;
   const int lane = threadIdx.x & 31, sub = lane % lpr;
-  const long long item = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (32 / lpr) + lane / lpr;
+  const int groups = 32 / lpr;
+  const long long first =
+      (((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * groups + lane / lpr) * PP_ITEMS;
   const long long rows = p.varlen ? p.total_q : (long long)p.B * p.sq;
-  if (item >= rows * p.heads) return;
-  const RowPos r = locate_row(item, p.heads, p.varlen, p.cu_q, p.B, p.sq);
-  const long long wrow = (long long)r.h * p.ws_sh + padded_row(p.varlen, p.cu_q, r.b, p.sq, r.q);
-  if (p.da && sub == 0)
-    reinterpret_cast<T*>(p.da)[(p.varlen ? 0 : (long long)r.b * p.da_sb) + (long long)r.h * p.da_sh + r.tok] =
-        T(p.da_accum[wrow] * p.scale);
-  if (sub * 8 >= p.head_dim) return;
-  const float4* src = reinterpret_cast<const float4*>(p.dq_accum + wrow * p.head_dim_pad + sub * 8);
-  const float4 v0 = __ldcs(src), v1 = __ldcs(src + 1);  // read once: do not keep in cache
-  uint4 o;
-  o.x = pack2<T>(v0.x * p.scale, v0.y * p.scale);
-  o.y = pack2<T>(v0.z * p.scale, v0.w * p.scale);
-  o.z = pack2<T>(v1.x * p.scale, v1.y * p.scale);
-  o.w = pack2<T>(v1.z * p.scale, v1.w * p.scale);
-  T* dst = reinterpret_cast<T*>(p.dq) + (p.varlen ? 0 : (long long)r.b * p.dq_sb) + r.tok * p.dq_sm +
-           (long long)r.h * p.dq_sh + sub * 8;
-  *reinterpret_cast<uint4*>(dst) = o;
+  const long long n_items = rows * p.heads;
+  RowPos r[PP_ITEMS];
+  long long wrow[PP_ITEMS];
+  float4 v0[PP_ITEMS], v1[PP_ITEMS];
+  bool live[PP_ITEMS];
+#pragma unroll
+  for (int u = 0; u < PP_ITEMS; ++u) {
+    live[u] = first + u < n_items;
+    r[u] = RowPos{0, 0, 0, 0};
+    wrow[u] = 0;
+    v0[u] = v1[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live[u]) {
+      r[u] = locate_row(first + u, p.heads, p.varlen, p.cu_q, p.B, p.sq);
+      wrow[u] = (long long)r[u].h * p.ws_sh + padded_row(p.varlen, p.cu_q, r[u].b, p.sq, r[u].q);
+      if (sub * 8 < p.head_dim) {
+        const float4* src = reinterpret_cast<const float4*>(p.dq_accum + wrow[u] * p.head_dim_pad + sub * 8);
+        v0[u] = __ldcs(src);  // read once: do not keep in cache
+        v1[u] = __ldcs(src + 1);
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < PP_ITEMS; ++u) {
+    if (!live[u]) continue;
+    if (p.da && sub == 0)
+      reinterpret_cast<T*>(p.da)[(p.varlen ? 0 : (long long)r[u].b * p.da_sb) + (long long)r[u].h * p.da_sh + r[u].tok] =
+          T(p.da_accum[wrow[u]] * p.scale);
+    if (sub * 8 >= p.head_dim) continue;
+    uint4 o;
+    o.x = pack2<T>(v0[u].x * p.scale, v0[u].y * p.scale);
+    o.y = pack2<T>(v0[u].z * p.scale, v0[u].w * p.scale);
+    o.z = pack2<T>(v1[u].x * p.scale, v1[u].y * p.scale);
+    o.w = pack2<T>(v1[u].z * p.scale, v1[u].w * p.scale);
+    T* dst = reinterpret_cast<T*>(p.dq) + (p.varlen ? 0 : (long long)r[u].b * p.dq_sb) + r[u].tok * p.dq_sm +
+             (long long)r[u].h * p.dq_sh + sub * 8;
+    *reinterpret_cast<uint4*>(dst) = o;
+  }
 }
 
 __global__ void __launch_bounds__(128) dq_order_kernel(DqOrderParams p) {
@@ -245,7 +291,7 @@ cudaError_t launch_bwd_pre(const BwdPreParams& p, int dtype, cudaStream_t stream
   const long long items = rows * p.heads;
   if (items <= 0) return cudaSuccess;
   if (p.head_dim_pad != 64 && p.head_dim_pad != 128) return cudaErrorInvalidValue;
-  const int per_block = 8 * (32 / (p.head_dim_pad >> 3));
+  const int per_block = 8 * (32 / (p.head_dim_pad >> 3)) * PP_ITEMS;
   const unsigned grid = (unsigned)((items + per_block - 1) / per_block);
   if (dtype == DT_BF16)
     bwd_pre_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
@@ -259,7 +305,7 @@ cudaError_t launch_bwd_post(const BwdPostParams& p, int dtype, cudaStream_t stre
   const long long items = rows * p.heads;
   if (items <= 0) return cudaSuccess;
   if (p.head_dim_pad != 64 && p.head_dim_pad != 128) return cudaErrorInvalidValue;
-  const int per_block = 8 * (32 / (p.head_dim_pad >> 3));
+  const int per_block = 8 * (32 / (p.head_dim_pad >> 3)) * PP_ITEMS;
   const unsigned grid = (unsigned)((items + per_block - 1) / per_block);
   if (dtype == DT_BF16)
     bwd_post_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);

@@ -29,6 +29,7 @@ struct BwdPreParams {
   float* lse2_ws;
   float* dpsum_ws;
   const int* cu_q;
+  float* dq_accum;    // optional: [heads, ws_sh, head_dim_pad] fp32, the rows of real queries are cleared here
   const void* alpha;  // optional (gated): T [B, heads, sq] | [heads, total_q]
   void* alpha_ws;     // optional (gated): T [heads, ws_sh], pre-zeroed; receives alpha at the padded rows
   long long a_sb, a_sh;
