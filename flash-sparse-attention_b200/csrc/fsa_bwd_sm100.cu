@@ -116,8 +116,12 @@ __device__ __forceinline__ SegList make_segments(const FsaBwdSched& s, bool caus
       l.total += e - b;
     }
   };
-  if (causal || local) add(s.m_min, s.m_min_no_mask, local ? FSA_MASK_LOCAL : FSA_MASK_CAUSAL);
-  if (!local) add((causal || local) ? s.m_min_no_mask : s.m_min, s.m_max, FSA_MASK_NONE);
+  // The reference clamps m_min_no_mask to m_max only under split-QO (scheduler.py:1041-1043); without the
+  // clamp its masked loop can run past the last query tile (a short query against a long key sequence), where
+  // every load is masked off. Here such a tile would read workspace rows that do not exist: clip it.
+  const int m_nm = fsa_imin(s.m_min_no_mask, s.m_max);
+  if (causal || local) add(s.m_min, m_nm, local ? FSA_MASK_LOCAL : FSA_MASK_CAUSAL);
+  if (!local) add((causal || local) ? m_nm : s.m_min, s.m_max, FSA_MASK_NONE);
   if (local) {
     add(s.win_min, s.win_min_no_mask, FSA_MASK_LOCAL);
     add(s.win_min_no_mask, s.win_max_no_mask, FSA_MASK_NONE);
@@ -676,7 +680,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
             const float gx = a8[j] * dlt;
             float gte = gx;
             if (logsig)
-              gte = fminf(gx, 0.f) - 0.6931471805599453f * lg2_approx(1.0f + ex2_approx(-fabsf(gx) * 1.4426950408889634f));
+              gte = log_sigmoid_fast(gx);
             sr[i + j] = __float_as_uint(__uint_as_float(sr[i + j]) + gte);
           }
         }

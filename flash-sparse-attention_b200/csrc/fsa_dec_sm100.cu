@@ -415,7 +415,7 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
             const float x = (e < 2 ? al0 : al1) * dk;
             float gte = x;
             if (logsig)
-              gte = fminf(x, 0.f) - 0.6931471805599453f * lg2_approx(1.0f + ex2_approx(-fabsf(x) * 1.4426950408889634f));
+              gte = log_sigmoid_fast(x);
             s[j][e] += gte;
           }
       }

@@ -30,6 +30,7 @@
 #ifdef FSA_PHASE_TIMING
 __device__ unsigned long long g_fwd_ticks[16];
 #define FWD_TICK_DECL long long ftk_[16] = {0}; long long ftk_t_ = clock64(); const bool ftk_on_ = (lane == 0) && (warp == 0)
+#define FWD_TICK_DECL_MMA long long ftk_[16] = {0}; long long ftk_t_ = clock64(); const bool ftk_on_ = (lane == 0)
 #define FWD_TICK(i)                          \
   do {                                       \
     const long long now_ = clock64();        \
@@ -44,6 +45,7 @@ __device__ unsigned long long g_fwd_ticks[16];
   } while (0)
 #else
 #define FWD_TICK_DECL
+#define FWD_TICK_DECL_MMA
 #define FWD_TICK(i)
 #define FWD_TICK_FLUSH
 #endif
@@ -423,21 +425,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     int cnt[2] = {0, 0};
     bool o_started[2] = {false, false};
     int n = first_tile();
+    // Every lane runs the same (warp-uniform) descriptor arithmetic; the MMA and commit instructions carry the
+    // one-lane predicate themselves.
+    const uint32_t lead = lane == 0 ? 1u : 0u;
+    const uint32_t dq_lo = umma_desc_lo(sQ, 16), dk_lo = umma_desc_lo(sK, 16), dv_lo = umma_desc_lo(sV, TN * 128);
     auto issue_s = [&](int q, int ks) {
-      if (lane == 0) {
+      const uint32_t aq = dq_lo + ((q * SM::kTileBytes) >> 4), bk = dk_lo + ((ks * SM::kTileBytes) >> 4);
 #pragma unroll
-        for (int kk = 0; kk < KK_QK; ++kk) {
-          const uint32_t koff = (kk >> 2) * (TM * 128) + (kk & 3) * 32;
-          if (F8)
-            umma_f8_ss(tmem_base + TMEM_S0 + q * 128, umma_smem_desc(sQ + q * SM::kTileBytes + koff, 16, 1024),
-                       umma_smem_desc(sK + ks * SM::kTileBytes + koff, 16, 1024), idesc_s, kk > 0);
-          else
-            umma_ss(tmem_base + TMEM_S0 + q * 128, umma_smem_desc(sQ + q * SM::kTileBytes + koff, 16, 1024),
-                    umma_smem_desc(sK + ks * SM::kTileBytes + koff, 16, 1024), idesc_s, kk > 0);
-        }
-        umma_commit(&bars->s_full[q]);
+      for (int kk = 0; kk < KK_QK; ++kk) {
+        const uint32_t koff = (kk >> 2) * (TM * 128) + (kk & 3) * 32;
+        if (F8)
+          umma_f8_ss_lead(lead, tmem_base + TMEM_S0 + q * 128, umma_desc_at(aq, koff), umma_desc_at(bk, koff), idesc_s,
+                          kk > 0);
+        else
+          umma_ss_lead(lead, tmem_base + TMEM_S0 + q * 128, umma_desc_at(aq, koff), umma_desc_at(bk, koff), idesc_s,
+                       kk > 0);
       }
-      __syncwarp();
+      umma_commit_lead(lead, &bars->s_full[q]);
     };
     if (n >= 0 && ok) {
       ok = mbar_wait(&bars->q_full, 0, abort_flag);
@@ -446,11 +450,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       if (ok) {
         for (int q = 0; q < 2; ++q)
           if (fsa_fwd_tile_mode(sched[q], n, causal, local) >= 0) issue_s(q, 0);
-        if (lane == 0) umma_commit(&bars->k_empty[0]);
-        __syncwarp();
+        umma_commit_lead(lead, &bars->k_empty[0]);
       }
     }
     int t = 0;
+    FWD_TICK_DECL_MMA;
     while (n >= 0 && ok) {
       const int n_next = next_tile(n);
       const int vs = t % VSTAGES;
@@ -459,12 +463,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
 #pragma unroll
       for (int q = 0; q < 2; ++q) {
         if (fsa_fwd_tile_mode(sched[q], n, causal, local) >= 0) {
+          FWD_TICK(14);
           ok = ok && mbar_wait(&bars->p_full[q], cnt[q] & 1, abort_flag);
+          FWD_TICK(10 + q);
           if (!ok) break;
           const bool skip = (KIND != KIND_DENSE) && bars->skip_flag[q][cnt[q] & 1];
           cnt[q]++;
           if (!v_ready) {
             ok = mbar_wait(&bars->v_full[vs], (t / VSTAGES) & 1, abort_flag);
+            FWD_TICK(12);
             if (!ok) break;
             v_ready = true;
             if ((p.flags & F_KV_RAGGED) && (n + 1) * TN > si.sk) {
@@ -483,38 +490,37 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
             }
           }
           tc_fence_after();
+          FWD_TICK(14);
           if (!skip) {
-            if (lane == 0) {
+            const uint32_t bv = dv_lo + ((vs * SM::kTileBytes) >> 4);
 #pragma unroll
-              for (int kk = 0; kk < KK_PV; ++kk) {
-                if (F8)
-                  umma_f8_ts(tmem_base + TMEM_O0 + q * 128, tmem_base + TMEM_S0 + q * 128 + kk * 8,
-                             umma_smem_desc(sV + vs * SM::kTileBytes + kk * 4096, TN * 128, 1024), idesc_o,
-                             (kk > 0 || o_started[q]) ? 1u : 0u);
-                else
-                  umma_ts(tmem_base + TMEM_O0 + q * 128, tmem_base + TMEM_S0 + q * 128 + kk * 8,
-                          umma_smem_desc(sV + vs * SM::kTileBytes + kk * 2048, TN * 128, 1024), idesc_o,
-                          (kk > 0 || o_started[q]) ? 1u : 0u);
-              }
+            for (int kk = 0; kk < KK_PV; ++kk) {
+              if (F8)
+                umma_f8_ts_lead(lead, tmem_base + TMEM_O0 + q * 128, tmem_base + TMEM_S0 + q * 128 + kk * 8,
+                                umma_desc_at(bv, kk * 4096), idesc_o, (kk > 0 || o_started[q]) ? 1u : 0u);
+              else
+                umma_ts_lead(lead, tmem_base + TMEM_O0 + q * 128, tmem_base + TMEM_S0 + q * 128 + kk * 8,
+                             umma_desc_at(bv, kk * 2048), idesc_o, (kk > 0 || o_started[q]) ? 1u : 0u);
             }
-            __syncwarp();
             o_started[q] = true;
             any_pv = true;
           }
+          FWD_TICK(15);
           // last key tile of this group: tell it when its output is complete
-          if (fsa_fwd_next_tile_below(sched[q], n, local) < 0) {
-            if (lane == 0) umma_commit(&bars->o_final[q]);
-            __syncwarp();
-          }
+          if (fsa_fwd_next_tile_below(sched[q], n, local) < 0) umma_commit_lead(lead, &bars->o_final[q]);
         }
         if (n_next >= 0 && fsa_fwd_tile_mode(sched[q], n_next, causal, local) >= 0) {
           if (!k_ready) {
+            FWD_TICK(14);
             ok = mbar_wait(&bars->k_full[ks_next], ((t + 1) / KSTAGES) & 1, abort_flag);
+            FWD_TICK(13);
             if (!ok) break;
             k_ready = true;
             tc_fence_after();
           }
+          FWD_TICK(14);
           issue_s(q, ks_next);
+          FWD_TICK(8);
         }
       }
       if (!ok) break;
@@ -523,17 +529,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
         // still keep the ring in step
         ok = mbar_wait(&bars->v_full[vs], (t / VSTAGES) & 1, abort_flag);
       }
-      if (lane == 0) {
-        if (any_pv)
-          umma_commit(&bars->v_empty[vs]);
-        else
-          mbar_arrive(&bars->v_empty[vs]);
-        if (n_next >= 0) umma_commit(&bars->k_empty[ks_next]);
-      }
-      __syncwarp();
+      if (any_pv)
+        umma_commit_lead(lead, &bars->v_empty[vs]);
+      else if (lane == 0)
+        mbar_arrive(&bars->v_empty[vs]);
+      if (n_next >= 0) umma_commit_lead(lead, &bars->k_empty[ks_next]);
       n = n_next;
       ++t;
     }
+    FWD_TICK(14);
+    FWD_TICK_FLUSH;
   }
   } else {
     // =============================== softmax groups ==========================================
@@ -679,7 +684,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
             const float x = alpha * dv[j];
             float gte = x;
             if (logsig)
-              gte = fminf(x, 0.f) - 0.6931471805599453f * lg2_approx(1.0f + ex2_approx(-fabsf(x) * 1.4426950408889634f));
+              gte = log_sigmoid_fast(x);
             sr[i + j] = __float_as_uint(__uint_as_float(sr[i + j]) + gte);
           }
         }

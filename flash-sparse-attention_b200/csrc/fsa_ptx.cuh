@@ -215,6 +215,48 @@ __device__ __forceinline__ void umma_f8_ss(uint32_t d_tmem, uint64_t adesc, uint
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Leader-predicated forms: the whole warp runs the (warp-uniform) address arithmetic and the instruction
+// carries the single-lane predicate, instead of a divergent branch around a block of MMAs. Inside a divergent
+// branch every descriptor word has to be moved from a vector to a uniform register right before its use, which
+// costs more issue time per MMA than the MMA takes to execute. `lead` is non-zero in exactly one lane.
+#define FSA_UMMA_LEAD(NAME, KIND, AFMT, ATYPE, ACONS)                                                        \
+  __device__ __forceinline__ void NAME(uint32_t lead, uint32_t d_tmem, ATYPE a, uint64_t bdesc, uint32_t idesc, \
+                                       uint32_t accumulate) {                                                \
+    asm volatile(                                                                                            \
+        "{\n\t"                                                                                              \
+        ".reg .pred p, e;\n\t"                                                                               \
+        "setp.ne.b32 p, %4, 0;\n\t"                                                                          \
+        "setp.ne.b32 e, %5, 0;\n\t"                                                                          \
+        "@e tcgen05.mma.cta_group::1.kind::" KIND " [%0], " AFMT ", %2, %3, p;\n\t"                          \
+        "}\n" ::"r"(d_tmem),                                                                                 \
+        ACONS(a), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(lead)                                         \
+        : "memory");                                                                                         \
+  }
+FSA_UMMA_LEAD(umma_ss_lead, "f16", "%1", uint64_t, "l")
+FSA_UMMA_LEAD(umma_ts_lead, "f16", "[%1]", uint32_t, "r")
+FSA_UMMA_LEAD(umma_f8_ss_lead, "f8f6f4", "%1", uint64_t, "l")
+FSA_UMMA_LEAD(umma_f8_ts_lead, "f8f6f4", "[%1]", uint32_t, "r")
+#undef FSA_UMMA_LEAD
+__device__ __forceinline__ void umma_commit_lead(uint32_t lead, uint64_t* bar) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred e;\n\t"
+      "setp.ne.b32 e, %1, 0;\n\t"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+      "}\n" ::"r"(smem_u32(bar)),
+      "r"(lead)
+      : "memory");
+}
+// Shared-memory descriptor of a 128-byte-swizzled operand with stride-byte-offset 1024 as (low word, constant
+// high word): advancing inside a tile is an add on the low word (the address field holds addr >> 4, 14 bits,
+// enough for every shared-memory address).
+constexpr uint32_t UMMA_DESC_HI_SW128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr >> 4) & 0x3FFFu) | ((lbo_bytes >> 4) << 16);
+}
+__device__ __forceinline__ uint64_t umma_desc_at(uint32_t lo, uint32_t byte_off) {
+  return (static_cast<uint64_t>(UMMA_DESC_HI_SW128) << 32) | static_cast<uint64_t>(lo + (byte_off >> 4));
+}
 // mbarrier arrives once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -281,6 +323,18 @@ __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// logsigmoid(x) = min(x, 0) - log1p(exp(-|x|)) with one special-function op (the exponential): log1p(u)
+// on u in (0, 1] is a degree-5 polynomial u * q(u), absolute error < 4.1e-5 - far below the rounding of the
+// 16-bit probabilities the gate ends up in. (flash_sparse_attn/ops/triton/activations.py:245-262)
+__device__ __forceinline__ float log_sigmoid_fast(float x) {
+  float u;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(u) : "f"(-fabsf(x) * 1.4426950408889634f));
+  float q = fmaf(u, 0.0415511145f, -0.157838377f);
+  q = fmaf(q, u, 0.3065611f);
+  q = fmaf(q, u, -0.497030843f);
+  q = fmaf(q, u, 0.999944993f);
+  return fminf(x, 0.f) - u * q;
 }
 __device__ __forceinline__ float lg2_approx(float x) {
   float y;

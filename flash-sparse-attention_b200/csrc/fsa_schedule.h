@@ -378,8 +378,10 @@ FSA_HD FsaBwdSched fsa_bwd_schedule(int sq, int sk, int n_block, int split_idx, 
 // flash_sparse_attn/ops/triton/flash_sparse_bwd.py:315-464).
 FSA_HD bool fsa_bwd_visits(const FsaBwdSched& s, int m, bool causal, bool local) {
   bool in = false;
-  if (causal || local) in |= (m >= s.m_min && m < s.m_min_no_mask);
-  if (!local) in |= (m >= ((causal || local) ? s.m_min_no_mask : s.m_min) && m < s.m_max);
+  // tiles past m_max lie beyond the query rows (the reference visits them with every load masked off)
+  const int m_nm = fsa_imin(s.m_min_no_mask, s.m_max);
+  if (causal || local) in |= (m >= s.m_min && m < m_nm);
+  if (!local) in |= (m >= ((causal || local) ? m_nm : s.m_min) && m < s.m_max);
   if (local) {
     in |= (m >= s.win_min && m < s.win_min_no_mask);
     in |= (m >= s.win_min_no_mask && m < s.win_max_no_mask);

@@ -319,11 +319,14 @@ def bwd_tiles(s: BwdSched, causal: bool, local: bool) -> List[Tuple[int, int]]:
     ascending within each phase: diagonal masked -> unmasked -> window (right-masked, interior,
     left-masked) -> sink."""
     out = []
+    # without split-QO the reference leaves m_min_no_mask unclamped (scheduler.py:1041-1043): tiles in
+    # [m_max, m_min_no_mask) lie past the query rows and contribute nothing, they are not listed
+    m_nm = min(s.m_min_no_mask, s.m_max)
     if causal or local:
-        for m in range(s.m_min, s.m_min_no_mask):
+        for m in range(s.m_min, m_nm):
             out.append((m, MASK_LOCAL if local else MASK_CAUSAL))
         if not local:
-            for m in range(s.m_min_no_mask, s.m_max):
+            for m in range(m_nm, s.m_max):
                 out.append((m, MASK_NONE))
     else:
         for m in range(s.m_min, s.m_max):

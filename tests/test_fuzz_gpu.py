@@ -1,0 +1,128 @@
+"""Randomised shapes and options against the eager oracle: forward, backward and decode with random
+sequence lengths (ragged against the 128 tile), GQA ratios, per-head windows, causal / local / split /
+packed-GQA switches. Seeds are fixed; every case is small enough for the CPU oracle."""
+
+import random
+
+import pytest
+import torch
+
+from fixtures import assert_close
+from oracle import eager
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _ops():
+    import flash_sparse_attn as fsa
+
+    return fsa
+
+
+def _case(seed):
+    rnd = random.Random(seed)
+    hkv = rnd.choice([1, 2, 4])
+    group = rnd.choice([1, 2, 4, 8])
+    head_dim = rnd.choice([32, 64, 96, 128])
+    sk = rnd.choice([17, 128, 129, 255, 384, 500, 777, 1024, 1100])
+    causal = rnd.random() < 0.6
+    sq = sk if rnd.random() < 0.5 else rnd.choice([1, 16, 100, 128, 200, 640])
+    if causal and sq > sk:
+        sq = sk
+    local = rnd.random() < 0.5
+    ws = None
+    if local:
+        ws = torch.tensor([[rnd.choice([0, 1, 16, 64, 130]), rnd.choice([0, 50, 128, 300]), rnd.choice([0, 33, 128]),
+                            rnd.choice([1, 17, 64, 128, 260])] for _ in range(hkv)], dtype=torch.int32)
+    return dict(b=rnd.choice([1, 2, 3]), sq=sq, sk=sk, hq=hkv * group, hkv=hkv, d=head_dim, causal=causal, ws=ws,
+                split=rnd.random() < 0.4, nsplit=rnd.choice([2, 3, 5]), pack=rnd.random() < 0.3,
+                dtype=rnd.choice([torch.bfloat16, torch.float16]))
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_forward_backward_fuzz(seed):
+    fsa = _ops()
+    c = _case(seed)
+    g = torch.Generator().manual_seed(seed)
+    mk = lambda *s: torch.randn(*s, generator=g).to(c["dtype"])  # noqa: E731
+    q, k, v = mk(c["b"], c["sq"], c["hq"], c["d"]), mk(c["b"], c["sk"], c["hkv"], c["d"]), mk(c["b"], c["sk"], c["hkv"], c["d"])
+    do = mk(c["b"], c["sq"], c["hq"], c["d"])
+    local = c["ws"] is not None
+    causal = c["causal"] and c["sq"] > 1
+    ref_out = eager.forward(q, k, v, None, causal, is_local=local, window_sizes=c["ws"])
+    ref_g = eager.backward(q, k, v, do, None, causal, is_local=local, window_sizes=c["ws"])
+    leaves = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    kw = dict(is_causal=causal, softmax_threshold=-128.0, pack_gqa=c["pack"])
+    if local:
+        kw["window_sizes"] = c["ws"].to(DEV)
+    if c["split"]:
+        kw.update(is_split_kv=True, is_split_qo=True, num_splits=c["nsplit"])
+    out = fsa.flash_sparse_attn_func(*leaves, **kw)
+    out.backward(do.to(DEV))
+    torch.cuda.synchronize()
+    fsa.check_status()
+    tag = f"seed{seed}-{ {k_: (v_ if not isinstance(v_, torch.Tensor) else v_.tolist()) for k_, v_ in c.items()} }"
+    # rows without any visible key are zero in the operator (empty softmax) and NaN in the eager oracle
+    ref_out = torch.nan_to_num(ref_out, nan=0.0)
+    assert_close("out " + tag, out, ref_out, rtol=2.5e-2, atol=2.5e-2)
+    for name, t, r in zip(("dq", "dk", "dv"), leaves, ref_g):
+        assert_close(f"{name} {tag}", t.grad, torch.nan_to_num(r, nan=0.0), rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("seed", range(30))
+def test_decode_fuzz(seed):
+    fsa = _ops()
+    rnd = random.Random(1000 + seed)
+    hkv = rnd.choice([1, 2, 4])
+    group = rnd.choice([1, 2, 4, 8, 16])
+    d = rnd.choice([32, 64, 96, 128])
+    b = rnd.choice([1, 2, 5])
+    sk = rnd.choice([1, 15, 16, 17, 100, 256, 1000, 2049])
+    mode = rnd.choice(["plain", "local", "gather", "paged", "used"])
+    nsplit = rnd.choice([None, 1, 2, 7])
+    g = torch.Generator().manual_seed(seed)
+    mk = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16)  # noqa: E731
+    q, k, v = mk(b, hkv * group, d), mk(b, sk, hkv, d), mk(b, sk, hkv, d)
+    kw = dict(softmax_threshold=-128.0, num_splits=nsplit)
+    if mode == "local":
+        ws = torch.tensor([[rnd.choice([0, 4, 64]), rnd.choice([0, 30, 200]), rnd.choice([0, 10, 100]), rnd.choice([1, 16, 50, 300])]
+                           for _ in range(hkv)], dtype=torch.int32)
+        ref = eager.decode(q, k, v, is_local=True, window_sizes=ws)
+        out = fsa.flash_sparse_attn_with_kvcache_func(q.to(DEV), k.to(DEV), v.to(DEV), window_sizes=ws.to(DEV), **kw)
+    elif mode == "gather":
+        topk = rnd.choice([1, 16, 40, min(sk, 512)])
+        topk = min(topk, sk)
+        idx = torch.stack([torch.randperm(sk, generator=g)[:topk] for _ in range(b)]).to(torch.int32)
+        if topk > 3:
+            idx[:, 1::3] = -1
+        ref = eager.gather_decode(q, k, v, idx)
+        out = fsa.flash_sparse_attn_with_kvcache_func(q.to(DEV), k.to(DEV), v.to(DEV), gather_kv_indices=idx.to(DEV), **kw)
+    elif mode == "paged":
+        page = rnd.choice([32, 64, 128, 256])
+        n_pp = -(-sk // page)
+        kp_log = torch.zeros(b, n_pp * page, hkv, d, dtype=torch.bfloat16)
+        vp_log = torch.zeros_like(kp_log)
+        kp_log[:, :sk], vp_log[:, :sk] = k, v
+        perm = torch.randperm(b * n_pp, generator=g)
+        table = torch.empty(b * n_pp, dtype=torch.int32)
+        table[perm] = torch.arange(b * n_pp, dtype=torch.int32)
+        kc = torch.empty(b * n_pp, page, hkv, d, dtype=torch.bfloat16)
+        vc = torch.empty_like(kc)
+        kc[table.long()] = kp_log.reshape(b * n_pp, page, hkv, d)
+        vc[table.long()] = vp_log.reshape(b * n_pp, page, hkv, d)
+        used = torch.full((b,), sk, dtype=torch.int32)
+        ref = eager.decode(q, k, v)
+        out = fsa.flash_sparse_attn_with_kvcache_func(q.to(DEV), kc.to(DEV), vc.to(DEV), page_table=table.reshape(b, n_pp).to(DEV),
+                                                      seqused_k=used.to(DEV), **kw)
+    elif mode == "used":
+        used = torch.tensor([rnd.randint(1, sk) for _ in range(b)], dtype=torch.int32)
+        ref = eager.decode(q, k, v, seqused_k=used)
+        out = fsa.flash_sparse_attn_with_kvcache_func(q.to(DEV), k.to(DEV), v.to(DEV), seqused_k=used.to(DEV), **kw)
+    else:
+        ref = eager.decode(q, k, v)
+        out = fsa.flash_sparse_attn_with_kvcache_func(q.to(DEV), k.to(DEV), v.to(DEV), **kw)
+    torch.cuda.synchronize()
+    fsa.check_status()
+    assert_close(f"decode seed{seed} {mode} b{b} sk{sk} hkv{hkv} g{group} d{d} ns{nsplit}", out, torch.nan_to_num(ref, nan=0.0),
+                 rtol=2.5e-2, atol=2.5e-2)

@@ -99,6 +99,20 @@ def test_bwd_exact_cover(local, ns):
         assert all(v == 1 for v in seen.values())
 
 
+def test_bwd_tiles_stay_inside_the_query_range():
+    """A short query against a long causal key sequence: the reference's unclamped m_min_no_mask
+    (scheduler.py:1028-1043) points past the last query tile; the listed tiles must not."""
+    for sq, sk in [(77, 300), (128, 300), (5, 1000), (129, 700)]:
+        for nb in range(-(-sk // 128)):
+            sched = S.bwd_schedule(sq, sk, nb, 0, [0, 0, 0, 0], 1, 128, 128, True, False, False)
+            tiles = [m for m, _ in S.bwd_tiles(sched, True, False)]
+            assert all(0 <= m < -(-sq // 128) for m in tiles), (sq, sk, nb, tiles)
+            assert len(set(tiles)) == len(tiles)
+    # the case that motivated this: the raw schedule value really is out of range
+    raw = S.bwd_schedule(77, 300, 2, 0, [0, 0, 0, 0], 1, 128, 128, True, False, False)
+    assert raw.m_min_no_mask == 2 and raw.m_max == 1
+
+
 def _decode_cover(sk, window, tn, nsub, gpack, cover):
     seen = {}
     for sp in range(nsub):
