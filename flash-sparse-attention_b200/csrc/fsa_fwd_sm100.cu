@@ -28,9 +28,9 @@
 // Development aid: with -DFSA_PHASE_TIMING lane 0 of softmax warp 0 adds up the clock cycles of its phases;
 // fsa_debug_fwd_ticks() reads the totals over all CTAs.
 #ifdef FSA_PHASE_TIMING
-__device__ unsigned long long g_fwd_ticks[16];
-#define FWD_TICK_DECL long long ftk_[16] = {0}; long long ftk_t_ = clock64(); const bool ftk_on_ = (lane == 0) && (warp == 0)
-#define FWD_TICK_DECL_MMA long long ftk_[16] = {0}; long long ftk_t_ = clock64(); const bool ftk_on_ = (lane == 0)
+__device__ unsigned long long g_fwd_ticks[24];
+#define FWD_TICK_DECL long long ftk_[24] = {0}; long long ftk_t_ = clock64(); const bool ftk_on_ = (lane == 0) && (warp == 0)
+#define FWD_TICK_DECL_MMA long long ftk_[24] = {0}; long long ftk_t_ = clock64(); const bool ftk_on_ = (lane == 0)
 #define FWD_TICK(i)                          \
   do {                                       \
     const long long now_ = clock64();        \
@@ -40,7 +40,7 @@ __device__ unsigned long long g_fwd_ticks[16];
 #define FWD_TICK_FLUSH                                                                      \
   do {                                                                                      \
     if (ftk_on_)                                                                            \
-      for (int i_ = 0; i_ < 16; ++i_)                                                       \
+      for (int i_ = 0; i_ < 24; ++i_)                                                       \
         if (ftk_[i_]) atomicAdd(&g_fwd_ticks[i_], (unsigned long long)ftk_[i_]);             \
   } while (0)
 #else
@@ -57,6 +57,9 @@ namespace {
 constexpr int TM = 128;  // query rows per softmax group
 constexpr int TN = 128;  // keys per tile
 constexpr int NTHREADS = 384;  // three warpgroups: softmax 0, softmax 1, {producer, MMA, 2 idle}
+// Two K and two V stages. (A third stage of either fills the 227 KB of shared memory, leaves no L1 for the
+// softmax warps' few spilled registers and measured slower.) V(t) and K(t + 1) are consumed by the same loop
+// step of the MMA issuer, so one "consumed" barrier per step releases both.
 constexpr int KSTAGES = 2;
 constexpr int VSTAGES = 2;
 
@@ -86,8 +89,8 @@ struct OutType<__nv_fp8_e5m2> {
 
 struct FwdBars {
   uint64_t q_full;
-  uint64_t k_full[KSTAGES], k_empty[KSTAGES];
-  uint64_t v_full[VSTAGES], v_empty[VSTAGES];
+  uint64_t k_full[KSTAGES], v_full[VSTAGES];
+  uint64_t kv_empty[2];  // signal c (slot c & 1): K(c) and V(c - 1) have been consumed; c = 0 comes from the prologue
   uint64_t s_full[2], p_full[2], o_final[2], vote[2], wg_sync[2];
   uint64_t d_full[2], d_empty[2], a_sync[2];  // gated: delta ring (stager warp -> softmax warps), alpha exchange
   uint32_t tmem_base;
@@ -96,6 +99,9 @@ struct FwdBars {
   int vote_any[2][2][4]; // [group][parity][warp]: bit0 = some row wants the tile, bit1 = some row votes skip
   float a_ext[2][4][2];  // gated: per group, per warp (max, min) of alpha
   float dl[2][TN + 4];   // gated: delta of the key tile as fp32, then its max and min
+#ifdef FSA_PHASE_TIMING
+  long long dbg_t[4];
+#endif
 };
 
 struct SeqInfo {
@@ -242,13 +248,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
   // ---- setup ---------------------------------------------------------------------------------
   if (tid == 0) {
     mbar_init(&bars->q_full, 1);
-    for (int s = 0; s < KSTAGES; ++s) {
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&bars->k_full[s], 1);
-      mbar_init(&bars->k_empty[s], 1);
-    }
-    for (int s = 0; s < VSTAGES; ++s) {
       mbar_init(&bars->v_full[s], 1);
-      mbar_init(&bars->v_empty[s], 1);
+      mbar_init(&bars->kv_empty[s], 1);
     }
     for (int q = 0; q < 2; ++q) {
       mbar_init(&bars->s_full[q], 1);
@@ -338,11 +341,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       }
       while (n >= 0 && ok) {
         const int n_next = next_tile(n);
+        // the slots of K(t + 1) and V(t) were last held by K(t - 1) and V(t - 2): both released by signal t - 1
+        if (t > 0) ok = mbar_wait(&bars->kv_empty[(t - 1) & 1], ((t - 1) >> 1) & 1, abort_flag);
+        if (!ok) break;
         if (n_next >= 0) {
           const int s = (t + 1) % KSTAGES;
-          const int use = (t + 1) / KSTAGES;
-          if (use > 0) ok = mbar_wait(&bars->k_empty[s], (use - 1) & 1, abort_flag);
-          if (!ok) break;
           load_kv(&p.map_k, smem + SM::kK + s * SM::kTileBytes, &bars->k_full[s], n_next);
         }
         // V is prefetched like K, before the softmax groups have voted on the tile: waiting for the vote
@@ -350,17 +353,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
         // tensor-bound kernel a V tile that ends up unused only costs an L2 read. (The reference skips
         // the load, flash_sparse_fwd.py:60-88; it matters there because its tiles are loaded by the same
         // warps that compute.) A skipped tile still skips the softmax work and the P V product.
-        const bool need_v = true;
-        {
-          const int s = t % VSTAGES;
-          const int use = t / VSTAGES;
-          if (use > 0) ok = mbar_wait(&bars->v_empty[s], (use - 1) & 1, abort_flag);
-          if (!ok) break;
-          if (need_v)
-            load_kv(&p.map_v, smem + SM::kV + s * SM::kTileBytes, &bars->v_full[s], n);
-          else
-            mbar_arrive(&bars->v_full[s]);
-        }
+        load_kv(&p.map_v, smem + SM::kV + (t % VSTAGES) * SM::kTileBytes, &bars->v_full[t % VSTAGES], n);
         n = n_next;
         ++t;
       }
@@ -450,49 +443,75 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       if (ok) {
         for (int q = 0; q < 2; ++q)
           if (fsa_fwd_tile_mode(sched[q], n, causal, local) >= 0) issue_s(q, 0);
-        umma_commit_lead(lead, &bars->k_empty[0]);
+        umma_commit_lead(lead, &bars->kv_empty[0]);
       }
     }
     int t = 0;
     FWD_TICK_DECL_MMA;
+    // The tensor pipe takes an MMA from a thread about as fast as it executes one: while its MMAs run this warp
+    // is blocked in their issue, and whatever it does between a group publishing P and the next MMA is time the
+    // pipe idles. So everything that does not depend on P (the walk over the tiles, who takes part in the next
+    // tile, the K / V arrivals) happens before the wait for P. (One issuer per group was tried: the second
+    // polling warp slows the softmax warps of its scheduler more than the overlap gains.)
+    bool act[2], last[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) act[q] = n >= 0 && fsa_fwd_tile_mode(sched[q], n, causal, local) >= 0;
     while (n >= 0 && ok) {
       const int n_next = next_tile(n);
       const int vs = t % VSTAGES;
-      bool v_ready = false, k_ready = false, any_pv = false;
       const int ks_next = (t + 1) % KSTAGES;
+      bool act_next[2];
 #pragma unroll
       for (int q = 0; q < 2; ++q) {
-        if (fsa_fwd_tile_mode(sched[q], n, causal, local) >= 0) {
+        if (!local) {  // one contiguous range of tiles per group
+          act_next[q] = n_next >= sched[q].n_min && n_next < sched[q].n_max;
+          last[q] = act[q] && n == sched[q].n_min;
+        } else {
+          act_next[q] = n_next >= 0 && fsa_fwd_tile_mode(sched[q], n_next, causal, local) >= 0;
+          last[q] = act[q] && fsa_fwd_next_tile_below(sched[q], n, local) < 0;
+        }
+      }
+      FWD_TICK(14);
+      ok = mbar_wait(&bars->v_full[vs], (t / VSTAGES) & 1, abort_flag);
+      FWD_TICK(12);
+      if (!ok) break;
+      if ((p.flags & F_KV_RAGGED) && (n + 1) * TN > si.sk) {
+        // keys past the sequence end carry probability 0 but their V rows may hold
+        // anything: clear them so that 0 * garbage cannot produce NaN
+        const int r0 = si.sk - n * TN;
+        uint8_t* vt = smem + SM::kV + vs * SM::kTileBytes;
+        constexpr int CPR = HD * ES / 16;  // 16-byte chunks per row
+        for (int i = lane; i < (TN - r0) * CPR; i += 32) {
+          const int r = r0 + i / CPR, c = i % CPR;
+          *reinterpret_cast<uint4*>(vt + (c >> 3) * (TN * 128) + sw128_offset(r, c & 7)) = make_uint4(0, 0, 0, 0);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+      }
+      if (act_next[0] || act_next[1]) {
+        ok = mbar_wait(&bars->k_full[ks_next], ((t + 1) / KSTAGES) & 1, abort_flag);
+        FWD_TICK(13);
+        if (!ok) break;
+      }
+      const uint32_t bv = dv_lo + ((vs * SM::kTileBytes) >> 4);
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        if (act[q]) {
           FWD_TICK(14);
           ok = ok && mbar_wait(&bars->p_full[q], cnt[q] & 1, abort_flag);
           FWD_TICK(10 + q);
+#ifdef FSA_PHASE_TIMING
+          if (q == 0) {
+            const long long d_ = clock64() - *reinterpret_cast<volatile long long*>(&bars->dbg_t[0]);
+            ftk_[16] += d_;
+          }
+#endif
           if (!ok) break;
           const bool skip = (KIND != KIND_DENSE) && bars->skip_flag[q][cnt[q] & 1];
           cnt[q]++;
-          if (!v_ready) {
-            ok = mbar_wait(&bars->v_full[vs], (t / VSTAGES) & 1, abort_flag);
-            FWD_TICK(12);
-            if (!ok) break;
-            v_ready = true;
-            if ((p.flags & F_KV_RAGGED) && (n + 1) * TN > si.sk) {
-              // keys past the sequence end carry probability 0 but their V rows may hold
-              // anything: clear them so that 0 * garbage cannot produce NaN
-              const int r0 = si.sk - n * TN;
-              uint8_t* vt = smem + SM::kV + vs * SM::kTileBytes;
-              constexpr int CPR = HD * ES / 16;  // 16-byte chunks per row
-              for (int i = lane; i < (TN - r0) * CPR; i += 32) {
-                const int r = r0 + i / CPR, c = i % CPR;
-                *reinterpret_cast<uint4*>(vt + (c >> 3) * (TN * 128) + sw128_offset(r, c & 7)) =
-                    make_uint4(0, 0, 0, 0);
-              }
-              fence_proxy_async_smem();
-              __syncwarp();
-            }
-          }
           tc_fence_after();
           FWD_TICK(14);
           if (!skip) {
-            const uint32_t bv = dv_lo + ((vs * SM::kTileBytes) >> 4);
 #pragma unroll
             for (int kk = 0; kk < KK_PV; ++kk) {
               if (F8)
@@ -503,38 +522,30 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
                              umma_desc_at(bv, kk * 2048), idesc_o, (kk > 0 || o_started[q]) ? 1u : 0u);
             }
             o_started[q] = true;
-            any_pv = true;
           }
           FWD_TICK(15);
           // last key tile of this group: tell it when its output is complete
-          if (fsa_fwd_next_tile_below(sched[q], n, local) < 0) umma_commit_lead(lead, &bars->o_final[q]);
+          if (last[q]) umma_commit_lead(lead, &bars->o_final[q]);
+          FWD_TICK(7);
         }
-        if (n_next >= 0 && fsa_fwd_tile_mode(sched[q], n_next, causal, local) >= 0) {
-          if (!k_ready) {
-            FWD_TICK(14);
-            ok = mbar_wait(&bars->k_full[ks_next], ((t + 1) / KSTAGES) & 1, abort_flag);
-            FWD_TICK(13);
-            if (!ok) break;
-            k_ready = true;
-            tc_fence_after();
-          }
+        if (act_next[q]) {
+          if (!act[q]) tc_fence_after();
           FWD_TICK(14);
           issue_s(q, ks_next);
           FWD_TICK(8);
+#ifdef FSA_PHASE_TIMING
+          if (q == 0 && lane == 0) *reinterpret_cast<volatile long long*>(&bars->dbg_t[1]) = clock64();
+#endif
         }
       }
       if (!ok) break;
-      if (!v_ready) {
-        // nobody consumed this V slot (cannot happen: every visited tile has an active group),
-        // still keep the ring in step
-        ok = mbar_wait(&bars->v_full[vs], (t / VSTAGES) & 1, abort_flag);
-      }
-      if (any_pv)
-        umma_commit_lead(lead, &bars->v_empty[vs]);
-      else if (lane == 0)
-        mbar_arrive(&bars->v_empty[vs]);
-      if (n_next >= 0) umma_commit_lead(lead, &bars->k_empty[ks_next]);
+      FWD_TICK(14);
+      // signal t + 1: V(t) and K(t + 1) are free once the MMAs issued so far have completed
+      umma_commit_lead(lead, &bars->kv_empty[(t + 1) & 1]);
+      FWD_TICK(7);
       n = n_next;
+      act[0] = act_next[0];
+      act[1] = act_next[1];
       ++t;
     }
     FWD_TICK(14);
@@ -636,6 +647,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       FWD_TICK(9);
       ok = mbar_wait(&bars->s_full[q], cnt_s & 1, abort_flag);
       FWD_TICK(0);
+#ifdef FSA_PHASE_TIMING
+      if (ftk_on_ && cnt_s > 0) ftk_[17] += clock64() - *reinterpret_cast<volatile long long*>(&bars->dbg_t[1]);
+#endif
       if (!ok) break;
       tc_fence_after();
       const int par = cnt_s & 1;
@@ -832,6 +846,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
+#ifdef FSA_PHASE_TIMING
+      if (warp == 0 && lane == 0) *reinterpret_cast<volatile long long*>(&bars->dbg_t[0]) = clock64();
+#endif
       if (lane == 0) mbar_arrive(&bars->p_full[q]);
       l_ref += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
       have_o = true;
@@ -925,9 +942,9 @@ cudaError_t launch_one(const FwdKernelParams& p, cudaStream_t stream) {
 #ifdef FSA_PHASE_TIMING
 extern "C" void fsa_debug_fwd_ticks(unsigned long long* out16, int reset) {
   cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out16, g_fwd_ticks, sizeof(unsigned long long) * 16);
+  cudaMemcpyFromSymbol(out16, g_fwd_ticks, sizeof(unsigned long long) * 24);
   if (reset) {
-    unsigned long long z[16] = {0};
+    unsigned long long z[24] = {0};
     cudaMemcpyToSymbol(g_fwd_ticks, z, sizeof(z));
   }
 }
