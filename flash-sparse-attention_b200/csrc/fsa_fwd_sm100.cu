@@ -91,7 +91,7 @@ struct FwdBars {
   uint64_t q_full;
   uint64_t k_full[KSTAGES], v_full[VSTAGES];
   uint64_t kv_empty[2];  // signal c (slot c & 1): K(c) and V(c - 1) have been consumed; c = 0 comes from the prologue
-  uint64_t s_full[2], p_full[2], o_final[2], vote[2], wg_sync[2];
+  uint64_t s_full[2], p_full[2], o_final[2], wg_sync[2];
   uint64_t d_full[2], d_empty[2], a_sync[2];  // gated: delta ring (stager warp -> softmax warps), alpha exchange
   uint32_t tmem_base;
   int abort_flag;
@@ -257,7 +257,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       mbar_init(&bars->s_full[q], 1);
       mbar_init(&bars->p_full[q], 4);  // one arrival per warp of the group
       mbar_init(&bars->o_final[q], 1);
-      mbar_init(&bars->vote[q], 1);
       mbar_init(&bars->wg_sync[q], 4);
       mbar_init(&bars->d_full[q], 1);
       mbar_init(&bars->d_empty[q], 8);
@@ -667,8 +666,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
                     p.n_tiles_k + n;
             p.tile_map[idx] = 3;
           }
-          __threadfence_block();
-          mbar_arrive(&bars->vote[q]);
         }
         // keep the group's vote barrier in step with the tile counter
         if (lane == 0) mbar_arrive(&bars->wg_sync[q]);
@@ -743,7 +740,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       // ---- tile skip vote (flash_sparse_attn/ops/triton/activations.py:129-138) -----------------
       bool skip = false;
       if (KIND != KIND_DENSE) {
-        const float d = (m_cur - m_ref) * c - log2f(l_ref);
+        const float d = (m_cur - m_ref) * c - lg2_approx(l_ref);
         const float val = d - thr_log2;
         const unsigned want = __ballot_sync(0xffffffffu, val >= 0.0f);
         const unsigned drop = __ballot_sync(0xffffffffu, val < 0.0f);
@@ -773,8 +770,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
                     p.n_tiles_k + n;
             p.tile_map[idx] = skip ? 2 : 1;
           }
-          __threadfence_block();
-          mbar_arrive(&bars->vote[q]);
+          // no fence: this thread's own arrival on p_full (release) orders the flag before the MMA issuer's read
         }
       }
       if (skip) {
