@@ -57,9 +57,10 @@ namespace {
 constexpr int TM = 128;  // query rows per softmax group
 constexpr int TN = 128;  // keys per tile
 constexpr int NTHREADS = 384;  // three warpgroups: softmax 0, softmax 1, {producer, MMA, 2 idle}
-// Two K and two V stages. (A third stage of either fills the 227 KB of shared memory, leaves no L1 for the
-// softmax warps' few spilled registers and measured slower.) V(t) and K(t + 1) are consumed by the same loop
-// step of the MMA issuer, so one "consumed" barrier per step releases both.
+// Two K and two V stages. V(t) and K(t + 1) are consumed by the same loop step of the MMA issuer, so they
+// arrive on one barrier and one "consumed" barrier per step releases both: every barrier the issuer touches
+// costs it 130-250 cycles even when it is already complete. (A third V stage, loaded a whole step earlier, did
+// not shorten the issuer's wait: it is not load latency.)
 constexpr int KSTAGES = 2;
 constexpr int VSTAGES = 2;
 
@@ -89,7 +90,8 @@ struct OutType<__nv_fp8_e5m2> {
 
 struct FwdBars {
   uint64_t q_full;
-  uint64_t k_full[KSTAGES], v_full[VSTAGES];
+  uint64_t k0_full;     // first K tile
+  uint64_t kv_full[2];  // step t (slot t & 1): V(t) and K(t + 1) have landed (two producer arrivals)
   uint64_t kv_empty[2];  // signal c (slot c & 1): K(c) and V(c - 1) have been consumed; c = 0 comes from the prologue
   uint64_t s_full[2], p_full[2], o_final[2], wg_sync[2];
   uint64_t d_full[2], d_empty[2], a_sync[2];  // gated: delta ring (stager warp -> softmax warps), alpha exchange
@@ -98,11 +100,13 @@ struct FwdBars {
   int skip_flag[2][2];   // [group][parity of the group's tile counter]
   int vote_any[2][2][4]; // [group][parity][warp]: bit0 = some row wants the tile, bit1 = some row votes skip
   float a_ext[2][4][2];  // gated: per group, per warp (max, min) of alpha
-  float dl[2][TN + 4];   // gated: delta of the key tile as fp32, then its max and min
+  alignas(16) float dl[2][TN + 4];  // gated: delta of the key tile as fp32 (read as float4), then its max and min
 #ifdef FSA_PHASE_TIMING
   long long dbg_t[4];
 #endif
 };
+
+static_assert(offsetof(FwdBars, dl) % 16 == 0 && sizeof(FwdBars) <= 2048, "FwdBars layout");
 
 struct SeqInfo {
   int b, split, head, hkv;  // head = query head, or kv head when packing GQA rows
@@ -248,9 +252,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
   // ---- setup ---------------------------------------------------------------------------------
   if (tid == 0) {
     mbar_init(&bars->q_full, 1);
+    mbar_init(&bars->k0_full, 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&bars->k_full[s], 1);
-      mbar_init(&bars->v_full[s], 1);
+      mbar_init(&bars->kv_full[s], 2);
       mbar_init(&bars->kv_empty[s], 1);
     }
     for (int q = 0; q < 2; ++q) {
@@ -332,27 +336,34 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
             tma_load_4d(dst + (d / SLAB) * (TN * 128), map, bar, d, si.hkv, si.off_k + n * TN, kv_row_coord_b);
         }
       };
-      int t = 0;
+      int t = 0, seen = 0;
       bool ok = true;
       int n = first_tile();
       if (n >= 0) {
-        load_kv(&p.map_k, smem + SM::kK, &bars->k_full[0], n);
+        load_kv(&p.map_k, smem + SM::kK, &bars->k0_full, n);
       }
       while (n >= 0 && ok) {
         const int n_next = next_tile(n);
-        // the slots of K(t + 1) and V(t) were last held by K(t - 1) and V(t - 2): both released by signal t - 1
-        if (t > 0) ok = mbar_wait(&bars->kv_empty[(t - 1) & 1], ((t - 1) >> 1) & 1, abort_flag);
+        // Release signals arrive in order (signal c: K(c) and V(c - 1) consumed). V(t) goes into the slot of
+        // V(t - 2) and K(t + 1) into the slot of K(t - 1): both free after signal t - 1.
+        auto need_signal = [&](int c) {
+          while (ok && seen <= c) {
+            ok = mbar_wait(&bars->kv_empty[seen & 1], (seen >> 1) & 1, abort_flag);
+            ++seen;
+          }
+        };
+        need_signal(t - 1);
         if (!ok) break;
-        if (n_next >= 0) {
-          const int s = (t + 1) % KSTAGES;
-          load_kv(&p.map_k, smem + SM::kK + s * SM::kTileBytes, &bars->k_full[s], n_next);
-        }
         // V is prefetched like K, before the softmax groups have voted on the tile: waiting for the vote
         // would put a full load latency between every S tile and its P V product, and in this
         // tensor-bound kernel a V tile that ends up unused only costs an L2 read. (The reference skips
         // the load, flash_sparse_fwd.py:60-88; it matters there because its tiles are loaded by the same
         // warps that compute.) A skipped tile still skips the softmax work and the P V product.
-        load_kv(&p.map_v, smem + SM::kV + (t % VSTAGES) * SM::kTileBytes, &bars->v_full[t % VSTAGES], n);
+        load_kv(&p.map_v, smem + SM::kV + (t % VSTAGES) * SM::kTileBytes, &bars->kv_full[t & 1], n);
+        if (n_next >= 0)
+          load_kv(&p.map_k, smem + SM::kK + ((t + 1) % KSTAGES) * SM::kTileBytes, &bars->kv_full[t & 1], n_next);
+        else
+          mbar_arrive(&bars->kv_full[t & 1]);  // the barrier counts two arrivals per step
         n = n_next;
         ++t;
       }
@@ -437,7 +448,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     };
     if (n >= 0 && ok) {
       ok = mbar_wait(&bars->q_full, 0, abort_flag);
-      ok = ok && mbar_wait(&bars->k_full[0], 0, abort_flag);
+      ok = ok && mbar_wait(&bars->k0_full, 0, abort_flag);
       tc_fence_after();
       if (ok) {
         for (int q = 0; q < 2; ++q)
@@ -471,7 +482,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
         }
       }
       FWD_TICK(14);
-      ok = mbar_wait(&bars->v_full[vs], (t / VSTAGES) & 1, abort_flag);
+      ok = mbar_wait(&bars->kv_full[t & 1], (t >> 1) & 1, abort_flag);  // V(t) and K(t + 1)
       FWD_TICK(12);
       if (!ok) break;
       if ((p.flags & F_KV_RAGGED) && (n + 1) * TN > si.sk) {
@@ -486,11 +497,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
         }
         fence_proxy_async_smem();
         __syncwarp();
-      }
-      if (act_next[0] || act_next[1]) {
-        ok = mbar_wait(&bars->k_full[ks_next], ((t + 1) / KSTAGES) & 1, abort_flag);
-        FWD_TICK(13);
-        if (!ok) break;
       }
       const uint32_t bv = dv_lo + ((vs * SM::kTileBytes) >> 4);
 #pragma unroll
