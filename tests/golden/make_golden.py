@@ -184,10 +184,49 @@ def topk_cases():
     save("topk", **res)
 
 
+def padding_cases():
+    """flash_sparse_attn/utils/padding.py:18-179: packing of right- and left-padded batches, with an
+    `unused_mask`, and the three query-length branches of `upad_input`."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("ref_padding", os.path.join(REF, "flash_sparse_attn", "utils", "padding.py"))
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    g = torch.Generator().manual_seed(5)
+    b, s = 3, 17
+    res = {}
+    for name, flip in (("right", False), ("left", True)):
+        lens = torch.randint(1, s + 1, (b,), generator=g)
+        mask = (torch.arange(s)[None] < lens[:, None]).to(torch.int32)
+        if flip:
+            mask = mask.flip(1)
+        unused = ((torch.rand(b, s, generator=g) < 0.3) & (mask == 0)).to(torch.int32)
+        x = torch.randn(b, s, 2, 4, generator=g)
+        res[f"{name}_mask"], res[f"{name}_unused"], res[f"{name}_x"] = mask, unused, x
+        for tag, um in (("", None), ("_u", unused)):
+            packed, idx, cu, mx, used = ref.unpad_input(x, mask, um)
+            res[f"{name}{tag}_packed"], res[f"{name}{tag}_idx"], res[f"{name}{tag}_cu"] = packed, idx, cu
+            res[f"{name}{tag}_max"], res[f"{name}{tag}_used"] = torch.tensor(mx), used
+        packed, idx, *_ = ref.unpad_input(x, mask)
+        res[f"{name}_repadded"] = ref.pad_input(packed, idx, b, s)
+        k = torch.randn(b, s + 2, 2, 4, generator=g)
+        v = torch.randn(b, s + 2, 2, 4, generator=g)
+        res[f"{name}_k"], res[f"{name}_v"] = k, v
+        for ql in (s, 1, 5):
+            q = torch.randn(b, ql, 2, 4, generator=g)
+            qo, ko, vo, iq, (cq, ck), (mq, mk) = ref.upad_input(q, k, v, mask, ql, ref.unpad_input)
+            pre = f"{name}_q{ql}"
+            res[pre + "_q"], res[pre + "_qo"], res[pre + "_ko"], res[pre + "_vo"] = q, qo, ko, vo
+            res[pre + "_iq"], res[pre + "_cq"], res[pre + "_ck"] = iq, cq, ck
+            res[pre + "_mq"], res[pre + "_mk"] = torch.tensor(mq), torch.tensor(mk)
+    save("padding", **res)
+
+
 if __name__ == "__main__":
     torch.set_num_threads(8)
     topk_cases()
-    if "--only-topk" in sys.argv:
+    padding_cases()
+    if "--only-topk" in sys.argv or "--only-small" in sys.argv:
         sys.exit(0)
     forward_cases()
     local_case()
