@@ -227,8 +227,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
   for (int q = 0; q < 2; ++q) {
     const int mb = pair * 2 + q;
     q_valid[q] = mb < m_blocks_here;
+    // One query position with windows and split-KV: the reference's rounding drops the first, partial tile of
+    // the near band (block_info.py:60-64) although its eager ground truth sees those keys; like the decode
+    // kernel, this one visits them (the flag only matters for that combination).
     sched[q] = fsa_fwd_schedule(si.sq, si.sk, mb, si.split, si.w, p.num_splits, TN, TM, causal, local, split_kv,
-                                gpack);
+                                gpack, /*cover_single_query=*/true);
     if (!q_valid[q] || fsa_fwd_sched_empty(sched[q])) {
       sched[q].n_min = sched[q].n_max = sched[q].n_max_no_mask = 0;
       sched[q].win_min = sched[q].win_max = sched[q].win_min_no_mask = sched[q].win_max_no_mask = 0;

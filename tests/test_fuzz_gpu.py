@@ -126,3 +126,40 @@ def test_decode_fuzz(seed):
     fsa.check_status()
     assert_close(f"decode seed{seed} {mode} b{b} sk{sk} hkv{hkv} g{group} d{d} ns{nsplit}", out, torch.nan_to_num(ref, nan=0.0),
                  rtol=2.5e-2, atol=2.5e-2)
+
+
+@pytest.mark.parametrize("seed", range(30))
+def test_gated_forward_backward_fuzz(seed):
+    """Gated operator on random shapes (short queries against long keys, ragged tiles, both gate forms, fp16 and
+    bf16): every gradient, including dalpha and ddelta, against the eager oracle."""
+    fsa = _ops()
+    c = _case(1000 + seed)
+    if c["d"] not in (64, 128):
+        c["d"] = 128
+    rnd = random.Random(5000 + seed)
+    logsig = rnd.random() < 0.6
+    g = torch.Generator().manual_seed(seed)
+    mk = lambda *s: torch.randn(*s, generator=g).to(c["dtype"])  # noqa: E731
+    q, k, v = mk(c["b"], c["sq"], c["hq"], c["d"]), mk(c["b"], c["sk"], c["hkv"], c["d"]), mk(c["b"], c["sk"], c["hkv"], c["d"])
+    a, d = mk(c["b"], c["sq"], c["hq"]), mk(c["b"], c["sk"], c["hkv"])
+    do = mk(c["b"], c["sq"], c["hq"], c["d"])
+    local = c["ws"] is not None
+    causal = c["causal"] and c["sq"] > 1
+    ref_out = eager.forward(q, k, v, None, causal, is_local=local, window_sizes=c["ws"], alpha=a, delta=d,
+                            is_logsigmoid_gate=logsig)
+    ref_g = eager.backward(q, k, v, do, None, causal, is_local=local, window_sizes=c["ws"], alpha=a, delta=d,
+                           is_logsigmoid_gate=logsig)
+    leaves = [t.to(DEV).requires_grad_(True) for t in (q, k, v, a, d)]
+    kw = dict(is_causal=causal, softmax_threshold=-128.0, gate_threshold=-128.0, is_logsigmoid_gate=logsig)
+    if local:
+        kw["window_sizes"] = c["ws"].to(DEV)
+    if c["split"]:
+        kw.update(is_split_kv=True, is_split_qo=True, num_splits=c["nsplit"])
+    out = fsa.flash_gated_attn_func(*leaves, **kw)
+    out.backward(do.to(DEV))
+    torch.cuda.synchronize()
+    fsa.check_status()
+    tag = f"seed{seed}-logsig{logsig}-{ {k_: (v_ if not isinstance(v_, torch.Tensor) else v_.tolist()) for k_, v_ in c.items()} }"
+    assert_close("gated out " + tag, out, torch.nan_to_num(ref_out, nan=0.0), rtol=2.5e-2, atol=2.5e-2)
+    for name, t, r in zip(("dq", "dk", "dv", "dalpha", "ddelta"), leaves, ref_g):
+        assert_close(f"gated {name} {tag}", t.grad, torch.nan_to_num(r, nan=0.0), rtol=3e-2, atol=3e-2)

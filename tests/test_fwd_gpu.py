@@ -257,3 +257,24 @@ def test_c2_full_size_properties():
     ref = eager.forward(q[:1, :, 5:6].cpu(), k[:1, :, 1:2].cpu(), v1[:1, :, 1:2].cpu(), None, True, is_local=True,
                         window_sizes=ws[:1].cpu())
     assert_close("c2-slice", o1[:1, :, 5:6], ref)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("num_splits", [2, 5])
+def test_single_query_local_split_covers_the_mask(num_splits):
+    """One query position, windows whose near band does not start on a tile boundary, split-KV: the reference's
+    schedule skips the band's first partial tile (block_info.py:60-64) although its eager ground truth
+    (tests/test_utils.py:541-563) sees those keys; the operator follows the ground truth."""
+    import flash_sparse_attn as fsa
+    from oracle import eager
+
+    g = torch.Generator().manual_seed(71)
+    mk = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16)  # noqa: E731
+    q, k, v = mk(2, 1, 8, 128), mk(2, 1100, 1, 128), mk(2, 1100, 1, 128)
+    ws = torch.tensor([[1, 128, 128, 260]], dtype=torch.int32)
+    ref = eager.forward(q, k, v, None, False, is_local=True, window_sizes=ws)
+    out = fsa.flash_sparse_attn_func(q.cuda(), k.cuda(), v.cuda(), is_causal=False, softmax_threshold=-128.0,
+                                     window_sizes=ws.cuda(), is_split_kv=True, num_splits=num_splits)
+    torch.cuda.synchronize()
+    fsa.check_status()
+    assert_close("single-query-local-split", out, ref)

@@ -135,6 +135,11 @@ def test_decode_schedule_cover():
         for tn, nsub, gpack in itertools.product((16, 64), (1, 4, 12), (1, 16)):
             seen, exp = _decode_cover(1500, window, tn, nsub, gpack, cover=True)
             assert set(seen) == exp and all(v == 1 for v in seen.values()), (window, tn, nsub, gpack)
+    # the forward kernel's tile size with one query position (flash_*_attn_func called with Sq = 1)
+    for window in ([1, 128, 128, 260], [32, 200, 100, 160]):
+        for nsub in (2, 3, 5):
+            seen, exp = _decode_cover(1100, window, 128, nsub, 1, cover=True)
+            assert set(seen) == exp and all(v == 1 for v in seen.values()), (window, nsub)
     seen, exp = _decode_cover(1500, [32, 200, 100, 160], 16, 4, 16, cover=False)
     assert sorted(exp - set(seen)) == [1340, 1341, 1342, 1343]
 
