@@ -593,6 +593,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     const float v_scale = p.qkv_scale ? p.qkv_scale[2] : p.v_scale;
     float m_ref = -INFINITY;  // reference maximum all stored exponentials are relative to
     float l_ref = 0.f;        // sum of exp2((s - m_ref) * c)
+    float lg_l = -INFINITY;   // log2(l_ref) for the skip test, refreshed at the end of a tile (off the S -> P path)
     bool have_o = false;      // some P V has been issued for this tile
     int cnt_s = 0;
     FWD_TICK_DECL;
@@ -749,7 +750,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       // ---- tile skip vote (flash_sparse_attn/ops/triton/activations.py:129-138) -----------------
       bool skip = false;
       if (KIND != KIND_DENSE) {
-        const float d = (m_cur - m_ref) * c - lg2_approx(l_ref);
+        const float d = (m_cur - m_ref) * c - lg_l;
         const float val = d - thr_log2;
         const unsigned want = __ballot_sync(0xffffffffu, val >= 0.0f);
         const unsigned drop = __ballot_sync(0xffffffffu, val < 0.0f);
@@ -771,18 +772,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
           // max over rows ignores NaN rows; a tile is skipped iff that max is < 0
           skip = !(v & 1) && (v & 2);
         }
-        if (wq == 0 && lane == 0) {
-          bars->skip_flag[q][par] = skip ? 1 : 0;
+      }
+      // The verdict goes to the MMA issuer (and to the tile map) right before this thread's arrival on p_full,
+      // whose release orders it: for a kept tile that is after the exponentials, not in front of them.
+      auto publish_verdict = [&](bool skipped) {
+        if (KIND != KIND_DENSE && wq == 0 && lane == 0) {
+          bars->skip_flag[q][par] = skipped ? 1 : 0;
           if (p.tile_map) {
             const long long idx =
                 ((((long long)si.b * p.hgrid + si.head) * p.num_m_blocks + mb) * p.num_splits + si.split) *
                     p.n_tiles_k + n;
-            p.tile_map[idx] = skip ? 2 : 1;
+            p.tile_map[idx] = skipped ? 2 : 1;
           }
-          // no fence: this thread's own arrival on p_full (release) orders the flag before the MMA issuer's read
         }
-      }
+      };
       if (skip) {
+        publish_verdict(true);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->p_full[q]);
@@ -854,8 +859,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
 #ifdef FSA_PHASE_TIMING
       if (warp == 0 && lane == 0) *reinterpret_cast<volatile long long*>(&bars->dbg_t[0]) = clock64();
 #endif
+      publish_verdict(false);
       if (lane == 0) mbar_arrive(&bars->p_full[q]);
       l_ref += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
+      if (KIND != KIND_DENSE) lg_l = lg2_approx(l_ref);
       have_o = true;
       FWD_TICK(6);
     }
