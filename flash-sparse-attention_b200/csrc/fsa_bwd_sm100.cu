@@ -537,6 +537,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
     // (flash_sparse_attn/ops/triton/flash_gated_bwd.py:406-421; keys past the sequence read as zero)
     float dlt = 0.f, d_max = 0.f, d_min = 0.f, dd_acc = 0.f, gate_max = -INFINITY;
     const bool logsig = p.flags & F_LOGSIGMOID;
+    const float lg_thr = p.softmax_thr > 0.f ? log2f(p.softmax_thr) : -INFINITY;  // for the skip thresholds
     if (KIND == KIND_GATED) {
       const T* dp = reinterpret_cast<const T*>(p.delta) + (long long)bk * p.d_sb + (long long)hkv * p.d_sh + off_k;
       float mx = -INFINITY, mn = INFINITY;
@@ -722,8 +723,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         const int q_first = m * TM + wg * 64;
         const float vis_first = causal ? float(q_first + off + 1) : float(sk);
         const float vis_last = causal ? float(q_first + 63 + off + 1) : float(sk);
-        const float thr_hi = log2f(fmaxf(fminf(p.softmax_thr / vis_first, 1.0f), 0.0f));
-        const float thr_lo = log2f(fmaxf(fminf(p.softmax_thr / vis_last, 1.0f), 0.0f));
+        // log2(clamp(threshold / visible, 0, 1)) = min(log2 threshold - log2 visible, 0); a threshold <= 0 gives -inf
+        const float thr_hi = fminf(lg_thr - lg2_approx(vis_first), 0.0f);
+        const float thr_lo = fminf(lg_thr - lg2_approx(vis_last), 0.0f);
         float mx = fmaxf(x[0], x[1]);
 #pragma unroll
         for (int i = 2; i < 64; i += 2) mx = max3(mx, x[i], x[i + 1]);
@@ -733,8 +735,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
           const int q_a = q_first + lane, q_b = q_a + 32;
           const float vis_a = causal ? float(q_a + off + 1) : float(sk);
           const float vis_b = causal ? float(q_b + off + 1) : float(sk);
-          const float thr_a = log2f(fmaxf(fminf(p.softmax_thr / vis_a, 1.0f), 0.0f));
-          const float thr_b = log2f(fmaxf(fminf(p.softmax_thr / vis_b, 1.0f), 0.0f));
+          const float thr_a = fminf(lg_thr - lg2_approx(vis_a), 0.0f);
+          const float thr_b = fminf(lg_thr - lg2_approx(vis_b), 0.0f);
           want = false;
           drop = false;
 #pragma unroll
@@ -756,15 +758,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
           mbar_arrive(&bars->vote_sync);
         }
         FSA_TICK(1);
-        if (!mbar_wait(&bars->vote_sync, par, abort_flag)) {
-          ok = false;
-          return true;
+        // A warp with an entry that wants the tile knows the outcome ("keep") and moves on; only warps whose
+        // entries all vote "skip" wait for the others. Every warp arrives once per step, and none reaches the vote
+        // of the step after next (same slot) before all have arrived here: S of the next step is only issued
+        // after all eight warps published P or the skip.
+        if (!w_any) {
+          if (!mbar_wait(&bars->vote_sync, par, abort_flag)) {
+            ok = false;
+            return true;
+          }
+          int v = 0;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v |= bars->vote_any[par][i];
+          skip = !(v & 1) && (v & 2);
         }
         FSA_TICK(2);
-        int v = 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v |= bars->vote_any[par][i];
-        skip = !(v & 1) && (v & 2);
         if (cw == 0 && lane == 0) {
           bars->skip_flag[par] = skip ? 1 : 0;
           if (p.tile_map) {
@@ -772,7 +780,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
             p.tile_map[((((long long)b * p.Hq + head) * p.n_tiles_k + n_block) * p.num_splits + split) *
                            p.num_m_blocks + m] = skip ? (gate_skip ? 3 : 2) : 1;
           }
-          __threadfence_block();
+          // no fence: this thread's arrival on p_full (release) orders the flag before the MMA issuer's read
         }
       }
       FSA_TICK(18);
