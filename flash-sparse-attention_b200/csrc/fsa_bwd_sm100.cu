@@ -617,6 +617,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       const int m = si_p.m, mode = si_p.mode;
       m_p = m;
       seg_next(segs, si_p);
+      // skip thresholds of the group's first and last query column: worked out before S is waited for
+      // (log2(clamp(threshold / visible, 0, 1)) = min(log2 threshold - log2 visible, 0); threshold <= 0 gives -inf)
+      const int q_first = m * TM + wg * 64;
+      const float vis_first = causal ? float(q_first + off + 1) : float(sk);
+      const float vis_last = causal ? float(q_first + 63 + off + 1) : float(sk);
+      float thr_hi = 0.f, thr_lo = 0.f;
+      if (KIND != KIND_DENSE) {
+        thr_hi = fminf(lg_thr - lg2_approx(vis_first), 0.0f);
+        thr_lo = fminf(lg_thr - lg2_approx(vis_last), 0.0f);
+      }
       FSA_TICK(9);
       if (!mbar_wait(&bars->s_full, par, abort_flag)) {
         ok = false;
@@ -720,15 +730,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         // The threshold falls as the query index grows (causal) or is one number (otherwise): the row
         // maximum against the thresholds of the group's first and last column settles most votes at
         // once; only a warp with a lane in between compares entry by entry.
-        const int q_first = m * TM + wg * 64;
-        const float vis_first = causal ? float(q_first + off + 1) : float(sk);
-        const float vis_last = causal ? float(q_first + 63 + off + 1) : float(sk);
-        // log2(clamp(threshold / visible, 0, 1)) = min(log2 threshold - log2 visible, 0); a threshold <= 0 gives -inf
-        const float thr_hi = fminf(lg_thr - lg2_approx(vis_first), 0.0f);
-        const float thr_lo = fminf(lg_thr - lg2_approx(vis_last), 0.0f);
-        float mx = fmaxf(x[0], x[1]);
+        float mx4[4];  // four independent chains
 #pragma unroll
-        for (int i = 2; i < 64; i += 2) mx = max3(mx, x[i], x[i + 1]);
+        for (int j = 0; j < 4; ++j) {
+          mx4[j] = fmaxf(x[j * 16], x[j * 16 + 1]);
+#pragma unroll
+          for (int i = 2; i < 16; i += 2) mx4[j] = max3(mx4[j], x[j * 16 + i], x[j * 16 + i + 1]);
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         bool want = mx >= thr_hi, drop = mx < thr_lo;
         const bool unsure = (vis_first < 1.0f) || (!want && !drop);
         if (__any_sync(0xffffffffu, unsure)) {
