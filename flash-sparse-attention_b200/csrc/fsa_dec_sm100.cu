@@ -279,6 +279,7 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
       }
     }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float lg_l[2] = {-INFINITY, -INFINITY};  // log2(l_run) for the skip test, refreshed after every update of l_run
     float o[HD / 8][4];
 #pragma unroll
     for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
@@ -440,8 +441,8 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
       bool skip = false;
       if (KIND != KIND_DENSE) {
         // flash_sparse_attn/ops/triton/activations.py:129-138 over the real rows of the tile
-        const float v0 = (m_cur[0] - m_run[0]) * c - log2f(l_run[0]) - thr_log2;
-        const float v1 = (m_cur[1] - m_run[1]) * c - log2f(l_run[1]) - thr_log2;
+        const float v0 = (m_cur[0] - m_run[0]) * c - lg_l[0] - thr_log2;
+        const float v1 = (m_cur[1] - m_run[1]) * c - lg_l[1] - thr_log2;
         const bool want = (row0_ok && v0 >= 0.f) || (row1_ok && v1 >= 0.f);
         const bool drop = (row0_ok && v0 < 0.f) || (row1_ok && v1 < 0.f);
         skip = !__any_sync(0xffffffffu, want) && __any_sync(0xffffffffu, drop);
@@ -475,6 +476,10 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
         sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
         l_run[0] = l_run[0] * scale[0] + sum0;
         l_run[1] = l_run[1] * scale[1] + sum1;
+        if (KIND != KIND_DENSE) {  // needed by the next tile's vote: its latency runs under the P V products
+          lg_l[0] = lg2_approx(l_run[0]);
+          lg_l[1] = lg2_approx(l_run[1]);
+        }
         if (__any_sync(0xffffffffu, scale[0] != 1.f || scale[1] != 1.f)) {
 #pragma unroll
           for (int j = 0; j < HD / 8; ++j) {
