@@ -55,6 +55,37 @@ def test_gated_config_full_size():
         assert_close(f"gated-full-b{bi}-h{head}-rows{r0}", out[bi:bi + 1, r0:r1, head:head + 1], ref)
 
 
+def test_gated_config_full_size_backward():
+    """Same configuration, backward: dq and dalpha of a 64-row block depend only on that block's rows and on the
+    keys before its end, so the eager oracle on the causal prefix reproduces them; two runs agree in dk, dv, ddelta
+    bit for bit (fixed accumulation order inside a CTA) and in dq to reduction noise."""
+    fsa = _ops()
+    b, s, hq, hkv, d = 4, 8192, 32, 8, 128
+    g = torch.Generator(device=DEV).manual_seed(4)
+    q, k, v = _randn(g, b, s, hq, d), _randn(g, b, s, hkv, d), _randn(g, b, s, hkv, d)
+    a, dl, do = _randn(g, b, s, hq), _randn(g, b, s, hkv), _randn(g, b, s, hq, d)
+    ws = torch.tensor([[0, w, 0, 0] for w in (512, 4096, 512, 4096, 1024, 4096, 1024, 2048)], dtype=torch.int32)
+    kw = dict(is_causal=True, window_sizes=ws.to(DEV), softmax_threshold=-128.0, gate_threshold=-128.0)
+    grads = []
+    for _ in range(2):
+        leaves = [t.detach().requires_grad_(True) for t in (q, k, v, a, dl)]
+        fsa.flash_gated_attn_func(*leaves, **kw).backward(do)
+        torch.cuda.synchronize()
+        fsa.check_status()
+        grads.append([t.grad for t in leaves])
+    for i in (1, 2, 4):
+        assert torch.equal(grads[0][i], grads[1][i])
+    assert (grads[0][0].float() - grads[1][0].float()).abs().max().item() < 2e-2
+    for bi, head, r0, r1 in ((1, 6, 0, 64), (3, 31, 8128, 8192)):
+        kvh = head // (hq // hkv)
+        ref = eager.backward(q[bi:bi + 1, r0:r1, head:head + 1].cpu(), k[bi:bi + 1, :r1, kvh:kvh + 1].cpu(),
+                             v[bi:bi + 1, :r1, kvh:kvh + 1].cpu(), do[bi:bi + 1, r0:r1, head:head + 1].cpu(), None, True,
+                             is_local=True, window_sizes=ws[kvh:kvh + 1], alpha=a[bi:bi + 1, r0:r1, head:head + 1].cpu(),
+                             delta=dl[bi:bi + 1, :r1, kvh:kvh + 1].cpu())
+        assert_close(f"gated-full-dq-b{bi}-h{head}", grads[0][0][bi:bi + 1, r0:r1, head:head + 1], ref[0], rtol=3e-2, atol=3e-2)
+        assert_close(f"gated-full-da-b{bi}-h{head}", grads[0][3][bi:bi + 1, r0:r1, head:head + 1], ref[3], rtol=3e-2, atol=3e-2)
+
+
 def test_varlen_quant_config_full_size():
     """16 packed sequences with lengths in [256, 4096], Hq=32, Hkv=8, D=128, FP8 inputs from `quantize_fp8`,
     split-KV on: two of the sequences against the eager oracle on the de-quantised tensors, run-to-run equality."""
