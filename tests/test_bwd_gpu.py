@@ -217,4 +217,6 @@ def test_deterministic_dq_varlen_and_skipped_tiles():
         assert torch.equal(a, o)
     ref = eager.varlen_backward(q, k, v, do, cu, cu, None, True)
     for name, a, r in zip(("dq", "dk", "dv"), outs[0], ref):
-        assert_close("det-varlen-" + name, a, r, rtol=5e-2, atol=5e-2)
+        # the eager oracle keeps the probability mass that the skipped tiles drop (threshold 1.0: up to
+        # 1 / visible_len per row and tile), so the element-wise bound is the skip error, not rounding
+        assert_close("det-varlen-" + name, a, r, rtol=5e-2, atol=5e-2, ew_rtol=5e-2, ew_atol=1e-1)

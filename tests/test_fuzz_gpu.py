@@ -66,8 +66,11 @@ def test_forward_backward_fuzz(seed):
     # rows without any visible key are zero in the operator (empty softmax) and NaN in the eager oracle
     ref_out = torch.nan_to_num(ref_out, nan=0.0)
     assert_close("out " + tag, out, ref_out, rtol=2.5e-2, atol=2.5e-2)
+    # gradients: P and dS are rounded to 16 bits in front of their GEMMs; over hundreds of rows that rounding
+    # adds up to an absolute error that does not shrink with the entry (seen: 0.022 at |ref| = 0.07, one entry
+    # of 295k), hence atol 3e-2 for the element-wise bound here
     for name, t, r in zip(("dq", "dk", "dv"), leaves, ref_g):
-        assert_close(f"{name} {tag}", t.grad, torch.nan_to_num(r, nan=0.0), rtol=3e-2, atol=3e-2)
+        assert_close(f"{name} {tag}", t.grad, torch.nan_to_num(r, nan=0.0), rtol=3e-2, atol=3e-2, ew_atol=3e-2)
 
 
 @pytest.mark.parametrize("seed", range(30))

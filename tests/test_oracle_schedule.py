@@ -168,3 +168,68 @@ def test_c_schedule_matches_oracle():
         ref = S.bwd_schedule(sq, sk, nb, sp, window, ns, tn, tm, causal, local, split).as_list()
         got = _lib.debug_bwd_schedule(sq, sk, nb, sp, window, ns, tn, tm, causal, local, split)
         assert got == ref, ("bwd", sq, sk, nb, sp, window, ns, tn, tm, causal, local, split)
+
+
+# --------------------------------------------------------------------------------------------------
+# pinned to the reference's own integers: golden/schedule.npz holds what block_info.py and the three
+# `create` schedulers of scheduler.py return when their Triton source runs on the CPU interpreter
+# (tests/golden/make_schedule_golden.py); everything below is compared with ==
+# --------------------------------------------------------------------------------------------------
+def _golden():
+    import numpy as np
+    import os
+
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "schedule.npz"))
+
+
+def test_oracle_block_ranges_equal_reference():
+    z = _golden()
+    for a, r in zip(z["fwd_args"].tolist(), z["fwd_out"].tolist()):
+        sq, sk, mb, sp, s_, l_, r_, n_, ns, tn, tm, causal, local, split, gpack = a
+        got = S.n_block_min_max(sq, sk, mb, sp, [s_, l_, r_, n_], ns, tn, tm, bool(causal), bool(local), bool(split), gpack)
+        assert list(got) == r, ("n_block_min_max", a)
+    for a, r in zip(z["bwd_args"].tolist(), z["bwd_out"].tolist()):
+        sq, sk, nb, sp, s_, l_, r_, n_, ns, tn, tm, causal, local, split = a
+        got = S.m_block_min_max(sq, sk, nb, sp, [s_, l_, r_, n_], ns, tn, tm, bool(causal), bool(local), bool(split))
+        assert list(got) == r, ("m_block_min_max", a)
+    for a, r in zip(z["edges_n_args"].tolist(), z["edges_n_out"].tolist()):
+        sq, sk, mb, n_min, l_, r_, n_, tn, tm, local, gpack = a
+        got = [S._n_min_causal_local_mask(sq, sk, mb, n_min, r_, n_, tn, tm, bool(local), gpack),
+               S._n_min_before_local_mask(sq, sk, mb, n_min, [0, l_, r_, n_], tn, tm, bool(local), gpack)]
+        assert got == r, ("edges_n", a)
+    for a, r in zip(z["edges_m_args"].tolist(), z["edges_m_out"].tolist()):
+        sq, sk, nb, m_lim, l_, r_, n_, tn, tm, causal, local = a
+        got = [S._m_min_causal_local_mask(sq, sk, nb, m_lim, r_, n_, tn, tm, bool(causal), bool(local)),
+               S._m_max_before_local_mask(sq, sk, nb, m_lim, [0, l_, r_, n_], tn, tm, bool(local))]
+        assert got == r, ("edges_m", a)
+    for a, r in zip(z["topk_args"].tolist(), z["topk_out"].tolist()):
+        topk, sp, ns, tn = a
+        sc = S.topk_schedule(topk, sp, ns, tn)
+        assert [sc.n_min, sc.n_max] == r, ("topk", a)
+
+
+def test_oracle_and_library_schedules_equal_reference_schedulers():
+    """The nine numbers of AttnFwdBlockScheduler.create / AttnBwdBlockScheduler.create / AttnDecBlockScheduler.create:
+    oracle/schedule.py and the C schedule behind fsa_debug_*_schedule both reproduce them exactly."""
+    from flash_sparse_attn import _lib
+
+    z = _golden()
+    for a, r in zip(z["fwd_args"].tolist(), z["fwd_create"].tolist()):
+        sq, sk, mb, sp, s_, l_, r_, n_, ns, tn, tm, causal, local, split, gpack = a
+        w = [s_, l_, r_, n_]
+        assert S.fwd_schedule(sq, sk, mb, sp, w, ns, tn, tm, bool(causal), bool(local), bool(split), gpack).as_list() == r, a
+        assert _lib.debug_fwd_schedule(sq, sk, mb, sp, w, ns, tn, tm, causal, local, split, gpack) == r, ("C fwd", a)
+    for a, r in zip(z["bwd_args"].tolist(), z["bwd_create"].tolist()):
+        sq, sk, nb, sp, s_, l_, r_, n_, ns, tn, tm, causal, local, split = a
+        w = [s_, l_, r_, n_]
+        assert S.bwd_schedule(sq, sk, nb, sp, w, ns, tn, tm, bool(causal), bool(local), bool(split)).as_list() == r, a
+        assert _lib.debug_bwd_schedule(sq, sk, nb, sp, w, ns, tn, tm, causal, local, split) == r, ("C bwd", a)
+    for a, r in zip(z["dec_args"].tolist(), z["dec_create"].tolist()):
+        sk, sp, s_, l_, r_, n_, ns, topk, tn, tm, local, gather, gpack = a
+        if gather:
+            got = S.topk_schedule(topk, sp, ns, tn).as_list()
+        else:
+            w = [s_, l_, r_, n_]
+            got = S.fwd_schedule(1, sk, 0, sp, w, ns, tn, tm, False, bool(local), True, gpack).as_list()
+            assert _lib.debug_fwd_schedule(1, sk, 0, sp, w, ns, tn, tm, 0, local, 1, gpack) == r, ("C dec", a)
+        assert got == r, ("dec", a)
