@@ -79,12 +79,9 @@ int cdiv(int a, int b) { return (a + b - 1) / b; }
 bool head_dim_ok(int d) { return d >= 8 && d <= 128 && d % 8 == 0; }
 int head_dim_kernel(int d) { return d <= 64 ? 64 : 128; }
 
-cudaEvent_t g_ev_before = nullptr, g_ev_after = nullptr;
-void mark_before(cudaStream_t s) {
-  if (g_ev_before) cudaEventRecord(g_ev_before, s);
-}
-void mark_after(cudaStream_t s) {
-  if (g_ev_after) cudaEventRecord(g_ev_after, s);
+// optional per-call timing events around the main kernel
+void mark(void* ev, cudaStream_t s) {
+  if (ev) cudaEventRecord(reinterpret_cast<cudaEvent_t>(ev), s);
 }
 
 }  // namespace
@@ -93,11 +90,6 @@ extern "C" {
 
 int fsa_abi_version(void) { return FSA_ABI_VERSION; }
 
-void fsa_set_profile_events(void* before, void* after) {
-  g_ev_before = reinterpret_cast<cudaEvent_t>(before);
-  g_ev_after = reinterpret_cast<cudaEvent_t>(after);
-}
-
 const char* fsa_status_string(int code) {
   switch (code) {
     case FSA_OK: return "ok";
@@ -105,6 +97,9 @@ const char* fsa_status_string(int code) {
     case FSA_ERR_UNSUPPORTED: return "unsupported combination (head_dim must be a multiple of 8 up to 128, dtype bf16/fp16/fp8, ...)";
     case FSA_ERR_LAUNCH: return "CUDA error at launch or tensor-map creation";
     case FSA_ERR_NO_DRIVER: return "CUDA driver entry point cuTensorMapEncodeTiled unavailable";
+    case FSA_ERR_SCRATCH_UNAVAILABLE:
+      return "the built-in workspace could not be set up on this device (cudaGetSymbolAddress failed: its first "
+             "use loads the array, which needs 16 MiB of free device memory)";
     case FSA_ERR_SCRATCH_TOO_SMALL:
       return "request does not fit the built-in workspace: num_splits * batch * heads_q * (head_dim + 1) floats "
              "must be at most 16 MiB";
@@ -158,6 +153,58 @@ static int fwd_geometry(const FsaFwdArgs* a, int* gpack, int* num_m_blocks, int*
   *hgrid = pack ? a->heads_kv : a->heads_q;
   *sk_static = a->page_table ? a->page_table_stride * a->page_size : a->seqlen_k;
   *n_tiles_k = cdiv(*sk_static, 128);
+  return FSA_OK;
+}
+
+int fsa_fwd_workspace_bytes(const FsaFwdArgs* a, FsaFwdWorkspace* w) {
+  if (!a || !w) return FSA_ERR_INVALID_ARG;
+  memset(w, 0, sizeof(*w));
+  int gpack, nmb, hgrid, sk, ntk;
+  const int rc = fwd_geometry(a, &gpack, &nmb, &hgrid, &sk, &ntk);
+  if (rc != FSA_OK) return rc;
+  if ((a->flags & FSA_F_SPLIT) && a->num_splits > 0) {
+    const size_t rows = a->cu_seqlens_q ? (size_t)a->total_q : (size_t)a->batch * a->seqlen_q;
+    w->out_partial = sizeof(float) * (size_t)a->num_splits * rows * a->heads_q * a->head_dim;
+    w->lse_partial = sizeof(float) * (size_t)a->num_splits * rows * a->heads_q;
+  }
+  if (a->kind == FSA_KIND_GATED) w->gate_ws = fsa::gate_ws_bytes(a->batch, hgrid, nmb, a->heads_kv, ntk);
+  return FSA_OK;
+}
+
+int fsa_bwd_workspace_bytes(const FsaBwdArgs* a, FsaBwdWorkspace* w) {
+  if (!a || !w) return FSA_ERR_INVALID_ARG;
+  memset(w, 0, sizeof(*w));
+  if (a->batch <= 0 || a->heads_q <= 0 || a->heads_kv <= 0 || !head_dim_ok(a->head_dim)) return FSA_ERR_INVALID_ARG;
+  const bool varlen_q = a->cu_seqlens_q != nullptr, varlen_k = a->cu_seqlens_k != nullptr;
+  const size_t R = (size_t)fsa_bwd_padded_rows(a->batch, a->seqlen_q, a->total_q, varlen_q);
+  const size_t es = dtype_bytes(a->dtype);
+  w->lse2_ws = w->dpsum_ws = sizeof(float) * (size_t)a->heads_q * R;
+  w->dq_accum = sizeof(float) * (size_t)a->heads_q * R * head_dim_kernel(a->head_dim);
+  const int ns = (a->flags & FSA_F_SPLIT) ? a->num_splits : 1;
+  const size_t rows_k = varlen_k ? (size_t)a->total_k : (size_t)a->batch * a->seqlen_k;
+  if (ns > 1) w->dk_partial = w->dv_partial = sizeof(float) * (size_t)ns * rows_k * a->heads_kv * a->head_dim;
+  if (a->kind == FSA_KIND_GATED) {
+    w->alpha_ws = es * (size_t)a->heads_q * R;
+    w->da_accum = sizeof(float) * (size_t)a->heads_q * R;
+    if (ns > 1) w->dd_partial = sizeof(float) * (size_t)ns * (size_t)a->delta_numel;
+  }
+  if (a->flags & FSA_F_DETERMINISTIC) {
+    const size_t ntk = cdiv(a->seqlen_k, 128), ntq = cdiv(a->seqlen_q, 128);
+    w->dq_order = sizeof(uint16_t) * (size_t)a->batch * a->heads_kv * ntk * ntq;
+    w->dq_turn = sizeof(int32_t) * (size_t)a->batch * a->heads_q * ntq;
+  }
+  return FSA_OK;
+}
+
+int fsa_decode_workspace_bytes(const FsaDecArgs* a, FsaDecWorkspace* w) {
+  if (!a || !w) return FSA_ERR_INVALID_ARG;
+  memset(w, 0, sizeof(*w));
+  if (a->batch <= 0 || a->heads_q <= 0 || a->head_dim <= 0) return FSA_ERR_INVALID_ARG;
+  const int ns = a->num_splits > 0 ? a->num_splits : 1;
+  if (ns > 1 || a->partial_only) {
+    w->out_partial = sizeof(float) * (size_t)ns * a->batch * a->heads_q * a->head_dim;
+    w->lse_partial = sizeof(float) * (size_t)ns * a->batch * a->heads_q;
+  }
   return FSA_OK;
 }
 
@@ -309,10 +356,10 @@ int fsa_fwd(const FsaFwdArgs* a, void* stream_) {
   if (a->flags & FSA_F_ADAPT_GATE) f |= fsa::F_ADAPT_GATE;
   p.flags = f;
 
-  mark_before(stream);
+  mark(a->ev_before, stream);
   p.D = a->head_dim;
   cudaError_t e = fsa::launch_fwd(p, a->kind, a->dtype, head_dim_kernel(a->head_dim), stream);
-  mark_after(stream);
+  mark(a->ev_after, stream);
   if (e == cudaErrorInvalidValue) return FSA_ERR_UNSUPPORTED;
   if (e != cudaSuccess) return FSA_ERR_LAUNCH;
 
@@ -529,10 +576,10 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
     p.dq_turn = a->dq_turn;
     p.flags |= fsa::F_DETERMINISTIC;
   }
-  mark_before(stream);
+  mark(a->ev_before, stream);
   p.D = a->head_dim;
   cudaError_t e = fsa::launch_bwd(p, a->kind, a->dtype, hdk, stream);
-  mark_after(stream);
+  mark(a->ev_after, stream);
   if (e == cudaErrorInvalidValue) return FSA_ERR_UNSUPPORTED;
   if (e != cudaSuccess) return FSA_ERR_LAUNCH;
 
@@ -593,7 +640,8 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
 }
 
 int fsa_combine(const float* out_partial, const float* lse_partial, void* out, float* lse, int num_partials,
-                int rows, int heads, int head_dim, int dtype, void* stream_) {
+                int rows, int heads, int head_dim, int dtype, int64_t out_partial_stride,
+                int64_t lse_partial_stride, void* stream_) {
   if (!out_partial || !lse_partial || !out || !lse || num_partials <= 0 || rows < 0 || heads <= 0)
     return FSA_ERR_INVALID_ARG;
   if (dtype != FSA_DT_BF16 && dtype != FSA_DT_FP16) return FSA_ERR_UNSUPPORTED;
@@ -603,8 +651,8 @@ int fsa_combine(const float* out_partial, const float* lse_partial, void* out, f
   c.lse_partial = lse_partial;
   c.out = out;
   c.lse = lse;
-  c.op_ss = (long long)rows * heads * head_dim;
-  c.lp_ss = (long long)rows * heads;
+  c.op_ss = out_partial_stride > 0 ? out_partial_stride : (long long)rows * heads * head_dim;
+  c.lp_ss = lse_partial_stride > 0 ? lse_partial_stride : (long long)rows * heads;
   c.lp_sh = rows;
   c.o_sb = (long long)heads * head_dim;
   c.o_sm = 0;
@@ -700,10 +748,15 @@ int fsa_decode(const FsaDecArgs* a, void* stream_) {
   if (a->seqused_k) f |= fsa::F_USED_K;
   if (a->flags & FSA_F_LOGSIGMOID) f |= fsa::F_LOGSIGMOID;
   p.flags = f;
-  mark_before(stream);
+  p.op_ss = a->out_partial_stride > 0 ? a->out_partial_stride : (long long)a->batch * a->heads_q * a->head_dim;
+  p.lp_ss = a->lse_partial_stride > 0 ? a->lse_partial_stride : (long long)a->batch * a->heads_q;
+  p.thr_sk = a->thr_seqlen_k;
+  p.key_lo = a->key_lo;
+  p.key_hi = gather ? a->key_hi : 0;
+  mark(a->ev_before, stream);
   p.D = a->head_dim;
   cudaError_t e = fsa::launch_dec(p, a->kind, a->dtype, head_dim_kernel(a->head_dim), stream);
-  mark_after(stream);
+  mark(a->ev_after, stream);
   if (e == cudaErrorInvalidValue) return FSA_ERR_UNSUPPORTED;
   if (e != cudaSuccess) return FSA_ERR_LAUNCH;
   if (partial && !a->partial_only) {
@@ -713,8 +766,8 @@ int fsa_decode(const FsaDecArgs* a, void* stream_) {
     c.lse_partial = a->lse_partial;
     c.out = a->out;
     c.lse = a->lse;
-    c.op_ss = (long long)a->batch * a->heads_q * a->head_dim;
-    c.lp_ss = (long long)a->batch * a->heads_q;
+    c.op_ss = p.op_ss;
+    c.lp_ss = p.lp_ss;
     c.lp_sh = a->batch;
     c.o_sb = a->o_stride_b;
     c.o_sm = 0;

@@ -30,28 +30,6 @@
 #include "fsa_schedule.h"
 #include "fsa_aux.h"
 
-// Development aid: with -DFSA_PHASE_TIMING one lane of a compute warp and of the MMA warp add up the
-// clock cycles they spend in each wait / phase; fsa_debug_bwd_ticks() reads the totals over all CTAs.
-#ifdef FSA_PHASE_TIMING
-__device__ unsigned long long g_bwd_ticks[24];
-#define FSA_TICK_DECL long long tk_[24] = {0}; long long tk_t_ = clock64(); const bool tk_on_ = (lane == 0) && (warp == 0 || warp == 9)
-#define FSA_TICK(i)                          \
-  do {                                       \
-    const long long now_ = clock64();        \
-    tk_[i] += now_ - tk_t_;                  \
-    tk_t_ = now_;                            \
-  } while (0)
-#define FSA_TICK_FLUSH                                                                      \
-  do {                                                                                      \
-    if (tk_on_)                                                                             \
-      for (int i_ = 0; i_ < 24; ++i_)                                                       \
-        if (tk_[i_]) atomicAdd(&g_bwd_ticks[i_], (unsigned long long)tk_[i_]);               \
-  } while (0)
-#else
-#define FSA_TICK_DECL
-#define FSA_TICK(i)
-#define FSA_TICK_FLUSH
-#endif
 
 namespace fsa {
 
@@ -341,12 +319,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       }
       int n_live = 0;  // steps that were not skipped so far
       bool acc_started = false;
-      FSA_TICK_DECL;
       for (int it = 0; it < N_IT && ok; ++it) {
         const int st = it & 1;
-        FSA_TICK(15);
         ok = mbar_wait(&bars->p_full, it & 1, abort_flag);
-        FSA_TICK(10);
         if (!ok) break;
         const bool skip = (KIND != KIND_DENSE) && bars->skip_flag[it & 1];
         ok = mbar_wait(&bars->do_full, it & 1, abort_flag);  // every phase is observed, skipped step or not
@@ -354,7 +329,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         tc_fence_after();
         if (!skip) {
           if (n_live > 0) ok = mbar_wait(&bars->dq_empty, (n_live - 1) & 1, abort_flag);
-          FSA_TICK(11);
           if (!ok) break;
           tc_fence_after();
           if (lane == 0) {
@@ -378,17 +352,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         if (lane == 0) umma_commit(&bars->do_empty);  // dO may be overwritten once dV has read it
         __syncwarp();
         if (it + 1 < N_IT) {
-          FSA_TICK(15);
           ok = mbar_wait(&bars->q_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_flag);
-          FSA_TICK(12);
           if (!ok) break;
           tc_fence_after();
           issue_st((it + 1) & 1);
         }
         if (!skip) {
-          FSA_TICK(15);
           ok = mbar_wait(&bars->ds_full, n_live & 1, abort_flag);
-          FSA_TICK(13);
           if (!ok) break;
           tc_fence_after();
           if (lane == 0) {
@@ -414,8 +384,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       }
       if (lane == 0) umma_commit(&bars->acc_full);
       __syncwarp();
-      FSA_TICK(15);
-      FSA_TICK_FLUSH;
     } else if (warp == 10) {
       // =============================== dQ drain =================================================
       // Deterministic mode only (otherwise every compute warp issues the reduce-add of its own buffer, which
@@ -500,7 +468,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
     uint8_t* ds_buf = smem + SM::kDS;
     uint8_t* stage = smem + SM::kStage + cw * 4096;
 
-    FSA_TICK_DECL;
     bool ok = !*abort_flag;
     uint32_t pk[32];  // P^T of the step in flight, packed pairs (this thread's 64 query columns)
     int n_live = 0;
@@ -627,7 +594,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         thr_hi = fminf(lg_thr - lg2_approx(vis_first), 0.0f);
         thr_lo = fminf(lg_thr - lg2_approx(vis_last), 0.0f);
       }
-      FSA_TICK(9);
       if (!mbar_wait(&bars->s_full, par, abort_flag)) {
         ok = false;
         return true;
@@ -637,7 +603,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         ok = false;
         return true;
       }
-      FSA_TICK(0);
       tc_fence_after();
       bool gate_skip = false;
       if (KIND == KIND_GATED) {
@@ -766,7 +731,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
           bars->vote_any[par][cw] = (w_any ? 1 : 0) | (d_any ? 2 : 0);
           mbar_arrive(&bars->vote_sync);
         }
-        FSA_TICK(1);
         // A warp with an entry that wants the tile knows the outcome ("keep") and moves on; only warps whose
         // entries all vote "skip" wait for the others. Every warp arrives once per step, and none reaches the vote
         // of the step after next (same slot) before all have arrived here: S of the next step is only issued
@@ -781,7 +745,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
           for (int i = 0; i < 8; ++i) v |= bars->vote_any[par][i];
           skip = !(v & 1) && (v & 2);
         }
-        FSA_TICK(2);
         if (cw == 0 && lane == 0) {
           bars->skip_flag[par] = skip ? 1 : 0;
           if (p.tile_map) {
@@ -792,7 +755,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
           // no fence: this thread's arrival on p_full (release) orders the flag before the MMA issuer's read
         }
       }
-      FSA_TICK(18);
       if (!skip) {
 #pragma unroll
         for (int i = 0; i < 64; i += 2) pk[i >> 1] = pack2<T>(ex2_approx(x[i]), ex2_approx(x[i + 1]));
@@ -804,25 +766,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_full);
-      FSA_TICK(1);
       return skip;
     };
 
     // ---- dS step: dS^T = P^T o (dP^T - dpsum) into shared memory ------------------------------------
     auto ds_step = [&](int it) {
       const int st = it & 1;
-      FSA_TICK(9);
       if (!mbar_wait(&bars->dp_full, n_live & 1, abort_flag)) {
         ok = false;
         return;
       }
-      FSA_TICK(3);
       tc_fence_after();
       uint32_t dr[64];
       tmem_ld32(tmem_base + lane_addr + TMEM_DP + wg * 64, &dr[0]);
       tmem_ld32(tmem_base + lane_addr + TMEM_DP + wg * 64 + 32, &dr[32]);
       tmem_ld_wait();
-      FSA_TICK(19);
       const float4* dps4 = reinterpret_cast<const float4*>(s_dps + st * 128 + wg * 64);
       const uint4* al4 = reinterpret_cast<const uint4*>(s_alpha + st * 128 + wg * 64);
       uint8_t* slab = ds_buf + wg * (128 * 128);
@@ -897,7 +855,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->ds_full);
-      FSA_TICK(5);
     };
 
     // ---- dQ step: TMEM -> registers -> shared staging; the drain warp issues the TMA reduce-adds -------
@@ -914,7 +871,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
     };
     auto dq_flush = [&]() {
       if (NCH > 1 && dq_pending) {
-        FSA_TICK(9);
         if (det) {
           stage_wait_free();
           if (!ok) return;
@@ -923,7 +879,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         } else {
           if (lane == 0) bulk_wait_read0();
           __syncwarp();
-          FSA_TICK(8);
           stage_store(dq_hold);
           if (lane == 0) {
             tma_reduce_add_3d(&p.map_dq, stage, wg * HALF + 32, dq_row + wq * 32, dq_head);
@@ -931,16 +886,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
           }
         }
         dq_pending = false;
-        FSA_TICK(7);
       }
     };
     auto dq_step = [&](int it) {
-      FSA_TICK(9);
       if (!mbar_wait(&bars->dq_full, n_live & 1, abort_flag)) {
         ok = false;
         return;
       }
-      FSA_TICK(6);
       tc_fence_after();
       uint32_t r[32];
       tmem_ld32(tmem_base + lane_addr + TMEM_DP + wg * HALF, r);
@@ -950,7 +902,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->dq_empty);
-      FSA_TICK(7);
       dq_row = (int)(pad_off + (long long)m_cur * TM);
       dq_head = hkv * p.G + g_cur;
       dq_m = m_cur;
@@ -962,7 +913,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       } else {
         if (lane == 0) bulk_wait_read0();  // the buffer went to the engine a whole phase ago
         __syncwarp();
-        FSA_TICK(14);
         stage_store(r);
         if (lane == 0) {
           tma_reduce_add_3d(&p.map_dq, stage, wg * HALF, dq_row + wq * 32, dq_head);
@@ -970,7 +920,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         }
       }
       dq_pending = NCH > 1;
-      FSA_TICK(7);
     };
 
     if (ok && N_IT > 0) {
@@ -1001,8 +950,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       stage_post(0, 0, 0, 2);  // the drain warp leaves (also when this warp is bailing out: it must not be left waiting)
     }
 
-    FSA_TICK(9);
-    FSA_TICK_FLUSH;
     // ---- epilogue: dK (scaled) and dV of this key tile ------------------------------------------------
     if (ok) {
       bool have = false;
@@ -1093,12 +1040,8 @@ template <int HD, typename T, int KIND>
 cudaError_t launch_one(const BwdKernelParams& p, cudaStream_t stream) {
   auto kern = bwd_kernel<HD, T, KIND>;
   constexpr int smem = BwdSmem<HD>::kTotal;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  static std::atomic<unsigned long long> opted_in{0};  // one bit per device: the attribute is per device
+  if (cudaError_t e = smem_opt_in(kern, smem, opted_in); e != cudaSuccess) return e;
   const long long grid = (long long)p.n_tiles_k * p.Hkv * p.B * p.num_splits;
   if (grid <= 0) return cudaSuccess;
   kern<<<(unsigned)grid, NTHREADS, smem, stream>>>(p);
@@ -1107,16 +1050,6 @@ cudaError_t launch_one(const BwdKernelParams& p, cudaStream_t stream) {
 
 }  // namespace
 
-#ifdef FSA_PHASE_TIMING
-extern "C" void fsa_debug_bwd_ticks(unsigned long long* out16, int reset) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out16, g_bwd_ticks, sizeof(unsigned long long) * 24);
-  if (reset) {
-    unsigned long long z[24] = {0};
-    cudaMemcpyToSymbol(g_bwd_ticks, z, sizeof(z));
-  }
-}
-#endif
 
 cudaError_t launch_bwd(const BwdKernelParams& p, int kind, int dtype, int head_dim, cudaStream_t stream) {
 #define FSA_BWD_CASE(HD_, T_, DT_)                                               \

@@ -166,7 +166,9 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
   const bool loc_sched = local && !gather;
   const float c = p.qkv_scale ? p.scale_log2 * p.qkv_scale[0] * p.qkv_scale[1] : p.scale_log2;
   const float v_scale = p.qkv_scale ? p.qkv_scale[2] : 1.0f;
-  const float thr_log2 = (KIND != KIND_DENSE) ? log2f(fmaxf(fminf(p.softmax_thr / float(sk), 1.0f), 0.0f)) : 0.f;
+  // threshold / visible keys (seqlen_info.py:141-149); a shard of a longer sequence is told the whole length
+  const float thr_keys = float(p.thr_sk ? p.thr_sk[b] : sk);
+  const float thr_log2 = (KIND != KIND_DENSE) ? log2f(fmaxf(fminf(p.softmax_thr / thr_keys, 1.0f), 0.0f)) : 0.f;
   const int* gidx = gather ? p.gather_idx + (long long)b * p.gi_stride : nullptr;
   const int* ptab = paged ? p.page_table + (long long)b * p.pt_stride : nullptr;
   const int capacity = paged ? p.pt_stride * p.page_size
@@ -196,9 +198,10 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
     int pos = -1;
     if (lane < DTN) {
       const int i = n * DTN + lane;
-      if (gather)
+      if (gather) {
         pos = (i < p.topk) ? gidx[i] : -1;
-      else
+        if (p.key_hi > 0) pos = (pos >= p.key_lo && pos < p.key_hi) ? pos - p.key_lo : -1;
+      } else
         pos = (i < sk) ? i : -1;
       e = row_elem(pos);
     }
@@ -577,10 +580,10 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
       const float inv = dead ? 1.f : v_scale / l_tot;
       const int head = hkv * p.G + row;
       if (p.flags & F_SPLIT) {
-        float* dst = p.out_partial + (((long long)split * p.B + b) * p.Hq + head) * p.D + d0;
+        float* dst = p.out_partial + (long long)split * p.op_ss + ((long long)b * p.Hq + head) * p.D + d0;
         *reinterpret_cast<float4*>(dst) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
         if (d0 == 0)
-          p.lse_partial[((long long)split * p.Hq + head) * p.B + b] = dead ? -INFINITY : m_tot * c + log2f(l_tot);
+          p.lse_partial[(long long)split * p.lp_ss + (long long)head * p.B + b] = dead ? -INFINITY : m_tot * c + log2f(l_tot);
       } else {
         TO* dst = reinterpret_cast<TO*>(p.out) + (long long)b * p.o_sb + (long long)head * p.o_sh + d0;
         uint2 v;
@@ -600,12 +603,8 @@ template <int HD, typename T, int KIND>
 cudaError_t launch_one(const DecKernelParams& p, cudaStream_t stream) {
   auto kern = dec_kernel<HD, T, KIND>;
   constexpr int smem = DecSmem<HD, sizeof(T)>::kTotal;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  static std::atomic<unsigned long long> opted_in{0};  // one bit per device: the attribute is per device
+  if (cudaError_t e = smem_opt_in(kern, smem, opted_in); e != cudaSuccess) return e;
   const long long grid = (long long)p.Hkv * p.B * p.num_splits;
   if (grid <= 0) return cudaSuccess;
   kern<<<(unsigned)grid, DWARPS * 32, smem, stream>>>(p);

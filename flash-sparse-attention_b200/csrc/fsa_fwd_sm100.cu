@@ -25,30 +25,6 @@
 #include "fsa_params.h"
 #include "fsa_schedule.h"
 
-// Development aid: with -DFSA_PHASE_TIMING lane 0 of softmax warp 0 adds up the clock cycles of its phases;
-// fsa_debug_fwd_ticks() reads the totals over all CTAs.
-#ifdef FSA_PHASE_TIMING
-__device__ unsigned long long g_fwd_ticks[24];
-#define FWD_TICK_DECL long long ftk_[24] = {0}; long long ftk_t_ = clock64(); const bool ftk_on_ = (lane == 0) && (warp == 0)
-#define FWD_TICK_DECL_MMA long long ftk_[24] = {0}; long long ftk_t_ = clock64(); const bool ftk_on_ = (lane == 0)
-#define FWD_TICK(i)                          \
-  do {                                       \
-    const long long now_ = clock64();        \
-    ftk_[i] += now_ - ftk_t_;                \
-    ftk_t_ = now_;                           \
-  } while (0)
-#define FWD_TICK_FLUSH                                                                      \
-  do {                                                                                      \
-    if (ftk_on_)                                                                            \
-      for (int i_ = 0; i_ < 24; ++i_)                                                       \
-        if (ftk_[i_]) atomicAdd(&g_fwd_ticks[i_], (unsigned long long)ftk_[i_]);             \
-  } while (0)
-#else
-#define FWD_TICK_DECL
-#define FWD_TICK_DECL_MMA
-#define FWD_TICK(i)
-#define FWD_TICK_FLUSH
-#endif
 
 namespace fsa {
 
@@ -101,9 +77,6 @@ struct FwdBars {
   int vote_any[2][2][4]; // [group][parity][warp]: bit0 = some row wants the tile, bit1 = some row votes skip
   float a_ext[2][4][2];  // gated: per group, per warp (max, min) of alpha
   alignas(16) float dl[2][TN + 4];  // gated: delta of the key tile as fp32 (read as float4), then its max and min
-#ifdef FSA_PHASE_TIMING
-  long long dbg_t[4];
-#endif
 };
 
 static_assert(offsetof(FwdBars, dl) % 16 == 0 && sizeof(FwdBars) <= 2048, "FwdBars layout");
@@ -460,7 +433,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       }
     }
     int t = 0;
-    FWD_TICK_DECL_MMA;
     // The tensor pipe takes an MMA from a thread about as fast as it executes one: while its MMAs run this warp
     // is blocked in their issue, and whatever it does between a group publishing P and the next MMA is time the
     // pipe idles. So everything that does not depend on P (the walk over the tiles, who takes part in the next
@@ -484,9 +456,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
           last[q] = act[q] && fsa_fwd_next_tile_below(sched[q], n, local) < 0;
         }
       }
-      FWD_TICK(14);
       ok = mbar_wait(&bars->kv_full[t & 1], (t >> 1) & 1, abort_flag);  // V(t) and K(t + 1)
-      FWD_TICK(12);
       if (!ok) break;
       if ((p.flags & F_KV_RAGGED) && (n + 1) * TN > si.sk) {
         // keys past the sequence end carry probability 0 but their V rows may hold
@@ -505,20 +475,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
 #pragma unroll
       for (int q = 0; q < 2; ++q) {
         if (act[q]) {
-          FWD_TICK(14);
           ok = ok && mbar_wait(&bars->p_full[q], cnt[q] & 1, abort_flag);
-          FWD_TICK(10 + q);
-#ifdef FSA_PHASE_TIMING
-          if (q == 0) {
-            const long long d_ = clock64() - *reinterpret_cast<volatile long long*>(&bars->dbg_t[0]);
-            ftk_[16] += d_;
-          }
-#endif
           if (!ok) break;
           const bool skip = (KIND != KIND_DENSE) && bars->skip_flag[q][cnt[q] & 1];
           cnt[q]++;
           tc_fence_after();
-          FWD_TICK(14);
           if (!skip) {
 #pragma unroll
             for (int kk = 0; kk < KK_PV; ++kk) {
@@ -531,33 +492,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
             }
             o_started[q] = true;
           }
-          FWD_TICK(15);
           // last key tile of this group: tell it when its output is complete
           if (last[q]) umma_commit_lead(lead, &bars->o_final[q]);
-          FWD_TICK(7);
         }
         if (act_next[q]) {
           if (!act[q]) tc_fence_after();
-          FWD_TICK(14);
           issue_s(q, ks_next);
-          FWD_TICK(8);
-#ifdef FSA_PHASE_TIMING
-          if (q == 0 && lane == 0) *reinterpret_cast<volatile long long*>(&bars->dbg_t[1]) = clock64();
-#endif
         }
       }
       if (!ok) break;
-      FWD_TICK(14);
       // signal t + 1: V(t) and K(t + 1) are free once the MMAs issued so far have completed
       umma_commit_lead(lead, &bars->kv_empty[(t + 1) & 1]);
-      FWD_TICK(7);
       n = n_next;
       act[0] = act_next[0];
       act[1] = act_next[1];
       ++t;
     }
-    FWD_TICK(14);
-    FWD_TICK_FLUSH;
   }
   } else {
     // =============================== softmax groups ==========================================
@@ -596,7 +546,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     float lg_l = -INFINITY;   // log2(l_ref) for the skip test, refreshed at the end of a tile (off the S -> P path)
     bool have_o = false;      // some P V has been issued for this tile
     int cnt_s = 0;
-    FWD_TICK_DECL;
     bool ok = !*abort_flag;
     const bool has_work = q_valid[q] && !fsa_fwd_sched_empty(my);
 
@@ -653,12 +602,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
         gate_skip = (gmc - gate_max) * c < gate_thr_log2;
         if (!gate_skip) gate_max = fmaxf(gmc, gate_max);
       }
-      FWD_TICK(9);
       ok = mbar_wait(&bars->s_full[q], cnt_s & 1, abort_flag);
-      FWD_TICK(0);
-#ifdef FSA_PHASE_TIMING
-      if (ftk_on_ && cnt_s > 0) ftk_[17] += clock64() - *reinterpret_cast<volatile long long*>(&bars->dbg_t[1]);
-#endif
       if (!ok) break;
       tc_fence_after();
       const int par = cnt_s & 1;
@@ -690,7 +634,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
 #pragma unroll
       for (int ch = 0; ch < TN / 32; ++ch) tmem_ld32(tS + ch * 32, &sr[ch * 32]);
       tmem_ld_wait();
-      FWD_TICK(1);
       if (KIND == KIND_GATED) {
         // logits = (q.k + g(alpha * delta_j)) * scale, g = logsigmoid or identity
         // (flash_sparse_attn/ops/triton/flash_gated_fwd.py:104-122, activations.py:245-262)
@@ -746,7 +689,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       }
       const float m_cur = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
 
-      FWD_TICK(2);
       // ---- tile skip vote (flash_sparse_attn/ops/triton/activations.py:129-138) -----------------
       bool skip = false;
       if (KIND != KIND_DENSE) {
@@ -794,7 +736,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
         continue;
       }
 
-      FWD_TICK(3);
       // ---- move the reference maximum only when it lags by more than 2^8 -------------------------
       float m_cand = fmaxf(m_cur, m_ref);
       if (mode != FSA_MASK_NONE) m_cand = fmaxf(m_cand, -1e6f);
@@ -818,7 +759,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
         }
       }
 
-      FWD_TICK(4);
       // ---- P = exp2(S*c - m*c), row sum, publish P (16-bit pairs) over the S columns -----------------
       const float2 c2 = make_float2(c, c);
       const float neg_mc = -(m_ref * c);
@@ -852,22 +792,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
         else
           tmem_st16(tS + ch * 16, pk);
       }
-      FWD_TICK(5);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-#ifdef FSA_PHASE_TIMING
-      if (warp == 0 && lane == 0) *reinterpret_cast<volatile long long*>(&bars->dbg_t[0]) = clock64();
-#endif
       publish_verdict(false);
       if (lane == 0) mbar_arrive(&bars->p_full[q]);
       l_ref += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
       if (KIND != KIND_DENSE) lg_l = lg2_approx(l_ref);
       have_o = true;
-      FWD_TICK(6);
     }
-    FWD_TICK(9);
-    FWD_TICK_FLUSH;
 
     // ---- epilogue (flash_sparse_attn/ops/triton/activations.py:169-203) ---------------------------
     if (ok && have_o) {
@@ -935,12 +868,8 @@ template <int HD, typename T, int KIND>
 cudaError_t launch_one(const FwdKernelParams& p, cudaStream_t stream) {
   auto kern = fwd_kernel<HD, T, KIND>;
   constexpr int smem = FwdSmem<HD, sizeof(T)>::kTotal;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  static std::atomic<unsigned long long> opted_in{0};  // one bit per device: the attribute is per device
+  if (cudaError_t e = smem_opt_in(kern, smem, opted_in); e != cudaSuccess) return e;
   const long long grid = (long long)p.num_pairs * p.hgrid * p.B * p.num_splits;
   if (grid <= 0) return cudaSuccess;
   kern<<<(unsigned)grid, NTHREADS, smem, stream>>>(p);
@@ -951,16 +880,6 @@ cudaError_t launch_one(const FwdKernelParams& p, cudaStream_t stream) {
 
 // kind: KIND_*, dtype: DT_BF16 / DT_FP16, head_dim: 64 or 128. Returns cudaErrorInvalidValue for
 // unsupported combinations.
-#ifdef FSA_PHASE_TIMING
-extern "C" void fsa_debug_fwd_ticks(unsigned long long* out16, int reset) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out16, g_fwd_ticks, sizeof(unsigned long long) * 24);
-  if (reset) {
-    unsigned long long z[24] = {0};
-    cudaMemcpyToSymbol(g_fwd_ticks, z, sizeof(z));
-  }
-}
-#endif
 
 cudaError_t launch_fwd(const FwdKernelParams& p, int kind, int dtype, int head_dim, cudaStream_t stream) {
 #define FSA_FWD_CASE(HD_, T_, DT_)                                                  \

@@ -2,7 +2,10 @@
 // into these by fsa_api.cu).
 #pragma once
 #include <cuda.h>
+#include <cuda_runtime.h>
 #include <stdint.h>
+
+#include <atomic>
 
 namespace fsa {
 
@@ -51,6 +54,7 @@ struct alignas(64) FwdKernelParams {
   int page_size, pt_stride, win_stride, n_tiles_k;
   float scale_log2, softmax_thr, gate_thr, v_scale;
   const float* qkv_scale;  // optional device fp32 [3]: de-quantisation scales of q, k, v
+  const float* gate_ws;    // gated: per-tile extremes, see GateWsLayout
   unsigned flags;
 };
 
@@ -107,8 +111,49 @@ struct DecKernelParams {
   int num_splits, page_size, pt_stride, gi_stride, win_stride, n_tiles;
   float scale_log2, softmax_thr, gate_thr;
   const float* qkv_scale;  // optional device fp32 [3]
+  const int* thr_sk;       // optional [B]: key count that normalises the softmax threshold (a shard passes the whole length)
+  long long op_ss, lp_ss;  // elements between the partials of consecutive splits
+  int key_lo, key_hi;      // gather: positions outside [key_lo, key_hi) are masked, others shifted by -key_lo (key_hi = 0: off)
   int D;  // real head size (<= the kernel's HD)
   unsigned flags;
 };
+
+// Gated forward workspace: float2 (max, min) of alpha per (batch, grid head, 128-row query tile), then float2
+// (max, min) of delta per (batch, KV head, 128-key tile). Rows / keys past a sequence count as 0, like the
+// reference's masked loads (scheduler.py:1658-1691).
+inline size_t gate_ws_alpha_floats(int B, int hgrid, int num_m_blocks) { return 2 * (size_t)B * hgrid * num_m_blocks; }
+inline size_t gate_ws_bytes(int B, int hgrid, int num_m_blocks, int Hkv, int n_tiles_k) {
+  return sizeof(float) * (gate_ws_alpha_floats(B, hgrid, num_m_blocks) + 2 * (size_t)B * Hkv * n_tiles_k);
+}
+
+// Opt a kernel in to `smem` bytes of dynamic shared memory on the CURRENT device. The attribute is per device, so
+// the caller keeps one bit per device ordinal (`done`, one word per kernel instantiation); setting it twice is
+// harmless, which makes a race between host threads benign. Devices beyond 63 set it on every launch.
+template <typename Kernel>
+inline cudaError_t smem_opt_in(Kernel kern, int smem, std::atomic<unsigned long long>& done) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const unsigned long long bit = dev < 64 ? (1ull << dev) : 0ull;
+  if (bit && (done.load(std::memory_order_acquire) & bit)) return cudaSuccess;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e == cudaSuccess && bit) done.fetch_or(bit, std::memory_order_release);
+  return e;
+}
+
+// Multiprocessor count of the current device (148 on B200), cached per device ordinal.
+inline int device_sm_count() {
+  static std::atomic<int> cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev < 64) {
+    const int c = cache[dev].load(std::memory_order_relaxed);
+    if (c > 0) return c;
+  }
+  int sms = 148;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 148;
+  if (dev < 64) cache[dev].store(sms, std::memory_order_relaxed);
+  return sms;
+}
 
 }  // namespace fsa

@@ -10,6 +10,7 @@
 #include <stdint.h>
 
 #include "../../include/fsa_b200.h"
+#include "fsa_params.h"
 
 namespace fsa {
 
@@ -108,8 +109,7 @@ __global__ void __launch_bounds__(QT) widen_kernel(const uint8_t* __restrict__ x
 }
 
 unsigned grid_for(long long n_items) {
-  int dev = 0, sms = 148;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int sms = fsa::device_sm_count();
   const long long want = (n_items + QT - 1) / QT;
   const long long cap = (long long)sms * 8;  // 8 resident blocks of 256 threads per SM
   return (unsigned)(want < 1 ? 1 : (want < cap ? want : cap));

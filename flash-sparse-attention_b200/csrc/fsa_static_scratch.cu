@@ -6,8 +6,13 @@
 // own KV-cache pool, a plugin running inside a host framework whose memory plan was frozen at load
 // time, or code that runs between other people's kernels and may not trigger the implicit device
 // synchronisation a cudaMalloc / cudaFree brings. For them this file keeps ONE fixed workspace inside
-// the library image itself (a file-scope __device__ array, so every GPU that loads the library holds
-// these 16 MiB until the process exits) and offers a decode call that uses it.
+// the library image itself (a file-scope __device__ array) and offers a decode call that uses it.
+// The array becomes resident on a GPU when that GPU first uses it: with CUDA's lazy module loading that
+// is the first call of this entry point on the device, which loads the module holding the array (16 MiB
+// taken from the device's free memory, with an implicit synchronisation) and keeps it until the process
+// exits. So that first call belongs to start-up, before a pool claims the rest of the GPU and before
+// any stream capture; every later call on that device allocates and synchronises nothing. A device with
+// less than 16 MiB free at that moment gets FSA_ERR_SCRATCH_UNAVAILABLE.
 //
 // Consequences of the workspace being a single shared array:
 //   * a request whose partials do not fit is refused (FSA_ERR_SCRATCH_TOO_SMALL), never truncated;
@@ -35,14 +40,14 @@ float* g_scratch_addr[kMaxDevices] = {nullptr};
 // Device address of the workspace on the current device (resolved once per device).
 int scratch_for_current_device(float** out) {
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FSA_ERR_LAUNCH;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FSA_ERR_SCRATCH_UNAVAILABLE;
   float* p = __atomic_load_n(&g_scratch_addr[dev], __ATOMIC_ACQUIRE);
   if (!p) {
     void* sym = nullptr;
     const cudaError_t e = cudaGetSymbolAddress(&sym, g_decode_scratch);
     if (e != cudaSuccess || !sym) {
       (void)cudaGetLastError();
-      return FSA_ERR_LAUNCH;
+      return FSA_ERR_SCRATCH_UNAVAILABLE;
     }
     p = static_cast<float*>(sym);
     __atomic_store_n(&g_scratch_addr[dev], p, __ATOMIC_RELEASE);

@@ -14,6 +14,7 @@
 #include <stdint.h>
 
 #include "../../include/fsa_b200.h"
+#include "fsa_params.h"
 
 namespace fsa {
 
@@ -89,7 +90,7 @@ __device__ __forceinline__ uint32_t block_scan(uint32_t v, uint32_t* warp_tot, u
 // row. The histograms of a radix pass are summed over the cluster through distributed shared memory (every CTA
 // reads all of them and walks the bins itself, so all agree without a broadcast); for the compaction every CTA
 // first counts the greater / equal entries of its slice and takes the counts of the slices before it as its base.
-// With 64 rows one CTA per row would leave more than half of the 148 SMs idle.
+// With 64 rows one CTA per row would leave more than half of a B200's 148 SMs idle.
 template <typename T, typename I>
 __global__ void __launch_bounds__(TK_THREADS) topk_kernel(const T* __restrict__ scores, long long row_stride, int n, int k,
                                                           I* __restrict__ out, int csize, int chunk) {
@@ -218,7 +219,8 @@ __global__ void __launch_bounds__(TK_THREADS) topk_kernel(const T* __restrict__ 
 // of at least one step per CTA.
 inline int topk_cluster_size(int rows, int n) {
   int c = 1;
-  while (c < 8 && rows * (c * 2) <= 148 && n / (c * 2) >= TK_THREADS * TK_V) c *= 2;
+  const int sms = device_sm_count();
+  while (c < 8 && rows * (c * 2) <= sms && n / (c * 2) >= TK_THREADS * TK_V) c *= 2;
   return c;
 }
 

@@ -7,6 +7,7 @@ holds ``csrc/``), and every entry point raises on a non-zero status.
 
 import ctypes
 import os
+import threading
 from ctypes import POINTER, c_float, c_int, c_int32, c_int64, c_size_t, c_uint32, c_uint8, c_void_p
 
 import torch
@@ -14,7 +15,7 @@ import torch
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(os.path.dirname(_HERE), "libfsa_b200.so")
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 KIND_DENSE, KIND_SPARSE, KIND_GATED = 0, 1, 2
 DT_BF16, DT_FP16, DT_E4M3, DT_E5M2, DT_F32 = 0, 1, 2, 3, 4
@@ -39,9 +40,6 @@ class FsaFwdArgs(ctypes.Structure):
         ("lse_partial", c_void_p),
         ("alpha", c_void_p),
         ("delta", c_void_p),
-        ("q_descale", c_void_p),
-        ("k_descale", c_void_p),
-        ("v_descale", c_void_p),
         ("cu_seqlens_q", c_void_p),
         ("cu_seqlens_k", c_void_p),
         ("seqused_q", c_void_p),
@@ -90,6 +88,9 @@ class FsaFwdArgs(ctypes.Structure):
         ("softmax_threshold", c_float),
         ("gate_threshold", c_float),
         ("qkv_scale", c_void_p),
+        ("gate_ws", c_void_p),
+        ("ev_before", c_void_p),
+        ("ev_after", c_void_p),
     ]
 
 
@@ -171,6 +172,8 @@ class FsaBwdArgs(ctypes.Structure):
         ("delta_numel", c_int64),
         ("dq_order", c_void_p),
         ("dq_turn", c_void_p),
+        ("ev_before", c_void_p),
+        ("ev_after", c_void_p),
     ]
 
 
@@ -226,7 +229,27 @@ class FsaDecArgs(ctypes.Structure):
         ("softmax_threshold", c_float),
         ("gate_threshold", c_float),
         ("qkv_scale", c_void_p),
+        ("thr_seqlen_k", c_void_p),
+        ("key_lo", c_int32),
+        ("key_hi", c_int32),
+        ("out_partial_stride", c_int64),
+        ("lse_partial_stride", c_int64),
+        ("ev_before", c_void_p),
+        ("ev_after", c_void_p),
     ]
+
+
+class FsaFwdWorkspace(ctypes.Structure):
+    _fields_ = [("out_partial", c_size_t), ("lse_partial", c_size_t), ("gate_ws", c_size_t)]
+
+
+class FsaBwdWorkspace(ctypes.Structure):
+    _fields_ = [(n, c_size_t) for n in ("lse2_ws", "dpsum_ws", "dq_accum", "dk_partial", "dv_partial", "alpha_ws",
+                                        "da_accum", "dd_partial", "dq_order", "dq_turn")]
+
+
+class FsaDecWorkspace(ctypes.Structure):
+    _fields_ = [("out_partial", c_size_t), ("lse_partial", c_size_t)]
 
 
 _lib = None
@@ -261,15 +284,20 @@ def load():
     lib.fsa_decode.restype = c_int
     lib.fsa_decode.argtypes = [POINTER(FsaDecArgs), c_void_p]
     lib.fsa_combine.restype = c_int
-    lib.fsa_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+    lib.fsa_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int64,
+                                c_int64, c_void_p]
     lib.fsa_quantize_fp8.restype = c_int
     lib.fsa_quantize_fp8.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
     lib.fsa_fp8_widen.restype = c_int
     lib.fsa_fp8_widen.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
     lib.fsa_topk_indices.restype = c_int
     lib.fsa_topk_indices.argtypes = [c_void_p, c_int, c_int, c_int, c_int64, c_int, c_void_p, c_int, c_void_p]
-    lib.fsa_set_profile_events.restype = None
-    lib.fsa_set_profile_events.argtypes = [c_void_p, c_void_p]
+    lib.fsa_fwd_workspace_bytes.restype = c_int
+    lib.fsa_fwd_workspace_bytes.argtypes = [POINTER(FsaFwdArgs), POINTER(FsaFwdWorkspace)]
+    lib.fsa_bwd_workspace_bytes.restype = c_int
+    lib.fsa_bwd_workspace_bytes.argtypes = [POINTER(FsaBwdArgs), POINTER(FsaBwdWorkspace)]
+    lib.fsa_decode_workspace_bytes.restype = c_int
+    lib.fsa_decode_workspace_bytes.argtypes = [POINTER(FsaDecArgs), POINTER(FsaDecWorkspace)]
     lib.fsa_debug_fwd_schedule.restype = None
     lib.fsa_debug_fwd_schedule.argtypes = [c_int] * 4 + [POINTER(c_int32)] + [c_int] * 7 + [POINTER(c_int32)]
     lib.fsa_debug_bwd_schedule.restype = None
@@ -328,11 +356,27 @@ def check_status(device=None):
             raise RuntimeError(f"fsa kernel reported device status {v} (a pipeline wait expired)")
 
 
+_profile = threading.local()
+
+
 def set_profile_events(before=None, after=None):
-    """Have the next operator calls of this thread record `before` / `after` (torch.cuda.Event, already
-    recorded once so that their handles exist) around their main kernel; None, None switches it off."""
-    load().fsa_set_profile_events(before.cuda_event if before is not None else None,
-                                  after.cuda_event if after is not None else None)
+    """Have the next operator calls of THIS THREAD record `before` / `after` (torch.cuda.Event, already
+    recorded once so that their handles exist) around their main kernel; None, None switches it off. The pair
+    travels in the argument block of each call (`ev_before` / `ev_after`): the library keeps no such state."""
+    _profile.before = before.cuda_event if before is not None else None
+    _profile.after = after.cuda_event if after is not None else None
+
+
+def attach_profile_events(args):
+    args.ev_before = getattr(_profile, "before", None)
+    args.ev_after = getattr(_profile, "after", None)
+
+
+def workspace(nbytes: int, device, dtype=torch.float32):
+    """A caller-owned workspace of `nbytes` bytes (size from fsa_*_workspace_bytes) viewed as `dtype`, or None."""
+    if nbytes == 0:
+        return None
+    return torch.empty(nbytes // torch.empty((), dtype=dtype).element_size(), dtype=dtype, device=device)
 
 
 def current_stream_ptr(device) -> int:

@@ -2,14 +2,22 @@
 
 Not part of the reference (it has no multi-GPU code); it is built from the same pieces as its split-KV
 decode: every rank produces the partial result of its key range exactly like one KV split
-(flash_sparse_attn/ops/triton/flash_sparse_dec.py:485-489 - base-2 log-sum-exp partials), one NCCL
+(flash_sparse_attn/ops/triton/flash_sparse_dec.py:485-489 - base-2 log-sum-exp partials), ONE NCCL
 all-gather lands all partials in local memory (2.1 MB per rank at batch 64, 64 heads, head_dim 128),
 and the decode combine (flash_dec_combine.py:15-153) merges them. No other collective is needed.
 
 Sharding convention: rank r owns the logical key positions [lo_r, hi_r) of every sequence and holds them
-as a local cache whose position 0 is global position lo_r. Gathered (top-k) indices are global positions;
-each rank keeps the ones inside its range and masks the others (-1), so the union over ranks is exactly the
-original index set.
+as a local cache whose position 0 is global position lo_r. Gathered (top-k) indices stay GLOBAL positions:
+the decode kernel itself masks the ones outside [lo_r, hi_r) and shifts the others (FsaDecArgs.key_lo /
+key_hi), so the union over ranks is exactly the original index set and the step runs no index arithmetic
+outside the kernel. The softmax threshold is normalised by the length of the WHOLE sequence on every rank
+(FsaDecArgs.thr_seqlen_k); each shard still compares against its own running maximum and sum, so with a
+positive threshold a shard can keep a tile that the unsharded call would skip or the other way round - the
+difference is bounded by the threshold mass, as between different split counts on one GPU.
+
+Wire format: one fp32 block of B*Hq*(D+1) elements per (rank, split): the partial outputs [B, Hq, D] followed by
+the base-2 log-sum-exps [Hq, B]. The all-gather concatenates the blocks of all ranks; the combine kernel reads
+them in place.
 """
 
 from typing import Callable, Optional, Tuple
@@ -28,45 +36,105 @@ def shard_bounds(seqlen_k: int, world_size: int, rank: int, align: int = 256) ->
 
 
 def localize_indices(gather_kv_indices: torch.Tensor, lo: int, hi: int) -> torch.Tensor:
-    """Global top-k positions -> positions inside the local shard [lo, hi); everything else becomes -1."""
+    """Global top-k positions -> positions inside the local shard [lo, hi); everything else becomes -1.
+    (What the decode kernel does for `key_range = (lo, hi)`; kept for host-side checks.)"""
     inside = (gather_kv_indices >= lo) & (gather_kv_indices < hi)
     return torch.where(inside, gather_kv_indices - lo, torch.full_like(gather_kv_indices, -1))
 
 
+def pack_partials(out_partial: torch.Tensor, lse_partial: torch.Tensor) -> torch.Tensor:
+    """[P, B, Hq, D] and [P, Hq, B] -> the wire format [P, B*Hq*(D+1)]."""
+    parts = out_partial.shape[0]
+    return torch.cat([out_partial.reshape(parts, -1), lse_partial.reshape(parts, -1)], dim=1).contiguous()
+
+
+def unpack_partials(packed: torch.Tensor, parts: int, batch: int, heads: int, head_dim: int):
+    blocks = packed.view(parts, batch * heads * (head_dim + 1))
+    n = batch * heads * head_dim
+    return blocks[:, :n].reshape(parts, batch, heads, head_dim), blocks[:, n:].reshape(parts, heads, batch)
+
+
 def context_parallel_decode(
-    partial_fn: Callable[..., Tuple[torch.Tensor, torch.Tensor]],
-    combine_fn: Callable[[torch.Tensor, torch.Tensor], Tuple[torch.Tensor, torch.Tensor]],
+    partial_fn: Callable[[], torch.Tensor],
+    combine_fn: Callable[[torch.Tensor, int], Tuple[torch.Tensor, torch.Tensor]],
     group: Optional[dist.ProcessGroup] = None,
-    **partial_kwargs,
+    gathered: Optional[torch.Tensor] = None,
 ):
-    """Run `partial_fn(**partial_kwargs)` -> (out_partial [P, B, Hq, D] fp32, lse_partial [P, Hq, B] fp32,
-    base 2) on this rank's shard, all-gather the partials of all ranks, and merge them with `combine_fn`.
-    Returns (out [B, Hq, D], lse [B, Hq]) - identical on every rank."""
-    out_p, lse_p = partial_fn(**partial_kwargs)
+    """`partial_fn()` -> this rank's partials in the wire format [P, B*Hq*(D+1)] (fp32); one all-gather; then
+    `combine_fn(all_partials, world * P)` -> (out [B, Hq, D], lse [B, Hq]), identical on every rank.
+    `gathered` optionally supplies the receive buffer (world * P blocks) so that the step allocates nothing."""
+    packed = partial_fn()
     world = dist.get_world_size(group)
+    parts = packed.shape[0]
     if world == 1:
-        return combine_fn(out_p, lse_p)
-    # concatenation along the partial axis: rank r's partials land at [r * P, (r + 1) * P)
-    out_all = torch.empty((world * out_p.shape[0],) + tuple(out_p.shape[1:]), dtype=out_p.dtype, device=out_p.device)
-    lse_all = torch.empty((world * lse_p.shape[0],) + tuple(lse_p.shape[1:]), dtype=lse_p.dtype, device=lse_p.device)
-    dist.all_gather_into_tensor(out_all, out_p.contiguous(), group=group)
-    dist.all_gather_into_tensor(lse_all, lse_p.contiguous(), group=group)
-    return combine_fn(out_all, lse_all)
+        return combine_fn(packed, parts)
+    if gathered is None:
+        gathered = torch.empty((world * parts, packed.shape[1]), dtype=packed.dtype, device=packed.device)
+    # concatenation along the partial axis: rank r's blocks land at [r * P, (r + 1) * P)
+    dist.all_gather_into_tensor(gathered, packed, group=group)
+    return combine_fn(gathered, world * parts)
+
+
+class ContextParallelDecoder:
+    """Sparse (or dense) decode with the KV sequence sharded over the ranks of `group`, with every buffer of the
+    step allocated once: decode kernel (partials in the wire format) -> one all-gather -> combine kernel.
+
+    `key_local / value_local` hold this rank's positions [shard_lo, shard_hi) (contiguous [B, S_local, Hkv, D], or
+    paged with `page_table`); `gather_kv_indices` are GLOBAL positions; `seqused_k_global` (int32 [B]) the lengths
+    of the whole sequences (normalises the softmax threshold; in gather mode it is all the kernel needs to know
+    about lengths), `seqused_k_local` the number of valid keys in the local shard (full-context mode)."""
+
+    def __init__(self, batch: int, heads_q: int, head_dim: int, dtype: torch.dtype, device, num_splits: int = 1,
+                 group=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.batch, self.heads, self.head_dim, self.dtype, self.ns = batch, heads_q, head_dim, dtype, num_splits
+        per = batch * heads_q * (head_dim + 1)
+        self.send = torch.empty((num_splits, per), dtype=torch.float32, device=device)
+        self.recv = torch.empty((self.world * num_splits, per), dtype=torch.float32, device=device)
+        self.out = torch.empty((batch, heads_q, head_dim), dtype=dtype, device=device)
+        self.lse = torch.empty((batch, heads_q), dtype=torch.float32, device=device)
+
+    def partial(self, query, key_local, value_local, shard_lo, shard_hi, gather_kv_indices=None,
+                seqused_k_global=None, seqused_k_local=None, page_table=None, softmax_scale=None,
+                softmax_threshold=None, kind="sparse"):
+        from flash_sparse_attn.ops.triton.flash_dec import attn_decode
+
+        gather = gather_kv_indices is not None
+        attn_decode(kind, query, key_local, value_local, partial_only=True, num_splits=self.ns,
+                    packed_partials=self.send, gather_kv_indices=gather_kv_indices,
+                    key_range=(shard_lo, shard_hi) if gather else None,
+                    seqused_k=seqused_k_global if gather else seqused_k_local,
+                    threshold_seqlen_k=None if gather else seqused_k_global, page_table=page_table,
+                    softmax_scale=softmax_scale, softmax_threshold=softmax_threshold)
+        return self.send
+
+    def exchange(self):
+        if self.world == 1:
+            return self.send
+        dist.all_gather_into_tensor(self.recv, self.send, group=self.group)
+        return self.recv
+
+    def combine(self, packed):
+        from flash_sparse_attn.ops.triton.flash_dec import combine_packed_partials
+
+        return combine_packed_partials(packed, packed.shape[0], self.batch, self.heads, self.head_dim, self.dtype,
+                                       out=self.out, lse=self.lse)
+
+    def __call__(self, *args, **kwargs):
+        self.partial(*args, **kwargs)
+        return self.combine(self.exchange())
 
 
 def flash_sparse_attn_with_kvcache_cp(query, key_local, value_local, shard_lo: int, shard_hi: int,
                                       gather_kv_indices=None, seqused_k_local=None, page_table=None,
                                       softmax_scale=None, softmax_threshold=None, num_splits: int = 1, kind="sparse",
-                                      group=None):
-    """Sparse (or dense) decode with the KV sequence sharded over the ranks of `group`.
-    `key_local/value_local` hold this rank's positions [shard_lo, shard_hi) (contiguous [B, S_local, Hkv, D]
-    or paged with `page_table`); `gather_kv_indices` are global positions."""
-    from flash_sparse_attn.ops.triton.flash_dec import attn_decode, combine_partials
-
-    idx = localize_indices(gather_kv_indices, shard_lo, shard_hi) if gather_kv_indices is not None else None
-    return context_parallel_decode(
-        lambda **kw: attn_decode(kind, query, key_local, value_local, partial_only=True, **kw),
-        lambda o, l: combine_partials(o, l, query.dtype),
-        group=group, gather_kv_indices=idx, seqused_k=seqused_k_local, page_table=page_table,
-        softmax_scale=softmax_scale, softmax_threshold=softmax_threshold, num_splits=num_splits,
-    )
+                                      group=None, seqused_k_global=None):
+    """One-shot form of ContextParallelDecoder (allocates its buffers on every call)."""
+    dec = ContextParallelDecoder(query.shape[0], query.shape[1], query.shape[2],
+                                 torch.bfloat16 if query.dtype.itemsize == 1 else query.dtype, query.device,
+                                 num_splits=num_splits, group=group)
+    out, lse = dec(query, key_local, value_local, shard_lo, shard_hi, gather_kv_indices=gather_kv_indices,
+                   seqused_k_global=seqused_k_global, seqused_k_local=seqused_k_local, page_table=page_table,
+                   softmax_scale=softmax_scale, softmax_threshold=softmax_threshold, kind=kind)
+    return out, lse

@@ -122,27 +122,13 @@ def attn_backward(
     dk = torch.empty_like(key, dtype=dout.dtype)
     dv = torch.empty_like(value, dtype=dout.dtype)
     lib = _lib.load()
-    rows_pad = lib.fsa_bwd_padded_rows(batch, seqlen_q, total_q, int(varlen))
-    lse2_ws = torch.empty((num_heads_q, rows_pad), dtype=torch.float32, device=device)
-    dpsum_ws = torch.empty((num_heads_q, rows_pad), dtype=torch.float32, device=device)
-    # rows of the accumulator are as wide as the kernel's head tile (64 or 128 columns)
-    dq_accum = torch.empty((num_heads_q, rows_pad, 64 if head_dim <= 64 else 128), dtype=torch.float32, device=device)
-    dk_partial = dv_partial = None
-    if use_split:
-        rows_k = total_k if varlen else batch * seqlen_k
-        dk_partial = torch.empty((num_splits, rows_k, num_heads_kv, head_dim), dtype=torch.float32, device=device)
-        dv_partial = torch.empty((num_splits, rows_k, num_heads_kv, head_dim), dtype=torch.float32, device=device)
-    da = dd = alpha_ws = da_accum = dd_partial = None
+    da = dd = None
     if kind == "gated":
         # alpha [B, Hq, Sq] / [Hq, Tq], delta [B, Hkv, Sk] / [Hkv, Tk] (position contiguous), 16-bit like dout
         alpha = alpha.to(dout.dtype).contiguous()
         delta = delta.to(dout.dtype).contiguous()
         da = torch.empty_like(alpha)
         dd = torch.empty_like(delta)
-        alpha_ws = torch.empty((num_heads_q, rows_pad), dtype=dout.dtype, device=device)
-        da_accum = torch.empty((num_heads_q, rows_pad), dtype=torch.float32, device=device)
-        if use_split:
-            dd_partial = torch.empty((num_splits, delta.numel()), dtype=torch.float32, device=device)
     if seqused_k is not None or seqused_q is not None:
         # rows outside the used part of a sequence receive no gradient
         dq.zero_()
@@ -151,18 +137,11 @@ def attn_backward(
         if kind == "gated":
             da.zero_()
             dd.zero_()
-            if use_split:
-                dd_partial.zero_()
-        if use_split:
-            dk_partial.zero_()
-            dv_partial.zero_()
 
     a = _lib.FsaBwdArgs()
     a.q, a.k, a.v = query.data_ptr(), key.data_ptr(), value.data_ptr()
     a.out, a.dout, a.lse = out.data_ptr(), dout.data_ptr(), lse.data_ptr()
     a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
-    a.lse2_ws, a.dpsum_ws, a.dq_accum = lse2_ws.data_ptr(), dpsum_ws.data_ptr(), dq_accum.data_ptr()
-    a.dk_partial, a.dv_partial = _lib.ptr(dk_partial), _lib.ptr(dv_partial)
     a.cu_seqlens_q, a.cu_seqlens_k = _lib.ptr(cu_seqlens_q), _lib.ptr(cu_seqlens_k)
     a.seqused_q, a.seqused_k = _lib.ptr(seqused_q), _lib.ptr(seqused_k)
     a.window_sizes = _lib.ptr(window_sizes)
@@ -203,14 +182,9 @@ def attn_backward(
     a.softmax_threshold = float(softmax_threshold)
     a.gate_threshold = float(gate_threshold) if gate_threshold is not None else 0.0
     if deterministic:
-        n_tiles_k, n_tiles_q = -(-seqlen_k // TILE_N), -(-seqlen_q // TILE_M)
-        dq_order = torch.empty((batch, num_heads_kv, n_tiles_k, n_tiles_q), dtype=torch.int16, device=device)
-        dq_turn = torch.empty((batch, num_heads_q, n_tiles_q), dtype=torch.int32, device=device)
-        a.dq_order, a.dq_turn = dq_order.data_ptr(), dq_turn.data_ptr()
         a.flags |= _lib.F_DETERMINISTIC
     if kind == "gated":
         a.alpha, a.delta, a.dalpha, a.ddelta = alpha.data_ptr(), delta.data_ptr(), da.data_ptr(), dd.data_ptr()
-        a.alpha_ws, a.da_accum, a.dd_partial = alpha_ws.data_ptr(), da_accum.data_ptr(), _lib.ptr(dd_partial)
         a.alpha_stride_b, a.alpha_stride_h = (0, alpha.stride(0)) if varlen else (alpha.stride(0), alpha.stride(1))
         a.delta_stride_b, a.delta_stride_h = (0, delta.stride(0)) if varlen else (delta.stride(0), delta.stride(1))
         a.delta_numel = delta.numel()
@@ -218,6 +192,20 @@ def attn_backward(
             a.flags |= _lib.F_LOGSIGMOID
         if is_adapt_gate:
             a.flags |= _lib.F_ADAPT_GATE
+
+    # caller-owned workspaces, sized by the library (fp32 unless noted): lse2 / dpsum [Hq, R], dq_accum [Hq, R, 64 | 128]
+    # with R tile-padded rows; split-QO partials of dK / dV (/ ddelta); gated: alpha copy (16-bit) and dalpha
+    # accumulator [Hq, R]; deterministic: visiting order (uint16) and turn counters (int32)
+    ws = _lib.FsaBwdWorkspace()
+    _lib.check(lib.fsa_bwd_workspace_bytes(ctypes.byref(a), ctypes.byref(ws)), "fsa_bwd_workspace_bytes")
+    bufs = {name: _lib.workspace(getattr(ws, name), device, torch.uint8) for name, _ in ws._fields_}
+    if seqused_k is not None or seqused_q is not None:
+        for name in ("dk_partial", "dv_partial", "dd_partial"):  # rows outside the used part receive no gradient
+            if bufs[name] is not None:
+                bufs[name].zero_()
+    for name, buf in bufs.items():
+        setattr(a, name, _lib.ptr(buf))
+    _lib.attach_profile_events(a)
 
     with torch.cuda.device(device):
         rc = lib.fsa_bwd(ctypes.byref(a), _lib.current_stream_ptr(device))

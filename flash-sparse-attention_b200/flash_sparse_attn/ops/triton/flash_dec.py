@@ -63,10 +63,18 @@ def attn_decode(
     tile_map: Optional[torch.Tensor] = None,
     partial_only: bool = False,
     workspace: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+    threshold_seqlen_k: Optional[torch.Tensor] = None,
+    key_range: Optional[Tuple[int, int]] = None,
+    packed_partials: Optional[torch.Tensor] = None,
 ):
     """Returns ``(out, lse)``; with ``partial_only`` returns ``(out_partial [ns,B,Hq,D] fp32,
     lse_partial [ns,Hq,B] fp32 base-2)`` instead (used by context-parallel decode).
-    ``workspace`` optionally supplies the two partial buffers so that no allocation happens."""
+    ``workspace`` optionally supplies the two partial buffers so that no allocation happens.
+    For a shard of a longer key sequence: ``threshold_seqlen_k`` (int32 [B]) is the key count that normalises the
+    softmax threshold (the whole sequence's, so that a shard skips by the same bound as an unsharded call);
+    ``key_range = (lo, hi)`` makes gathered positions outside [lo, hi) masked and addresses the others at
+    position - lo. ``packed_partials`` (fp32, at least splits * B * Hq * (D + 1) elements) receives the partials
+    of every split as one block - outputs then log-sum-exps - so that they travel in a single all-gather."""
     if not query.is_cuda:
         raise RuntimeError("flash_sparse_attn (B200 build) only runs on CUDA tensors; there is no CPU path")
     device = query.device
@@ -99,7 +107,10 @@ def attn_decode(
             window_sizes=window_sizes, alpha=alpha, delta=delta, cu_seqlens_k=cu_seqlens_k, seqused_k=seqused_k,
             page_table=page_table, gather_kv_indices=gather_kv_indices, num_heads_q=num_heads_q,
             num_heads_kv=num_heads_kv, head_dim=head_dim, page_size=page_size, is_quant=is_quant, device=device,
+            tile_mn=tile_mn,
         )
+        assert_inputs.check_out_buffers(out, lse, query.shape, torch.bfloat16 if is_quant else query.dtype,
+                                        query.shape[:2])
 
     qkv_scale = None
     if is_quant:
@@ -119,18 +130,9 @@ def attn_decode(
         out = torch.empty(query.shape, dtype=out_dtype, device=device)
     if lse is None and not partial_only:
         lse = torch.empty((batch, num_heads_q), dtype=torch.float32, device=device)
-    out_partial = lse_partial = None
-    if num_splits > 1 or partial_only:
-        if workspace is not None:
-            out_partial, lse_partial = workspace
-        else:
-            out_partial = torch.empty((num_splits, batch, num_heads_q, head_dim), dtype=torch.float32, device=device)
-            lse_partial = torch.empty((num_splits, num_heads_q, batch), dtype=torch.float32, device=device)
-
     a = _lib.FsaDecArgs()
     a.q, a.k, a.v = query.data_ptr(), key.data_ptr(), value.data_ptr()
     a.out, a.lse = _lib.ptr(out), _lib.ptr(lse)
-    a.out_partial, a.lse_partial = _lib.ptr(out_partial), _lib.ptr(lse_partial)
     a.cu_seqlens_k, a.seqused_k = _lib.ptr(cu_seqlens_k), _lib.ptr(seqused_k)
     a.page_table, a.gather_kv_indices = _lib.ptr(page_table), _lib.ptr(gather_kv_indices)
     a.window_sizes = _lib.ptr(window_sizes)
@@ -169,25 +171,67 @@ def attn_decode(
     a.softmax_threshold = float(softmax_threshold)
     a.gate_threshold = float(gate_threshold)
     a.qkv_scale = _lib.ptr(qkv_scale)
+    a.thr_seqlen_k = _lib.ptr(threshold_seqlen_k)
+    if key_range is not None:
+        a.key_lo, a.key_hi = int(key_range[0]), int(key_range[1])
+
+    # split partials [splits, B, Hq, D] / [splits, Hq, B] (base-2 lse): the caller's, or sized by the library
+    lib = _lib.load()
+    out_partial = lse_partial = None
+    if packed_partials is not None:
+        # one buffer [splits, B*Hq*(D+1)]: the partial outputs of a split followed by its log-sum-exps
+        per = batch * num_heads_q * (head_dim + 1)
+        assert packed_partials.dtype == torch.float32 and packed_partials.numel() >= num_splits * per
+        flat = packed_partials.view(-1)
+        out_partial, lse_partial = flat, flat[batch * num_heads_q * head_dim:]
+        a.out_partial_stride = a.lse_partial_stride = per
+    elif workspace is not None:
+        out_partial, lse_partial = workspace
+    else:
+        ws = _lib.FsaDecWorkspace()
+        _lib.check(lib.fsa_decode_workspace_bytes(ctypes.byref(a), ctypes.byref(ws)), "fsa_decode_workspace_bytes")
+        if ws.out_partial:
+            out_partial = _lib.workspace(ws.out_partial, device).view(num_splits, batch, num_heads_q, head_dim)
+            lse_partial = _lib.workspace(ws.lse_partial, device).view(num_splits, num_heads_q, batch)
+    a.out_partial, a.lse_partial = _lib.ptr(out_partial), _lib.ptr(lse_partial)
+    _lib.attach_profile_events(a)
 
     with torch.cuda.device(device):
-        rc = _lib.load().fsa_decode(ctypes.byref(a), _lib.current_stream_ptr(device))
+        rc = lib.fsa_decode(ctypes.byref(a), _lib.current_stream_ptr(device))
     _lib.check(rc, f"fsa_decode[{kind}]")
     if partial_only:
         return out_partial, lse_partial
     return out, lse
 
 
-def combine_partials(out_partial: torch.Tensor, lse_partial: torch.Tensor, dtype: torch.dtype):
+def combine_partials(out_partial: torch.Tensor, lse_partial: torch.Tensor, dtype: torch.dtype, out=None, lse=None):
     """Merge partial decode results ``[P, B, Hq, D]`` / ``[P, Hq, B]`` (base-2 lse) into ``(out [B,Hq,D],
     lse [B,Hq])`` with the library's combine kernel."""
     parts, batch, heads, head_dim = out_partial.shape
     device = out_partial.device
-    out = torch.empty((batch, heads, head_dim), dtype=dtype, device=device)
-    lse = torch.empty((batch, heads), dtype=torch.float32, device=device)
+    out = torch.empty((batch, heads, head_dim), dtype=dtype, device=device) if out is None else out
+    lse = torch.empty((batch, heads), dtype=torch.float32, device=device) if lse is None else lse
     with torch.cuda.device(device):
         rc = _lib.load().fsa_combine(out_partial.data_ptr(), lse_partial.data_ptr(), out.data_ptr(), lse.data_ptr(),
-                                     parts, batch, heads, head_dim, _lib.dtype_code(dtype),
+                                     parts, batch, heads, head_dim, _lib.dtype_code(dtype), 0, 0,
+                                     _lib.current_stream_ptr(device))
+    _lib.check(rc, "fsa_combine")
+    return out, lse
+
+
+def combine_packed_partials(packed: torch.Tensor, parts: int, batch: int, heads: int, head_dim: int,
+                            dtype: torch.dtype, out=None, lse=None):
+    """Merge `parts` partials stored as blocks of B*Hq*(D+1) floats (outputs, then base-2 log-sum-exps [Hq, B]):
+    the layout ``attn_decode(..., packed_partials=...)`` writes and an all-gather of it concatenates."""
+    device = packed.device
+    per = batch * heads * (head_dim + 1)
+    flat = packed.view(-1)
+    assert flat.numel() >= parts * per
+    out = torch.empty((batch, heads, head_dim), dtype=dtype, device=device) if out is None else out
+    lse = torch.empty((batch, heads), dtype=torch.float32, device=device) if lse is None else lse
+    with torch.cuda.device(device):
+        rc = _lib.load().fsa_combine(flat.data_ptr(), flat[batch * heads * head_dim:].data_ptr(), out.data_ptr(),
+                                     lse.data_ptr(), parts, batch, heads, head_dim, _lib.dtype_code(dtype), per, per,
                                      _lib.current_stream_ptr(device))
     _lib.check(rc, "fsa_combine")
     return out, lse

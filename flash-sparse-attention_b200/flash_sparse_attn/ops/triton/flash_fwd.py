@@ -105,8 +105,11 @@ def attn_forward(
             window_sizes=window_sizes, alpha=alpha, delta=delta, cu_seqlens_q=cu_seqlens_q,
             cu_seqlens_k=cu_seqlens_k, seqused_q=seqused_q, seqused_k=seqused_k, num_heads_q=num_heads_q,
             num_heads_kv=num_heads_kv, head_dim=head_dim, page_size=page_size, tile_mn=tile_mn, is_quant=is_quant,
-            device=device,
+            device=device, page_table=page_table,
         )
+        assert_inputs.check_out_buffers(
+            out, lse, query.shape, torch.bfloat16 if is_quant else query.dtype,
+            (num_heads_q, total_q) if varlen else (batch, num_heads_q, seqlen_q))
 
     qkv_scale = None
     if is_quant:
@@ -140,20 +143,9 @@ def attn_forward(
         lse_shape = (num_heads_q, total_q) if varlen else (batch, num_heads_q, seqlen_q)
         lse = torch.empty(lse_shape, dtype=torch.float32, device=device)
 
-    out_partial = lse_partial = None
-    if use_split:
-        rows = total_q if varlen else batch * seqlen_q
-        out_partial = torch.empty((num_splits, rows, num_heads_q, head_dim), dtype=torch.float32, device=device)
-        if varlen and seqused_q is not None:
-            lse_partial = torch.full((num_splits, num_heads_q, rows), float("-inf"), dtype=torch.float32,
-                                     device=device)
-        else:
-            lse_partial = torch.empty((num_splits, num_heads_q, rows), dtype=torch.float32, device=device)
-
     a = _lib.FsaFwdArgs()
     a.q, a.k, a.v = query.data_ptr(), key.data_ptr(), value.data_ptr()
     a.out, a.lse = out.data_ptr(), lse.data_ptr()
-    a.out_partial, a.lse_partial = _lib.ptr(out_partial), _lib.ptr(lse_partial)
     a.alpha, a.delta = _lib.ptr(alpha), _lib.ptr(delta)
     a.cu_seqlens_q, a.cu_seqlens_k = _lib.ptr(cu_seqlens_q), _lib.ptr(cu_seqlens_k)
     a.seqused_q, a.seqused_k = _lib.ptr(seqused_q), _lib.ptr(seqused_k)
@@ -208,8 +200,20 @@ def attn_forward(
     a.softmax_threshold = float(softmax_threshold)
     a.gate_threshold = float(gate_threshold)
 
+    # caller-owned workspaces, sized by the library: split-KV partials [splits, rows, Hq, D] / [splits, Hq, rows]
+    # and the gated kind's per-tile extremes
+    lib = _lib.load()
+    ws = _lib.FsaFwdWorkspace()
+    _lib.check(lib.fsa_fwd_workspace_bytes(ctypes.byref(a), ctypes.byref(ws)), "fsa_fwd_workspace_bytes")
+    out_partial, lse_partial = _lib.workspace(ws.out_partial, device), _lib.workspace(ws.lse_partial, device)
+    gate_ws = _lib.workspace(ws.gate_ws, device)
+    if lse_partial is not None and varlen and seqused_q is not None:
+        lse_partial.fill_(float("-inf"))  # rows past seqused_q are never written
+    a.out_partial, a.lse_partial, a.gate_ws = _lib.ptr(out_partial), _lib.ptr(lse_partial), _lib.ptr(gate_ws)
+    _lib.attach_profile_events(a)
+
     with torch.cuda.device(device):
-        rc = _lib.load().fsa_fwd(ctypes.byref(a), _lib.current_stream_ptr(device))
+        rc = lib.fsa_fwd(ctypes.byref(a), _lib.current_stream_ptr(device))
     _lib.check(rc, f"fsa_fwd[{kind}]")
     return out, lse, softmax_scale, softmax_threshold, gate_threshold
 

@@ -590,3 +590,29 @@ def flash_gated_attn_varlen_with_kvcache_func(
                    key_scale, value_scale, window_sizes, softmax_threshold, gate_threshold, is_logsigmoid_gate,
                    is_local, is_quant, num_splits, None, gather_kv_indices, seqused_k, out, lse, is_autotune,
                    tile_mn, skip_checks, return_lse)
+
+
+# ----------------------------------------------------------------------------------------------------
+# the reference's autograd Function names (interface.py:45, :163, :317, :439, :597, :745 there): callers that use
+# `FlashSparseAttnFunc.apply(q, k, v, is_causal, ...)` with the positional list of the matching *_func keep working
+# ----------------------------------------------------------------------------------------------------
+class _FunctionAlias:
+    """`apply(*positional)` forwards to the operator, which takes the same positional list and runs the one shared
+    autograd Function of this module."""
+
+    def __init__(self, name, fn):
+        self.__name__ = name
+        self._fn = fn
+
+    def apply(self, *args, **kwargs):
+        return self._fn(*args, **kwargs)
+
+    __call__ = apply
+
+
+FlashDenseAttnFunc = _FunctionAlias("FlashDenseAttnFunc", flash_dense_attn_func)
+FlashDenseAttnVarlenFunc = _FunctionAlias("FlashDenseAttnVarlenFunc", flash_dense_attn_varlen_func)
+FlashSparseAttnFunc = _FunctionAlias("FlashSparseAttnFunc", flash_sparse_attn_func)
+FlashSparseAttnVarlenFunc = _FunctionAlias("FlashSparseAttnVarlenFunc", flash_sparse_attn_varlen_func)
+FlashGatedAttnFunc = _FunctionAlias("FlashGatedAttnFunc", flash_gated_attn_func)
+FlashGatedAttnVarlenFunc = _FunctionAlias("FlashGatedAttnVarlenFunc", flash_gated_attn_varlen_func)

@@ -21,8 +21,19 @@ def decode_static_scratch(kind: str, query, key, value, out, lse, num_splits: in
                           softmax_threshold: float = 1.0, page_table=None, gather_kv_indices=None, seqused_k=None):
     """Split-KV decode of ``query [B, Hq, D]`` against ``key/value`` ([B, Sk, Hkv, D] or a paged cache with
     ``page_table``) into the caller's ``out [B, Hq, D]`` / ``lse [B, Hq]``. Raises RuntimeError when
-    ``num_splits * B * Hq * (D + 1)`` floats exceed the built-in workspace. The first call on a device must
-    happen outside stream capture; overlapping calls on one GPU must be ordered by the caller."""
+    ``num_splits * B * Hq * (D + 1)`` floats exceed the built-in workspace. The first call on a device loads the
+    workspace (16 MiB of device memory, an implicit synchronisation): make it at start-up, before a memory pool
+    takes the rest of the GPU and outside stream capture; later calls allocate nothing. Overlapping calls on one
+    GPU must be ordered by the caller."""
+    if value.stride() != key.stride() or value.shape != key.shape:
+        raise ValueError("value must have key's shape and strides (the C ABI passes one set of strides for both)")
+    want = torch.bfloat16 if query.dtype in (torch.float8_e4m3fn, torch.float8_e5m2) else query.dtype
+    if out.dtype != want or tuple(out.shape) != tuple(query.shape) or out.stride(-1) != 1:
+        raise ValueError(f"out must be a {want} tensor shaped like query with a contiguous last dimension")
+    if lse.dtype != torch.float32 or tuple(lse.shape) != tuple(query.shape[:2]):
+        raise ValueError("lse must be a float32 tensor of shape [batch, heads_q]")
+    if query.stride(-1) != 1 or key.stride(-1) != 1:
+        raise ValueError("query, key and value must be contiguous along head_dim")
     lib = _lib.load()
     lib.fsa_decode_static_scratch.restype = ctypes.c_int
     lib.fsa_decode_static_scratch.argtypes = [ctypes.POINTER(_lib.FsaDecArgs), ctypes.c_void_p]

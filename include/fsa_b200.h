@@ -4,8 +4,20 @@
  * Every entry point takes plain device pointers, sizes and element strides; it never allocates,
  * frees or keeps a pointer past its return, never synchronises the host with the device and launches
  * on the CUDA stream handed in (a cudaStream_t passed as void*), so a call sequence can be captured
- * into a CUDA graph by the caller. All workspaces are caller-owned. Return value: 0 on success, a
- * negative FSA_ERR_* code otherwise (fsa_status_string() names it); nothing throws or aborts.
+ * into a CUDA graph by the caller. All workspaces are caller-owned; the fsa_*_workspace_bytes functions
+ * say how large each has to be. The library keeps no per-call state: the only process-wide data are caches of
+ * per-device facts (multiprocessor count, which kernels were opted in to large shared memory, the driver entry
+ * point for tensor maps), all safe to race on. Return value: 0 on success, a negative FSA_ERR_* code otherwise
+ * (fsa_status_string() names it); nothing throws or aborts.
+ *
+ * Device-side trouble: every kernel wait is bounded; a kernel that gives up sets the caller's `status` word
+ * (non-zero) and drains. The word is STICKY: kernels launched while it is non-zero return at once without
+ * writing their outputs, so a caller must read it (after synchronising) before trusting results, and zero it to
+ * go on.
+ *
+ * ev_before / ev_after (optional, may be null): cudaEvent_t handles recorded on the launch stream right before
+ * and right after the call's MAIN kernel, so that a benchmark can time that kernel inside a full step without a
+ * profiler (the reference's benchmarks time whole operator calls, tests/benchmark_forward.py:114).
  *
  * Each function states which host launcher of the reference Python package it stands in for
  * (paths relative to the reference repository root).
@@ -20,7 +32,7 @@
 extern "C" {
 #endif
 
-#define FSA_ABI_VERSION 1
+#define FSA_ABI_VERSION 2
 
 enum {
   FSA_OK = 0,
@@ -28,7 +40,9 @@ enum {
   FSA_ERR_UNSUPPORTED = -2, /* valid request outside what the kernels implement */
   FSA_ERR_LAUNCH = -3,      /* CUDA reported an error at launch / descriptor creation */
   FSA_ERR_NO_DRIVER = -4,   /* cuTensorMapEncodeTiled could not be resolved (no CUDA driver) */
-  FSA_ERR_SCRATCH_TOO_SMALL = -5 /* fsa_decode_static_scratch: the partials exceed the built-in workspace */
+  FSA_ERR_SCRATCH_TOO_SMALL = -5, /* fsa_decode_static_scratch: the partials exceed the built-in workspace */
+  FSA_ERR_SCRATCH_UNAVAILABLE = -6 /* fsa_decode_static_scratch: the built-in workspace could not be set up on this
+                                      device (its first use loads it; a device with no free memory refuses) */
 };
 
 enum { FSA_KIND_DENSE = 0, FSA_KIND_SPARSE = 1, FSA_KIND_GATED = 2 };
@@ -72,9 +86,6 @@ typedef struct FsaFwdArgs {
   float* lse_partial;
   const void* alpha; /* gated: [batch, heads_q, seqlen_q] (or [heads_q, total_q]), dtype of q */
   const void* delta; /* gated: [batch, heads_kv, seqlen_k] (or [heads_kv, total_k]) */
-  const float* q_descale; /* FP8 inputs: device scalars (x = x_fp8 * descale); null otherwise */
-  const float* k_descale;
-  const float* v_descale;
   const int32_t* cu_seqlens_q; /* [batch + 1] */
   const int32_t* cu_seqlens_k;
   const int32_t* seqused_q; /* [batch] */
@@ -104,6 +115,12 @@ typedef struct FsaFwdArgs {
    * With dtype FSA_DT_E4M3 / FSA_DT_E5M2 (head_dim 128) q, k, v are FP8, both GEMMs run as
    * tcgen05 kind::f8f6f4 with P rounded to the same FP8 format, out / alpha / delta are bf16. */
   const float* qkv_scale;
+  /* gated kind: workspace of fsa_fwd_workspace_bytes().gate_ws bytes (written by this call): per-tile extremes
+   * of alpha and delta, from which every role of the kernel derives the gate-skip decisions before a key tile
+   * is loaded. */
+  float* gate_ws;
+  void* ev_before;
+  void* ev_after;
 } FsaFwdArgs;
 
 int fsa_fwd(const FsaFwdArgs* args, void* stream);
@@ -188,6 +205,8 @@ typedef struct FsaBwdArgs {
    * the key tiles above it before its reduce-add into a query tile; results are bitwise reproducible. */
   uint16_t* dq_order;
   int32_t* dq_turn;
+  void* ev_before;
+  void* ev_after;
 } FsaBwdArgs;
 
 int fsa_bwd(const FsaBwdArgs* args, void* stream);
@@ -246,6 +265,21 @@ typedef struct FsaDecArgs {
   uint32_t flags;
   float softmax_scale, softmax_threshold, gate_threshold;
   const float* qkv_scale; /* optional, as in FsaFwdArgs */
+  /* Decoding one shard of a longer key sequence (KV-sequence context parallelism); all optional.
+   *   thr_seqlen_k [batch]: key count that normalises the softmax threshold (threshold / count,
+   *     seqlen_info.py:141-149) and the default gate threshold; null = the count this call sees. A shard passes
+   *     the length of the whole sequence so that its skip decisions use the same bound as an unsharded call.
+   *   key_lo, key_hi: with gather_kv_indices, positions outside [key_lo, key_hi) are treated as masked (-1) and
+   *     the others address the cache at position - key_lo; key_hi = 0 switches this off. */
+  const int32_t* thr_seqlen_k;
+  int32_t key_lo, key_hi;
+  /* Elements between the partials of consecutive splits in out_partial / lse_partial; 0 = dense
+   * (batch*heads_q*head_dim and heads_q*batch). A caller that wants partial outputs and log-sum-exps of one
+   * split side by side in ONE buffer (to ship them with a single all-gather) sets both to
+   * batch*heads_q*(head_dim + 1) and points lse_partial at out_partial + batch*heads_q*head_dim. */
+  int64_t out_partial_stride, lse_partial_stride;
+  void* ev_before;
+  void* ev_after;
 } FsaDecArgs;
 
 int fsa_decode(const FsaDecArgs* args, void* stream);
@@ -257,9 +291,11 @@ int fsa_decode(const FsaDecArgs* args, void* stream);
  * context parallelism) can be merged with the same arithmetic.
  *   out_partial [num_partials, rows, heads, head_dim] fp32, lse_partial [num_partials, heads, rows] fp32
  *   out [rows, heads, head_dim] (contiguous, dtype), lse [rows, heads] fp32 natural log
+ *   out_partial_stride / lse_partial_stride: elements between consecutive partials, 0 = dense (see FsaDecArgs)
  */
 int fsa_combine(const float* out_partial, const float* lse_partial, void* out, float* lse, int num_partials,
-                int rows, int heads, int head_dim, int dtype, void* stream);
+                int rows, int heads, int head_dim, int dtype, int64_t out_partial_stride,
+                int64_t lse_partial_stride, void* stream);
 
 /*
  * Split-KV decode without any caller-provided (or freshly allocated) workspace. This entry point has
@@ -267,7 +303,7 @@ int fsa_combine(const float* out_partial, const float* lse_partial, void* out, f
  * every call (flash_sparse_attn/ops/triton/flash_sparse_dec.py:637-646).
  *
  * It is fsa_decode with the split workspace taken from a fixed array of FSA_STATIC_SCRATCH_BYTES that
- * is part of the library image on every GPU: meant for callers that cannot obtain device memory at
+ * is part of the library image: meant for callers that cannot obtain device memory at
  * call time (all memory already owned by a serving pool, a frozen memory plan, no tolerance for the
  * implicit synchronisation of cudaMalloc / cudaFree). args->out_partial / lse_partial are ignored and
  * partial_only must be 0; everything else means what it means for fsa_decode.
@@ -276,9 +312,13 @@ int fsa_combine(const float* out_partial, const float* lse_partial, void* out, f
  *   - The array is shared by all calls and keeps the previous call's contents; the kernels overwrite
  *     every slot they later read, so nothing has to be cleared. Calls that may run concurrently on
  *     one GPU race on it: order them.
- *   - The first call on each device resolves the array's address with cudaGetSymbolAddress; make that
- *     first call before starting any stream capture.
- * It calls no cudaMalloc, cudaFree or other allocating routine.
+ *   - The first call on each device resolves the array's address with cudaGetSymbolAddress. Under CUDA's lazy
+ *     module loading that look-up is also what makes the array resident on the device: it takes the 16 MiB
+ *     from the device's free memory and synchronises implicitly (FSA_ERR_SCRATCH_UNAVAILABLE if the device
+ *     cannot provide them). Make that first call at start-up, before a memory pool claims the rest of the GPU
+ *     and before starting any stream capture. From then on a GPU holds the array until the process exits.
+ * It calls no cudaMalloc, cudaFree or other allocating routine; after the first call per device it changes
+ * neither the device's free memory nor the host-device synchronisation state.
  */
 #define FSA_STATIC_SCRATCH_BYTES (16u * 1024u * 1024u)
 int fsa_decode_static_scratch(const FsaDecArgs* args, void* stream);
@@ -300,13 +340,28 @@ void fsa_debug_bwd_schedule(int seqlen_q, int seqlen_k, int n_block, int split_i
                             int num_splits, int tile_n, int tile_m, int is_causal, int is_local, int is_split,
                             int32_t out9[9]);
 
-/* Measurement hook (process-wide host state, no device work of its own): the next
- * fsa_fwd / fsa_bwd / fsa_decode calls record CUDA event `before` right before and
- * `after` right after their MAIN kernel on the launch stream (cudaEvent_t handles passed as void*).
- * Null, null switches the hook off. No counterpart in the reference (its benchmarks time whole
- * operator calls, tests/benchmark_forward.py:114); it exists so that a benchmark can time one
- * kernel inside a full step without a profiler. */
-void fsa_set_profile_events(void* before, void* after);
+/*
+ * Sizes in bytes of the caller-owned workspaces of one call (0 = not needed), from the dimensions, kind, dtype,
+ * flags and num_splits of the argument block; pointers in it are not read. The reference's launchers derive the
+ * same sizes inline (flash_sparse_fwd.py:637-660, flash_sparse_bwd.py:610-668, flash_sparse_dec.py:637-646).
+ * Host arithmetic only.
+ */
+typedef struct FsaFwdWorkspace {
+  size_t out_partial, lse_partial; /* split-KV partials */
+  size_t gate_ws;                  /* gated kind */
+} FsaFwdWorkspace;
+typedef struct FsaBwdWorkspace {
+  size_t lse2_ws, dpsum_ws, dq_accum;
+  size_t dk_partial, dv_partial; /* split-QO */
+  size_t alpha_ws, da_accum, dd_partial; /* gated kind */
+  size_t dq_order, dq_turn;      /* FSA_F_DETERMINISTIC */
+} FsaBwdWorkspace;
+typedef struct FsaDecWorkspace {
+  size_t out_partial, lse_partial;
+} FsaDecWorkspace;
+int fsa_fwd_workspace_bytes(const FsaFwdArgs* args, FsaFwdWorkspace* sizes);
+int fsa_bwd_workspace_bytes(const FsaBwdArgs* args, FsaBwdWorkspace* sizes);
+int fsa_decode_workspace_bytes(const FsaDecArgs* args, FsaDecWorkspace* sizes);
 
 const char* fsa_status_string(int code);
 /*

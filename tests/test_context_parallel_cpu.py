@@ -13,17 +13,33 @@ import torch.multiprocessing as mp
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _oracle_partial(q, k, v, idx, scale):
-    """One KV split of the decode: normalised partial output and base-2 log-sum-exp (flash_sparse_dec.py:485-489)."""
-    from oracle import eager
+def _oracle_partial(q, k, v, idx, scale, threshold=None, sk_global=None):
+    """One KV split of the decode in the wire format: normalised partial output and base-2 log-sum-exp
+    (flash_sparse_dec.py:485-489). With a threshold the shard runs the tile-faithful decode, its skip bound
+    normalised by the length of the whole sequence."""
+    from flash_sparse_attn.ops.triton import context_parallel as cp
+    from oracle import eager, tiled
 
-    out, lse = eager.gather_decode(q, k, v, idx, scale, return_lse=True)
+    if threshold is None:
+        out, lse = eager.gather_decode(q, k, v, idx, scale, return_lse=True)
+    else:
+        out, lse, _ = tiled.decode_tiled(q, k, v, scale, softmax_threshold=threshold, gather_kv_indices=idx,
+                                         threshold_seqlen_k=torch.full((q.shape[0],), sk_global))
     lse2 = lse * 1.4426950408889634
-    return out.float().unsqueeze(0), lse2.t().contiguous().unsqueeze(0)  # [1,B,Hq,D], [1,Hq,B]
+    return cp.pack_partials(out.float().unsqueeze(0), lse2.t().contiguous().unsqueeze(0))  # [1, B*Hq*(D+1)]
 
 
-def _oracle_combine(out_p, lse_p):
+def _oracle_combine(shape):
     """flash_dec_combine.py:15-153 in torch: weights exp2(lse - max), -inf partials contribute 0."""
+    from flash_sparse_attn.ops.triton import context_parallel as cp
+
+    def combine(packed, parts):
+        return _merge(*cp.unpack_partials(packed, parts, *shape))
+
+    return combine
+
+
+def _merge(out_p, lse_p):
     m = lse_p.max(dim=0).values
     w = torch.where(torch.isinf(lse_p) & (lse_p < 0), torch.zeros_like(lse_p), torch.exp2(lse_p - m))
     s = w.sum(dim=0)
@@ -56,9 +72,17 @@ def _worker(rank, world, port, ret):
     assert torch.equal(kept, (idx >= 0).to(torch.int32))
     assert torch.equal(local[local >= 0] + lo, idx[(idx >= lo) & (idx < hi)])
     out, lse = cp.context_parallel_decode(
-        lambda **kw: _oracle_partial(q, k[:, lo:hi], v[:, lo:hi], local, scale), _oracle_combine)
+        lambda: _oracle_partial(q, k[:, lo:hi], v[:, lo:hi], local, scale), _oracle_combine((b, hq, d)))
     ref, ref_lse = eager.gather_decode(q, k, v, idx, scale, return_lse=True)
     ok = torch.allclose(out, ref.float(), atol=1e-2) and torch.allclose(lse, ref_lse, atol=1e-4)
+    # with the softmax threshold on: peaked queries so that tiles are skipped; every shard normalises the
+    # threshold by the whole length, and the merged result stays within tolerance of the exact one
+    qp = (k[:, -1].repeat_interleave(hq // hkv, dim=1).float() * 3).to(torch.bfloat16)
+    out_t, _ = cp.context_parallel_decode(
+        lambda: _oracle_partial(qp, k[:, lo:hi], v[:, lo:hi], local, scale, threshold=1.0, sk_global=sk),
+        _oracle_combine((b, hq, d)))
+    ref_t = eager.gather_decode(qp, k, v, idx, scale)
+    ok = ok and torch.allclose(out_t, ref_t.float(), atol=2e-2, rtol=2e-2)
     ret[rank] = bool(ok)
     dist.destroy_process_group()
 

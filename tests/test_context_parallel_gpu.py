@@ -42,10 +42,23 @@ def _worker(rank, world, port, ret):
     out2, _ = cp.flash_sparse_attn_with_kvcache_cp(q, k[:, lo:hi].contiguous(), v[:, lo:hi].contiguous(), lo, hi,
                                                    kind="dense", num_splits=1)
     ref2, _ = attn_decode("dense", q, k, v, num_splits=1)
+    # threshold on, peaked queries (tiles are skipped): every shard normalises the threshold by the whole length
+    qp = (k[:, -1].repeat_interleave(hq // hkv, dim=1).float() * 3).to(torch.bfloat16)
+    used = torch.full((b,), sk, dtype=torch.int32, device=dev)
+    out3, _ = cp.flash_sparse_attn_with_kvcache_cp(qp, k[:, lo:hi].contiguous(), v[:, lo:hi].contiguous(), lo, hi,
+                                                   gather_kv_indices=idx, softmax_threshold=1.0, num_splits=1,
+                                                   seqused_k_global=used)
+    ref3, _ = attn_decode("sparse", qp, k, v, gather_kv_indices=idx, softmax_threshold=-128.0, num_splits=1)
+    used_local = torch.full((b,), hi - lo, dtype=torch.int32, device=dev)
+    out4, _ = cp.flash_sparse_attn_with_kvcache_cp(qp, k[:, lo:hi].contiguous(), v[:, lo:hi].contiguous(), lo, hi,
+                                                   softmax_threshold=1.0, num_splits=1, seqused_k_global=used,
+                                                   seqused_k_local=used_local)
+    ref4, _ = attn_decode("sparse", qp, k, v, softmax_threshold=-128.0, num_splits=1)
     torch.cuda.synchronize()
     fsa.check_status()
+    close = lambda a, r: bool(((a.float() - r.float()).abs() <= 2e-2 + 2e-2 * r.float().abs()).all())  # noqa: E731
     ok = ((out.float() - ref.float()).abs().max().item() < 1e-2 and (lse - ref_lse).abs().max().item() < 1e-3
-          and (out2.float() - ref2.float()).abs().max().item() < 1e-2)
+          and (out2.float() - ref2.float()).abs().max().item() < 1e-2 and close(out3, ref3) and close(out4, ref4))
     ret[rank] = bool(ok)
     dist.destroy_process_group()
 

@@ -173,3 +173,40 @@ def test_decode_skip_map():
     assert (tmap == 2).sum().item() > 0 and (tmap != 0).all()
     ref = eager.decode(q, k, v)
     assert_close("skip", out, ref, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("mode", ["gather", "full"])
+@pytest.mark.parametrize("splits", [1, 2])
+def test_sharded_decode_pieces_on_one_gpu(mode, splits):
+    """The per-rank pieces of context-parallel decode, run one after the other on a single GPU: every 'rank' decodes
+    its key range into the wire format (global top-k positions localised inside the kernel via key_range, threshold
+    normalised by the whole length), the blocks are concatenated as an all-gather would, one combine merges them."""
+    from flash_sparse_attn.ops.triton import context_parallel as cp
+    from flash_sparse_attn.ops.triton.flash_dec import attn_decode, combine_packed_partials
+
+    g = torch.Generator().manual_seed(21)
+    b, sk, hq, hkv, d, topk, world = 3, 2300, 16, 2, 128, 384, 3
+    q = torch.randn(b, hq, d, generator=g).to(torch.bfloat16).to(DEV)
+    k = torch.randn(b, sk, hkv, d, generator=g).to(torch.bfloat16).to(DEV)
+    v = torch.randn(b, sk, hkv, d, generator=g).to(torch.bfloat16).to(DEV)
+    idx = torch.stack([torch.randperm(sk, generator=g)[:topk] for _ in range(b)]).to(torch.int32).to(DEV)
+    idx[:, 7::23] = -1
+    used = torch.full((b,), sk, dtype=torch.int32, device=DEV)
+    per = b * hq * (d + 1)
+    recv = torch.empty(world * splits, per, dtype=torch.float32, device=DEV)
+    for r in range(world):
+        lo, hi = cp.shard_bounds(sk, world, r)
+        send = recv[r * splits:(r + 1) * splits]
+        kl, vl = k[:, lo:hi].contiguous(), v[:, lo:hi].contiguous()
+        if mode == "gather":
+            attn_decode("sparse", q, kl, vl, partial_only=True, num_splits=splits, packed_partials=send,
+                        gather_kv_indices=idx, key_range=(lo, hi), seqused_k=used, softmax_threshold=-128.0)
+        else:
+            attn_decode("sparse", q, kl, vl, partial_only=True, num_splits=splits, packed_partials=send,
+                        threshold_seqlen_k=used, softmax_threshold=-128.0)
+    out, lse = combine_packed_partials(recv, world * splits, b, hq, d, torch.bfloat16)
+    kw = dict(gather_kv_indices=idx) if mode == "gather" else {}
+    ref, ref_lse = attn_decode("sparse", q, k, v, softmax_threshold=-128.0, num_splits=1, **kw)
+    _sync()
+    assert_close(f"sharded-{mode}", out, ref)
+    assert torch.allclose(lse, ref_lse, rtol=0, atol=2e-3)

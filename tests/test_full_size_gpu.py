@@ -1,4 +1,4 @@
-"""The gated, packed + quantised and paged top-k decode configurations of BASELINE.json at their FULL sizes:
+"""The gated, packed + quantised and paged top-k decode benchmark configurations at their FULL sizes:
 size-independent properties (run-to-run equality, rows summing to one, linearity in V, the prefix property of a
 causal mask) plus slices small enough for the eager oracle. Synthetic seeded inputs with the configurations'
 shapes; tile skipping is switched off (threshold -128) where a slice is compared with the oracle, whose softmax

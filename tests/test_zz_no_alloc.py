@@ -34,9 +34,14 @@ def test_static_scratch_decode_matches_regular_entry_point_twice():
         ref_out, ref_lse = attn_decode("sparse", q, k, v, softmax_threshold=1.0, num_splits=ns)
         out = torch.empty_like(q)
         lse = torch.empty(b, hq, dtype=torch.float32, device=DEV)
+        torch.cuda.synchronize()
+        free_before, torch_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
         static_scratch.decode_static_scratch("sparse", q, k, v, out, lse, num_splits=ns, softmax_threshold=1.0)
         torch.cuda.synchronize()
         fsa.check_status()
+        if call > 0:  # the first call on a device may load the workspace; later ones take no memory at all
+            assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the device's free memory"
+            assert torch.cuda.memory_allocated() == torch_before, "the call allocated through torch"
         # same kernels, same split count, same arithmetic: bit-identical
         assert torch.equal(out, ref_out), f"call {call}: outputs differ"
         assert torch.equal(lse, ref_lse), f"call {call}: lse differs"
