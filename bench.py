@@ -1,35 +1,52 @@
-"""Headline benchmark: forward + backward of the sparse attention operator on the reference's
-window configuration, reported as effective TFLOP/s.
+"""Benchmark of the attention hot path: one JSON line.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-cpu] [--no-extra]
 
-Workload (N = 1): batch 2, seqlen 4096, 32 query / 8 KV heads, head_dim 128, bf16, causal with a
-1024-token left window on every head (window_sizes = [[0, 1024, 0, 0]] * 8), softmax_threshold 1.0,
-is_split_kv = is_split_qo = True. Q/K/V/dO are iid N(0, 1) from a fixed seed (synthetic). One step =
-one forward and one backward through the public operator (``flash_sparse_attn_func`` + autograd).
-With N > 1 every rank runs its own copy of that batch (independent (batch, head) slices, no
-collective in the data path): weak scaling, value = sum over ranks / max time over ranks.
+Headline (metric / value / e2e / roofline): forward + backward of the sparse attention operator on the window
+configuration - batch 2, seqlen 4096, 32 query / 8 KV heads, head_dim 128, bf16, causal with a 1024-token left
+window on every head (window_sizes = [[0, 1024, 0, 0]] * 8), softmax_threshold 1.0, is_split_kv = is_split_qo =
+True - as effective TFLOP/s. Q/K/V/dO are iid N(0, 1) from a fixed seed (synthetic). One step = one forward and
+one backward through the public operator (``flash_sparse_attn_func`` + autograd). With N > 1 every rank runs its
+own copy of that batch (independent (batch, head) slices, no collective in the data path): weak scaling, value =
+sum over ranks / max time over ranks.
 
-metric  fwd_bwd_effective_tflops = dense-causal-equivalent FLOPs of the step (4*D*B*Hq*S(S+1)/2 for the
-        forward, 2.5x that for the backward) / device time of the step.
-e2e     the same with HOST buffers: pinned Q/K/V/dO copied in, out/dQ/dK/dV copied back, every step.
-roofline the backward main kernel (the dominant one): executed FLOPs at 128x128 tile granularity /
-        its CUDA-event duration inside the timed steps, against the measured dense bf16 peak.
-cpu_baseline  the CPU oracle (eager fp32 forward + autograd backward) on a bounded number of
-        (batch, head) slices of the same workload, scaled to the same metric.
+metric   fwd_bwd_effective_tflops = dense-causal-equivalent FLOPs of the step (4*D*B*Hq*S(S+1)/2 for the forward,
+         2.5x that for the backward) / device time of the step; `executed_tflops` beside it counts only the FLOPs of
+         the 128x128 tiles the kernels really compute.
+e2e      the same with HOST buffers: pinned Q/K/V/dO copied in, out/dQ/dK/dV copied back, every step.
+roofline the backward main kernel (the dominant one): executed FLOPs / its CUDA-event duration inside the timed
+         steps, against the measured burst bf16 peak (the timed region lasts tens of milliseconds at full clocks);
+         the fraction of the nominal 2250 TFLOP/s is given as well.
+cpu_baseline  the CPU oracle (a port: eager fp32 forward + autograd backward) on a bounded number of (batch, head)
+         slices of the same workload, scaled to the same metric.
 
-``--impl reference`` prints the CPU arm alone on the same metric / config.
+Further device-timed measurements in the same line (N = 1 only unless noted):
+long_context  sparse causal forward and backward at S = 16384 (B1, Hq32 / Hkv8, D128, threshold 1.0) on iid and on
+         llm-like inputs: kernel times, executed and effective TFLOP/s, fractions of the measured and nominal peak.
+decode   paged top-k decode (B64, contexts 4K-128K, Hq64 / Hkv8, D128, 256-token pages, top-k 2048) under CUDA-graph
+         replay: microseconds per step, algorithmic GB/s, fraction of the measured copy bandwidth.
+decode_cp  (every N) the same decode with every sequence's KV cut into N page-aligned shards, one per rank: decode
+         kernel -> ONE all-gather of the packed partials -> combine kernel; microseconds per step and the share of
+         the exchange.
+context  other implementations on the same GPU, same tensors: the upstream Triton back end (when its package is
+         present under baseline/_ref) and PyTorch SDPA.
+
+``--impl reference`` prints the CPU arm alone (the CPU oracle port) on the same metric / config.
 """
 
 import argparse
+import importlib.util
 import json
 import os
+import subprocess
 import sys
+import tempfile
 import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
-for p in (os.path.join(ROOT, "flash-sparse-attention_b200"), ROOT):
+PKG = os.path.join(ROOT, "flash-sparse-attention_b200")
+for p in (PKG, ROOT):
     if p not in sys.path:
         sys.path.insert(0, p)
 
@@ -40,11 +57,22 @@ WINDOW = 1024
 THRESHOLD = 1.0
 METRIC = "fwd_bwd_effective_tflops"
 UNIT = "TFLOP/s"
+NOMINAL_BF16_TFLOPS = 2250.0
+NOMINAL_HBM_GBS = 8000.0
+# DRAM bytes per launch of the backward main kernel on this workload: a constant copied from the ncu capture that
+# profiles/bwd_kernel_c2.txt summarises (dram__bytes_read.sum + dram__bytes_write.sum); NOT measured by this run
+TRAFFIC_BWD_KERNEL_C2 = 444.6e6
 
 
-def effective_flops(batch=B, heads=HQ):
-    fwd = 4.0 * D * batch * heads * S * (S + 1) / 2
-    return 3.5 * fwd
+def workloads():
+    spec = importlib.util.spec_from_file_location("fsa_workloads", os.path.join(PKG, "benchmarks", "workloads.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def effective_flops(batch=B, heads=HQ, s=S):
+    return 3.5 * 4.0 * D * batch * heads * s * (s + 1) / 2
 
 
 def executed_pairs_tile_granular():
@@ -59,9 +87,19 @@ def config_dict(n_gpus):
         "workload": "C2 sparse causal local-window attention fwd+bwd",
         "batch_per_gpu": B, "seqlen": S, "heads_q": HQ, "heads_kv": HKV, "head_dim": D,
         "window_sizes": [0, WINDOW, 0, 0], "softmax_threshold": THRESHOLD, "is_split_kv": True,
-        "is_split_qo": True, "global_batch": B * n_gpus, "parallelism": f"dp{n_gpus} (independent batch slices)",
+        "is_split_qo": True,
+        "num_splits_used": "1 (the operator keeps one split when batch x heads x tiles already gives every SM two "
+                           "CTAs; the reference's heuristic would pick 4)",
+        "global_batch": B * n_gpus, "parallelism": f"dp{n_gpus} (independent batch slices)",
         "l2": "inputs (168 MB) and working set (>450 MB) exceed the 126 MB L2; no flush needed",
     }
+
+
+def peaks():
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        return {}
 
 
 # --------------------------------------------------------------------------------------------------
@@ -91,6 +129,7 @@ def cpu_baseline(budget_s=20.0):
     per_slice = sorted(times)[len(times) // 2]
     value = effective_flops(1, 1) / per_slice / 1e12
     return {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+            "what": "CPU oracle: a port of the reference tests' eager fp32 attention (not the reference's Triton code)",
             "sample": f"{len(times)} (batch, head) slices of the same workload (S={S}, D={D}, window {WINDOW}), "
                       f"eager fp32 forward + autograd backward; median {per_slice:.2f} s per slice"}
 
@@ -119,6 +158,8 @@ def run_reference(args):
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic", "config": config_dict(args.gpus),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "what": "CPU oracle: a port of the reference tests' eager fp32 attention (the reference's "
+                                 "own implementation of this path is Triton GPU code and has no CPU form)",
                          "sample": f"each step = {slices} (batch, head) slice(s) of the workload through the CPU "
                                    "oracle (eager fp32 forward + autograd backward)"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -180,20 +221,224 @@ class ClockSampler(threading.Thread):
 
 
 # --------------------------------------------------------------------------------------------------
+# device-timed extras
+# --------------------------------------------------------------------------------------------------
+def time_events(fn, reps, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def tflops_block(flops_exec, flops_eff, ms, pk):
+    burst = pk.get("bf16_tflops") or 1590.0
+    ach = flops_exec / (ms / 1e3) / 1e12
+    return {"ms": ms, "executed_tflops": ach, "effective_tflops": flops_eff / (ms / 1e3) / 1e12,
+            "frac_of_measured_burst": ach / burst, "frac_of_nominal": ach / NOMINAL_BF16_TFLOPS,
+            "effective_frac_of_nominal": flops_eff / (ms / 1e3) / 1e12 / NOMINAL_BF16_TFLOPS}
+
+
+def long_context(pk, reps):
+    """S = 16384 sparse causal forward / backward, iid and llm-like inputs: main-kernel times through the per-call
+    event hook, executed FLOPs from the kernels' own tile maps (tiles really computed)."""
+    import flash_sparse_attn as fsa
+    from flash_sparse_attn import _lib
+    from flash_sparse_attn.ops.triton import flash_bwd, flash_fwd
+
+    wl = workloads()
+    res = {"config": "B1 S16384 Hq32 Hkv8 D128 causal, softmax_threshold 1.0, bf16; inputs 336 MB > L2",
+           "peak_measured_burst_tflops": pk.get("bf16_tflops"), "peak_nominal_tflops": NOMINAL_BF16_TFLOPS}
+    s = 16384
+    eff_fwd = wl.causal_flops(1, HQ, s, D)
+    for data in ("iid", "llm"):
+        w = wl.s16k("cuda", data=data)
+        q, k, v, do, kw = w["q"], w["k"], w["v"], w["dout"], w["kwargs"]
+        # tiles computed (untimed): forward map [1, Hq, m, 1, n], backward map [1, Hq, n, 1, m]
+        tm_f = torch.zeros(flash_fwd.tile_map_numel(1, s, s, HQ, HKV), dtype=torch.uint8, device="cuda")
+        out, lse, *_ = flash_fwd.attn_forward("sparse", q, k, v, is_causal=True, softmax_threshold=THRESHOLD, tile_map=tm_f)
+        tm_b = torch.zeros(flash_bwd.tile_map_numel(1, s, s, HQ), dtype=torch.uint8, device="cuda")
+        flash_bwd.attn_backward("sparse", q, k, v, out, do, lse, is_causal=True, softmax_threshold=THRESHOLD, tile_map=tm_b)
+        torch.cuda.synchronize()
+        n_f, v_f = int((tm_f == 1).sum()), int((tm_f != 0).sum())
+        n_b, v_b = int((tm_b == 1).sum()), int((tm_b != 0).sum())
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        for e in ev:
+            e.record()
+        qg, kg, vg = (t.detach().requires_grad_(True) for t in (q, k, v))
+        f_ms, b_ms = [], []
+        for i in range(reps + 2):
+            qg.grad = kg.grad = vg.grad = None
+            _lib.set_profile_events(ev[0], ev[1])
+            o = fsa.flash_sparse_attn_func(qg, kg, vg, **kw)
+            _lib.set_profile_events(ev[2], ev[3])
+            o.backward(do)
+            _lib.set_profile_events(None, None)
+            torch.cuda.synchronize()
+            if i >= 2:
+                f_ms.append(ev[0].elapsed_time(ev[1]))
+                b_ms.append(ev[2].elapsed_time(ev[3]))
+        fsa.check_status()
+        f, b = sum(f_ms) / len(f_ms), sum(b_ms) / len(b_ms)
+        res[data] = {
+            "fwd_kernel": dict(tflops_block(4.0 * D * n_f * 128 * 128, eff_fwd, f, pk), tiles_computed=n_f, tiles_visited=v_f),
+            "bwd_kernel": dict(tflops_block(10.0 * D * n_b * 128 * 128, 2.5 * eff_fwd, b, pk), tiles_computed=n_b,
+                               tiles_visited=v_b),
+        }
+        del w, q, k, v, do, out, lse, qg, kg, vg, o
+        torch.cuda.empty_cache()
+    return res
+
+
+def graph_time_us(fn, iters):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    return time_events(graph.replay, iters) * 1e3
+
+
+def decode_c5(pk, iters):
+    import flash_sparse_attn as fsa
+
+    wl = workloads()
+    w = wl.c5("cuda", paged=True)
+    fn = lambda: fsa.flash_sparse_attn_with_kvcache_func(w["q"], w["k"], w["v"], softmax_threshold=THRESHOLD, **w["kwargs"])  # noqa: E731
+    us = graph_time_us(fn, iters)
+    fsa.check_status()
+    gbs = w["bytes"] / us / 1e3
+    hbm = pk.get("hbm_gbs") or 6650.0
+    res = {"config": "paged top-k decode B64 ctx 4096-131072 Hq64 Hkv8 D128 page 256 top-k 2048, bf16, CUDA-graph replay; "
+                     f"cache {w['k'].numel() * 4 / 1e9:.1f} GB, gathered rows scattered over it (no L2 reuse between steps)",
+           "us_per_step": us, "algorithmic_mb": w["bytes"] / 1e6, "achieved_gbs": gbs,
+           "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm,
+                        "frac_of_nominal": gbs / NOMINAL_HBM_GBS, "traffic": None,
+                        "peak_source": "measured copy bandwidth (MEASURED_PEAKS.json)" if pk else "fallback"}}
+    del w
+    torch.cuda.empty_cache()
+    return res
+
+
+def decode_cp(rank, world, dev, iters):
+    """Context-parallel top-k decode: every sequence's keys cut into `world` page-aligned parts; this rank holds
+    part `rank` as a contiguous local cache [B, S_local, Hkv, D] (synthetic values). Global top-k positions go to the
+    kernel as they are, with the per-sequence bounds."""
+    import torch.distributed as dist
+
+    import flash_sparse_attn as fsa
+    from flash_sparse_attn.ops.triton import context_parallel as cp
+
+    wl = workloads()
+    hq, hkv, d, page, topk, batch = 64, 8, 128, 256, 2048, 64
+    ctx, _, _, idx = wl.c5_indices(0, batch)
+    per = ((ctx + world - 1) // world + page - 1) // page * page
+    lo = torch.minimum(per * rank, ctx)
+    hi = torch.minimum(lo + per, ctx)
+    bounds = torch.stack([lo, hi], dim=1).to(torch.int32).to(dev)
+    s_loc = int(per.max())
+    g = torch.Generator(device=dev).manual_seed(77 + rank)
+    k = torch.randn(batch, s_loc, hkv, d, generator=g, device=dev, dtype=torch.bfloat16)
+    v = torch.randn(batch, s_loc, hkv, d, generator=g, device=dev, dtype=torch.bfloat16)
+    q = torch.randn(batch, hq, d, generator=torch.Generator(device=dev).manual_seed(5), device=dev, dtype=torch.bfloat16)
+    idx_d, used = idx.to(dev), ctx.to(torch.int32).to(dev)
+    dec = cp.ContextParallelDecoder(batch, hq, d, torch.bfloat16, dev, num_splits=1)
+
+    def local():
+        dec.partial(q, k, v, bounds, None, gather_kv_indices=idx_d, seqused_k_global=used, softmax_threshold=THRESHOLD)
+        dec.combine(dec.send)
+
+    def step():
+        dec.partial(q, k, v, bounds, None, gather_kv_indices=idx_d, seqused_k_global=used, softmax_threshold=THRESHOLD)
+        dec.combine(dec.exchange())
+
+    mode = "cuda-graph replay"
+    try:
+        t_local = graph_time_us(local, iters)
+        t_full = graph_time_us(step, iters) if world > 1 else t_local
+    except Exception as e:  # noqa: BLE001  (a collective that cannot be captured: time eager launches instead)
+        mode = f"eager launches ({type(e).__name__} during graph capture)"
+        torch.cuda.synchronize()
+        t_local = time_events(local, iters) * 1e3
+        t_full = time_events(step, iters) * 1e3 if world > 1 else t_local
+    fsa.check_status()
+    t = torch.tensor([t_full, t_local], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    t_full, t_local = t.tolist()
+    nbytes = batch * hkv * topk * d * 2 * 2 + batch * topk * 4 + 2 * batch * hq * d * 2
+    res = {"config": f"top-k decode B64 ctx 4096-131072 Hq64 Hkv8 D128 top-k 2048, KV of every sequence cut into {world} "
+                     "page-aligned shards (one per rank), one all-gather of packed (O, lse) partials, combine",
+           "timing": mode, "us_per_step": t_full, "us_decode_plus_combine": t_local,
+           "exchange_share": max(0.0, (t_full - t_local) / t_full) if world > 1 else 0.0,
+           "allgather_bytes_per_rank": batch * hq * (d + 1) * 4,
+           "algorithmic_mb_all_ranks": nbytes / 1e6, "aggregate_gbs": nbytes / t_full / 1e3}
+    del k, v
+    torch.cuda.empty_cache()
+    return res
+
+
+def upstream_triton(cases=("c2", "s16k")):
+    """Timings of the upstream Triton back end on the same GPU and tensors (child process; the package is looked up
+    under baseline/_ref or FSA_REFERENCE_DIR). is_autotune=False: its default 64x64 tiles and the 128x128 tiles used
+    here."""
+    ref_dir = os.environ.get("FSA_REFERENCE_DIR", os.path.join(ROOT, "baseline", "_ref"))
+    if not os.path.isdir(os.path.join(ref_dir, "flash_sparse_attn")):
+        return {"unavailable": f"upstream package not found under {ref_dir}"}
+    res = {"what": "upstream flash_sparse_attn Triton kernels, is_autotune=False, same seeded tensors; ms per call"}
+    env = {k: v for k, v in os.environ.items() if k not in ("PYTHONPATH", "RANK", "WORLD_SIZE", "LOCAL_RANK")}
+    for case in cases:
+        for tile in (64, 128):
+            out = os.path.join(tempfile.mkdtemp(prefix="fsa_ref_"), f"{case}.pt")
+            cmd = [sys.executable, os.path.join(ROOT, "tests", "ref_triton_runner.py"), "--ref-dir", ref_dir, "--case", case,
+                   "--out", out, "--reps", "3", "--tile", str(tile)]
+            try:
+                subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
+                rec = torch.load(out)
+                res[f"{case}_tile{tile}"] = rec["ms"] if not rec["error"] else {"error": rec["error"][-200:]}
+            except Exception as e:  # noqa: BLE001
+                res[f"{case}_tile{tile}"] = {"error": repr(e)[:200]}
+    return res
+
+
+def sdpa_context(reps):
+    """PyTorch scaled_dot_product_attention (library kernels) on the dense causal S = 16384 shape."""
+    import torch.nn.functional as F
+
+    wl = workloads()
+    w = wl.s16k("cuda")
+    g = HQ // HKV
+    q = w["q"].transpose(1, 2).contiguous()
+    k = w["k"].transpose(1, 2).repeat_interleave(g, dim=1).contiguous()
+    v = w["v"].transpose(1, 2).repeat_interleave(g, dim=1).contiguous()
+    do = w["dout"].transpose(1, 2).contiguous()
+    res = {"what": "torch SDPA (is_causal, dense: it has no tile skipping), B1 S16384 H32 D128 bf16, KV heads repeated"}
+    try:
+        with torch.no_grad():
+            f = time_events(lambda: F.scaled_dot_product_attention(q, k, v, is_causal=True), reps)
+        qg, kg, vg = (t.requires_grad_(True) for t in (q, k, v))
+
+        def step():
+            qg.grad = kg.grad = vg.grad = None
+            F.scaled_dot_product_attention(qg, kg, vg, is_causal=True).backward(do)
+
+        fb = time_events(step, reps)
+        eff = wl.causal_flops(1, HQ, 16384, D)
+        res.update(fwd_ms=f, fwd_bwd_ms=fb, fwd_tflops=eff / f / 1e9, bwd_tflops=2.5 * eff / max(fb - f, 1e-6) / 1e9)
+    except Exception as e:  # noqa: BLE001
+        res["error"] = repr(e)[:200]
+    return res
+
+
+# --------------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------------
-def traffic_from_profile():
-    """DRAM bytes per launch of the backward main kernel, from the committed ncu summary (or None)."""
-    path = os.path.join(ROOT, "profiles", "bwd_kernel_c2.txt")
-    try:
-        for line in open(path):
-            if line.startswith("traffic_bytes_per_launch:"):
-                return float(line.split(":")[1].strip())
-    except OSError:
-        pass
-    return None
-
-
 def run_gpu(args):
     import torch.distributed as dist
 
@@ -321,47 +566,99 @@ def run_gpu(args):
     torch.cuda.synchronize()
     if not torch.equal(host_out[(e_steps - 1) & 1][0], out.detach().cpu()):  # same inputs, same forward bits
         raise RuntimeError("end-to-end leg: the output that reached the host differs from the device-resident run")
+    # the same copies with no kernels in between: what the host side (PCIe links / switches shared by the ranks,
+    # pinned host memory) can deliver at this N; an e2e step cannot be shorter than this
+    def copies_only(n):
+        for i in range(n):
+            b = i & 1
+            with torch.cuda.stream(s_in):
+                for d, h in zip(dev_in[b], (hq, hk, hv, hdo)):
+                    d.copy_(h, non_blocking=True)
+            with torch.cuda.stream(s_out):
+                for h, d in zip(host_out[b], (dev_in[b][0], dev_in[b][0], dev_in[b][1], dev_in[b][2])):
+                    h.copy_(d, non_blocking=True)
+        s_cur.wait_stream(s_out)
+        s_cur.wait_stream(s_in)
+
+    copies_only(2)
+    barrier()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    copies_only(e_steps)
+    c1.record()
+    barrier()
+    copy_ms = c0.elapsed_time(c1) / e_steps
+    h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hdo))
+    d2h = sum(t.numel() * t.element_size() for t in host_out[0])
+    del hq, hk, hv, hdo, host_out, dev_in, results, qg, kg, vg, q, k, v, do, out
+    torch.cuda.empty_cache()
+
+    # ---- context-parallel decode (the multi-GPU path with a collective), every N ---------------------------
+    cp_res = None
+    if not args.no_extra:
+        barrier()
+        try:
+            cp_res = decode_cp(rank, world, dev, 30)
+        except Exception as e:  # noqa: BLE001
+            cp_res = {"error": repr(e)[:300]}
+        barrier()
 
     # ---- reduce over ranks: max time ------------------------------------------------------------------
-    times = torch.tensor([ms_total, e2e_ms, kern_ms_avg], device=dev, dtype=torch.float64)
+    times = torch.tensor([ms_total, e2e_ms, kern_ms_avg, copy_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms, kern_ms_avg = times.tolist()
+    ms_total, e2e_ms, kern_ms_avg, copy_ms = times.tolist()
     ms_per_step = ms_total / args.steps
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
+    pk = peaks()
     flops_step = effective_flops() * world
     value = flops_step / (ms_per_step / 1e3) / 1e12
     e2e_value = flops_step / (e2e_ms / 1e3) / 1e12
-    peaks = {}
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-    except OSError:
-        pass
-    peak = peaks.get("bf16_tflops_sustained") or 1590.0 * 0.88
-    peak_src = "measured (sustained cuBLAS bf16, MEASURED_PEAKS.json)" if peaks else "fallback"
+    burst = pk.get("bf16_tflops") or 1590.0
+    peak_src = ("measured burst cuBLAS bf16 (MEASURED_PEAKS.json bf16_tflops): the timed region lasts tens of ms at "
+                "full clocks, not the seconds-long power-capped state of the sustained figure") if pk else "fallback"
     exec_flops_bwd = 2.5 * 4.0 * D * executed_pairs_tile_granular() * B * HQ
+    exec_flops_step = 3.5 * 4.0 * D * executed_pairs_tile_granular() * B * HQ * world
     achieved = exec_flops_bwd / (kern_ms_avg / 1e3) / 1e12
-    h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hdo))
-    d2h = sum(t.numel() * t.element_size() for t in host_out[0])
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": config_dict(world),
+        "executed_tflops": exec_flops_step / (ms_per_step / 1e3) / 1e12,
         "clocks": sampler.summary(),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms,
+                "host_copy_gbs_all_ranks": (h2d + d2h) * world / (e2e_ms / 1e3) / 1e9,
+                "copies_only_ms_per_step": copy_ms,
+                "copies_only_note": "the step's host<->device copies alone (no kernels), max over ranks: the floor the "
+                                    "host side sets for an end-to-end step at this N",
                 "overlap": "copy-in of step i+1 and copy-out of step i-1 run on their own streams beside the kernels of step i"},
         "gpu_launches": 4 * args.steps,
-        "roofline": {"bound": "tensor", "kernel": "bwd_kernel<128, bf16, sparse>", "achieved": achieved, "peak": peak,
-                     "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic_from_profile(),
+        "roofline": {"bound": "tensor", "kernel": "bwd_kernel<128, bf16, sparse>", "achieved": achieved, "peak": burst,
+                     "unit": "TFLOP/s", "frac": achieved / burst, "frac_of_nominal": achieved / NOMINAL_BF16_TFLOPS,
+                     "frac_of_measured_sustained": achieved / (pk.get("bf16_tflops_sustained") or 1400.0),
+                     "traffic": TRAFFIC_BWD_KERNEL_C2,
+                     "traffic_source": "constant copied from the committed ncu summary profiles/bwd_kernel_c2.txt; "
+                                       "not measured in this run",
                      "peak_source": peak_src, "kernel_ms": kern_ms_avg,
                      "flops_per_launch": exec_flops_bwd,
                      "note": "executed FLOPs = 2.5 * 4*D*(pairs in visited 128x128 tiles); of measured peak"},
     }
+    if cp_res is not None:
+        line["decode_cp"] = cp_res
+    if world == 1 and not args.no_extra:
+        for name, fn in (("long_context", lambda: long_context(pk, 8)), ("decode", lambda: decode_c5(pk, 50)),
+                         ("sdpa", lambda: sdpa_context(5))):
+            try:
+                line[name] = fn()
+            except Exception as e:  # noqa: BLE001
+                line[name] = {"error": repr(e)[:300]}
+            torch.cuda.empty_cache()
+        line["context"] = {"upstream_triton": upstream_triton(), "sdpa": line.pop("sdpa")}
     if world == 1 and not args.no_cpu:
         torch.set_num_threads(max(1, os.cpu_count() or 1))
         line["cpu_baseline"] = cpu_baseline()
@@ -377,6 +674,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--no-extra", action="store_true", help="only the headline workload (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

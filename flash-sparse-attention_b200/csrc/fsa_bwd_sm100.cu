@@ -673,6 +673,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         x[i + 2] = xb.x;
         x[i + 3] = xb.y;
       }
+      // A tile that the reference runs WITHOUT a mask (flash_sparse_bwd.py:339-359) takes part in its skip vote with
+      // whatever lies past the sequence ends: a query column past sq reads S = 0 (plus the gate of alpha = 0) and
+      // lse2 = 0 (masked loads, scheduler.py:2173-2179), so its log2 p - threshold is >= 0 unless the threshold is
+      // 0, and the tile is kept; a key row past sk reads S = gate only and votes with g c - lse2[q]. Those entries
+      // are masked out of P below, but their vote is reproduced here.
+      bool oor_want = false;
+      if (KIND != KIND_DENSE && mode == FSA_MASK_NONE && ragged) {
+        if ((m + 1) * TM > sq) {
+          const float x_oor = (KIND == KIND_GATED && logsig) ? -0.6931472f * c : 0.f;
+          const float vis_oor = causal ? float(m * TM + TM - 1 + off + 1) : float(sk);
+          oor_want = x_oor - fminf(lg_thr - lg2_approx(vis_oor), 0.0f) >= 0.0f;
+        } else if (!row_ok) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const float vis_i = causal ? float(q_first + i + off + 1) : float(sk);
+            oor_want |= (x[i] - fminf(lg_thr - lg2_approx(vis_i), 0.0f) >= 0.0f);
+          }
+        }
+      }
       if (masked) {
         const int n_iv = (cm.len[0] != 0u) + (cm.len[1] != 0u) + (cm.len[2] != 0u);
         if (__all_sync(0xffffffffu, n_iv <= 1)) {  // at most one interval per key row: one compare per entry
@@ -721,6 +740,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
             drop |= (v < 0.0f);
           }
         }
+        want |= oor_want;
         if (KIND == KIND_GATED && gate_skip) {
           want = false;
           drop = true;

@@ -170,6 +170,7 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
   const float thr_keys = float(p.thr_sk ? p.thr_sk[b] : sk);
   const float thr_log2 = (KIND != KIND_DENSE) ? log2f(fmaxf(fminf(p.softmax_thr / thr_keys, 1.0f), 0.0f)) : 0.f;
   const int* gidx = gather ? p.gather_idx + (long long)b * p.gi_stride : nullptr;
+  const int key_lo = p.key_bounds ? p.key_bounds[2 * b] : 0, key_hi = p.key_bounds ? p.key_bounds[2 * b + 1] : 0;
   const int* ptab = paged ? p.page_table + (long long)b * p.pt_stride : nullptr;
   const int capacity = paged ? p.pt_stride * p.page_size
                              : ((p.flags & F_VARLEN_K) ? p.cu_k[b + 1] - off_k : p.sk_capacity);
@@ -200,7 +201,7 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
       const int i = n * DTN + lane;
       if (gather) {
         pos = (i < p.topk) ? gidx[i] : -1;
-        if (p.key_hi > 0) pos = (pos >= p.key_lo && pos < p.key_hi) ? pos - p.key_lo : -1;
+        if (p.key_bounds) pos = (pos >= key_lo && pos < key_hi) ? pos - key_lo : -1;
       } else
         pos = (i < sk) ? i : -1;
       e = row_elem(pos);

@@ -230,8 +230,7 @@ class FsaDecArgs(ctypes.Structure):
         ("gate_threshold", c_float),
         ("qkv_scale", c_void_p),
         ("thr_seqlen_k", c_void_p),
-        ("key_lo", c_int32),
-        ("key_hi", c_int32),
+        ("key_bounds", c_void_p),
         ("out_partial_stride", c_int64),
         ("lse_partial_stride", c_int64),
         ("ev_before", c_void_p),

@@ -64,7 +64,8 @@ def _check_gate(alpha, delta, alpha_shape=None, delta_shape=None):
     if alpha is None and delta is None:
         return
     assert alpha is not None and delta is not None, "alpha and delta must be given together"
-    assert alpha.stride(-1) == 1 and delta.stride(-1) == 1, "alpha and delta must be contiguous along positions"
+    assert (alpha.shape[-1] == 1 or alpha.stride(-1) == 1) and (delta.shape[-1] == 1 or delta.stride(-1) == 1), (
+        "alpha and delta must be contiguous along positions")
     if alpha_shape is not None:
         assert tuple(alpha.shape) == tuple(alpha_shape), f"alpha must have shape {tuple(alpha_shape)}"
     if delta_shape is not None:
@@ -76,11 +77,11 @@ def check_out_buffers(out, lse, out_shape, out_dtype, lse_shape):
     if out is not None:
         assert tuple(out.shape) == tuple(out_shape) and out.dtype == out_dtype, (
             f"out must have shape {tuple(out_shape)} and dtype {out_dtype}")
-        assert out.stride(-1) == 1, "out must be contiguous along head_dim"
+        assert out.shape[-1] == 1 or out.stride(-1) == 1, "out must be contiguous along head_dim"
     if lse is not None:
         assert tuple(lse.shape) == tuple(lse_shape) and lse.dtype == torch.float32, (
             f"lse must have shape {tuple(lse_shape)} and dtype float32")
-        assert lse.stride(-1) == 1, "lse must be contiguous along its last dimension"
+        assert lse.shape[-1] == 1 or lse.stride(-1) == 1, "lse must be contiguous along its last dimension"
 
 
 def _check_windows(window_sizes):

@@ -8,8 +8,8 @@ and the decode combine (flash_dec_combine.py:15-153) merges them. No other colle
 
 Sharding convention: rank r owns the logical key positions [lo_r, hi_r) of every sequence and holds them
 as a local cache whose position 0 is global position lo_r. Gathered (top-k) indices stay GLOBAL positions:
-the decode kernel itself masks the ones outside [lo_r, hi_r) and shifts the others (FsaDecArgs.key_lo /
-key_hi), so the union over ranks is exactly the original index set and the step runs no index arithmetic
+the decode kernel itself masks the ones outside [lo_r, hi_r) and shifts the others (FsaDecArgs.key_bounds,
+one (lo, hi) pair per sequence, so that sequences of different lengths can each be cut into equal parts), so the union over ranks is exactly the original index set and the step runs no index arithmetic
 outside the kernel. The softmax threshold is normalised by the length of the WHOLE sequence on every rank
 (FsaDecArgs.thr_seqlen_k); each shard still compares against its own running maximum and sum, so with a
 positive threshold a shard can keep a tile that the unsharded call would skip or the other way round - the
@@ -80,7 +80,7 @@ class ContextParallelDecoder:
     step allocated once: decode kernel (partials in the wire format) -> one all-gather -> combine kernel.
 
     `key_local / value_local` hold this rank's positions [shard_lo, shard_hi) (contiguous [B, S_local, Hkv, D], or
-    paged with `page_table`); `gather_kv_indices` are GLOBAL positions; `seqused_k_global` (int32 [B]) the lengths
+    paged with `page_table`); `shard_lo` may also be an int32 [B, 2] tensor of per-sequence (lo, hi) bounds; `gather_kv_indices` are GLOBAL positions; `seqused_k_global` (int32 [B]) the lengths
     of the whole sequences (normalises the softmax threshold; in gather mode it is all the kernel needs to know
     about lengths), `seqused_k_local` the number of valid keys in the local shard (full-context mode)."""
 
@@ -103,7 +103,7 @@ class ContextParallelDecoder:
         gather = gather_kv_indices is not None
         attn_decode(kind, query, key_local, value_local, partial_only=True, num_splits=self.ns,
                     packed_partials=self.send, gather_kv_indices=gather_kv_indices,
-                    key_range=(shard_lo, shard_hi) if gather else None,
+                    key_range=(shard_lo if isinstance(shard_lo, torch.Tensor) else (shard_lo, shard_hi)) if gather else None,
                     seqused_k=seqused_k_global if gather else seqused_k_local,
                     threshold_seqlen_k=None if gather else seqused_k_global, page_table=page_table,
                     softmax_scale=softmax_scale, softmax_threshold=softmax_threshold)

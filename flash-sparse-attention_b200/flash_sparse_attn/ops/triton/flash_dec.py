@@ -64,7 +64,7 @@ def attn_decode(
     partial_only: bool = False,
     workspace: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
     threshold_seqlen_k: Optional[torch.Tensor] = None,
-    key_range: Optional[Tuple[int, int]] = None,
+    key_range=None,
     packed_partials: Optional[torch.Tensor] = None,
 ):
     """Returns ``(out, lse)``; with ``partial_only`` returns ``(out_partial [ns,B,Hq,D] fp32,
@@ -72,8 +72,8 @@ def attn_decode(
     ``workspace`` optionally supplies the two partial buffers so that no allocation happens.
     For a shard of a longer key sequence: ``threshold_seqlen_k`` (int32 [B]) is the key count that normalises the
     softmax threshold (the whole sequence's, so that a shard skips by the same bound as an unsharded call);
-    ``key_range = (lo, hi)`` makes gathered positions outside [lo, hi) masked and addresses the others at
-    position - lo. ``packed_partials`` (fp32, at least splits * B * Hq * (D + 1) elements) receives the partials
+    ``key_range`` (int32 [B, 2] of (lo, hi) per sequence, or one (lo, hi) tuple) makes gathered positions outside
+    [lo, hi) masked and addresses the others at position - lo. ``packed_partials`` (fp32, at least splits * B * Hq * (D + 1) elements) receives the partials
     of every split as one block - outputs then log-sum-exps - so that they travel in a single all-gather."""
     if not query.is_cuda:
         raise RuntimeError("flash_sparse_attn (B200 build) only runs on CUDA tensors; there is no CPU path")
@@ -173,7 +173,10 @@ def attn_decode(
     a.qkv_scale = _lib.ptr(qkv_scale)
     a.thr_seqlen_k = _lib.ptr(threshold_seqlen_k)
     if key_range is not None:
-        a.key_lo, a.key_hi = int(key_range[0]), int(key_range[1])
+        if not isinstance(key_range, torch.Tensor):  # one (lo, hi) for every sequence
+            key_range = torch.tensor([[int(key_range[0]), int(key_range[1])]] * batch, dtype=torch.int32, device=device)
+        assert key_range.dtype == torch.int32 and tuple(key_range.shape) == (batch, 2) and key_range.is_contiguous()
+        a.key_bounds = key_range.data_ptr()
 
     # split partials [splits, B, Hq, D] / [splits, Hq, B] (base-2 lse): the caller's, or sized by the library
     lib = _lib.load()

@@ -269,10 +269,10 @@ typedef struct FsaDecArgs {
    *   thr_seqlen_k [batch]: key count that normalises the softmax threshold (threshold / count,
    *     seqlen_info.py:141-149) and the default gate threshold; null = the count this call sees. A shard passes
    *     the length of the whole sequence so that its skip decisions use the same bound as an unsharded call.
-   *   key_lo, key_hi: with gather_kv_indices, positions outside [key_lo, key_hi) are treated as masked (-1) and
-   *     the others address the cache at position - key_lo; key_hi = 0 switches this off. */
+   *   key_bounds [batch, 2] = (lo, hi) per sequence: with gather_kv_indices, positions outside [lo, hi) are
+   *     treated as masked (-1) and the others address the cache at position - lo; null switches this off. */
   const int32_t* thr_seqlen_k;
-  int32_t key_lo, key_hi;
+  const int32_t* key_bounds;
   /* Elements between the partials of consecutive splits in out_partial / lse_partial; 0 = dense
    * (batch*heads_q*head_dim and heads_q*batch). A caller that wants partial outputs and log-sum-exps of one
    * split side by side in ONE buffer (to ship them with a single all-gather) sets both to

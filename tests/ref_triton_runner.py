@@ -104,7 +104,8 @@ def main():
                     ("dq", "dk", "dv", "dalpha", "ddelta"))
         elif args.case == "c4":
             w = wl.c4(dev, n_seq=4 if args.small else 16)
-            w["kwargs"]["is_quant"] = True  # per-tensor e5m2, the only quantised mode upstream has
+            # bf16: upstream's FP8 (is_quant) path on packed sequences ended with "Triton Error [CUDA]: misaligned
+            # address" on a B200 and is not run again
             fwd_bwd(ref.flash_sparse_attn_varlen_func, w, (w["q"], w["k"], w["v"]), ("dq", "dk", "dv"))
         elif args.case == "c5":
             w = wl.c5(dev, batch=8 if args.small else 64, paged=False)

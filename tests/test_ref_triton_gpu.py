@@ -4,8 +4,7 @@ The upstream package is located through FSA_REFERENCE_DIR (default: baseline/_re
 `pip install --target` puts it); the module is skipped when it is absent. Upstream runs in a child process
 (tests/ref_triton_runner.py: both packages are called `flash_sparse_attn`) with is_autotune=False and
 tile_mn=(128, 128), the tile shape of the kernels here; inputs come from benchmarks/workloads.py with the same seed
-in both processes. Tolerance: element-wise rtol 2e-2 / atol 2e-2 for bf16 outputs and gradients, 1.5e-1 for the
-FP8 case (upstream quantises to e5m2 per tensor, so do we)."""
+in both processes. Tolerance: element-wise rtol 2e-2 / atol 2e-2 for bf16 outputs and gradients."""
 
 import importlib.util
 import os
@@ -16,7 +15,7 @@ import tempfile
 import pytest
 import torch
 
-from fixtures import FP8_TOL, assert_close
+from fixtures import assert_close
 
 pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
@@ -84,14 +83,15 @@ def test_gated_config_against_upstream():
     _check("c3", ("out", "dq", "dk", "dv", "dalpha", "ddelta"), [out] + g, ref)
 
 
-def test_packed_quantised_config_against_upstream():
+def test_packed_config_against_upstream():
+    """The packed-sequence configuration in bf16. Its fused-quant (FP8) form is not compared: upstream's is_quant
+    path on packed sequences raised "Triton Error [CUDA]: misaligned address" on the B200 and is not run again."""
     import flash_sparse_attn as fsa
 
     ref = _run_upstream("c4")
     w = _workloads().c4(DEV, n_seq=4)
-    w["kwargs"]["is_quant"] = True
     out, g = _grads(fsa.flash_sparse_attn_varlen_func, w, (w["q"], w["k"], w["v"]))
-    _check("c4", ("out", "dq", "dk", "dv"), [out] + g, ref, rtol=FP8_TOL, atol=FP8_TOL)
+    _check("c4", ("out", "dq", "dk", "dv"), [out] + g, ref)
 
 
 def test_topk_decode_against_upstream():

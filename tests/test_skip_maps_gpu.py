@@ -202,7 +202,7 @@ def test_decode_softmax_skip_map(mode, group, splits):
     n_tiles = -(-sk // 16)
     if mode == "gather":
         idx = torch.stack([torch.randperm(sk, generator=g)[:700] for _ in range(b)]).to(torch.int32)
-        idx[:, 0] = sk - 1
+        idx[:, -1] = sk - 1   # the peak sits in the first tile the walk visits (it descends from the last slot)
         idx[:, 5] = -1
         kw["gather_kv_indices"] = idx.to(DEV)
         okw["gather_kv_indices"] = idx
