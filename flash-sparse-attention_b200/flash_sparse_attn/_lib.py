@@ -7,7 +7,6 @@ holds ``csrc/``), and every entry point raises on a non-zero status.
 
 import ctypes
 import os
-import threading
 from ctypes import POINTER, c_float, c_int, c_int32, c_int64, c_size_t, c_uint32, c_uint8, c_void_p
 
 import torch
@@ -355,20 +354,21 @@ def check_status(device=None):
             raise RuntimeError(f"fsa kernel reported device status {v} (a pipeline wait expired)")
 
 
-_profile = threading.local()
+_profile = {"before": None, "after": None}
 
 
 def set_profile_events(before=None, after=None):
-    """Have the next operator calls of THIS THREAD record `before` / `after` (torch.cuda.Event, already
-    recorded once so that their handles exist) around their main kernel; None, None switches it off. The pair
-    travels in the argument block of each call (`ev_before` / `ev_after`): the library keeps no such state."""
-    _profile.before = before.cuda_event if before is not None else None
-    _profile.after = after.cuda_event if after is not None else None
+    """Have the next operator calls of this process record `before` / `after` (torch.cuda.Event, already recorded
+    once so that their handles exist) around their main kernel; None, None switches it off. The pair is Python
+    state of this module (process-wide rather than per thread: autograd runs a backward call on a thread of its
+    own) and travels in the argument block of each call (`ev_before` / `ev_after`); the library keeps no state."""
+    _profile["before"] = before.cuda_event if before is not None else None
+    _profile["after"] = after.cuda_event if after is not None else None
 
 
 def attach_profile_events(args):
-    args.ev_before = getattr(_profile, "before", None)
-    args.ev_after = getattr(_profile, "after", None)
+    args.ev_before = _profile["before"]
+    args.ev_after = _profile["after"]
 
 
 def workspace(nbytes: int, device, dtype=torch.float32):
