@@ -356,6 +356,38 @@ int fsa_fwd(const FsaFwdArgs* a, void* stream_) {
   if (a->flags & FSA_F_ADAPT_GATE) f |= fsa::F_ADAPT_GATE;
   p.flags = f;
 
+  if (a->kind == FSA_KIND_GATED) {
+    if (!a->gate_ws) return FSA_ERR_INVALID_ARG;
+    fsa::GateExtParams ge;
+    memset(&ge, 0, sizeof(ge));
+    ge.alpha = a->alpha;
+    ge.delta = a->delta;
+    ge.gate_ws = a->gate_ws;
+    ge.cu_q = a->cu_seqlens_q;
+    ge.cu_k = a->cu_seqlens_k;
+    ge.used_q = a->seqused_q;
+    ge.used_k = a->seqused_k;
+    ge.page_table = a->page_table;
+    ge.a_sb = a->alpha_stride_b;
+    ge.a_sh = a->alpha_stride_h;
+    ge.d_sb = a->delta_stride_b;
+    ge.d_sh = a->delta_stride_h;
+    ge.B = a->batch;
+    ge.Hq = a->heads_q;
+    ge.Hkv = a->heads_kv;
+    ge.G = G;
+    ge.gpack = gpack;
+    ge.hgrid = hgrid;
+    ge.sq = a->seqlen_q;
+    ge.sk = sk_static;
+    ge.num_m_blocks = num_m_blocks;
+    ge.n_tiles_k = n_tiles_k;
+    ge.page_size = a->page_size;
+    ge.pt_stride = a->page_table_stride;
+    ge.flags = f & (fsa::F_VARLEN_Q | fsa::F_VARLEN_K | fsa::F_USED_Q | fsa::F_USED_K | fsa::F_PAGED);
+    if (fsa::launch_gate_ext(ge, out_dtype, stream) != cudaSuccess) return FSA_ERR_LAUNCH;
+    p.gate_ws = a->gate_ws;
+  }
   mark(a->ev_before, stream);
   p.D = a->head_dim;
   cudaError_t e = fsa::launch_fwd(p, a->kind, a->dtype, head_dim_kernel(a->head_dim), stream);

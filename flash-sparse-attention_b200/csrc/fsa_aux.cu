@@ -105,6 +105,70 @@ __device__ __forceinline__ RowPos locate_row(long long item, int heads, int varl
   return r;
 }
 
+// One warp per tile: max / min of alpha over the 128 rows of a query tile (rows of a packed-GQA tile interleave the
+// G heads of a KV head, seqlen_info.py:262-265), or of delta over the 128 keys of a key tile. Rows / keys past
+// the sequence count as 0, like the reference's masked loads (scheduler.py:1658-1691).
+template <typename T>
+__global__ void __launch_bounds__(256) gate_ext_kernel(GateExtParams p) {
+  const int lane = threadIdx.x & 31;
+  long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long n_alpha = (long long)p.B * p.hgrid * p.num_m_blocks;
+  const long long n_delta = (long long)p.B * p.Hkv * p.n_tiles_k;
+  if (item >= n_alpha + n_delta) return;
+  float mx = -INFINITY, mn = INFINITY;
+  float* dst;
+  if (item < n_alpha) {
+    const int mb = (int)(item % p.num_m_blocks);
+    const int head = (int)((item / p.num_m_blocks) % p.hgrid);
+    const int b = (int)(item / ((long long)p.num_m_blocks * p.hgrid));
+    const int off_q = (p.flags & F_VARLEN_Q) ? p.cu_q[b] : 0;
+    const int sq = (p.flags & F_USED_Q) ? p.used_q[b] : ((p.flags & F_VARLEN_Q) ? p.cu_q[b + 1] - off_q : p.sq);
+    const T* base = reinterpret_cast<const T*>(p.alpha) + ((p.flags & F_VARLEN_Q) ? 0 : (long long)b * p.a_sb);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int offs_m = mb * 128 + j * 32 + lane;
+      const int q_idx = offs_m / p.gpack;
+      const int q_head = p.gpack > 1 ? head * p.G + (offs_m - q_idx * p.gpack) : head;
+      const float v = q_idx < sq ? float(base[(long long)q_head * p.a_sh + off_q + q_idx]) : 0.f;
+      mx = fmaxf(mx, v);
+      mn = fminf(mn, v);
+    }
+    dst = p.gate_ws + 2 * item;
+  } else {
+    item -= n_alpha;
+    const int n = (int)(item % p.n_tiles_k);
+    const int hkv = (int)((item / p.n_tiles_k) % p.Hkv);
+    const int b = (int)(item / ((long long)p.n_tiles_k * p.Hkv));
+    const int off_k = (p.flags & F_VARLEN_K) ? p.cu_k[b] : 0;
+    const int sk = (p.flags & F_USED_K) ? p.used_k[b] : ((p.flags & F_VARLEN_K) ? p.cu_k[b + 1] - off_k : p.sk);
+    const T* base = reinterpret_cast<const T*>(p.delta);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int k = n * 128 + j * 32 + lane;
+      float v = 0.f;
+      if (k < sk) {
+        long long e;
+        if (p.flags & F_PAGED) {
+          const int page = p.page_table[(long long)b * p.pt_stride + k / p.page_size];
+          e = (long long)page * p.d_sb + (long long)hkv * p.d_sh + (k % p.page_size);
+        } else {
+          e = (long long)((p.flags & F_VARLEN_K) ? 0 : b) * p.d_sb + (long long)hkv * p.d_sh + off_k + k;
+        }
+        v = float(base[e]);
+      }
+      mx = fmaxf(mx, v);
+      mn = fminf(mn, v);
+    }
+    dst = p.gate_ws + 2 * n_alpha + 2 * item;
+  }
+#pragma unroll
+  for (int sft = 16; sft > 0; sft >>= 1) {
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sft));
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, sft));
+  }
+  if (lane == 0) *reinterpret_cast<float2*>(dst) = make_float2(mx, mn);
+}
+
 constexpr int PP_ITEMS = 4;  // (row, head) items per lane group in the pre / post passes: more loads in flight
 
 // head_dim / 8 lanes per (query row, head), 16-byte loads; also clears the row of the fp32 dQ accumulator.
@@ -311,6 +375,17 @@ cudaError_t launch_bwd_post(const BwdPostParams& p, int dtype, cudaStream_t stre
     bwd_post_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
   else
     bwd_post_kernel<__half><<<grid, 256, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gate_ext(const GateExtParams& p, int dtype, cudaStream_t stream) {
+  const long long items = (long long)p.B * p.hgrid * p.num_m_blocks + (long long)p.B * p.Hkv * p.n_tiles_k;
+  if (items <= 0) return cudaSuccess;
+  const unsigned grid = (unsigned)((items + 7) / 8);
+  if (dtype == DT_FP16)
+    gate_ext_kernel<__half><<<grid, 256, 0, stream>>>(p);
+  else
+    gate_ext_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
   return cudaGetLastError();
 }
 

@@ -80,6 +80,22 @@ struct DqOrderParams {
   int B, Hkv, sq, sk, num_splits, n_tiles_k, num_m_blocks, win_stride;
   unsigned flags;  // F_CAUSAL | F_LOCAL | F_SPLIT | F_VARLEN_* | F_USED_*
 };
+// Gated forward: per-tile extremes of alpha and delta (layout: gate_ws_bytes in fsa_params.h). The kernels derive
+// every gate-skip decision from these, before a key tile is loaded (activations.py:265-299 needs nothing else).
+struct GateExtParams {
+  const void* alpha;  // T [B, Hq, Sq] | [Hq, Tq], position-contiguous
+  const void* delta;  // T [B, Hkv, Sk] | [Hkv, Tk] | paged [pages, Hkv, page]
+  float* gate_ws;
+  const int* cu_q;
+  const int* cu_k;
+  const int* used_q;
+  const int* used_k;
+  const int* page_table;
+  long long a_sb, a_sh, d_sb, d_sh;
+  int B, Hq, Hkv, G, gpack, hgrid, sq, sk, num_m_blocks, n_tiles_k, page_size, pt_stride;
+  unsigned flags;  // F_VARLEN_* | F_USED_* | F_PAGED
+};
+cudaError_t launch_gate_ext(const GateExtParams& p, int dtype, cudaStream_t stream);
 cudaError_t launch_dq_order(const DqOrderParams& p, cudaStream_t stream);
 cudaError_t launch_flat_sum(const FlatSumParams& p, int dtype, cudaStream_t stream);
 cudaError_t launch_bwd_pre(const BwdPreParams& p, int dtype, cudaStream_t stream);

@@ -181,8 +181,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
     n_block = p.n_tiles_k - 1 - idx / per_tile;
     idx %= per_tile;
   } else {
-    n_block = idx % p.n_tiles_k;
-    idx /= p.n_tiles_k;
+    // Key tiles in ascending order, slowest index: under a causal / window mask the first key tiles meet the most
+    // query tiles, so the longest CTAs start first and the short ones fill the tail (512 CTAs on 148 SMs are 3.5
+    // rounds: with the key tile as the fastest index the last round began with the longest CTAs). CTAs that run
+    // side by side still share their Q / dO tiles through L2: neighbouring key tiles of one head are per_tile apart.
+    const int per_tile = p.Hkv * p.B * p.num_splits;
+    n_block = idx / per_tile;
+    idx %= per_tile;
   }
   const int hkv = idx % p.Hkv;
   idx /= p.Hkv;

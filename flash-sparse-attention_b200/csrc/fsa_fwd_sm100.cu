@@ -70,12 +70,11 @@ struct FwdBars {
   uint64_t kv_full[2];  // step t (slot t & 1): V(t) and K(t + 1) have landed (two producer arrivals)
   uint64_t kv_empty[2];  // signal c (slot c & 1): K(c) and V(c - 1) have been consumed; c = 0 comes from the prologue
   uint64_t s_full[2], p_full[2], o_final[2], wg_sync[2];
-  uint64_t d_full[2], d_empty[2], a_sync[2];  // gated: delta ring (stager warp -> softmax warps), alpha exchange
+  uint64_t d_full[2], d_empty[2];  // gated: delta ring (stager warp -> softmax warps)
   uint32_t tmem_base;
   int abort_flag;
   int skip_flag[2][2];   // [group][parity of the group's tile counter]
   int vote_any[2][2][4]; // [group][parity][warp]: bit0 = some row wants the tile, bit1 = some row votes skip
-  float a_ext[2][4][2];  // gated: per group, per warp (max, min) of alpha
   alignas(16) float dl[2][TN + 4];  // gated: delta of the key tile as fp32 (read as float4), then its max and min
 };
 
@@ -225,6 +224,70 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     return fsa_imax(a, b);
   };
 
+  // ---- gated: which tiles each group really computes ---------------------------------------------
+  // The gate bound of a tile (flash_sparse_attn/ops/triton/activations.py:265-299) needs only the extremes of alpha
+  // over the query tile and of delta over the key tile - both computed beforehand by gate_ext_kernel - and one
+  // running scalar per query tile. So every role (producer, MMA issuer, delta stager, softmax warps) walks the
+  // tiles with its own copy of that scalar and reaches the same decisions without talking to the others: a tile
+  // that both groups skip is never loaded, multiplied or staged (flash_gated_fwd.py:54-56 runs nothing for it).
+  // The first tile of a group is never skipped: its running bound starts at -inf, the difference is +inf.
+  float gw_amax[2] = {0.f, 0.f}, gw_amin[2] = {0.f, 0.f}, gw_thr[2] = {0.f, 0.f}, gw_run[2] = {-INFINITY, -INFINITY};
+  float gw_c = 0.f;
+  const float2* gw_dext = nullptr;
+  if (KIND == KIND_GATED) {
+    gw_c = p.qkv_scale ? p.scale_log2 * p.qkv_scale[0] * p.qkv_scale[1] : p.scale_log2;
+    const float2* aext = reinterpret_cast<const float2*>(p.gate_ws);
+    gw_dext = aext + (long long)p.B * p.hgrid * p.num_m_blocks + ((long long)si.b * p.Hkv + si.hkv) * p.n_tiles_k;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int mb = pair * 2 + q;
+      if (mb < p.num_m_blocks) {
+        const float2 e = __ldg(aext + ((long long)si.b * p.hgrid + si.head) * p.num_m_blocks + mb);
+        gw_amax[q] = e.x;
+        gw_amin[q] = e.y;
+      }
+      // flash_sparse_attn/ops/triton/seqlen_info.py:156-191: the adaptive bound is smallest at the tile's first row
+      float g_thr = p.gate_thr;
+      if (causal && (p.flags & F_ADAPT_GATE))
+        g_thr = p.gate_thr * (float((mb * TM) / gpack + (si.sk - si.sq)) + 1.0f) / float(si.sk);
+      gw_thr[q] = log2f(g_thr);
+    }
+  }
+  // Next tile below n_prev that at least one group computes; keep[q] says which. mark_q >= 0: this thread records
+  // the gate-skipped tiles of group mark_q in the tile map (value 3).
+  auto walk_next = [&](int n_prev, bool* keep, int mark_q) -> int {
+    int n = next_tile(n_prev);
+    if constexpr (KIND != KIND_GATED) {
+      keep[0] = n >= 0 && fsa_fwd_tile_mode(sched[0], n, causal, local) >= 0;
+      keep[1] = n >= 0 && fsa_fwd_tile_mode(sched[1], n, causal, local) >= 0;
+      return n;
+    } else {
+    while (n >= 0) {
+      const float2 de = __ldg(gw_dext + n);  // (max, min) of delta over the key tile
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        keep[q] = fsa_fwd_tile_mode(sched[q], n, causal, local) >= 0;
+        if (keep[q]) {
+          const float gmc = fmaxf(fmaxf(gw_amax[q] * de.x, gw_amax[q] * de.y), fmaxf(gw_amin[q] * de.x, gw_amin[q] * de.y));
+          const bool skip = (gmc - gw_run[q]) * gw_c < gw_thr[q];
+          if (!skip) gw_run[q] = fmaxf(gmc, gw_run[q]);
+          keep[q] = !skip;
+          if (skip && mark_q == q && p.tile_map) {
+            const int mb = pair * 2 + q;
+            p.tile_map[((((long long)si.b * p.hgrid + si.head) * p.num_m_blocks + mb) * p.num_splits + si.split) *
+                           p.n_tiles_k + n] = 3;
+          }
+        }
+      }
+      if (keep[0] || keep[1]) return n;
+      n = next_tile(n);
+    }
+    keep[0] = keep[1] = false;
+    return -1;
+    }
+  };
+  constexpr int WALK_START = 1 << 28;
+
   // ---- setup ---------------------------------------------------------------------------------
   if (tid == 0) {
     mbar_init(&bars->q_full, 1);
@@ -240,7 +303,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       mbar_init(&bars->wg_sync[q], 4);
       mbar_init(&bars->d_full[q], 1);
       mbar_init(&bars->d_empty[q], 8);
-      mbar_init(&bars->a_sync[q], 4);
     }
     bars->abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
     mbar_fence_init();
@@ -314,12 +376,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       };
       int t = 0, seen = 0;
       bool ok = true;
-      int n = first_tile();
+      bool keep_unused[2];
+      int n = (KIND == KIND_GATED) ? walk_next(WALK_START, keep_unused, -1) : first_tile();
       if (n >= 0) {
         load_kv(&p.map_k, smem + SM::kK, &bars->k0_full, n);
       }
       while (n >= 0 && ok) {
-        const int n_next = next_tile(n);
+        const int n_next = (KIND == KIND_GATED) ? walk_next(n, keep_unused, -1) : next_tile(n);
         // Release signals arrive in order (signal c: K(c) and V(c - 1) consumed). V(t) goes into the slot of
         // V(t - 2) and K(t + 1) into the slot of K(t - 1): both free after signal t - 1.
         auto need_signal = [&](int c) {
@@ -354,7 +417,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       bool ok = !*abort_flag;
       const TO* dbase = reinterpret_cast<const TO*>(p.delta);
       int t = 0;
-      for (int n = first_tile(); n >= 0 && ok; n = next_tile(n), ++t) {
+      bool keep_unused[2];
+      for (int n = walk_next(WALK_START, keep_unused, -1); n >= 0 && ok; n = walk_next(n, keep_unused, -1), ++t) {
         const int s = t & 1, use = t >> 1;
         if (use > 0) ok = mbar_wait(&bars->d_empty[s], (use - 1) & 1, abort_flag);
         if (!ok) break;
@@ -403,7 +467,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     bool ok = !*abort_flag;
     int cnt[2] = {0, 0};
     bool o_started[2] = {false, false};
-    int n = first_tile();
+    bool act[2], last[2];
+    int n = (KIND == KIND_GATED) ? walk_next(WALK_START, act, -1) : first_tile();
     // Every lane runs the same (warp-uniform) descriptor arithmetic; the MMA and commit instructions carry the
     // one-lane predicate themselves.
     const uint32_t lead = lane == 0 ? 1u : 0u;
@@ -428,7 +493,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       tc_fence_after();
       if (ok) {
         for (int q = 0; q < 2; ++q)
-          if (fsa_fwd_tile_mode(sched[q], n, causal, local) >= 0) issue_s(q, 0);
+          if ((KIND == KIND_GATED) ? act[q] : (fsa_fwd_tile_mode(sched[q], n, causal, local) >= 0)) issue_s(q, 0);
         umma_commit_lead(lead, &bars->kv_empty[0]);
       }
     }
@@ -438,17 +503,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     // pipe idles. So everything that does not depend on P (the walk over the tiles, who takes part in the next
     // tile, the K / V arrivals) happens before the wait for P. (One issuer per group was tried: the second
     // polling warp slows the softmax warps of its scheduler more than the overlap gains.)
-    bool act[2], last[2];
+    if (KIND != KIND_GATED) {
 #pragma unroll
-    for (int q = 0; q < 2; ++q) act[q] = n >= 0 && fsa_fwd_tile_mode(sched[q], n, causal, local) >= 0;
+      for (int q = 0; q < 2; ++q) act[q] = n >= 0 && fsa_fwd_tile_mode(sched[q], n, causal, local) >= 0;
+    }
     while (n >= 0 && ok) {
-      const int n_next = next_tile(n);
+      bool act_next[2];
+      const int n_next = (KIND == KIND_GATED) ? walk_next(n, act_next, -1) : next_tile(n);
       const int vs = t % VSTAGES;
       const int ks_next = (t + 1) % KSTAGES;
-      bool act_next[2];
 #pragma unroll
       for (int q = 0; q < 2; ++q) {
-        if (!local) {  // one contiguous range of tiles per group
+        if (KIND == KIND_GATED) {
+          // whether a later tile of this group survives the gate is not known yet: the output barriers are
+          // committed after the loop instead
+          last[q] = false;
+        } else if (!local) {  // one contiguous range of tiles per group
           act_next[q] = n_next >= sched[q].n_min && n_next < sched[q].n_max;
           last[q] = act[q] && n == sched[q].n_min;
         } else {
@@ -508,6 +578,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       act[1] = act_next[1];
       ++t;
     }
+    if (KIND == KIND_GATED && ok) {
+      // completion of everything issued so far = both outputs are final
+      for (int q = 0; q < 2; ++q)
+        if (o_started[q]) umma_commit_lead(lead, &bars->o_final[q]);
+    }
   }
   } else {
     // =============================== softmax groups ==========================================
@@ -549,58 +624,39 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     bool ok = !*abort_flag;
     const bool has_work = q_valid[q] && !fsa_fwd_sched_empty(my);
 
-    // ---- gated: alpha of this row, its extremes over the tile, the gate threshold ------------------
-    float alpha = 0.f, a_max = 0.f, a_min = 0.f, gate_max = -INFINITY, gate_thr_log2 = 0.f;
+    // ---- gated: alpha of this row ----------------------------------------------------------------------
+    float alpha = 0.f;
     if (KIND == KIND_GATED) {
       if (rm.row_ok && q_valid[q]) {
         const TO* ab = reinterpret_cast<const TO*>(p.alpha);
         alpha = float(ab[(long long)((p.flags & F_VARLEN_Q) ? 0 : si.b) * p.a_sb + (long long)q_head * p.a_sh +
                          si.off_q + q_idx]);
       }
-      float mx = alpha, mn = alpha;
-#pragma unroll
-      for (int sft = 16; sft > 0; sft >>= 1) {
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sft));
-        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, sft));
-      }
-      if (lane == 0) {
-        bars->a_ext[q][wq][0] = mx;
-        bars->a_ext[q][wq][1] = mn;
-        mbar_arrive(&bars->a_sync[q]);
-      }
-      ok = ok && mbar_wait(&bars->a_sync[q], 0, abort_flag);
-      a_max = fmaxf(fmaxf(bars->a_ext[q][0][0], bars->a_ext[q][1][0]), fmaxf(bars->a_ext[q][2][0], bars->a_ext[q][3][0]));
-      a_min = fminf(fminf(bars->a_ext[q][0][1], bars->a_ext[q][1][1]), fminf(bars->a_ext[q][2][1], bars->a_ext[q][3][1]));
-      // flash_sparse_attn/ops/triton/seqlen_info.py:156-191: the adaptive bound is smallest at the tile's first row
-      float g_thr = p.gate_thr;
-      if (causal && (p.flags & F_ADAPT_GATE))
-        g_thr = p.gate_thr * (float((mb * TM) / gpack + (si.sk - si.sq)) + 1.0f) / float(si.sk);
-      gate_thr_log2 = log2f(g_thr);
     }
 
     int t_merged = -1;
-    for (int n = (KIND == KIND_GATED || has_work) ? first_tile() : -1; n >= 0 && ok; n = next_tile(n)) {
+    bool keep[2] = {false, false};
+    const int mark_q = (wq == 0 && lane == 0) ? q : -1;  // one thread per group records its gate-skipped tiles
+    int n = -1;
+    if (KIND == KIND_GATED)
+      n = walk_next(WALK_START, keep, mark_q);
+    else if (has_work)
+      n = first_tile();
+    for (; n >= 0 && ok; n = (KIND == KIND_GATED) ? walk_next(n, keep, mark_q) : next_tile(n)) {
       ++t_merged;
       const int mode = has_work ? fsa_fwd_tile_mode(my, n, causal, local) : -1;
       const int ds = t_merged & 1;
       if (KIND == KIND_GATED) {
+        // every tile that reaches this loop was staged by the delta warp (one of the groups computes it)
         ok = mbar_wait(&bars->d_full[ds], (t_merged >> 1) & 1, abort_flag);
         if (!ok) break;
-      }
-      if (mode < 0) {
-        if (KIND == KIND_GATED) {
+        if (!keep[q]) {  // not in this group's schedule, or skipped by its gate: nothing was issued for it
           __syncwarp();
           if (lane == 0) mbar_arrive(&bars->d_empty[ds]);
+          continue;
         }
+      } else if (mode < 0) {
         continue;
-      }
-      // gate bound of the tile (flash_sparse_attn/ops/triton/activations.py:265-299): a running scalar
-      bool gate_skip = false;
-      if (KIND == KIND_GATED) {
-        const float dmax = bars->dl[ds][TN], dmin = bars->dl[ds][TN + 1];
-        const float gmc = fmaxf(fmaxf(a_max * dmax, a_max * dmin), fmaxf(a_min * dmax, a_min * dmin));
-        gate_skip = (gmc - gate_max) * c < gate_thr_log2;
-        if (!gate_skip) gate_max = fmaxf(gmc, gate_max);
       }
       ok = mbar_wait(&bars->s_full[q], cnt_s & 1, abort_flag);
       if (!ok) break;
@@ -608,26 +664,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       const int par = cnt_s & 1;
       cnt_s++;
       const int k0 = n * TN;
-      if (gate_skip) {
-        // the tile contributes nothing: publish "skipped" to the producer and the MMA warp
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->d_empty[ds]);
-        if (wq == 0 && lane == 0) {
-          bars->skip_flag[q][par] = 1;
-          if (p.tile_map) {
-            const long long idx =
-                ((((long long)si.b * p.hgrid + si.head) * p.num_m_blocks + mb) * p.num_splits + si.split) *
-                    p.n_tiles_k + n;
-            p.tile_map[idx] = 3;
-          }
-        }
-        // keep the group's vote barrier in step with the tile counter
-        if (lane == 0) mbar_arrive(&bars->wg_sync[q]);
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->p_full[q]);
-        continue;
-      }
 
       // ---- scores of this row: TMEM -> registers (warp-collective loads, one wait) ---------------
       uint32_t sr[TN];
