@@ -23,8 +23,9 @@ cpu_baseline  the CPU oracle (a port: eager fp32 forward + autograd backward) on
 Further device-timed measurements in the same line (N = 1 only unless noted):
 long_context  sparse causal forward and backward at S = 16384 (B1, Hq32 / Hkv8, D128, threshold 1.0) on iid and on
          llm-like inputs: kernel times, executed and effective TFLOP/s, fractions of the measured and nominal peak.
-decode   paged top-k decode (B64, contexts 4K-128K, Hq64 / Hkv8, D128, 256-token pages, top-k 2048) under CUDA-graph
-         replay: microseconds per step, algorithmic GB/s, fraction of the measured copy bandwidth.
+decode   (every N, batch-sharded: each rank its own 64 sequences) paged top-k decode (B64, contexts 4K-128K, Hq64 /
+         Hkv8, D128, 256-token pages, top-k 2048) under CUDA-graph replay: microseconds per step, algorithmic GB/s,
+         fraction of the measured copy bandwidth.
 decode_cp  (every N) the same decode with every sequence's KV cut into N page-aligned shards, one per rank: decode
          kernel -> ONE all-gather of the packed partials -> combine kernel; microseconds per step and the share of
          the exchange.
@@ -305,18 +306,28 @@ def graph_time_us(fn, iters):
     return time_events(graph.replay, iters) * 1e3
 
 
-def decode_c5(pk, iters):
+def decode_c5(pk, iters, rank=0, world=1):
+    """Every rank decodes its own batch of 64 sequences (batch-sharded decode: no collective); time = max over ranks."""
     import flash_sparse_attn as fsa
 
     wl = workloads()
-    w = wl.c5("cuda", paged=True)
+    w = wl.c5("cuda", seed=rank, paged=True)
     fn = lambda: fsa.flash_sparse_attn_with_kvcache_func(w["q"], w["k"], w["v"], softmax_threshold=THRESHOLD, **w["kwargs"])  # noqa: E731
     us = graph_time_us(fn, iters)
     fsa.check_status()
+    if world > 1:
+        import torch.distributed as dist
+
+        t = torch.tensor([us], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us = float(t.item())
     gbs = w["bytes"] / us / 1e3
     hbm = pk.get("hbm_gbs") or 6650.0
     res = {"config": "paged top-k decode B64 ctx 4096-131072 Hq64 Hkv8 D128 page 256 top-k 2048, bf16, CUDA-graph replay; "
                      f"cache {w['k'].numel() * 4 / 1e9:.1f} GB, gathered rows scattered over it (no L2 reuse between steps)",
+           "sharding": f"batch-sharded over {world} GPU(s): every rank decodes its own 64 sequences, no collective; "
+                       "per-GPU figures, time = max over ranks",
+           "sequences_per_step_all_ranks": 64 * world, "aggregate_gbs_all_ranks": gbs * world,
            "us_per_step": us, "algorithmic_mb": w["bytes"] / 1e6, "achieved_gbs": gbs,
            "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm,
                         "frac_of_nominal": gbs / NOMINAL_HBM_GBS, "traffic": None,
@@ -594,13 +605,18 @@ def run_gpu(args):
     torch.cuda.empty_cache()
 
     # ---- context-parallel decode (the multi-GPU path with a collective), every N ---------------------------
-    cp_res = None
+    cp_res = dec_res = None
     if not args.no_extra:
         barrier()
         try:
             cp_res = decode_cp(rank, world, dev, 30)
         except Exception as e:  # noqa: BLE001
             cp_res = {"error": repr(e)[:300]}
+        barrier()
+        try:
+            dec_res = decode_c5(peaks(), 50, rank, world)
+        except Exception as e:  # noqa: BLE001
+            dec_res = {"error": repr(e)[:300]}
         barrier()
 
     # ---- reduce over ranks: max time ------------------------------------------------------------------
@@ -650,9 +666,9 @@ def run_gpu(args):
     }
     if cp_res is not None:
         line["decode_cp"] = cp_res
+        line["decode"] = dec_res
     if world == 1 and not args.no_extra:
-        for name, fn in (("long_context", lambda: long_context(pk, 8)), ("decode", lambda: decode_c5(pk, 50)),
-                         ("sdpa", lambda: sdpa_context(5))):
+        for name, fn in (("long_context", lambda: long_context(pk, 8)), ("sdpa", lambda: sdpa_context(5))):
             try:
                 line[name] = fn()
             except Exception as e:  # noqa: BLE001

@@ -24,6 +24,7 @@ SOURCES = [
     "fsa_static_scratch.cu",
     "fsa_quant.cu",
     "fsa_topk.cu",
+    "fsa_kvcache.cu",
 ]
 
 NVCC_FLAGS = [

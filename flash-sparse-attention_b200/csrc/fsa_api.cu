@@ -784,6 +784,7 @@ int fsa_decode(const FsaDecArgs* a, void* stream_) {
   p.lp_ss = a->lse_partial_stride > 0 ? a->lse_partial_stride : (long long)a->batch * a->heads_q;
   p.thr_sk = a->thr_seqlen_k;
   p.key_bounds = gather ? a->key_bounds : nullptr;
+  p.gather_count = gather ? a->gather_count : nullptr;
   mark(a->ev_before, stream);
   p.D = a->head_dim;
   cudaError_t e = fsa::launch_dec(p, a->kind, a->dtype, head_dim_kernel(a->head_dim), stream);

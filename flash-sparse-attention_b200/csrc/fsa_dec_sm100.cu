@@ -160,7 +160,9 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
   }
   const int nsub = p.num_splits * DWARPS;
   const int sub = split * DWARPS + warp;
-  const FsaFwdSched sched = gather ? fsa_topk_schedule(p.topk, sub, nsub, DTN)
+  // gathered rows: only the leading `topk` entries can be valid (all of them unless the caller says fewer)
+  const int topk = (gather && p.gather_count) ? min(p.topk, p.gather_count[b]) : p.topk;
+  const FsaFwdSched sched = gather ? fsa_topk_schedule(topk, sub, nsub, DTN)
                                    : fsa_fwd_schedule(1, sk, 0, sub, w, nsub, DTN, 16, false, local, true, p.G,
                                                       /*cover_single_query=*/true);
   const bool loc_sched = local && !gather;
@@ -200,7 +202,7 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
     if (lane < DTN) {
       const int i = n * DTN + lane;
       if (gather) {
-        pos = (i < p.topk) ? gidx[i] : -1;
+        pos = (i < topk) ? gidx[i] : -1;
         if (p.key_bounds) pos = (pos >= key_lo && pos < key_hi) ? pos - key_lo : -1;
       } else
         pos = (i < sk) ? i : -1;

@@ -230,10 +230,40 @@ class FsaDecArgs(ctypes.Structure):
         ("qkv_scale", c_void_p),
         ("thr_seqlen_k", c_void_p),
         ("key_bounds", c_void_p),
+        ("gather_count", c_void_p),
         ("out_partial_stride", c_int64),
         ("lse_partial_stride", c_int64),
         ("ev_before", c_void_p),
         ("ev_after", c_void_p),
+    ]
+
+
+class FsaKvAppendArgs(ctypes.Structure):
+    _fields_ = [
+        ("k_new", c_void_p),
+        ("v_new", c_void_p),
+        ("k_cache", c_void_p),
+        ("v_cache", c_void_p),
+        ("seqused_k", c_void_p),
+        ("page_table", c_void_p),
+        ("free_pages", c_void_p),
+        ("free_count", c_void_p),
+        ("pos_ws", c_void_p),
+        ("status", c_void_p),
+        ("new_stride_b", c_int64),
+        ("new_stride_s", c_int64),
+        ("new_stride_h", c_int64),
+        ("cache_stride_b", c_int64),
+        ("cache_stride_s", c_int64),
+        ("cache_stride_h", c_int64),
+        ("batch", c_int32),
+        ("new_tokens", c_int32),
+        ("heads_kv", c_int32),
+        ("head_dim", c_int32),
+        ("capacity", c_int32),
+        ("page_size", c_int32),
+        ("page_table_stride", c_int32),
+        ("dtype", c_int32),
     ]
 
 
@@ -290,6 +320,10 @@ def load():
     lib.fsa_fp8_widen.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
     lib.fsa_topk_indices.restype = c_int
     lib.fsa_topk_indices.argtypes = [c_void_p, c_int, c_int, c_int, c_int64, c_int, c_void_p, c_int, c_void_p]
+    lib.fsa_kv_append.restype = c_int
+    lib.fsa_kv_append.argtypes = [POINTER(FsaKvAppendArgs), c_void_p]
+    lib.fsa_localize_indices.restype = c_int
+    lib.fsa_localize_indices.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]
     lib.fsa_fwd_workspace_bytes.restype = c_int
     lib.fsa_fwd_workspace_bytes.argtypes = [POINTER(FsaFwdArgs), POINTER(FsaFwdWorkspace)]
     lib.fsa_bwd_workspace_bytes.restype = c_int

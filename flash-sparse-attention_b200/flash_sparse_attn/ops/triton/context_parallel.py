@@ -6,11 +6,13 @@ decode: every rank produces the partial result of its key range exactly like one
 all-gather lands all partials in local memory (2.1 MB per rank at batch 64, 64 heads, head_dim 128),
 and the decode combine (flash_dec_combine.py:15-153) merges them. No other collective is needed.
 
-Sharding convention: rank r owns the logical key positions [lo_r, hi_r) of every sequence and holds them
-as a local cache whose position 0 is global position lo_r. Gathered (top-k) indices stay GLOBAL positions:
-the decode kernel itself masks the ones outside [lo_r, hi_r) and shifts the others (FsaDecArgs.key_bounds,
-one (lo, hi) pair per sequence, so that sequences of different lengths can each be cut into equal parts), so the union over ranks is exactly the original index set and the step runs no index arithmetic
-outside the kernel. The softmax threshold is normalised by the length of the WHOLE sequence on every rank
+Sharding convention: rank r owns the logical key positions [lo_r, hi_r) of every sequence (one (lo, hi) pair per
+sequence, so that sequences of different lengths can each be cut into equal parts) and holds them as a local cache
+whose position 0 is global position lo_r. Gathered (top-k) indices arrive as GLOBAL positions; one small kernel
+(fsa_localize_indices) keeps the ones inside [lo_r, hi_r), shifts them and moves them to the front of the row, and
+the decode kernel visits only the tiles that hold them, so a rank's work shrinks with the number of shards. The
+union over ranks is exactly the original index set and the step runs no eager index arithmetic. (The decode kernel
+can also mask and shift global positions itself, FsaDecArgs.key_bounds, without the compaction.) The softmax threshold is normalised by the length of the WHOLE sequence on every rank
 (FsaDecArgs.thr_seqlen_k); each shard still compares against its own running maximum and sum, so with a
 positive threshold a shard can keep a tile that the unsharded call would skip or the other way round - the
 difference is bounded by the threshold mass, as between different split counts on one GPU.
@@ -94,16 +96,33 @@ class ContextParallelDecoder:
         self.recv = torch.empty((self.world * num_splits, per), dtype=torch.float32, device=device)
         self.out = torch.empty((batch, heads_q, head_dim), dtype=dtype, device=device)
         self.lse = torch.empty((batch, heads_q), dtype=torch.float32, device=device)
+        self._bounds = self._bounds_key = self._idx = self._count = None
 
     def partial(self, query, key_local, value_local, shard_lo, shard_hi, gather_kv_indices=None,
                 seqused_k_global=None, seqused_k_local=None, page_table=None, softmax_scale=None,
                 softmax_threshold=None, kind="sparse"):
         from flash_sparse_attn.ops.triton.flash_dec import attn_decode
+        from flash_sparse_attn.utils.kvcache import localize_indices as localize_on_device
 
         gather = gather_kv_indices is not None
+        idx = count = None
+        if gather:
+            # one small kernel: this shard's positions, shard-local, at the front of every row, and how many - the
+            # decode kernel then only visits the tiles that hold them (its work shrinks with the number of shards)
+            if isinstance(shard_lo, torch.Tensor):
+                bounds = shard_lo
+            else:
+                if self._bounds is None or self._bounds_key != (shard_lo, shard_hi):
+                    self._bounds = torch.tensor([[int(shard_lo), int(shard_hi)]] * self.batch, dtype=torch.int32,
+                                                device=query.device)
+                    self._bounds_key = (shard_lo, shard_hi)
+                bounds = self._bounds
+            if self._idx is None or self._idx.shape != gather_kv_indices.shape:
+                self._idx = torch.empty_like(gather_kv_indices)
+                self._count = torch.empty(self.batch, dtype=torch.int32, device=query.device)
+            idx, count = localize_on_device(gather_kv_indices, bounds, out=self._idx, count=self._count)
         attn_decode(kind, query, key_local, value_local, partial_only=True, num_splits=self.ns,
-                    packed_partials=self.send, gather_kv_indices=gather_kv_indices,
-                    key_range=(shard_lo if isinstance(shard_lo, torch.Tensor) else (shard_lo, shard_hi)) if gather else None,
+                    packed_partials=self.send, gather_kv_indices=idx, gather_count=count,
                     seqused_k=seqused_k_global if gather else seqused_k_local,
                     threshold_seqlen_k=None if gather else seqused_k_global, page_table=page_table,
                     softmax_scale=softmax_scale, softmax_threshold=softmax_threshold)

@@ -66,6 +66,7 @@ def attn_decode(
     threshold_seqlen_k: Optional[torch.Tensor] = None,
     key_range=None,
     packed_partials: Optional[torch.Tensor] = None,
+    gather_count: Optional[torch.Tensor] = None,
 ):
     """Returns ``(out, lse)``; with ``partial_only`` returns ``(out_partial [ns,B,Hq,D] fp32,
     lse_partial [ns,Hq,B] fp32 base-2)`` instead (used by context-parallel decode).
@@ -74,7 +75,9 @@ def attn_decode(
     softmax threshold (the whole sequence's, so that a shard skips by the same bound as an unsharded call);
     ``key_range`` (int32 [B, 2] of (lo, hi) per sequence, or one (lo, hi) tuple) makes gathered positions outside
     [lo, hi) masked and addresses the others at position - lo. ``packed_partials`` (fp32, at least splits * B * Hq * (D + 1) elements) receives the partials
-    of every split as one block - outputs then log-sum-exps - so that they travel in a single all-gather."""
+    of every split as one block - outputs then log-sum-exps - so that they travel in a single all-gather.
+    ``gather_count`` (int32 [B]): only that many leading entries of each row of ``gather_kv_indices`` can be valid
+    (see ``flash_sparse_attn.utils.kvcache.localize_indices``); the kernel visits only the tiles that hold them."""
     if not query.is_cuda:
         raise RuntimeError("flash_sparse_attn (B200 build) only runs on CUDA tensors; there is no CPU path")
     device = query.device
@@ -172,6 +175,7 @@ def attn_decode(
     a.gate_threshold = float(gate_threshold)
     a.qkv_scale = _lib.ptr(qkv_scale)
     a.thr_seqlen_k = _lib.ptr(threshold_seqlen_k)
+    a.gather_count = _lib.ptr(gather_count)
     if key_range is not None:
         if not isinstance(key_range, torch.Tensor):  # one (lo, hi) for every sequence
             key_range = torch.tensor([[int(key_range[0]), int(key_range[1])]] * batch, dtype=torch.int32, device=device)

@@ -273,6 +273,10 @@ typedef struct FsaDecArgs {
    *     treated as masked (-1) and the others address the cache at position - lo; null switches this off. */
   const int32_t* thr_seqlen_k;
   const int32_t* key_bounds;
+  /* gather_count [batch] (optional): only the first gather_count[b] entries of row b of gather_kv_indices can be
+   * valid (the rest are -1), so the kernel visits only the 16-key tiles that hold them: what
+   * fsa_localize_indices produces for one shard of a sharded cache. */
+  const int32_t* gather_count;
   /* Elements between the partials of consecutive splits in out_partial / lse_partial; 0 = dense
    * (batch*heads_q*head_dim and heads_q*batch). A caller that wants partial outputs and log-sum-exps of one
    * split side by side in ONE buffer (to ship them with a single all-gather) sets both to
@@ -392,6 +396,48 @@ int fsa_fp8_widen(const void* x_fp8, void* out, const void* scale, int64_t n, in
  */
 int fsa_topk_indices(const void* scores, int dtype, int rows, int n, int64_t row_stride, int k, void* out,
                      int out_is_int64, void* stream);
+
+/*
+ * KV-cache append: k_new / v_new [batch, new_tokens, heads_kv, head_dim] go to positions seqused_k[b] ..
+ * seqused_k[b] + new_tokens of the cache, then seqused_k[b] advances by new_tokens; no host round trip, two
+ * small kernels. The cache is contiguous [batch, capacity, heads_kv, head_dim] or, with page_table, paged
+ * [num_pages, page_size, heads_kv, head_dim] - the layouts the decode entry points read. Paged: a page-table slot
+ * that holds a negative number has no page yet; the call pops one from `free_pages` (a stack of free page
+ * numbers whose height is the device counter *free_count). Rows that find no room (capacity exceeded, page table
+ * full, free stack empty) are dropped and the status word is set to 3.
+ * No counterpart in the reference, which leaves cache management to the caller (its README lists a KV-cache
+ * manager as future work); the layout is the one its decode reads (flash_sparse_attn/ops/triton/paged_kv.py:10-30).
+ * All strides in elements; rows move in 16-byte chunks (head_dim * element size and all strides multiples of 16
+ * bytes). pos_ws: caller-owned int32 [batch] workspace.
+ */
+typedef struct FsaKvAppendArgs {
+  const void* k_new;
+  const void* v_new;
+  void* k_cache;
+  void* v_cache;
+  int32_t* seqused_k;  /* [batch] */
+  int32_t* page_table; /* [batch, page_table_stride] or null */
+  int32_t* free_pages; /* optional */
+  int32_t* free_count; /* optional */
+  int32_t* pos_ws;
+  int32_t* status;
+  int64_t new_stride_b, new_stride_s, new_stride_h;
+  int64_t cache_stride_b, cache_stride_s, cache_stride_h; /* paged: _b = page stride; v_cache shares them */
+  int32_t batch, new_tokens, heads_kv, head_dim;
+  int32_t capacity; /* contiguous cache: positions per sequence */
+  int32_t page_size, page_table_stride;
+  int32_t dtype;
+} FsaKvAppendArgs;
+int fsa_kv_append(const FsaKvAppendArgs* args, void* stream);
+
+/*
+ * One shard's view of global top-k positions: for every row keep the positions inside [lo, hi) (key_bounds
+ * [rows, 2]), shift them by -lo, move them to the front of the output row in their original order, fill the rest
+ * with -1 and write how many were kept to count[row]. Feeds FsaDecArgs.gather_kv_indices / gather_count of a rank
+ * that holds positions [lo, hi) of every sequence. No counterpart in the reference (it has no multi-GPU code).
+ */
+int fsa_localize_indices(const int32_t* indices, int64_t indices_stride, const int32_t* key_bounds, int32_t* out,
+                         int64_t out_stride, int32_t* count, int rows, int topk, void* stream);
 
 int fsa_abi_version(void);
 

@@ -37,7 +37,7 @@ def test_struct_layout_matches_header():
 
     text = open(os.path.join(ROOT, "include", "fsa_b200.h")).read()
     for cname, cls in (("FsaFwdArgs", _lib.FsaFwdArgs), ("FsaBwdArgs", _lib.FsaBwdArgs),
-                       ("FsaDecArgs", _lib.FsaDecArgs)):
+                       ("FsaDecArgs", _lib.FsaDecArgs), ("FsaKvAppendArgs", _lib.FsaKvAppendArgs)):
         body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), text, flags=re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         fields = []

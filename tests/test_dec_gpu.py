@@ -183,6 +183,7 @@ def test_sharded_decode_pieces_on_one_gpu(mode, splits):
     normalised by the whole length), the blocks are concatenated as an all-gather would, one combine merges them."""
     from flash_sparse_attn.ops.triton import context_parallel as cp
     from flash_sparse_attn.ops.triton.flash_dec import attn_decode, combine_packed_partials
+    from flash_sparse_attn.utils.kvcache import localize_indices
 
     g = torch.Generator().manual_seed(21)
     b, sk, hq, hkv, d, topk, world = 3, 2300, 16, 2, 128, 384, 3
@@ -198,9 +199,14 @@ def test_sharded_decode_pieces_on_one_gpu(mode, splits):
         lo, hi = cp.shard_bounds(sk, world, r)
         send = recv[r * splits:(r + 1) * splits]
         kl, vl = k[:, lo:hi].contiguous(), v[:, lo:hi].contiguous()
-        if mode == "gather":
+        if mode == "gather" and r == 1:   # masking and shifting inside the decode kernel
             attn_decode("sparse", q, kl, vl, partial_only=True, num_splits=splits, packed_partials=send,
                         gather_kv_indices=idx, key_range=(lo, hi), seqused_k=used, softmax_threshold=-128.0)
+        elif mode == "gather":            # compacted by fsa_localize_indices: only the tiles that hold indices
+            bounds = torch.tensor([[lo, hi]] * b, dtype=torch.int32, device=DEV)
+            local, count = localize_indices(idx, bounds)
+            attn_decode("sparse", q, kl, vl, partial_only=True, num_splits=splits, packed_partials=send,
+                        gather_kv_indices=local, gather_count=count, seqused_k=used, softmax_threshold=-128.0)
         else:
             attn_decode("sparse", q, kl, vl, partial_only=True, num_splits=splits, packed_partials=send,
                         threshold_seqlen_k=used, softmax_threshold=-128.0)
