@@ -187,6 +187,7 @@ int fsa_bwd_workspace_bytes(const FsaBwdArgs* a, FsaBwdWorkspace* w) {
     w->alpha_ws = es * (size_t)a->heads_q * R;
     w->da_accum = sizeof(float) * (size_t)a->heads_q * R;
     if (ns > 1) w->dd_partial = sizeof(float) * (size_t)ns * (size_t)a->delta_numel;
+    w->gate_ws = fsa::gate_ws_bytes(a->batch, a->heads_q, cdiv(a->seqlen_q, 128), a->heads_kv, cdiv(a->seqlen_k, 128));
   }
   if (a->flags & FSA_F_DETERMINISTIC) {
     const size_t ntk = cdiv(a->seqlen_k, 128), ntq = cdiv(a->seqlen_q, 128);
@@ -607,6 +608,34 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
     p.dq_order = a->dq_order;
     p.dq_turn = a->dq_turn;
     p.flags |= fsa::F_DETERMINISTIC;
+  }
+  if (gated && a->gate_ws) {
+    fsa::GateExtParams ge;
+    memset(&ge, 0, sizeof(ge));
+    ge.alpha = a->alpha;
+    ge.delta = a->delta;
+    ge.gate_ws = a->gate_ws;
+    ge.cu_q = a->cu_seqlens_q;
+    ge.cu_k = a->cu_seqlens_k;
+    ge.used_q = a->seqused_q;
+    ge.used_k = a->seqused_k;
+    ge.a_sb = a->alpha_stride_b;
+    ge.a_sh = a->alpha_stride_h;
+    ge.d_sb = a->delta_stride_b;
+    ge.d_sh = a->delta_stride_h;
+    ge.B = a->batch;
+    ge.Hq = a->heads_q;
+    ge.Hkv = a->heads_kv;
+    ge.G = p.G;
+    ge.gpack = 1;
+    ge.hgrid = a->heads_q;
+    ge.sq = a->seqlen_q;
+    ge.sk = a->seqlen_k;
+    ge.num_m_blocks = p.num_m_blocks;
+    ge.n_tiles_k = p.n_tiles_k;
+    ge.flags = f & (fsa::F_VARLEN_Q | fsa::F_VARLEN_K | fsa::F_USED_Q | fsa::F_USED_K);
+    if (fsa::launch_gate_ext(ge, a->dtype, stream) != cudaSuccess) return FSA_ERR_LAUNCH;
+    p.gate_ws = a->gate_ws;
   }
   mark(a->ev_before, stream);
   p.D = a->head_dim;

@@ -215,7 +215,75 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
   const FsaBwdSched sched = fsa_bwd_schedule(sq, sk, n_block, split, w, p.num_splits, TN, TM, causal, local, split_qo);
   const SegList segs = make_segments(sched, causal, local);
   const int NT = segs.total;       // query tiles per head
-  const int N_IT = NT * p.G;       // steps of this CTA
+  const int N_IT = NT * p.G;       // steps of this CTA (before gate-skipped ones are dropped)
+
+  // ---- the steps of this CTA, in order: (head of the group, query tile) ------------------------------------
+  // Gated kind: the gate bound of a step (flash_sparse_attn/ops/triton/flash_gated_bwd.py:61-79,
+  // activations.py:265-299) needs only the extremes of delta over this key tile, the extremes of alpha over the
+  // query tile (both precomputed by gate_ext_kernel) and a running scalar that restarts with every head, so every
+  // role walks the steps with its own copy of that scalar and drops the same ones: for a gate-skipped step no
+  // Q / dO tile is loaded and no MMA is issued (the reference runs nothing for it either). The deterministic
+  // mode keeps every step in the stream (a skipped one still has to pass its turn on) and takes the decision in
+  // the compute warps, after S^T, as before.
+  const bool preskip = (KIND == KIND_GATED) && !(p.flags & F_DETERMINISTIC) && p.gate_ws != nullptr;
+  float gw_dmax = 0.f, gw_dmin = 0.f;
+  const float2* gw_aext = nullptr;
+  if (preskip) {
+    const float2* ext = reinterpret_cast<const float2*>(p.gate_ws);
+    const float2 de = __ldg(ext + (long long)p.B * p.Hq * p.num_m_blocks + ((long long)b * p.Hkv + hkv) * p.n_tiles_k + n_block);
+    gw_dmax = de.x;
+    gw_dmin = de.y;
+    gw_aext = ext + ((long long)b * p.Hq + (long long)hkv * p.G) * p.num_m_blocks;
+  }
+  struct StepWalk {
+    int g, idx;
+    SegIter si;
+    float run;
+  };
+  auto walk_begin = [&]() {
+    StepWalk w;
+    w.g = 0;
+    w.idx = 0;
+    w.si = seg_begin(segs);
+    w.run = -INFINITY;
+    return w;
+  };
+  // Next step that is computed: head g of the group, query tile m, mask mode, first step of its head. `mark`: this
+  // thread records the dropped steps in the tile map (value 3). Returns false at the end.
+  auto walk_next = [&](StepWalk& w, int& g, int& m, int& mode, bool& first, bool mark) -> bool {
+    for (;;) {
+      if (NT == 0 || w.g >= p.G) return false;
+      if (w.idx == NT) {
+        w.g++;
+        w.idx = 0;
+        w.si = seg_begin(segs);
+        w.run = -INFINITY;
+        continue;
+      }
+      g = w.g;
+      m = w.si.m;
+      mode = w.si.mode;
+      first = w.idx == 0;
+      seg_next(segs, w.si);
+      w.idx++;
+      if (preskip) {
+        const float2 ae = __ldg(gw_aext + (long long)g * p.num_m_blocks + m);
+        float g_thr = p.gate_thr;
+        if (causal && (p.flags & F_ADAPT_GATE)) g_thr = p.gate_thr * (float(m * TM + (sk - sq)) + 1.0f) / float(sk);
+        const float gmc = fmaxf(fmaxf(ae.x * gw_dmax, ae.x * gw_dmin), fmaxf(ae.y * gw_dmax, ae.y * gw_dmin));
+        const bool skip = (gmc - w.run) * p.scale_log2 < log2f(g_thr);
+        if (!skip) {
+          w.run = fmaxf(gmc, w.run);
+        } else {
+          if (mark && p.tile_map)
+            p.tile_map[((((long long)b * p.Hq + hkv * p.G + g) * p.n_tiles_k + n_block) * p.num_splits + split) *
+                           p.num_m_blocks + m] = 3;
+          continue;
+        }
+      }
+      return true;
+    }
+  };
 
   // ---- setup ---------------------------------------------------------------------------------
   if (tid == 0) {
@@ -268,13 +336,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         // Q (with the row statistics of its tile) runs two steps ahead in a 2-stage ring; dO has one
         // buffer and is reloaded as soon as dV of the previous step has consumed it.
         bool ok = true;
-        SegIter si_q = seg_begin(segs);
-        for (int it = 0; it < N_IT && ok; ++it) {
+        StepWalk wk = walk_begin();
+        int g = 0, m = 0, mode_unused = 0;
+        bool first_unused = false;
+        for (int it = 0; ok && walk_next(wk, g, m, mode_unused, first_unused, false); ++it) {
           const int st = it & 1, use = it >> 1;
-          const int g = it / NT;
-          if (it == g * NT) si_q = seg_begin(segs);
-          const int m = si_q.m;
-          seg_next(segs, si_q);
           const int head = hkv * p.G + g;
           if (use > 0) ok = mbar_wait(&bars->q_empty[st], (use - 1) & 1, abort_flag);
           if (!ok) break;
@@ -304,6 +370,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       const uint32_t sK = smem_u32(smem + SM::kK), sV = smem_u32(smem + SM::kV), sQ = smem_u32(smem + SM::kQ),
                      sDO = smem_u32(smem + SM::kDO), sDS = smem_u32(smem + SM::kDS);
       bool ok = !*abort_flag && N_IT > 0;
+      (void)N_IT;
       auto issue_st = [&](int st) {
         if (lane == 0) {
 #pragma unroll
@@ -316,7 +383,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         }
         __syncwarp();
       };
-      if (ok) {
+      StepWalk wk = walk_begin();
+      int g_unused = 0, m_unused = 0, mode_unused = 0;
+      bool first_unused = false;
+      bool has_cur = ok && walk_next(wk, g_unused, m_unused, mode_unused, first_unused, false);
+      if (has_cur) {
         ok = mbar_wait(&bars->kv_full, 0, abort_flag);
         ok = ok && mbar_wait(&bars->q_full[0], 0, abort_flag);
         tc_fence_after();
@@ -324,8 +395,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       }
       int n_live = 0;  // steps that were not skipped so far
       bool acc_started = false;
-      for (int it = 0; it < N_IT && ok; ++it) {
+      for (int it = 0; has_cur && ok; ++it) {
         const int st = it & 1;
+        const bool has_next = walk_next(wk, g_unused, m_unused, mode_unused, first_unused, false);
         ok = mbar_wait(&bars->p_full, it & 1, abort_flag);
         if (!ok) break;
         const bool skip = (KIND != KIND_DENSE) && bars->skip_flag[it & 1];
@@ -356,7 +428,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         }
         if (lane == 0) umma_commit(&bars->do_empty);  // dO may be overwritten once dV has read it
         __syncwarp();
-        if (it + 1 < N_IT) {
+        if (has_next) {
           ok = mbar_wait(&bars->q_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
@@ -386,6 +458,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         }
         if (lane == 0) umma_commit(&bars->q_empty[st]);
         __syncwarp();
+        has_cur = has_next;
       }
       if (lane == 0) umma_commit(&bars->acc_full);
       __syncwarp();
@@ -576,19 +649,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
     };
 
     // ---- P step: scores -> probabilities (and the skip vote) ------------------------------------
-    SegIter si_p = seg_begin(segs);
-    int m_p = 0, g_p = 0, it_head = 0;  // query tile and head (within the group) of the step p_step just handled
-    auto p_step = [&](int it) -> bool {  // returns the skip decision; steps are visited in order
+    StepWalk wk = walk_begin();
+    const bool mark_steps = cw == 0 && lane == 0;  // one thread records the dropped steps in the tile map
+    int m_p = 0, g_p = 0;  // query tile and head (within the group) of the step p_step just handled
+    // returns the skip decision; steps are visited in order: (g, m, mode, first step of its head) from the walk
+    auto p_step = [&](int it, int g, int m, int mode, bool first_of_head) -> bool {
       const int st = it & 1, par = it & 1;
-      if (it - it_head == NT) {
-        it_head = it;
-        g_p++;
-        si_p = seg_begin(segs);
-      }
-      const int g = g_p;
-      const int m = si_p.m, mode = si_p.mode;
+      g_p = g;
       m_p = m;
-      seg_next(segs, si_p);
       // skip thresholds of the group's first and last query column: worked out before S is waited for
       // (log2(clamp(threshold / visible, 0, 1)) = min(log2 threshold - log2 visible, 0); threshold <= 0 gives -inf)
       const int q_first = m * TM + wg * 64;
@@ -610,10 +678,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       }
       tc_fence_after();
       bool gate_skip = false;
-      if (KIND == KIND_GATED) {
+      if (KIND == KIND_GATED && !preskip) {
         // bound of the gate over the tile against a running maximum that restarts with every query head
         // (flash_gated_bwd.py:61-79, activations.py:265-299, seqlen_info.py:156-191)
-        if (it == it_head) gate_max = -INFINITY;
+        if (first_of_head) gate_max = -INFINITY;
         const uint2 av = *reinterpret_cast<const uint2*>(s_alpha + st * 128 + lane * 4);
         float a4[4];
         unpack16(av.x, a4[0], a4[1]);
@@ -947,16 +1015,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       dq_pending = NCH > 1;
     };
 
-    if (ok && N_IT > 0) {
-      skip_cur = p_step(0);
+    int w_g = 0, w_m = 0, w_mode = 0;
+    bool w_first = false;
+    bool has_cur = ok && walk_next(wk, w_g, w_m, w_mode, w_first, mark_steps);
+    const bool any_step = has_cur;
+    if (has_cur) {
+      skip_cur = p_step(0, w_g, w_m, w_mode, w_first);
       m_cur = m_p;
       g_cur = g_p;
     }
-    for (int it = 0; it < N_IT && ok; ++it) {
+    for (int it = 0; has_cur && ok; ++it) {
       if (!skip_cur) ds_step(it);
       dq_flush();
       bool skip_next = false;
-      if (ok && it + 1 < N_IT) skip_next = p_step(it + 1);
+      const bool has_next = walk_next(wk, w_g, w_m, w_mode, w_first, mark_steps);
+      if (ok && has_next) skip_next = p_step(it + 1, w_g, w_m, w_mode, w_first);
       if (ok && !skip_cur) {
         dq_step(it);
         n_live++;
@@ -968,6 +1041,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       skip_cur = skip_next;
       m_cur = m_p;
       g_cur = g_p;
+      has_cur = has_next;
     }
     dq_flush();
     if (det) {
@@ -978,7 +1052,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
     // ---- epilogue: dK (scaled) and dV of this key tile ------------------------------------------------
     if (ok) {
       bool have = false;
-      if (N_IT > 0) {
+      if (any_step) {
         ok = mbar_wait(&bars->acc_full, 0, abort_flag);
         tc_fence_after();
         have = n_live > 0;

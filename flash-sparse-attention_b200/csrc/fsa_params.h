@@ -74,6 +74,7 @@ struct alignas(64) BwdKernelParams {
   const void* alpha_ws;  // gated: T [Hq, ws_sh], tile-padded rows, zero outside the sequences
   const void* delta;     // gated: T [B, Hkv, Sk] | [Hkv, Tk]
   float* da_accum;       // gated: [Hq, ws_sh] fp32, zeroed; receives atomic adds
+  const float* gate_ws;  // gated: per-tile extremes of alpha / delta (gate_ws_bytes), or null
   const unsigned short* dq_order;  // deterministic: [B, Hkv, n_tiles_k, num_m_blocks] rank of a key tile among
                                    // the key tiles that add into a query tile (descending key index)
   int* dq_turn;                    // deterministic: [B, Hq, num_m_blocks] zeroed; one tick per finished key tile

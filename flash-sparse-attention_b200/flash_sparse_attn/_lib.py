@@ -171,6 +171,7 @@ class FsaBwdArgs(ctypes.Structure):
         ("delta_numel", c_int64),
         ("dq_order", c_void_p),
         ("dq_turn", c_void_p),
+        ("gate_ws", c_void_p),
         ("ev_before", c_void_p),
         ("ev_after", c_void_p),
     ]
@@ -273,7 +274,7 @@ class FsaFwdWorkspace(ctypes.Structure):
 
 class FsaBwdWorkspace(ctypes.Structure):
     _fields_ = [(n, c_size_t) for n in ("lse2_ws", "dpsum_ws", "dq_accum", "dk_partial", "dv_partial", "alpha_ws",
-                                        "da_accum", "dd_partial", "dq_order", "dq_turn")]
+                                        "da_accum", "dd_partial", "gate_ws", "dq_order", "dq_turn")]
 
 
 class FsaDecWorkspace(ctypes.Structure):

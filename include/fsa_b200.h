@@ -205,6 +205,10 @@ typedef struct FsaBwdArgs {
    * the key tiles above it before its reduce-add into a query tile; results are bitwise reproducible. */
   uint16_t* dq_order;
   int32_t* dq_turn;
+  /* gated kind: workspace of fsa_bwd_workspace_bytes().gate_ws bytes (written by this call): per-tile extremes of
+   * alpha and delta, from which every role of the kernel takes the gate-skip decisions before a query tile is
+   * loaded. */
+  float* gate_ws;
   void* ev_before;
   void* ev_after;
 } FsaBwdArgs;
@@ -357,7 +361,7 @@ typedef struct FsaFwdWorkspace {
 typedef struct FsaBwdWorkspace {
   size_t lse2_ws, dpsum_ws, dq_accum;
   size_t dk_partial, dv_partial; /* split-QO */
-  size_t alpha_ws, da_accum, dd_partial; /* gated kind */
+  size_t alpha_ws, da_accum, dd_partial, gate_ws; /* gated kind */
   size_t dq_order, dq_turn;      /* FSA_F_DETERMINISTIC */
 } FsaBwdWorkspace;
 typedef struct FsaDecWorkspace {
