@@ -206,6 +206,10 @@ int fsa_decode_workspace_bytes(const FsaDecArgs* a, FsaDecWorkspace* w) {
     w->out_partial = sizeof(float) * (size_t)ns * a->batch * a->heads_q * a->head_dim;
     w->lse_partial = sizeof(float) * (size_t)ns * a->batch * a->heads_q;
   }
+  if (a->kind == FSA_KIND_GATED && a->heads_kv > 0) {
+    const int keys = a->gather_kv_indices ? a->topk : (a->page_table ? a->page_table_stride * a->page_size : a->seqlen_k);
+    w->gate_ws = sizeof(float) * 2 * (size_t)a->batch * a->heads_kv * cdiv(keys, 16);
+  }
   return FSA_OK;
 }
 
@@ -496,7 +500,9 @@ int fsa_bwd(const FsaBwdArgs* a, void* stream_) {
   // padding rows of dpsum must hold finite values (they meet zero probabilities in a packed product)
   if (cudaMemsetAsync(a->dpsum_ws, 0, sizeof(float) * (size_t)a->heads_q * R, stream) != cudaSuccess)
     return FSA_ERR_LAUNCH;
-  pre.dq_accum = a->dq_accum;  // the pre-pass clears the accumulator rows it visits (padding rows are never read)
+  // the pre-pass clears the accumulator rows it visits (padding rows are never read); a cudaMemsetAsync of the
+  // whole accumulator in front of a pre-pass that only reads measured slower (0.795 vs 0.778 ms per bench step)
+  pre.dq_accum = a->dq_accum;
   if (fsa::launch_bwd_pre(pre, a->dtype, stream) != cudaSuccess) return FSA_ERR_LAUNCH;
 
   fsa::BwdKernelParams p;
@@ -814,6 +820,7 @@ int fsa_decode(const FsaDecArgs* a, void* stream_) {
   p.thr_sk = a->thr_seqlen_k;
   p.key_bounds = gather ? a->key_bounds : nullptr;
   p.gather_count = gather ? a->gather_count : nullptr;
+  p.gate_ws = a->gate_ws;
   mark(a->ev_before, stream);
   p.D = a->head_dim;
   cudaError_t e = fsa::launch_dec(p, a->kind, a->dtype, head_dim_kernel(a->head_dim), stream);

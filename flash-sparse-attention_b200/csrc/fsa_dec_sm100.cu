@@ -268,6 +268,12 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
     const bool row0_ok = mt * 16 + g < p.G, row1_ok = mt * 16 + g + 8 < p.G;
     // ---- gated: alpha of the two rows, its extremes over the real rows, the running gate bound ----
     float al0 = 0.f, al1 = 0.f, a_max = 0.f, a_min = 0.f, gate_max = -INFINITY;
+    // Gate decisions taken BEFORE a tile's rows are requested: with the per-tile extremes of delta in gate_ws
+    // (dec_gate_ext_kernel) the bound of activations.py:265-299 is evaluated when the walk reaches a tile, and a
+    // gate-skipped tile never enters the ring. Without the workspace the bound is evaluated when the tile is consumed.
+    const bool gate_early = (KIND == KIND_GATED) && p.gate_ws != nullptr;
+    const float2* gext = gate_early ? reinterpret_cast<const float2*>(p.gate_ws) + ((long long)b * p.Hkv + hkv) * p.n_tiles
+                                    : nullptr;
     float dlq[DSTAGES];  // gated: delta of key (lane & 15) of the tiles in the ring, oldest first
 #pragma unroll
     for (int i = 0; i < DSTAGES; ++i) dlq[i] = 0.f;
@@ -295,37 +301,58 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
     auto tile_below = [&](int n) {
       return loc_sched ? fsa_fwd_next_tile_below(sched, n, true) : (n - 1 >= sched.n_min ? n - 1 : -1);
     };
-    const int n_first = fsa_fwd_next_tile_below(sched, 1 << 28, loc_sched);
-    int n_load = n_first;
+    int n_walk = fsa_fwd_next_tile_below(sched, 1 << 28, loc_sched);
+    // next tile whose rows are fetched (-1: none left)
+    auto next_fetch = [&]() -> int {
+      while (n_walk >= 0) {
+        const int n = n_walk;
+        n_walk = tile_below(n_walk);
+        if (gate_early) {
+          const float2 de = __ldg(gext + n);
+          const float gmc = fmaxf(fmaxf(a_max * de.x, a_max * de.y), fmaxf(a_min * de.x, a_min * de.y));
+          const bool gskip = (gmc - gate_max) * c < gate_thr_log2;
+          if (gskip) {
+            if (p.tile_map && lane == 0 && mt == 0) p.tile_map[((long long)b * p.Hkv + hkv) * p.n_tiles + n] = 3;
+            continue;
+          }
+          gate_max = fmaxf(gmc, gate_max);
+        }
+        return n;
+      }
+      return -1;
+    };
     unsigned present_q[DSTAGES];  // presence masks of the tiles in the ring, oldest first
+    int n_q[DSTAGES];             // their tile indices (-1: empty)
     int slot_load = 0;
 #pragma unroll
     for (int s = 0; s < DSTAGES - 1; ++s) {
       present_q[s] = 0;
-      if (n_load >= 0) {
-        present_q[s] = issue_tile(n_load, s, &dlq[s]);
-        n_load = tile_below(n_load);
-      }
+      n_q[s] = next_fetch();
+      if (n_q[s] >= 0) present_q[s] = issue_tile(n_q[s], s, &dlq[s]);
       cp_async_commit();
     }
     present_q[DSTAGES - 1] = 0;
+    n_q[DSTAGES - 1] = -1;
     slot_load = DSTAGES - 1;
     int slot = 0;
-    for (int n = n_first; n >= 0; n = tile_below(n)) {
+    while (n_q[0] >= 0) {
+      const int n = n_q[0];
       // keep the ring full, then wait for the oldest tile
       unsigned pres_new = 0;
-      if (n_load >= 0) {
-        pres_new = issue_tile(n_load, slot_load, &dlq[DSTAGES - 1]);
-        n_load = tile_below(n_load);
-      }
+      const int n_new = next_fetch();
+      if (n_new >= 0) pres_new = issue_tile(n_new, slot_load, &dlq[DSTAGES - 1]);
       cp_async_commit();
       present_q[DSTAGES - 1] = pres_new;
+      n_q[DSTAGES - 1] = n_new;
       slot_load = (slot_load + 1) % DSTAGES;
       cp_async_wait<DSTAGES - 1>();
       __syncwarp();
       const unsigned present = present_q[0];
 #pragma unroll
-      for (int i = 0; i + 1 < DSTAGES; ++i) present_q[i] = present_q[i + 1];
+      for (int i = 0; i + 1 < DSTAGES; ++i) {
+        present_q[i] = present_q[i + 1];
+        n_q[i] = n_q[i + 1];
+      }
       const uint32_t kt = smem_u32(ring + slot * 2 * SM::kTile);
       const uint32_t vt = kt + SM::kTile;
 
@@ -350,7 +377,7 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
 
       // ---- gated: bound of the gate over the tile, running maximum, skip
       // (flash_sparse_attn/ops/triton/activations.py:265-299) ------------------------------------------
-      if (KIND == KIND_GATED) {
+      if (KIND == KIND_GATED && !gate_early) {
         float dmax = dlq[0], dmin = dlq[0];
 #pragma unroll
         for (int sft = 8; sft > 0; sft >>= 1) {
@@ -602,6 +629,55 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
   }
 }
 
+// One half-warp per (sequence, KV head, 16-key tile): the extremes of delta over the tile's keys, with the key
+// addressing of the decode kernel (contiguous, packed, paged, gathered) and 0 for keys that do not exist (the
+// reference's masked loads read 0 there, scheduler.py:2572-2600). The decode kernel takes its gate decisions from
+// these before it requests a tile's rows.
+template <typename TO>
+__global__ void __launch_bounds__(256) dec_gate_ext_kernel(const DecKernelParams p) {
+  const int lane = threadIdx.x & 31, l16 = lane & 15;
+  const long long item = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 2 + (lane >> 4);
+  const long long n_items = (long long)p.B * p.Hkv * p.n_tiles;
+  float v = 0.f;
+  if (item < n_items) {
+    const int n = (int)(item % p.n_tiles);
+    const int hkv = (int)((item / p.n_tiles) % p.Hkv);
+    const int b = (int)(item / ((long long)p.n_tiles * p.Hkv));
+    const bool gather = p.flags & F_GATHER, paged = p.flags & F_PAGED;
+    const int off_k = (p.flags & F_VARLEN_K) ? p.cu_k[b] : 0;
+    const int sk = (p.flags & F_USED_K) ? p.used_k[b] : ((p.flags & F_VARLEN_K) ? p.cu_k[b + 1] - off_k : p.sk);
+    const int bk = (p.flags & F_VARLEN_K) ? 0 : b;
+    const int capacity = paged ? p.pt_stride * p.page_size
+                               : ((p.flags & F_VARLEN_K) ? p.cu_k[b + 1] - off_k : p.sk_capacity);
+    const int i = n * DTN + l16;
+    int pos;
+    if (gather) {
+      const int topk = p.gather_count ? min(p.topk, p.gather_count[b]) : p.topk;
+      pos = (i < topk) ? p.gather_idx[(long long)b * p.gi_stride + i] : -1;
+      if (p.key_bounds) pos = (pos >= p.key_bounds[2 * b] && pos < p.key_bounds[2 * b + 1]) ? pos - p.key_bounds[2 * b] : -1;
+    } else {
+      pos = (i < sk) ? i : -1;
+    }
+    if (pos >= 0 && pos < capacity) {
+      long long de;
+      if (paged) {
+        const int page = p.page_table[(long long)b * p.pt_stride + pos / p.page_size];
+        de = (long long)page * p.d_sb + (long long)hkv * p.d_sh + (pos % p.page_size);
+      } else {
+        de = (long long)bk * p.d_sb + (long long)hkv * p.d_sh + off_k + pos;
+      }
+      v = float(reinterpret_cast<const TO*>(p.delta)[de]);
+    }
+  }
+  float mx = v, mn = v;
+#pragma unroll
+  for (int sft = 8; sft > 0; sft >>= 1) {
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sft));
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, sft));
+  }
+  if (l16 == 0 && item < n_items) reinterpret_cast<float2*>(p.gate_ws)[item] = make_float2(mx, mn);
+}
+
 template <int HD, typename T, int KIND>
 cudaError_t launch_one(const DecKernelParams& p, cudaStream_t stream) {
   auto kern = dec_kernel<HD, T, KIND>;
@@ -610,6 +686,13 @@ cudaError_t launch_one(const DecKernelParams& p, cudaStream_t stream) {
   if (cudaError_t e = smem_opt_in(kern, smem, opted_in); e != cudaSuccess) return e;
   const long long grid = (long long)p.Hkv * p.B * p.num_splits;
   if (grid <= 0) return cudaSuccess;
+  if (KIND == KIND_GATED && p.gate_ws) {
+    const long long items = (long long)p.B * p.Hkv * p.n_tiles;
+    if (items > 0) {
+      dec_gate_ext_kernel<typename DecTypes<T>::out><<<(unsigned)((items + 15) / 16), 256, 0, stream>>>(p);
+      if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return e;
+    }
+  }
   kern<<<(unsigned)grid, DWARPS * 32, smem, stream>>>(p);
   return cudaGetLastError();
 }

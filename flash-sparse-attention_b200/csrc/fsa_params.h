@@ -114,6 +114,7 @@ struct DecKernelParams {
   const float* qkv_scale;  // optional device fp32 [3]
   const int* thr_sk;       // optional [B]: key count that normalises the softmax threshold (a shard passes the whole length)
   long long op_ss, lp_ss;  // elements between the partials of consecutive splits
+  float* gate_ws;          // gated, optional: float2 (max, min) of delta per (sequence, KV head, 16-key tile)
   const int* gather_count; // optional [B]: leading entries of a row of gather_idx that can be valid
   const int* key_bounds;   // optional [B, 2]: gathered positions outside [lo, hi) are masked, others shifted by -lo
   int D;  // real head size (<= the kernel's HD)

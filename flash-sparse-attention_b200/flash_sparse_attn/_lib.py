@@ -234,6 +234,7 @@ class FsaDecArgs(ctypes.Structure):
         ("gather_count", c_void_p),
         ("out_partial_stride", c_int64),
         ("lse_partial_stride", c_int64),
+        ("gate_ws", c_void_p),
         ("ev_before", c_void_p),
         ("ev_after", c_void_p),
     ]
@@ -278,7 +279,7 @@ class FsaBwdWorkspace(ctypes.Structure):
 
 
 class FsaDecWorkspace(ctypes.Structure):
-    _fields_ = [("out_partial", c_size_t), ("lse_partial", c_size_t)]
+    _fields_ = [("out_partial", c_size_t), ("lse_partial", c_size_t), ("gate_ws", c_size_t)]
 
 
 _lib = None

@@ -184,6 +184,10 @@ def attn_decode(
 
     # split partials [splits, B, Hq, D] / [splits, Hq, B] (base-2 lse): the caller's, or sized by the library
     lib = _lib.load()
+    ws = _lib.FsaDecWorkspace()
+    _lib.check(lib.fsa_decode_workspace_bytes(ctypes.byref(a), ctypes.byref(ws)), "fsa_decode_workspace_bytes")
+    gate_ws = _lib.workspace(ws.gate_ws, device)  # gated kind: extremes of delta per 16-key tile
+    a.gate_ws = _lib.ptr(gate_ws)
     out_partial = lse_partial = None
     if packed_partials is not None:
         # one buffer [splits, B*Hq*(D+1)]: the partial outputs of a split followed by its log-sum-exps
@@ -195,8 +199,6 @@ def attn_decode(
     elif workspace is not None:
         out_partial, lse_partial = workspace
     else:
-        ws = _lib.FsaDecWorkspace()
-        _lib.check(lib.fsa_decode_workspace_bytes(ctypes.byref(a), ctypes.byref(ws)), "fsa_decode_workspace_bytes")
         if ws.out_partial:
             out_partial = _lib.workspace(ws.out_partial, device).view(num_splits, batch, num_heads_q, head_dim)
             lse_partial = _lib.workspace(ws.lse_partial, device).view(num_splits, num_heads_q, batch)

@@ -286,6 +286,10 @@ typedef struct FsaDecArgs {
    * split side by side in ONE buffer (to ship them with a single all-gather) sets both to
    * batch*heads_q*(head_dim + 1) and points lse_partial at out_partial + batch*heads_q*head_dim. */
   int64_t out_partial_stride, lse_partial_stride;
+  /* gated kind, optional: workspace of fsa_decode_workspace_bytes().gate_ws bytes (written by this call) with the
+   * extremes of delta per 16-key tile; with it the gate-skip decision of a tile is taken before its rows are
+   * requested, without it when the tile is consumed. */
+  float* gate_ws;
   void* ev_before;
   void* ev_after;
 } FsaDecArgs;
@@ -366,6 +370,7 @@ typedef struct FsaBwdWorkspace {
 } FsaBwdWorkspace;
 typedef struct FsaDecWorkspace {
   size_t out_partial, lse_partial;
+  size_t gate_ws; /* gated kind */
 } FsaDecWorkspace;
 int fsa_fwd_workspace_bytes(const FsaFwdArgs* args, FsaFwdWorkspace* sizes);
 int fsa_bwd_workspace_bytes(const FsaBwdArgs* args, FsaBwdWorkspace* sizes);
