@@ -361,6 +361,14 @@ int fsa_fwd(const FsaFwdArgs* a, void* stream_) {
   if (a->flags & FSA_F_ADAPT_GATE) f |= fsa::F_ADAPT_GATE;
   p.flags = f;
 
+  if (a->q_block_scale || a->k_block_scale || a->v_block_scale) {
+    if (!a->q_block_scale || !a->k_block_scale || !a->v_block_scale || a->qkv_scale)
+      return FSA_ERR_INVALID_ARG;
+    if (!fp8 || a->kind == FSA_KIND_GATED || gpack > 1 || paged) return FSA_ERR_UNSUPPORTED;
+    p.q_bscale = a->q_block_scale;
+    p.k_bscale = a->k_block_scale;
+    p.v_bscale = a->v_block_scale;
+  }
   if (a->kind == FSA_KIND_GATED) {
     if (!a->gate_ws) return FSA_ERR_INVALID_ARG;
     fsa::GateExtParams ge;

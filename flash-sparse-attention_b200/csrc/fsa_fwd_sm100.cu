@@ -616,7 +616,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       const float visible = causal ? float(q_idx + (si.sk - si.sq) + 1) : float(si.sk);
       thr_log2 = log2f(fmaxf(fminf(p.softmax_thr / visible, 1.0f), 0.0f));
     }
-    const float c = p.qkv_scale ? p.scale_log2 * p.qkv_scale[0] * p.qkv_scale[1] : p.scale_log2;
+    // Block-scaled FP8: the scale of the logits changes from key tile to key tile, so the scores are multiplied by it
+    // right after they leave TMEM and everything below works on scaled logits (cc = 1). The value block's scale is
+    // folded into P relative to a running reference v_run - the largest value scale this row has met so far - and
+    // the output accumulator is rescaled when that reference grows (like the running maximum); the output is
+    // multiplied by the final reference. Blocks more than 2^9 below the running reference underflow in FP8 P, i.e.
+    // contributions that small relative to the largest block a row has seen are dropped.
+    const bool bscaled = F8 && p.k_bscale != nullptr;
+    const float* kbs = bscaled ? p.k_bscale + ((long long)si.b * p.Hkv + si.hkv) * p.n_tiles_k : nullptr;
+    const float* vbs = bscaled ? p.v_bscale + ((long long)si.b * p.Hkv + si.hkv) * p.n_tiles_k : nullptr;
+    const float c = bscaled ? p.scale_log2 * p.q_bscale[((long long)si.b * p.Hq + q_head) * p.num_m_blocks +
+                                                        (mb < p.num_m_blocks ? mb : 0)]
+                            : (p.qkv_scale ? p.scale_log2 * p.qkv_scale[0] * p.qkv_scale[1] : p.scale_log2);
+    const float cc = bscaled ? 1.0f : c;  // factor between the values held in sr[] and base-2 logits
+    float v_run = 0.f;  // block-scaled: running reference of the value scale (uniform over the tile's rows)
     const float v_scale = p.qkv_scale ? p.qkv_scale[2] : p.v_scale;
     float m_ref = -INFINITY;  // reference maximum all stored exponentials are relative to
     float l_ref = 0.f;        // sum of exp2((s - m_ref) * c)
@@ -672,6 +685,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
 #pragma unroll
       for (int ch = 0; ch < TN / 32; ++ch) tmem_ld32(tS + ch * 32, &sr[ch * 32]);
       tmem_ld_wait();
+      float p_mul = 1.0f, o_mul = 1.0f;
+      if constexpr (F8) {
+        if (bscaled) {
+          const float ct = c * kbs[n];
+#pragma unroll
+          for (int i = 0; i < TN; ++i) sr[i] = __float_as_uint(__uint_as_float(sr[i]) * ct);
+        }
+      }
       if (KIND == KIND_GATED) {
         // logits = (q.k + g(alpha * delta_j)) * scale, g = logsigmoid or identity
         // (flash_sparse_attn/ops/triton/flash_gated_fwd.py:104-122, activations.py:245-262)
@@ -730,7 +751,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       // ---- tile skip vote (flash_sparse_attn/ops/triton/activations.py:129-138) -----------------
       bool skip = false;
       if (KIND != KIND_DENSE) {
-        const float d = (m_cur - m_ref) * c - lg_l;
+        const float d = (m_cur - m_ref) * cc - lg_l;
         const float val = d - thr_log2;
         const unsigned want = __ballot_sync(0xffffffffu, val >= 0.0f);
         const unsigned drop = __ballot_sync(0xffffffffu, val < 0.0f);
@@ -777,29 +798,40 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
       // ---- move the reference maximum only when it lags by more than 2^8 -------------------------
       float m_cand = fmaxf(m_cur, m_ref);
       if (mode != FSA_MASK_NONE) m_cand = fmaxf(m_cand, -1e6f);
-      const bool need = !((m_cand - m_ref) * c <= 8.0f);  // also true on the first tile (m_ref = -inf)
+      const bool need = !((m_cand - m_ref) * cc <= 8.0f);  // also true on the first tile (m_ref = -inf)
       float scale = 1.0f;
       if (need) {
-        scale = ex2_approx((m_ref - m_cand) * c);
+        scale = ex2_approx((m_ref - m_cand) * cc);
         m_ref = m_cand;
         l_ref *= scale;
       }
+      if constexpr (F8) {
+        if (bscaled) {  // only for a tile that is kept: a skipped tile must not move the reference
+          const float svn = vbs[n];
+          if (svn > v_run) {  // the accumulator moves to the larger unit (nothing to move before the first P V)
+            o_mul = v_run > 0.f ? __fdividef(v_run, svn) : 1.0f;
+            v_run = svn;
+          }
+          p_mul = v_run > 0.f ? __fdividef(svn, v_run) : 0.0f;
+        }
+      }
       // s_full for this tile was committed after the previous P V of this group, so O is at rest
-      if (have_o && __any_sync(0xffffffffu, need)) {
+      if (have_o && (__any_sync(0xffffffffu, need) || o_mul != 1.0f)) {
+        const float o_scale = scale * o_mul;
 #pragma unroll
         for (int ch = 0; ch < OCH; ++ch) {
           uint32_t r[32];
           tmem_ld32(tO + ch * 32, r);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * scale);
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * o_scale);
           tmem_st32(tO + ch * 32, r);
         }
       }
 
       // ---- P = exp2(S*c - m*c), row sum, publish P (16-bit pairs) over the S columns -----------------
-      const float2 c2 = make_float2(c, c);
-      const float neg_mc = -(m_ref * c);
+      const float2 c2 = make_float2(cc, cc);
+      const float neg_mc = -(m_ref * cc);
       const float2 nm2 = make_float2(neg_mc, neg_mc);
       float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
@@ -819,7 +851,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
           sum2[0] = add2(sum2[0], ea);
           sum2[1] = add2(sum2[1], eb);
           if constexpr (F8) {
-            pk[i >> 2] = pack4_fp8<T>(ea.x, ea.y, eb.x, eb.y);
+            pk[i >> 2] = bscaled ? pack4_fp8<T>(ea.x * p_mul, ea.y * p_mul, eb.x * p_mul, eb.y * p_mul)
+                                 : pack4_fp8<T>(ea.x, ea.y, eb.x, eb.y);
           } else {
             pk[i >> 1] = pack2<T>(ea.x, ea.y);
             pk[(i >> 1) + 1] = pack2<T>(eb.x, eb.y);
@@ -847,8 +880,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     }
     if (ok && q_valid[q]) {
       const bool dead = (l_ref == 0.0f) || (l_ref != l_ref);
-      const float inv = dead ? 1.0f : v_scale / l_ref;
-      float lse = dead ? -INFINITY : m_ref * c + log2f(l_ref);
+      const float inv = dead ? 1.0f : (bscaled ? v_run : v_scale) / l_ref;
+      float lse = dead ? -INFINITY : m_ref * cc + log2f(l_ref);
       if (!(p.flags & F_LSE_LOG2)) lse *= 0.6931471805599453f;
       const long long tok = si.off_q + q_idx;
       if (rm.row_ok)

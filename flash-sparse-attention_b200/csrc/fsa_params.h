@@ -55,6 +55,9 @@ struct alignas(64) FwdKernelParams {
   float scale_log2, softmax_thr, gate_thr, v_scale;
   const float* qkv_scale;  // optional device fp32 [3]: de-quantisation scales of q, k, v
   const float* gate_ws;    // gated: per-tile extremes, see GateWsLayout
+  const float* q_bscale;   // block-scaled FP8: [B, Hq, num_m_blocks], [B, Hkv, n_tiles_k] x 2; or all null
+  const float* k_bscale;
+  const float* v_bscale;
   unsigned flags;
 };
 

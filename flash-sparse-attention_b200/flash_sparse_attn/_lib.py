@@ -88,8 +88,33 @@ class FsaFwdArgs(ctypes.Structure):
         ("gate_threshold", c_float),
         ("qkv_scale", c_void_p),
         ("gate_ws", c_void_p),
+        ("q_block_scale", c_void_p),
+        ("k_block_scale", c_void_p),
+        ("v_block_scale", c_void_p),
         ("ev_before", c_void_p),
         ("ev_after", c_void_p),
+    ]
+
+
+class FsaBlockQuantArgs(ctypes.Structure):
+    _fields_ = [
+        ("x16", c_void_p),
+        ("x8", c_void_p),
+        ("scales", c_void_p),
+        ("cu_seqlens", c_void_p),
+        ("x_stride_b", c_int64),
+        ("x_stride_s", c_int64),
+        ("x_stride_h", c_int64),
+        ("q_stride_b", c_int64),
+        ("q_stride_s", c_int64),
+        ("q_stride_h", c_int64),
+        ("batch", c_int32),
+        ("seqlen", c_int32),
+        ("heads", c_int32),
+        ("head_dim", c_int32),
+        ("x_dtype", c_int32),
+        ("fp8_dtype", c_int32),
+        ("dequantize", c_int32),
     ]
 
 
@@ -322,6 +347,8 @@ def load():
     lib.fsa_fp8_widen.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
     lib.fsa_topk_indices.restype = c_int
     lib.fsa_topk_indices.argtypes = [c_void_p, c_int, c_int, c_int, c_int64, c_int, c_void_p, c_int, c_void_p]
+    lib.fsa_quantize_fp8_blockwise.restype = c_int
+    lib.fsa_quantize_fp8_blockwise.argtypes = [POINTER(FsaBlockQuantArgs), c_void_p]
     lib.fsa_kv_append.restype = c_int
     lib.fsa_kv_append.argtypes = [POINTER(FsaKvAppendArgs), c_void_p]
     lib.fsa_localize_indices.restype = c_int

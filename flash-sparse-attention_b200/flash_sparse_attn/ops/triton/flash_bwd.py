@@ -99,7 +99,11 @@ def attn_backward(
             num_heads_q=num_heads_q, num_heads_kv=num_heads_kv, head_dim=head_dim, is_quant=is_quant, device=device,
         )
 
-    if is_quant:
+    if is_quant and quant.is_block_scale(key_scale):
+        query = quant.dequantize_fp8_blockwise(query, query_scale, dout.dtype, cu_seqlens_q, max_seqlen_q)
+        key = quant.dequantize_fp8_blockwise(key, key_scale, dout.dtype, cu_seqlens_k, max_seqlen_k)
+        value = quant.dequantize_fp8_blockwise(value, value_scale, dout.dtype, cu_seqlens_k, max_seqlen_k)
+    elif is_quant:
         query = _dequantize(query, query_scale, dout.dtype)
         key = _dequantize(key, key_scale, dout.dtype)
         value = _dequantize(value, value_scale, dout.dtype)

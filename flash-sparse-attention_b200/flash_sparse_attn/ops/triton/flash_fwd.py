@@ -112,7 +112,14 @@ def attn_forward(
             (num_heads_q, total_q) if varlen else (batch, num_heads_q, seqlen_q))
 
     qkv_scale = None
-    if is_quant:
+    block_scales = None
+    if is_quant and quant.is_block_scale(key_scale):
+        # block-scaled FP8 (scales per 128 positions and head): native kernels only; the scales go in per tile
+        if head_dim != 128 or kind == "gated" or pack_gqa or page_table is not None:
+            raise RuntimeError("block-scaled FP8 needs head_dim 128, the dense or sparse kind, no packed GQA, no paging")
+        sq, sk, sv = (t.float().contiguous() for t in (query_scale, key_scale, value_scale))
+        block_scales = (sq, sk, sv)
+    elif is_quant:
         # FP8 inputs: widened (exactly) to bf16 in one pass; the per-tensor scales stay on the device and
         # enter the kernel as in scheduler.py:298-307 (logit scale *= q_scale * k_scale, out *= v_scale)
         qkv_scale = quant.scales_f32(query_scale, key_scale, value_scale, device)
@@ -153,6 +160,8 @@ def attn_forward(
     a.status = _lib.status_word(device).data_ptr()
     a.tile_map = _lib.ptr(tile_map)
     a.qkv_scale = _lib.ptr(qkv_scale)
+    if block_scales is not None:
+        a.q_block_scale, a.k_block_scale, a.v_block_scale = (t.data_ptr() for t in block_scales)
     if varlen:
         a.q_stride_b, a.q_stride_s, a.q_stride_h = 0, query.stride(0), query.stride(1)
         a.k_stride_b, a.k_stride_s, a.k_stride_h = 0, key.stride(0), key.stride(1)

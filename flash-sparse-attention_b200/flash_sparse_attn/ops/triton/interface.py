@@ -35,8 +35,15 @@ def _normalise(single_query: bool, is_causal, window_sizes, is_local, num_splits
     return is_causal, is_local, is_split_kv, is_split_qo
 
 
-def _maybe_quantize(is_quant, query, key, value, query_scale, key_scale, value_scale):
+def _maybe_quantize(is_quant, query, key, value, query_scale, key_scale, value_scale, cu_q=None, cu_k=None, max_q=None,
+                    max_k=None, block_ok=True):
     if is_quant and (query_scale is None or key_scale is None or value_scale is None):
+        if quant.block_scaled_enabled() and block_ok and query.shape[-1] == 128:
+            # internal format (not in the reference): e4m3 with one scale per 128 positions and head
+            query, query_scale = quant.quantize_fp8_blockwise(query, cu_seqlens=cu_q, max_seqlen=max_q)
+            key, key_scale = quant.quantize_fp8_blockwise(key, cu_seqlens=cu_k, max_seqlen=max_k)
+            value, value_scale = quant.quantize_fp8_blockwise(value, cu_seqlens=cu_k, max_seqlen=max_k)
+            return query, key, value, query_scale, key_scale, value_scale
         query, query_scale = quant.quantize_fp8(query)
         key, key_scale = quant.quantize_fp8(key)
         value, value_scale = quant.quantize_fp8(value)
@@ -61,7 +68,8 @@ class _AttnFunc(torch.autograd.Function):
             single, is_causal, window_sizes, is_local, num_splits, is_split_kv, is_split_qo
         )
         query, key, value, query_scale, key_scale, value_scale = _maybe_quantize(
-            is_quant, query, key, value, query_scale, key_scale, value_scale
+            is_quant, query, key, value, query_scale, key_scale, value_scale, cu_seqlens_q, cu_seqlens_k,
+            max_seqlen_q, max_seqlen_k, block_ok=(kind != "gated" and not pack_gqa and page_table is None)
         )
         if kind == "gated":
             # kernels read alpha as [.., heads, positions] rows, like the reference's transposed copies
@@ -385,7 +393,7 @@ def _decode(kind, query, key, value, alpha, delta, cu_seqlens_k, max_seqlen_k, s
             num_splits, page_table, gather_kv_indices, seqused_k, out, lse, is_autotune, tile_mn, skip_checks,
             return_lse):
     query, key, value, query_scale, key_scale, value_scale = _maybe_quantize(
-        is_quant, query, key, value, query_scale, key_scale, value_scale
+        is_quant, query, key, value, query_scale, key_scale, value_scale, block_ok=False  # decode: per tensor only
     )
     if window_sizes is not None:
         is_local = True

@@ -119,6 +119,18 @@ typedef struct FsaFwdArgs {
    * of alpha and delta, from which every role of the kernel derives the gate-skip decisions before a key tile
    * is loaded. */
   float* gate_ws;
+  /* Block-scaled FP8 inputs (dtype FSA_DT_E4M3 / FSA_DT_E5M2, head_dim 128, dense and sparse kinds, no packed
+   * GQA): fp32 scales per 128-position block, as fsa_quantize_fp8_blockwise writes them -
+   * q_block_scale [batch, heads_q, ceil(seqlen_q / 128)], k_block_scale / v_block_scale [batch, heads_kv,
+   * ceil(seqlen_k / 128)] (blocks counted from the start of each sequence, i.e. the kernel's own tiles). All
+   * three or none; with them qkv_scale must be null. logits = (Q8 K8^T) * q_scale[m] * k_scale[n] *
+   * softmax_scale per tile; P is multiplied by v_scale[n] / v_run before it is rounded to FP8, v_run being the
+   * largest value scale the query tile has met so far (the accumulator is rescaled when it grows), and the
+   * output by the final v_run. Not in the reference, whose quantisation is per tensor
+   * (flash_sparse_attn/ops/triton/quant.py:42-64). */
+  const float* q_block_scale;
+  const float* k_block_scale;
+  const float* v_block_scale;
   void* ev_before;
   void* ev_after;
 } FsaFwdArgs;
@@ -386,6 +398,27 @@ const char* fsa_status_string(int code);
  */
 int fsa_quantize_fp8(const void* x, void* x_fp8, void* scale_out, float* amax_ws, int64_t n, int x_dtype,
                      int fp8_dtype, void* stream);
+
+/*
+ * Block-scaled FP8 quantisation of a [batch, seqlen, heads, head_dim] tensor (or packed [total, heads, head_dim] with
+ * cu_seqlens; seqlen is then the longest sequence): for every (sequence, head, block of 128 consecutive positions
+ * counted from the start of the sequence) scale = max|x| / FP8_MAX (0 for an all-zero block), x8 = rne(x / scale),
+ * scales[batch, heads, ceil(seqlen / 128)] fp32. With `dequantize` set the call runs the other way round:
+ * x16 = x8 * scale (what the backward pass runs on). head_dim a multiple of 8 up to 128; strides in elements.
+ * Not in the reference (per-tensor scales only, quant.py:42-64): an internal format with its own error bound.
+ */
+typedef struct FsaBlockQuantArgs {
+  void* x16;      /* bf16 / fp16: input of the quantisation, output of the de-quantisation */
+  void* x8;       /* FP8: output / input */
+  float* scales;  /* [batch, heads, ceil(seqlen / 128)] */
+  const int32_t* cu_seqlens; /* [batch + 1] or null */
+  int64_t x_stride_b, x_stride_s, x_stride_h;
+  int64_t q_stride_b, q_stride_s, q_stride_h;
+  int32_t batch, seqlen, heads, head_dim;
+  int32_t x_dtype, fp8_dtype;
+  int32_t dequantize;
+} FsaBlockQuantArgs;
+int fsa_quantize_fp8_blockwise(const FsaBlockQuantArgs* args, void* stream);
 
 /*
  * out[i] = (out_dtype)(float(x_fp8[i]) * *scale), scale optional (one element of out_dtype on the

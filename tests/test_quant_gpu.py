@@ -196,3 +196,144 @@ def test_quant_decode_paged_gather_split(fp8):
                                                   num_splits=4, **kw)
     _sync()
     assert_close("quant-paged-gather-decode", out, eager.gather_decode(qd, kd, vd, idx), **QTOL)
+
+
+# ---------------------------------------------------------------------------------------------------
+# block-scaled e4m3: an internal format (one scale per 128 positions and head), not in the reference
+# ---------------------------------------------------------------------------------------------------
+def _block_ref(x, fp8=torch.float8_e4m3fn, fmax=448.0):
+    """Torch restatement of fsa_quantize_fp8_blockwise on [B, S, H, D]."""
+    b, s, h, d = x.shape
+    nblk = -(-s // 128)
+    pad = nblk * 128 - s
+    xf = torch.nn.functional.pad(x.float(), (0, 0, 0, 0, 0, pad)).view(b, nblk, 128, h, d)
+    amax = xf.abs().amax(dim=(2, 4))                                   # [B, nblk, H]
+    # (a python scalar divided by a tensor is evaluated as reciprocal * scalar by torch: spell the division out)
+    scale = torch.where(amax > 0, amax / fmax, torch.zeros_like(amax))
+    inv = torch.where(amax > 0, torch.full_like(amax, fmax) / amax, torch.zeros_like(amax))
+    x8 = (xf * inv[:, :, None, :, None]).to(fp8).view(b, nblk * 128, h, d)[:, :s]
+    return x8, scale.permute(0, 2, 1).contiguous()
+
+
+def test_blockwise_quantiser_is_bit_exact():
+    from flash_sparse_attn.ops.triton import quant
+
+    g = torch.Generator().manual_seed(21)
+    x = (torch.randn(2, 300, 3, 128, generator=g) * torch.rand(2, 300, 3, 1, generator=g) * 8).to(torch.bfloat16)
+    x[0, 128:256, 1] = 0  # an all-zero block gets scale 0
+    x8, sc = quant.quantize_fp8_blockwise(x.to(DEV))
+    _sync()
+    r8, rs = _block_ref(x)
+    assert torch.equal(sc.cpu(), rs)
+    assert torch.equal(x8.cpu().view(torch.uint8), r8.view(torch.uint8))
+    back = quant.dequantize_fp8_blockwise(x8, sc, torch.bfloat16)
+    _sync()
+    ref_back = (r8.float() * rs.permute(0, 2, 1).repeat_interleave(128, dim=1)[:, :300, :, None]).to(torch.bfloat16)
+    assert torch.equal(back.cpu(), ref_back)
+
+
+@pytest.mark.parametrize("kind,causal,split", [("dense", False, False), ("sparse", True, False), ("sparse", True, True)])
+def test_block_scaled_forward_matches_the_dequantised_oracle(kind, causal, split):
+    fsa = _ops()
+    from flash_sparse_attn.ops.triton import quant
+
+    b, sq, sk, hq, hkv, d = 2, 333, 400, 4, 2, 128
+    q, k, v = seeded_qkv(31, b, sq, sk, hq, hkv, d)
+    (q8, sq_), (k8, sk_), (v8, sv_) = (quant.quantize_fp8_blockwise(t.to(DEV)) for t in (q, k, v))
+    qd, kd, vd = (quant.dequantize_fp8_blockwise(t, s, torch.bfloat16).cpu() for t, s in ((q8, sq_), (k8, sk_), (v8, sv_)))
+    ref = eager.forward(qd, kd, vd, None, causal)
+    f = fsa.flash_dense_attn_func if kind == "dense" else fsa.flash_sparse_attn_func
+    kw = dict(softmax_threshold=-128.0) if kind == "sparse" else {}
+    if split:
+        kw.update(is_split_kv=True, num_splits=3)
+    out = f(q8, k8, v8, is_causal=causal, query_scale=sq_, key_scale=sk_, value_scale=sv_, is_quant=True, **kw)
+    _sync()
+    assert out.dtype == torch.bfloat16
+    assert_close(f"blockquant-{kind}", out, ref, **QTOL)
+
+
+def test_block_scaled_error_bound_against_the_exact_result():
+    """Error of the block-scaled e4m3 forward against the EXACT (unquantised) attention on iid N(0, 1) inputs: the
+    stated bound of the format is 4e-2 mean absolute / 2.5e-1 maximum at S = 1024, D = 128 (e4m3 keeps three
+    mantissa bits; Q, K, V and P are all rounded). FP8 is a floating-point format, so on ordinary data one scale per
+    tensor is about as accurate; block scales protect blocks whose magnitude lies more than 2^9 below the tensor's
+    maximum (here: values scaled by 2^-13 after the first 128 positions), where per-tensor e4m3 underflows."""
+    fsa = _ops()
+    from flash_sparse_attn.ops.triton import quant
+
+    b, s, hq, hkv, d = 1, 1024, 4, 2, 128
+    q, k, v = seeded_qkv(33, b, s, s, hq, hkv, d)
+
+    def run(vv, blockwise):
+        qd, kd, vd = (t.to(DEV) for t in (q, k, vv))
+        if blockwise:
+            (q8, a), (k8, b_), (v8, c) = (quant.quantize_fp8_blockwise(t) for t in (qd, kd, vd))
+        else:
+            (q8, a), (k8, b_), (v8, c) = (quant.quantize_fp8(t, torch.float8_e4m3fn) for t in (qd, kd, vd))
+        out = fsa.flash_sparse_attn_func(q8, k8, v8, is_causal=True, query_scale=a, key_scale=b_, value_scale=c,
+                                         is_quant=True, softmax_threshold=-128.0)
+        _sync()
+        return out.float().cpu()
+
+    exact = eager.forward(q, k, v, None, True).float()
+    err = (run(v, True) - exact).abs()
+    assert err.mean().item() < 4e-2 and err.max().item() < 2.5e-1, (err.mean().item(), err.max().item())
+    # non-causal rows that only see small values: keys 128.. carry V scaled by 2^-20 (below the smallest
+    # e4m3 step of a per-tensor scale, so that form loses them entirely), queries look at those alone
+    v_small = v.clone()
+    v_small[:, 128:] = (v_small[:, 128:].float() * 2.0 ** -20).to(torch.bfloat16)
+    ws = torch.tensor([[0, 0, 0, 64]] * hkv, dtype=torch.int32)  # 64-key sliding window: rows >= 192 see only small V
+    exact_w = eager.forward(q, k, v_small, None, True, is_local=True, window_sizes=ws).float()[:, 256:]
+
+    def run_w(blockwise):
+        qd, kd, vd = (t.to(DEV) for t in (q, k, v_small))
+        quantise = quant.quantize_fp8_blockwise if blockwise else (lambda t: quant.quantize_fp8(t, torch.float8_e4m3fn))
+        (q8, a), (k8, b_), (v8, c) = (quantise(t) for t in (qd, kd, vd))
+        out = fsa.flash_sparse_attn_func(q8, k8, v8, is_causal=True, window_sizes=ws.to(DEV), query_scale=a,
+                                         key_scale=b_, value_scale=c, is_quant=True, softmax_threshold=-128.0)
+        _sync()
+        return out.float().cpu()[:, 256:]
+
+    rel = lambda o: ((o - exact_w).abs().mean() / exact_w.abs().mean()).item()  # noqa: E731
+    r_block, r_tensor = rel(run_w(True)), rel(run_w(False))
+    assert r_block < 0.1 and r_tensor > 0.5, (r_block, r_tensor)
+
+
+def test_block_scaled_switch_forward_backward_and_packed():
+    """set_block_scaled(True): is_quant=True quantises to block-scaled e4m3 inside the operator; the backward runs on
+    the de-quantised tensors. Batched and packed sequences."""
+    fsa = _ops()
+    from flash_sparse_attn.ops.triton import quant
+
+    quant.set_block_scaled(True)
+    try:
+        b, s, hq, hkv, d = 2, 300, 4, 2, 128
+        q, k, v = seeded_qkv(35, b, s, s, hq, hkv, d)
+        do = torch.randn(b, s, hq, d, generator=torch.Generator().manual_seed(36)).to(torch.bfloat16)
+        leaves = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+        out = fsa.flash_sparse_attn_func(*leaves, is_causal=True, is_quant=True, softmax_threshold=-128.0)
+        out.backward(do.to(DEV))
+        _sync()
+        qd, kd, vd = (quant.dequantize_fp8_blockwise(*quant.quantize_fp8_blockwise(t.to(DEV)), torch.bfloat16).cpu()
+                      for t in (q, k, v))
+        assert_close("blockquant-switch-out", out, eager.forward(qd, kd, vd, None, True), **QTOL)
+        for name, t, r in zip(("dq", "dk", "dv"), leaves, eager.backward(qd, kd, vd, do, None, True)):
+            assert_close("blockquant-switch-" + name, t.grad, r, **QTOL, ew_atol=2.5e-1)
+        # packed: two sequences of 200 and 333 tokens
+        cu = torch.tensor([0, 200, 533], dtype=torch.int32)
+        g = torch.Generator().manual_seed(37)
+        qp = torch.randn(533, hq, d, generator=g).to(torch.bfloat16)
+        kp = torch.randn(533, hkv, d, generator=g).to(torch.bfloat16)
+        vp = torch.randn(533, hkv, d, generator=g).to(torch.bfloat16)
+        outp = fsa.flash_sparse_attn_varlen_func(qp.to(DEV), kp.to(DEV), vp.to(DEV), cu.to(DEV), cu.to(DEV), 333, 333,
+                                                 is_causal=True, is_quant=True, softmax_threshold=-128.0)
+        _sync()
+        for i, (lo, hi) in enumerate(((0, 200), (200, 533))):
+            parts = []
+            for t in (qp, kp, vp):
+                x8, sc = quant.quantize_fp8_blockwise(t[lo:hi].unsqueeze(0).to(DEV))
+                parts.append(quant.dequantize_fp8_blockwise(x8, sc, torch.bfloat16).cpu())
+            ref = eager.forward(*parts, None, True)
+            assert_close(f"blockquant-packed-{i}", outp[lo:hi].unsqueeze(0), ref, **QTOL)
+    finally:
+        quant.set_block_scaled(False)
