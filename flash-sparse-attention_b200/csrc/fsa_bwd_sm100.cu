@@ -20,9 +20,12 @@
 //   dK  += dS^T Q      (A = dS^T from shared memory, K-major)
 //   dQ   = dS K        (A = dS^T from shared memory, read MN-major)
 //
-// Roles (384 threads): warps 0-7 compute (warps 0-3 own query columns 0-63 of the tile, warps 4-7
-// columns 64-127; both cover all 128 key lanes), warp 8 producer (TMA), warp 9 MMA issuer, warp 10 dQ
-// drain (deterministic mode only: takes the turns and issues the TMA reduce-adds of the staged dQ tiles).
+// Roles (512 threads, four warpgroups): warps 0-7 compute P^T and dS^T (warps 0-3 own query columns 0-63 of the
+// tile, warps 4-7 columns 64-127; both cover all 128 key lanes), warp 8 producer (TMA), warp 9 MMA issuer, warp 10
+// dQ drain (deterministic mode only: takes the turns and issues the TMA reduce-adds of the staged dQ tiles), warp
+// 11 idle (register budgets are set per warpgroup), warps 12-15 dQ read-out: TMEM -> registers -> staging ->
+// TMA reduce-add, so that the accumulator block shared by dP^T and dQ is free again a few hundred cycles after
+// the dQ MMAs finish and the compute warps never touch dQ.
 // TMEM columns: [0,128) S^T, then P^T packed into [0,32) and [96,128) | [128,256) dP^T, later dQ |
 // [256,384) dV | [384,512) dK.
 #include "fsa_ptx.cuh"
@@ -37,7 +40,7 @@ namespace {
 
 constexpr int TM = 128;  // query rows per step
 constexpr int TN = 128;  // keys per CTA
-constexpr int NTHREADS = 384;
+constexpr int NTHREADS = 512;
 
 template <int HD>
 struct BwdSmem {
@@ -59,10 +62,10 @@ struct BwdBars {
   uint64_t dd_sync;  // gated: second column group -> first, partial ddelta handed over in shared memory
   uint64_t stg_full, stg_free;  // dQ staging: compute warps -> drain warp (job posted) and back (buffers read)
   int job[2][4];                // job descriptors {first row, head, query tile, code}, slot = job index & 1
+  int dqjob[2][4];              // MMA issuer -> dQ warps: {first row, head, query tile, code} of the dQ tile in TMEM
   uint32_t tmem_base;
   int abort_flag;
-  int skip_flag[2];
-  int vote_any[2][8];
+  unsigned char vote_any[2][8];
 };
 static_assert(sizeof(BwdBars) <= 256, "barrier block too large");
 
@@ -108,29 +111,29 @@ __device__ __forceinline__ SegList make_segments(const FsaBwdSched& s, bool caus
   }
   return l;
 }
-// Walks the query tiles of a SegList in order without searching: (m, mode) of the current step.
+// Walks the query tiles of a SegList in order without searching: (m, mode) of the current step. The common case
+// (the next tile of the same segment) is an increment and a compare; the segment table is only touched when a
+// segment ends.
 struct SegIter {
-  int seg, m, mode;
+  int seg, m, end, mode;
 };
 __device__ __forceinline__ SegIter seg_begin(const SegList& l) {
   SegIter s;
   s.seg = 0;
   s.m = l.n > 0 ? l.beg[0] : 0;
+  s.end = l.n > 0 ? l.end[0] : 0;
   s.mode = l.n > 0 ? l.mode[0] : FSA_MASK_NONE;
   return s;
 }
 __device__ __forceinline__ void seg_next(const SegList& l, SegIter& s) {
   s.m++;
-  bool wrap = false;
-#pragma unroll
-  for (int i = 0; i < 6; ++i)
-    if (i == s.seg && i < l.n && s.m >= l.end[i]) wrap = true;
-  if (wrap) {
+  if (s.m >= s.end) {
     s.seg++;
 #pragma unroll
     for (int i = 1; i < 6; ++i)
       if (i == s.seg && i < l.n) {
         s.m = l.beg[i];
+        s.end = l.end[i];
         s.mode = l.mode[i];
       }
   }
@@ -297,13 +300,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
     mbar_init(&bars->dp_full, 1);
     mbar_init(&bars->ds_full, 8);
     mbar_init(&bars->dq_full, 1);
-    mbar_init(&bars->dq_empty, 8);
+    mbar_init(&bars->dq_empty, 4);
     mbar_init(&bars->do_full, 1);
     mbar_init(&bars->do_empty, 1);
     mbar_init(&bars->vote_sync, 8);
     mbar_init(&bars->acc_full, 1);
     mbar_init(&bars->dd_sync, 4);
-    mbar_init(&bars->stg_full, 8);
+    mbar_init(&bars->stg_full, 4);
     mbar_init(&bars->stg_free, 1);
     bars->abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
     mbar_fence_init();
@@ -319,8 +322,100 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
   const int bq = (p.flags & F_VARLEN_Q) ? 0 : b;
   const int bk = (p.flags & F_VARLEN_K) ? 0 : b;
 
-  if (warp >= 8) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+  if (warp >= 12) {
+    // =============================== dQ read-out ================================================
+    // One warp per TMEM lane quadrant (32 query rows). Per dQ tile: 64 columns at a time leave TMEM for registers
+    // and go through this warp's two 4 KB staging buffers into TMA reduce-adds; the TMEM block is handed back
+    // as soon as the last columns are in registers. The path from an SM to L2 moves about 21 bytes per clock, so
+    // the 64 KB of a tile take about as long as the MMAs of a step: these warps pace themselves on the reads of
+    // the staging buffers and nobody else waits for them.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+    const int wq = warp & 3;
+    const uint32_t lane_addr = uint32_t(wq * 32) << 16;
+    uint8_t* stage = smem + SM::kStage + wq * 8192;
+    const bool det = p.flags & F_DETERMINISTIC;
+    constexpr int NP = HD / 64;  // 64-column pairs of 32-column chunks per dQ tile
+    constexpr uint32_t TMEM_DQ = 128;
+    bool ok = !*abort_flag;
+    int jobs = 0;  // staging jobs handed to the drain warp so far (deterministic mode; same count in all four warps)
+    // wait until the drain warp's TMA reads of the previous job have left the staging buffers
+    auto stage_wait_free = [&]() {
+      if (jobs > 0 && !mbar_wait(&bars->stg_free, (jobs - 1) & 1, abort_flag)) ok = false;
+    };
+    // hand a job to the drain warp: {first row of the tile, head, query tile, code}
+    // code = kind (0 chunk pair, 1 pass, 2 exit) | pair << 4 | last pair of the tile << 8
+    auto stage_post = [&](int row0, int head, int m, int code) {
+      if (wq == 0 && lane == 0) {
+        volatile int* jd = bars->job[jobs & 1];
+        jd[0] = row0;
+        jd[1] = head;
+        jd[2] = m;
+        jd[3] = code;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->stg_full);
+      jobs++;
+    };
+    auto stage_store = [&](uint8_t* buf, const uint32_t* r) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+            make_uint4(r[j * 4], r[j * 4 + 1], r[j * 4 + 2], r[j * 4 + 3]);
+    };
+    for (int j = 0; ok; ++j) {
+      ok = mbar_wait(&bars->dq_full, j & 1, abort_flag);
+      if (!ok) break;
+      const volatile int* jd = bars->dqjob[j & 1];
+      const int row0 = jd[0], head = jd[1], m = jd[2], code = jd[3];
+      if (code == 2) break;
+      if (code == 1) {  // deterministic mode: a skipped tile adds nothing but still takes (and passes on) its turn
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->dq_empty);
+        stage_wait_free();
+        if (!ok) break;
+        stage_post(0, head, m, 1);
+        continue;
+      }
+      tc_fence_after();
+#pragma unroll
+      for (int cp = 0; cp < NP; ++cp) {
+        uint32_t r[64];
+        tmem_ld32(tmem_base + lane_addr + TMEM_DQ + cp * 64, &r[0]);
+        tmem_ld32(tmem_base + lane_addr + TMEM_DQ + cp * 64 + 32, &r[32]);
+        tmem_ld_wait();
+        if (cp == NP - 1) {  // all of this warp's dQ values are in registers: the TMEM block may be overwritten
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->dq_empty);
+        }
+        if (det) {
+          stage_wait_free();
+          if (!ok) break;
+        } else {
+          if (lane == 0) bulk_wait_read0();  // the engine has read the previous contents of both buffers
+          __syncwarp();
+        }
+        stage_store(stage, &r[0]);
+        stage_store(stage + 4096, &r[32]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (det) {
+          stage_post(row0, head, m, 0 | (cp << 4) | ((cp == NP - 1 ? 1 : 0) << 8));
+        } else if (lane == 0) {
+          tma_reduce_add_3d(&p.map_dq, stage, cp * 64, row0 + wq * 32, head);
+          tma_reduce_add_3d(&p.map_dq, stage + 4096, cp * 64 + 32, row0 + wq * 32, head);
+          bulk_commit();
+        }
+      }
+    }
+    if (det) {
+      stage_wait_free();
+      stage_post(0, 0, 0, 2);  // the drain warp leaves (also when this warp is bailing out: it must not be left waiting)
+    }
+    if (lane == 0) bulk_wait0();
+    __syncwarp();
+  } else if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
     if (warp == 8) {
       // =============================== producer ==============================================
       if (lane == 0 && !*abort_flag) {
@@ -371,22 +466,40 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
                      sDO = smem_u32(smem + SM::kDO), sDS = smem_u32(smem + SM::kDS);
       bool ok = !*abort_flag && N_IT > 0;
       (void)N_IT;
+      // The whole warp runs the (uniform) descriptor arithmetic and every MMA carries the single-lane predicate: a
+      // divergent branch around the MMAs would cost more issue time per MMA than the MMA takes to execute. A
+      // descriptor is (low word, constant high word); moving inside a tile is an add on the low word.
+      const uint32_t lead = lane == 0 ? 1u : 0u;
+      const uint32_t k_lo = umma_desc_lo(sK, 16), v_lo = umma_desc_lo(sV, 16), do_lo = umma_desc_lo(sDO, 16),
+                     ds_lo = umma_desc_lo(sDS, 16);                                  // K-major operands
+      const uint32_t do_mn = umma_desc_lo(sDO, TM * 128), ds_mn = umma_desc_lo(sDS, 128 * 128),
+                     k_mn = umma_desc_lo(sK, TN * 128);                              // MN-major operands
+      const uint32_t q_lo0 = umma_desc_lo(sQ, 16), q_mn0 = umma_desc_lo(sQ, TM * 128);
+      constexpr uint32_t Q_STAGE = SM::kTile >> 4;  // low-word distance between the two Q stages
       auto issue_st = [&](int st) {
-        if (lane == 0) {
+        const uint32_t q_lo = q_lo0 + st * Q_STAGE;
 #pragma unroll
-          for (int kk = 0; kk < KK_D; ++kk) {
-            const uint32_t koff = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
-            umma_ss(tmem_base + TMEM_S, umma_smem_desc(sK + koff, 16, 1024),
-                    umma_smem_desc(sQ + st * SM::kTile + koff, 16, 1024), idesc_s, kk > 0);
-          }
-          umma_commit(&bars->s_full);
+        for (int kk = 0; kk < KK_D; ++kk) {
+          const uint32_t koff = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
+          umma_ss_lead(lead, tmem_base + TMEM_S, umma_desc_at(k_lo, koff), umma_desc_at(q_lo, koff), idesc_s, kk > 0);
         }
-        __syncwarp();
+        umma_commit_lead(lead, &bars->s_full);
       };
       StepWalk wk = walk_begin();
-      int g_unused = 0, m_unused = 0, mode_unused = 0;
+      int g_nxt = 0, m_nxt = 0, mode_unused = 0;
       bool first_unused = false;
-      bool has_cur = ok && walk_next(wk, g_unused, m_unused, mode_unused, first_unused, false);
+      bool has_cur = ok && walk_next(wk, g_nxt, m_nxt, mode_unused, first_unused, false);
+      const bool det = p.flags & F_DETERMINISTIC;
+      int n_jobs = 0;  // dQ tiles (and, deterministic mode, passes) handed to the dQ warps so far
+      // descriptor of the dQ tile the next commit on dq_full announces; written well before the MMAs it follows
+      auto post_dq_job = [&](int g, int m, int code) {
+        if (lane == 0) {
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(smem_u32(bars->dqjob[n_jobs & 1])),
+                       "r"((int)(pad_off + (long long)m * TM)), "r"(hkv * p.G + g), "r"(m), "r"(code)
+                       : "memory");
+          __threadfence_block();
+        }
+      };
       if (has_cur) {
         ok = mbar_wait(&bars->kv_full, 0, abort_flag);
         ok = ok && mbar_wait(&bars->q_full[0], 0, abort_flag);
@@ -397,37 +510,54 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       bool acc_started = false;
       for (int it = 0; has_cur && ok; ++it) {
         const int st = it & 1;
-        const bool has_next = walk_next(wk, g_unused, m_unused, mode_unused, first_unused, false);
-        ok = mbar_wait(&bars->p_full, it & 1, abort_flag);
-        if (!ok) break;
-        const bool skip = (KIND != KIND_DENSE) && bars->skip_flag[it & 1];
+        const int g_cur = g_nxt, m_cur = m_nxt;
+        const bool has_next = walk_next(wk, g_nxt, m_nxt, mode_unused, first_unused, false);
+        // The verdict of the skip vote is read straight from the votes (the compute warps publish them well before
+        // the exponentials), so that dP^T is under way while P^T is still being computed.
+        bool skip = false;
+        if (KIND != KIND_DENSE) {
+          ok = mbar_wait(&bars->vote_sync, it & 1, abort_flag);
+          if (!ok) break;
+          const unsigned long long vv = *reinterpret_cast<const volatile unsigned long long*>(&bars->vote_any[it & 1][0]);
+          const bool any_want = (vv & 0x0101010101010101ull) != 0ull, any_drop = (vv & 0x0202020202020202ull) != 0ull;
+          skip = !any_want && any_drop;
+        }
         ok = mbar_wait(&bars->do_full, it & 1, abort_flag);  // every phase is observed, skipped step or not
         if (!ok) break;
         tc_fence_after();
-        if (!skip) {
-          if (n_live > 0) ok = mbar_wait(&bars->dq_empty, (n_live - 1) & 1, abort_flag);
+        if (!skip || det) {
+          // the dQ warps have read the previous tile out of the block that dP^T is about to overwrite (and both
+          // descriptor slots are free again)
+          if (n_jobs > 0) ok = mbar_wait(&bars->dq_empty, (n_jobs - 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          if (lane == 0) {
-#pragma unroll
-            for (int kk = 0; kk < KK_D; ++kk) {
-              const uint32_t koff = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
-              umma_ss(tmem_base + TMEM_DP, umma_smem_desc(sV + koff, 16, 1024),
-                      umma_smem_desc(sDO + koff, 16, 1024), idesc_s, kk > 0);
-            }
-            umma_commit(&bars->dp_full);
-#pragma unroll
-            for (int kk = 0; kk < KK_M; ++kk) {
-              const uint32_t a_col = (kk < 4) ? kk * 8 : 96 + (kk - 4) * 8;
-              umma_ts(tmem_base + TMEM_DV, tmem_base + TMEM_S + a_col,
-                      umma_smem_desc(sDO + kk * 2048, TM * 128, 1024), idesc_dv,
-                      (kk > 0 || acc_started) ? 1u : 0u);
-            }
-          }
-          __syncwarp();
         }
-        if (lane == 0) umma_commit(&bars->do_empty);  // dO may be overwritten once dV has read it
-        __syncwarp();
+        if (skip && det) {  // a skipped tile still takes its turn in the order of the dQ adds
+          post_dq_job(g_cur, m_cur, 1);
+          umma_commit_lead(lead, &bars->dq_full);
+          n_jobs++;
+        }
+        if (!skip) {
+          post_dq_job(g_cur, m_cur, 0);
+#pragma unroll
+          for (int kk = 0; kk < KK_D; ++kk) {
+            const uint32_t koff = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
+            umma_ss_lead(lead, tmem_base + TMEM_DP, umma_desc_at(v_lo, koff), umma_desc_at(do_lo, koff), idesc_s, kk > 0);
+          }
+          umma_commit_lead(lead, &bars->dp_full);
+        }
+        ok = mbar_wait(&bars->p_full, it & 1, abort_flag);  // P^T is in TMEM (every phase is observed)
+        if (!ok) break;
+        tc_fence_after();
+        if (!skip) {
+#pragma unroll
+          for (int kk = 0; kk < KK_M; ++kk) {
+            const uint32_t a_col = (kk < 4) ? kk * 8 : 96 + (kk - 4) * 8;
+            umma_ts_lead(lead, tmem_base + TMEM_DV, tmem_base + TMEM_S + a_col, umma_desc_at(do_mn, kk * 2048), idesc_dv,
+                         (kk > 0 || acc_started) ? 1u : 0u);
+          }
+        }
+        umma_commit_lead(lead, &bars->do_empty);  // dO may be overwritten once dV has read it
         if (has_next) {
           ok = mbar_wait(&bars->q_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_flag);
           if (!ok) break;
@@ -438,39 +568,40 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
           ok = mbar_wait(&bars->ds_full, n_live & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          if (lane == 0) {
+          // dQ first: its tile has to leave TMEM before dP^T of the next step can be issued
 #pragma unroll
-            for (int kk = 0; kk < KK_M; ++kk) {
-              umma_ss(tmem_base + TMEM_DK, umma_smem_desc(sDS + (kk >> 2) * (128 * 128) + (kk & 3) * 32, 16, 1024),
-                      umma_smem_desc(sQ + st * SM::kTile + kk * 2048, TM * 128, 1024), idesc_dk,
-                      (kk > 0 || acc_started) ? 1u : 0u);
-            }
+          for (int kk = 0; kk < KK_N; ++kk)
+            umma_ss_lead(lead, tmem_base + TMEM_DP, umma_desc_at(ds_mn, kk * 2048), umma_desc_at(k_mn, kk * 2048), idesc_dq,
+                         kk > 0);
+          umma_commit_lead(lead, &bars->dq_full);
+          const uint32_t q_mn = q_mn0 + st * Q_STAGE;
 #pragma unroll
-            for (int kk = 0; kk < KK_N; ++kk) {
-              umma_ss(tmem_base + TMEM_DP, umma_smem_desc(sDS + kk * 2048, 128 * 128, 1024),
-                      umma_smem_desc(sK + kk * 2048, TN * 128, 1024), idesc_dq, kk > 0);
-            }
-            umma_commit(&bars->dq_full);
-          }
-          __syncwarp();
+          for (int kk = 0; kk < KK_M; ++kk)
+            umma_ss_lead(lead, tmem_base + TMEM_DK, umma_desc_at(ds_lo, (kk >> 2) * (128 * 128) + (kk & 3) * 32),
+                         umma_desc_at(q_mn, kk * 2048), idesc_dk, (kk > 0 || acc_started) ? 1u : 0u);
           acc_started = true;
           n_live++;
+          n_jobs++;
         }
-        if (lane == 0) umma_commit(&bars->q_empty[st]);
-        __syncwarp();
+        umma_commit_lead(lead, &bars->q_empty[st]);
         has_cur = has_next;
       }
-      if (lane == 0) umma_commit(&bars->acc_full);
-      __syncwarp();
+      umma_commit_lead(lead, &bars->acc_full);
+      // The dQ warps leave. Every one of them must have seen the phase of the last tile before dq_full moves on
+      // again (two arrivals in a row would carry the barrier past a waiter's parity).
+      if (n_jobs > 0 && ok) ok = mbar_wait(&bars->dq_empty, (n_jobs - 1) & 1, abort_flag);
+      if (!*abort_flag) {
+        post_dq_job(0, 0, 2);
+        umma_commit_lead(lead, &bars->dq_full);
+      }
     } else if (warp == 10) {
       // =============================== dQ drain =================================================
-      // Deterministic mode only (otherwise every compute warp issues the reduce-add of its own buffer, which
-      // measured 3 % faster). Jobs arrive in order: a 32-column chunk of a dQ tile staged by the eight
-      // compute warps (lane i issues the reduce-add of warp i's 4 KB buffer), "pass" for a skipped tile and
+      // Deterministic mode only (otherwise every dQ warp issues the reduce-adds of its own buffers, which
+      // measured 3 % faster). Jobs arrive in order: a 64-column pair of chunks of a dQ tile staged by the four
+      // dQ warps (lane i issues the reduce-add of the 4 KB buffer i), "pass" for a skipped tile and
       // "exit". This warp waits for the tile's turn before the first chunk and passes it on when the adds
       // of the last chunk have completed (one tick of the per-(head, query tile) counter per key tile), so
-      // the compute warps never wait for a turn or for the completion of an add.
-      constexpr int HALF_ = HD / 2;
+      // the dQ warps never wait for a turn or for the completion of an add.
       const bool det = p.flags & F_DETERMINISTIC;
       bool ok = det && !*abort_flag;  // without deterministic mode the compute warps issue their own reduce-adds
       // one counter per (head, query tile); a link of the chain costs the issue-to-completion latency of the
@@ -515,8 +646,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
           if (*abort_flag) break;
         }
         if (kind == 0 && lane < 8) {
-          tma_reduce_add_3d(&p.map_dq, smem + SM::kStage + lane * 4096, (lane >> 2) * HALF_ + chunk * 32,
-                            row0 + (lane & 3) * 32, head);
+          tma_reduce_add_3d(&p.map_dq, smem + SM::kStage + lane * 4096, chunk * 64 + (lane & 1) * 32,
+                            row0 + (lane >> 1) * 32, head);
           bulk_commit();
           bulk_wait_read0();
         }
@@ -533,50 +664,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
     }
   } else {
     // =============================== compute warps ===========================================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
     const int cw = warp;            // 0..7
     const int wg = cw >> 2;         // which half of the query columns / output columns
     const int wq = cw & 3;          // TMEM lane quadrant
-    const int row = wq * 32 + lane; // key row (S^T, dP^T, dV, dK) or query row (dQ)
+    const int row = wq * 32 + lane; // key row (S^T, dP^T, dV, dK)
     const uint32_t lane_addr = uint32_t(wq * 32) << 16;
     const int k_idx = n_block * TN + row;
     const bool row_ok = k_idx < sk;
     const int off = sk - sq;
     const float c = p.scale_log2;
     uint8_t* ds_buf = smem + SM::kDS;
-    uint8_t* stage = smem + SM::kStage + cw * 4096;
 
     bool ok = !*abort_flag;
     uint32_t pk[32];  // P^T of the step in flight, packed pairs (this thread's 64 query columns)
     int n_live = 0;
     bool skip_cur = false;
-    // dQ leaves in 32-column chunks through this warp's 4 KB staging buffer; a second chunk waits in
-    // registers until the TMA engine has read the first one out of the buffer
-    constexpr int NCH = HALF / 32;
-    uint32_t dq_hold[32];
-    bool dq_pending = false;
-    int dq_row = 0, dq_head = 0, dq_m = 0;
-    int m_cur = 0, g_cur = 0;  // query tile / head of the step whose dS and dQ are being handled
-    const bool det = p.flags & F_DETERMINISTIC;
-    int jobs = 0;  // staging jobs handed to the drain warp so far (same count in every compute warp)
-    // wait until the drain warp's TMA reads of the previous job have left the staging buffers
-    auto stage_wait_free = [&]() {
-      if (jobs > 0 && !mbar_wait(&bars->stg_free, (jobs - 1) & 1, abort_flag)) ok = false;
-    };
-    // hand a job to the drain warp: {first row of the tile, head, query tile, code}
-    // code = kind (0 chunk, 1 pass, 2 exit) | chunk << 4 | last chunk of the tile << 8
-    auto stage_post = [&](int row0, int head, int m, int code) {
-      if (cw == 0 && lane == 0) {
-        volatile int* jd = bars->job[jobs & 1];
-        jd[0] = row0;
-        jd[1] = head;
-        jd[2] = m;
-        jd[3] = code;
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->stg_full);
-      jobs++;
-    };
+    int m_cur = 0, g_cur = 0;  // query tile / head of the step whose dS is being handled
 
     // ---- gated: delta of this key row, its extremes over the key tile, running gate bound --------
     // (flash_sparse_attn/ops/triton/flash_gated_bwd.py:406-421; keys past the sequence read as zero)
@@ -839,13 +943,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
           skip = !(v & 1) && (v & 2);
         }
         if (cw == 0 && lane == 0) {
-          bars->skip_flag[par] = skip ? 1 : 0;
           if (p.tile_map) {
             const int head = hkv * p.G + g;
             p.tile_map[((((long long)b * p.Hq + head) * p.n_tiles_k + n_block) * p.num_splits + split) *
                            p.num_m_blocks + m] = skip ? (gate_skip ? 3 : 2) : 1;
           }
-          // no fence: this thread's arrival on p_full (release) orders the flag before the MMA issuer's read
         }
       }
       if (!skip) {
@@ -950,71 +1052,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       if (lane == 0) mbar_arrive(&bars->ds_full);
     };
 
-    // ---- dQ step: TMEM -> registers -> shared staging; the drain warp issues the TMA reduce-adds -------
-    // The path from an SM to L2 moves about 21 bytes per clock, so the 64 KB of a dQ tile take as long as
-    // the five MMAs of a step: nobody waits for it. The first 32 columns are staged at once, the second 32
-    // stay in registers until the next phase has passed (dq_flush) and the engine has drained the buffers.
-    auto stage_store = [&](const uint32_t* r) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) =
-            make_uint4(r[j * 4], r[j * 4 + 1], r[j * 4 + 2], r[j * 4 + 3]);
-      fence_proxy_async_smem();
-      __syncwarp();
-    };
-    auto dq_flush = [&]() {
-      if (NCH > 1 && dq_pending) {
-        if (det) {
-          stage_wait_free();
-          if (!ok) return;
-          stage_store(dq_hold);
-          stage_post(dq_row, dq_head, dq_m, 0 | (1 << 4) | (1 << 8));
-        } else {
-          if (lane == 0) bulk_wait_read0();
-          __syncwarp();
-          stage_store(dq_hold);
-          if (lane == 0) {
-            tma_reduce_add_3d(&p.map_dq, stage, wg * HALF + 32, dq_row + wq * 32, dq_head);
-            bulk_commit();
-          }
-        }
-        dq_pending = false;
-      }
-    };
-    auto dq_step = [&](int it) {
-      if (!mbar_wait(&bars->dq_full, n_live & 1, abort_flag)) {
-        ok = false;
-        return;
-      }
-      tc_fence_after();
-      uint32_t r[32];
-      tmem_ld32(tmem_base + lane_addr + TMEM_DP + wg * HALF, r);
-      if (NCH > 1) tmem_ld32(tmem_base + lane_addr + TMEM_DP + wg * HALF + 32, dq_hold);
-      tmem_ld_wait();
-      // all of this warp's dQ values are in registers: the TMEM block may be overwritten
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->dq_empty);
-      dq_row = (int)(pad_off + (long long)m_cur * TM);
-      dq_head = hkv * p.G + g_cur;
-      dq_m = m_cur;
-      if (det) {
-        stage_wait_free();
-        if (!ok) return;
-        stage_store(r);
-        stage_post(dq_row, dq_head, dq_m, 0 | (0 << 4) | ((NCH == 1 ? 1 : 0) << 8));
-      } else {
-        if (lane == 0) bulk_wait_read0();  // the buffer went to the engine a whole phase ago
-        __syncwarp();
-        stage_store(r);
-        if (lane == 0) {
-          tma_reduce_add_3d(&p.map_dq, stage, wg * HALF, dq_row + wq * 32, dq_head);
-          bulk_commit();
-        }
-      }
-      dq_pending = NCH > 1;
-    };
-
     int w_g = 0, w_m = 0, w_mode = 0;
     bool w_first = false;
     bool has_cur = ok && walk_next(wk, w_g, w_m, w_mode, w_first, mark_steps);
@@ -1025,28 +1062,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       g_cur = g_p;
     }
     for (int it = 0; has_cur && ok; ++it) {
-      if (!skip_cur) ds_step(it);
-      dq_flush();
+      if (!skip_cur) {
+        ds_step(it);
+        n_live++;
+      }
       bool skip_next = false;
       const bool has_next = walk_next(wk, w_g, w_m, w_mode, w_first, mark_steps);
       if (ok && has_next) skip_next = p_step(it + 1, w_g, w_m, w_mode, w_first);
-      if (ok && !skip_cur) {
-        dq_step(it);
-        n_live++;
-      } else if (ok && det) {
-        // a skipped tile adds nothing but still takes (and passes on) its turn
-        stage_wait_free();
-        if (ok) stage_post(0, hkv * p.G + g_cur, m_cur, 1);
-      }
       skip_cur = skip_next;
       m_cur = m_p;
       g_cur = g_p;
       has_cur = has_next;
-    }
-    dq_flush();
-    if (det) {
-      stage_wait_free();
-      stage_post(0, 0, 0, 2);  // the drain warp leaves (also when this warp is bailing out: it must not be left waiting)
     }
 
     // ---- epilogue: dK (scaled) and dV of this key tile ------------------------------------------------
@@ -1121,8 +1147,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         }
       }
     }
-    if (lane == 0) bulk_wait0();
-    __syncwarp();
   }
 
   // ---- teardown ------------------------------------------------------------------------------------
