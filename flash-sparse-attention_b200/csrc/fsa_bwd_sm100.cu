@@ -814,7 +814,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
       tmem_ld_wait();
       const bool ragged = ((m + 1) * TM > sq) || ((n_block + 1) * TN > sk);
       const bool masked = (mode != FSA_MASK_NONE) || ragged;
-      const ColMask cm = col_mask(mode, m);
+      ColMask cm = {{0, 0, 0}, {0u, 0u, 0u}};
+      if (masked) cm = col_mask(mode, m);  // 64-bit interval arithmetic: only for the tiles that need it
       const float4* lse4 = reinterpret_cast<const float4*>(s_lse + st * 128 + wg * 64);
       float x[64];  // log2 of the probabilities
       if (KIND == KIND_GATED) {
@@ -891,30 +892,40 @@ __global__ void __launch_bounds__(NTHREADS, 1) bwd_kernel(const __grid_constant_
         // The threshold falls as the query index grows (causal) or is one number (otherwise): the row
         // maximum against the thresholds of the group's first and last column settles most votes at
         // once; only a warp with a lane in between compares entry by entry.
-        float mx4[4];  // four independent chains
+        // The verdict is one bit for the whole tile ("does any entry want it"), so the common case is settled by the
+        // first sixteen columns: if the maximum of those reaches the largest threshold of the group in any lane,
+        // the tile is kept and the rest of the vote is not computed.
+        const bool exact_only = vis_first < 1.0f;  // warp-uniform
+        auto chain16 = [&](int j) {
+          float v = fmaxf(x[j * 16], x[j * 16 + 1]);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          mx4[j] = fmaxf(x[j * 16], x[j * 16 + 1]);
+          for (int i = 2; i < 16; i += 2) v = max3(v, x[j * 16 + i], x[j * 16 + i + 1]);
+          return v;
+        };
+        const float mx_first = chain16(0);
+        bool want = mx_first >= thr_hi, drop = false;
+        if (exact_only || !__any_sync(0xffffffffu, want)) {
+          const float mx = fmaxf(fmaxf(mx_first, chain16(1)), fmaxf(chain16(2), chain16(3)));
+          want = mx >= thr_hi;
+          drop = mx < thr_lo;
+          const bool unsure = exact_only || (!want && !drop);
+          // once a lane of this warp is sure that it wants the tile, the lanes in between do not matter any more
+          const bool settled = !exact_only && __any_sync(0xffffffffu, want);
+          if (!settled && __any_sync(0xffffffffu, unsure)) {
+            const int q_a = q_first + lane, q_b = q_a + 32;
+            const float vis_a = causal ? float(q_a + off + 1) : float(sk);
+            const float vis_b = causal ? float(q_b + off + 1) : float(sk);
+            const float thr_a = fminf(lg_thr - lg2_approx(vis_a), 0.0f);
+            const float thr_b = fminf(lg_thr - lg2_approx(vis_b), 0.0f);
+            want = false;
+            drop = false;
 #pragma unroll
-          for (int i = 2; i < 16; i += 2) mx4[j] = max3(mx4[j], x[j * 16 + i], x[j * 16 + i + 1]);
-        }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        bool want = mx >= thr_hi, drop = mx < thr_lo;
-        const bool unsure = (vis_first < 1.0f) || (!want && !drop);
-        if (__any_sync(0xffffffffu, unsure)) {
-          const int q_a = q_first + lane, q_b = q_a + 32;
-          const float vis_a = causal ? float(q_a + off + 1) : float(sk);
-          const float vis_b = causal ? float(q_b + off + 1) : float(sk);
-          const float thr_a = fminf(lg_thr - lg2_approx(vis_a), 0.0f);
-          const float thr_b = fminf(lg_thr - lg2_approx(vis_b), 0.0f);
-          want = false;
-          drop = false;
-#pragma unroll
-          for (int i = 0; i < 64; ++i) {
-            const float t = __shfl_sync(0xffffffffu, i < 32 ? thr_a : thr_b, i & 31);
-            const float v = x[i] - t;
-            want |= (v >= 0.0f);
-            drop |= (v < 0.0f);
+            for (int i = 0; i < 64; ++i) {
+              const float t = __shfl_sync(0xffffffffu, i < 32 ? thr_a : thr_b, i & 31);
+              const float v = x[i] - t;
+              want |= (v >= 0.0f);
+              drop |= (v < 0.0f);
+            }
           }
         }
         want |= oor_want;
