@@ -9,7 +9,7 @@
 //    [lo, hi) of each sequence, shift them to shard-local positions and move them to the front of the row (order
 //    kept); the count per row lets the decode kernel visit only the tiles that hold indices.
 //
-// Both are HBM-bound copies / integer passes: 16-byte row chunks, one warp per row.
+// Both are HBM-bound copies / integer passes: 16-byte chunks, one warp per cache row, one CTA per row of indices.
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -83,27 +83,55 @@ __global__ void __launch_bounds__(256) kv_copy_kernel(const FsaKvAppendArgs a, i
   }
 }
 
-// One warp per row of indices: stable compaction of the positions inside [lo, hi), shifted by -lo.
+// One CTA of 256 threads per row of indices: stable compaction of the positions inside [lo, hi), shifted by -lo.
+// Every thread takes eight consecutive entries of a 2048-entry chunk (two 16-byte loads), the CTA scans the
+// per-thread counts (warp shuffles, then the eight warp totals), and the kept entries go out in their original order.
 __global__ void __launch_bounds__(256) localize_kernel(const int32_t* idx, long long idx_stride, const int32_t* bounds,
-                                                       int32_t* out, long long out_stride, int32_t* count, int rows,
-                                                       int topk) {
-  const int lane = threadIdx.x & 31;
-  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (row >= rows) return;
+                                                       int32_t* out, long long out_stride, int32_t* count, int topk) {
+  __shared__ int warp_tot[8];
+  __shared__ int carry_s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int row = blockIdx.x;
   const int lo = bounds[2 * row], hi = bounds[2 * row + 1];
   const int32_t* src = idx + (long long)row * idx_stride;
   int32_t* dst = out + (long long)row * out_stride;
-  int kept = 0;
-  for (int i0 = 0; i0 < topk; i0 += 32) {
-    const int i = i0 + lane;
-    const int pos = i < topk ? src[i] : -1;
-    const bool in = pos >= lo && pos < hi;
-    const unsigned m = __ballot_sync(0xffffffffu, in);
-    if (in) dst[kept + __popc(m & ((1u << lane) - 1))] = pos - lo;
-    kept += __popc(m);
+  const bool vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && ((topk & 7) == 0);
+  int carry = 0;
+  for (int c0 = 0; c0 < topk; c0 += 2048) {
+    const int i0 = c0 + tid * 8;
+    int v[8];
+    if (vec && i0 + 8 <= topk) {
+      const int4 a = __ldg(reinterpret_cast<const int4*>(src + i0)), b = __ldg(reinterpret_cast<const int4*>(src + i0 + 4));
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+      v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = (i0 + j < topk) ? __ldg(src + i0 + j) : -1;
+    }
+    int n = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) n += (v[j] >= lo && v[j] < hi) ? 1 : 0;
+    int incl = n;  // inclusive scan over the warp
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, s);
+      if (lane >= s) incl += t;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    int base = carry;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) base += (w < warp) ? warp_tot[w] : 0;
+    int at = base + incl - n;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (v[j] >= lo && v[j] < hi) dst[at++] = v[j] - lo;
+    if (tid == 255) carry_s = base + incl;
+    __syncthreads();
+    carry = carry_s;
   }
-  for (int i = kept + lane; i < topk; i += 32) dst[i] = -1;
-  if (lane == 0) count[row] = kept;
+  for (int i = carry + tid; i < topk; i += 256) dst[i] = -1;
+  if (tid == 0) count[row] = carry;
 }
 
 }  // namespace
@@ -138,7 +166,6 @@ extern "C" int fsa_localize_indices(const int32_t* indices, int64_t indices_stri
   if (!indices || !key_bounds || !out || !count || rows < 0 || topk <= 0) return FSA_ERR_INVALID_ARG;
   if (rows == 0) return FSA_OK;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  fsa::localize_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(indices, indices_stride, key_bounds, out, out_stride, count,
-                                                          rows, topk);
+  fsa::localize_kernel<<<rows, 256, 0, stream>>>(indices, indices_stride, key_bounds, out, out_stride, count, topk);
   return cudaGetLastError() == cudaSuccess ? FSA_OK : FSA_ERR_LAUNCH;
 }
