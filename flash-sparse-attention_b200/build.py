@@ -25,6 +25,7 @@ SOURCES = [
     "fsa_quant.cu",
     "fsa_topk.cu",
     "fsa_kvcache.cu",
+    "fsa_peer.cu",
 ]
 
 NVCC_FLAGS = [

@@ -16,14 +16,40 @@ template <typename T, int VEC>
 __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
   const int lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  long long buf_off = 0;
+  if (p.peer_flags) {
+    // partials stored by other GPUs: wait for every rank's arrivals of this step (bounded: on expiry the status word
+    // is set and the kernel goes on with whatever is there)
+    __shared__ unsigned long long step_s;
+    if (threadIdx.x == 0) step_s = *reinterpret_cast<const volatile unsigned long long*>(p.peer_step);
+    __syncthreads();
+    const unsigned long long step = step_s;
+    if (threadIdx.x < p.peer_world) {
+      const unsigned long long want = step * (unsigned long long)p.arrivals_per_step;
+      const unsigned long long* f = p.peer_flags + threadIdx.x;
+      const long long t0 = clock64();
+      for (;;) {
+        unsigned long long seen;
+        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(f) : "memory");
+        if (seen >= want) break;
+        if (clock64() - t0 > FSA_WAIT_CYCLES) {
+          atomicExch(p.status, 4);
+          break;
+        }
+        __nanosleep(100);
+      }
+    }
+    __syncthreads();
+    buf_off = (long long)((step - 1) & 1ull) * p.buf_stride;
+  }
   if (item >= (long long)p.rows * p.heads) return;
   const int h = (int)(item % p.heads);
   const long long row = item / p.heads;
   const int b = (int)(row / p.rows_per_batch);
   const long long s = row - (long long)b * p.rows_per_batch;
 
-  const float* lp = p.lse_partial + (long long)h * p.lp_sh + row;
-  const float* op = p.out_partial + (row * p.heads + h) * p.head_dim;
+  const float* lp = p.lse_partial + buf_off + (long long)h * p.lp_sh + row;
+  const float* op = p.out_partial + buf_off + (row * p.heads + h) * p.head_dim;
   float e_max = -INFINITY, e_sum = 0.f;
   float acc[VEC];
 #pragma unroll

@@ -18,6 +18,14 @@ struct CombineParams {
   long long o_sb, o_sm, o_sh;
   long long l_sb, l_sh;
   int rows, rows_per_batch, heads, head_dim, num_splits;
+  // Peer exchange (context-parallel decode): when `peer_flags` is set the partials were stored by other GPUs. Every
+  // CTA first waits (bounded) until flag r of every rank r has reached step * arrivals_per_step, `step` being the
+  // count of exchanges this rank has sent; the partials are read from buffer (step - 1) & 1, `buf_stride` floats apart.
+  const unsigned long long* peer_flags;
+  const unsigned long long* peer_step;
+  int* status;
+  long long buf_stride;
+  int peer_world, arrivals_per_step;
 };
 
 // Backward pre-pass over every (query row, head): dpsum = sum_d O*dO, lse2 = lse * log2(e) (NaN -> 1e6,

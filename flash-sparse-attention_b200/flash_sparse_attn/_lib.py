@@ -294,6 +294,17 @@ class FsaKvAppendArgs(ctypes.Structure):
     ]
 
 
+PEER_MAX_RANKS = 16
+
+
+class FsaIpcHandle(ctypes.Structure):
+    _fields_ = [("bytes", ctypes.c_ubyte * 64)]
+
+
+class FsaPeerArgs(ctypes.Structure):
+    _fields_ = [("region", c_void_p * PEER_MAX_RANKS), ("world", c_int32), ("rank", c_int32), ("block_floats", c_int64)]
+
+
 class FsaFwdWorkspace(ctypes.Structure):
     _fields_ = [("out_partial", c_size_t), ("lse_partial", c_size_t), ("gate_ws", c_size_t)]
 
@@ -353,6 +364,21 @@ def load():
     lib.fsa_kv_append.argtypes = [POINTER(FsaKvAppendArgs), c_void_p]
     lib.fsa_localize_indices.restype = c_int
     lib.fsa_localize_indices.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]
+    lib.fsa_peer_region_bytes.restype = c_int
+    lib.fsa_peer_region_bytes.argtypes = [c_int, c_int64, POINTER(c_int64)]
+    lib.fsa_peer_alloc.restype = c_int
+    lib.fsa_peer_alloc.argtypes = [c_int64, POINTER(c_void_p), POINTER(FsaIpcHandle)]
+    lib.fsa_peer_open.restype = c_int
+    lib.fsa_peer_open.argtypes = [POINTER(FsaIpcHandle), POINTER(c_void_p)]
+    lib.fsa_peer_close.restype = c_int
+    lib.fsa_peer_close.argtypes = [c_void_p]
+    lib.fsa_peer_free.restype = c_int
+    lib.fsa_peer_free.argtypes = [c_void_p]
+    lib.fsa_peer_push.restype = c_int
+    lib.fsa_peer_push.argtypes = [POINTER(FsaPeerArgs), c_void_p, c_void_p]
+    lib.fsa_peer_combine.restype = c_int
+    lib.fsa_peer_combine.argtypes = [POINTER(FsaPeerArgs), c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                     c_void_p]
     lib.fsa_fwd_workspace_bytes.restype = c_int
     lib.fsa_fwd_workspace_bytes.argtypes = [POINTER(FsaFwdArgs), POINTER(FsaFwdWorkspace)]
     lib.fsa_bwd_workspace_bytes.restype = c_int

@@ -20,6 +20,12 @@ difference is bounded by the threshold mass, as between different split counts o
 Wire format: one fp32 block of B*Hq*(D+1) elements per (rank, split): the partial outputs [B, Hq, D] followed by
 the base-2 log-sum-exps [Hq, B]. The all-gather concatenates the blocks of all ranks; the combine kernel reads
 them in place.
+
+Exchange: with `exchange="peer"` (ranks on the GPUs of one node, one process per GPU) the all-gather is replaced by
+the library's own kernels: every rank stores its block straight into the receive buffers of all ranks over NVLink
+(`fsa_peer_push`: plain peer stores into memory mapped through CUDA IPC, an arrival counter per sender) and the
+combine kernel waits, bounded, for the arrivals of the step (`fsa_peer_combine`). No multicast is involved. The
+default `exchange="nccl"` keeps the single NCCL all-gather.
 """
 
 from typing import Callable, Optional, Tuple
@@ -87,7 +93,8 @@ class ContextParallelDecoder:
     about lengths), `seqused_k_local` the number of valid keys in the local shard (full-context mode)."""
 
     def __init__(self, batch: int, heads_q: int, head_dim: int, dtype: torch.dtype, device, num_splits: int = 1,
-                 group=None):
+                 group=None, exchange: str = "nccl"):
+        assert exchange in ("nccl", "peer")
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.batch, self.heads, self.head_dim, self.dtype, self.ns = batch, heads_q, head_dim, dtype, num_splits
@@ -97,6 +104,9 @@ class ContextParallelDecoder:
         self.out = torch.empty((batch, heads_q, head_dim), dtype=dtype, device=device)
         self.lse = torch.empty((batch, heads_q), dtype=torch.float32, device=device)
         self._bounds = self._bounds_key = self._idx = self._count = None
+        self.peers = None
+        if exchange == "peer" and self.world > 1:
+            self.peers = PeerExchange(num_splits * per, device, group)
 
     def partial(self, query, key_local, value_local, shard_lo, shard_hi, gather_kv_indices=None,
                 seqused_k_global=None, seqused_k_local=None, page_table=None, softmax_scale=None,
@@ -131,18 +141,97 @@ class ContextParallelDecoder:
     def exchange(self):
         if self.world == 1:
             return self.send
+        if self.peers is not None:
+            self.peers.push(self.send)
+            return None  # the partials are in the peer region; combine() waits for them
         dist.all_gather_into_tensor(self.recv, self.send, group=self.group)
         return self.recv
 
     def combine(self, packed):
         from flash_sparse_attn.ops.triton.flash_dec import combine_packed_partials
 
+        if packed is None:
+            return self.peers.combine(self.out, self.lse, self.ns, self.batch, self.heads, self.head_dim)
         return combine_packed_partials(packed, packed.shape[0], self.batch, self.heads, self.head_dim, self.dtype,
                                        out=self.out, lse=self.lse)
 
     def __call__(self, *args, **kwargs):
         self.partial(*args, **kwargs)
         return self.combine(self.exchange())
+
+
+class PeerExchange:
+    """The receive region of this rank and the mapped regions of the others (see the module docstring). Set-up is
+    collective over `group` (one all-gather of the 64-byte handles through the process group) and synchronises;
+    `push` / `combine` only enqueue kernels and can be captured in a CUDA graph. Every rank must run the same
+    sequence of push / combine pairs."""
+
+    def __init__(self, block_floats: int, device, group=None):
+        import ctypes
+
+        from flash_sparse_attn import _lib
+
+        self._lib = _lib
+        self.device = torch.device(device)
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        assert self.world <= _lib.PEER_MAX_RANKS and block_floats % 4 == 0
+        lib = _lib.load()
+        nbytes = ctypes.c_int64()
+        _lib.check(lib.fsa_peer_region_bytes(self.world, block_floats, ctypes.byref(nbytes)), "fsa_peer_region_bytes")
+        own, handle = ctypes.c_void_p(), _lib.FsaIpcHandle()
+        with torch.cuda.device(self.device):
+            _lib.check(lib.fsa_peer_alloc(nbytes.value, ctypes.byref(own), ctypes.byref(handle)), "fsa_peer_alloc")
+        self._own = own.value
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.bytes), group=group)
+        self.args = _lib.FsaPeerArgs()
+        self.args.world, self.args.rank, self.args.block_floats = self.world, self.rank, block_floats
+        self._opened = []
+        with torch.cuda.device(self.device):
+            for r in range(self.world):
+                if r == self.rank:
+                    self.args.region[r] = self._own
+                    continue
+                h = _lib.FsaIpcHandle()
+                ctypes.memmove(h.bytes, handles[r], 64)
+                ptr = ctypes.c_void_p()
+                _lib.check(lib.fsa_peer_open(ctypes.byref(h), ctypes.byref(ptr)), "fsa_peer_open")
+                self.args.region[r] = ptr.value
+                self._opened.append(ptr.value)
+        dist.barrier(group=group)  # every region is zeroed and mapped before anybody sends
+
+    def push(self, block: torch.Tensor):
+        import ctypes
+
+        assert block.dtype == torch.float32 and block.is_contiguous() and block.numel() == self.args.block_floats
+        with torch.cuda.device(self.device):
+            rc = self._lib.load().fsa_peer_push(ctypes.byref(self.args), block.data_ptr(),
+                                                self._lib.current_stream_ptr(self.device))
+        self._lib.check(rc, "fsa_peer_push")
+
+    def combine(self, out, lse, partials_per_rank, batch, heads, head_dim):
+        import ctypes
+
+        status = self._lib.status_word(self.device)
+        with torch.cuda.device(self.device):
+            rc = self._lib.load().fsa_peer_combine(ctypes.byref(self.args), out.data_ptr(), lse.data_ptr(),
+                                                   partials_per_rank, batch, heads, head_dim,
+                                                   self._lib.dtype_code(out.dtype), status.data_ptr(),
+                                                   self._lib.current_stream_ptr(self.device))
+        self._lib.check(rc, "fsa_peer_combine")
+        return out, lse
+
+    def close(self):
+        """Unmap the other ranks' regions and free this rank's (after all ranks have finished their last step)."""
+        lib = self._lib.load()
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            for ptr in self._opened:
+                lib.fsa_peer_close(ptr)
+            self._opened = []
+            if self._own:
+                lib.fsa_peer_free(self._own)
+                self._own = None
 
 
 def flash_sparse_attn_with_kvcache_cp(query, key_local, value_local, shard_lo: int, shard_hi: int,

@@ -472,6 +472,34 @@ typedef struct FsaKvAppendArgs {
 } FsaKvAppendArgs;
 int fsa_kv_append(const FsaKvAppendArgs* args, void* stream);
 
+/* ---- Peer exchange of decode partials (context-parallel decode over the GPUs of one node) -------------------
+ * No counterpart in the reference (it has no multi-GPU code). Every rank owns one region (fsa_peer_alloc: cudaMalloc,
+ * so that it can be exported), opens the regions of the others (fsa_peer_open on their handles) and then, per step:
+ * fsa_decode with partial_only writes this rank's partials in the packed form (out_partial_stride /
+ * lse_partial_stride), fsa_peer_push stores that block into the receive buffer of EVERY rank (plain peer stores, no
+ * multicast) and counts an arrival there, fsa_peer_combine waits until every rank's arrivals of the step are in and
+ * merges world * partials_per_rank partials. The wait is bounded (about two seconds): on expiry the status word is
+ * set to 4 and the kernel finishes with what it has. The step counter lives on the device, so a captured CUDA graph
+ * of the three calls can be replayed. All ranks must run the same number of steps; the two receive buffers alternate. */
+#define FSA_PEER_MAX_RANKS 16
+typedef struct {
+  unsigned char bytes[64];
+} FsaIpcHandle;
+typedef struct {
+  void* region[FSA_PEER_MAX_RANKS]; /* region of rank r as mapped in THIS process (own: from fsa_peer_alloc) */
+  int world;
+  int rank;
+  int64_t block_floats; /* floats one rank sends per step: partials_per_rank * rows * heads * (head_dim + 1) */
+} FsaPeerArgs;
+int fsa_peer_region_bytes(int world, int64_t block_floats, int64_t* bytes);
+int fsa_peer_alloc(int64_t bytes, void** region, FsaIpcHandle* handle); /* synchronises; call at set-up time */
+int fsa_peer_open(const FsaIpcHandle* handle, void** region);           /* FSA_ERR_UNSUPPORTED if it cannot be mapped */
+int fsa_peer_close(void* region);
+int fsa_peer_free(void* region);
+int fsa_peer_push(const FsaPeerArgs* args, const float* block, void* stream);
+int fsa_peer_combine(const FsaPeerArgs* args, void* out, float* lse, int partials_per_rank, int rows, int heads,
+                     int head_dim, int dtype, int* status, void* stream);
+
 /*
  * One shard's view of global top-k positions: for every row keep the positions inside [lo, hi) (key_bounds
  * [rows, 2]), shift them by -lo, move them to the front of the output row in their original order, fill the rest
