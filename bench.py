@@ -361,12 +361,14 @@ def decode_cp(rank, world, dev, iters):
     idx_d, used = idx.to(dev), ctx.to(torch.int32).to(dev)
     dec = cp.ContextParallelDecoder(batch, hq, d, torch.bfloat16, dev, num_splits=1)
     peer_note = None
-    dec_peer = None
+    dec_peer = dec_fused = None
     if world > 1:
         try:  # the library's own exchange: peer stores into IPC-mapped receive buffers, bounded wait in the combine
             dec_peer = cp.ContextParallelDecoder(batch, hq, d, torch.bfloat16, dev, num_splits=1, exchange="peer")
+            dec_fused = cp.ContextParallelDecoder(batch, hq, d, torch.bfloat16, dev, num_splits=1, exchange="fused")
         except Exception as e:  # noqa: BLE001  (no peer mapping between these GPUs / processes)
             peer_note = f"peer exchange unavailable ({type(e).__name__}: {str(e)[:80]})"
+            dec_peer = dec_fused = None
 
     def local():
         dec.partial(q, k, v, bounds, None, gather_kv_indices=idx_d, seqused_k_global=used, softmax_threshold=THRESHOLD)
@@ -377,12 +379,13 @@ def decode_cp(rank, world, dev, iters):
         which.combine(which.exchange())
 
     mode = "cuda-graph replay"
-    t_peer = float("nan")
+    t_peer = t_fused = 0.0
     try:
         t_local = graph_time_us(local, iters)
         t_nccl = graph_time_us(lambda: step(dec), iters) if world > 1 else t_local
         if dec_peer is not None:
             t_peer = graph_time_us(lambda: step(dec_peer), iters)
+            t_fused = graph_time_us(lambda: step(dec_fused), iters)
     except Exception as e:  # noqa: BLE001  (a collective that cannot be captured: time eager launches instead)
         mode = f"eager launches ({type(e).__name__} during graph capture)"
         torch.cuda.synchronize()
@@ -390,23 +393,27 @@ def decode_cp(rank, world, dev, iters):
         t_nccl = time_events(lambda: step(dec), iters) * 1e3 if world > 1 else t_local
         if dec_peer is not None:
             t_peer = time_events(lambda: step(dec_peer), iters) * 1e3
+            t_fused = time_events(lambda: step(dec_fused), iters) * 1e3
     fsa.check_status()
-    t = torch.tensor([t_nccl, t_local, t_peer if dec_peer is not None else 0.0], device=dev, dtype=torch.float64)
+    t = torch.tensor([t_nccl, t_local, t_peer, t_fused], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    t_nccl, t_local, t_peer = t.tolist()
+    t_nccl, t_local, t_peer, t_fused = t.tolist()
     if dec_peer is not None:
         dist.barrier()
         dec_peer.peers.close()
+        dec_fused.peers.close()
     t_full = t_peer if dec_peer is not None else t_nccl
     nbytes = batch * hkv * topk * d * 2 * 2 + batch * topk * 4 + 2 * batch * hq * d * 2
     res = {"config": f"top-k decode B64 ctx 4096-131072 Hq64 Hkv8 D128 top-k 2048, KV of every sequence cut into {world} "
                      "page-aligned shards (one per rank), exchange of packed (O, lse) partials, combine",
-           "exchange": ("peer stores over NVLink into IPC-mapped receive buffers + bounded wait in the combine kernel"
+           "exchange": ("a push kernel stores this rank's partials into the IPC-mapped receive buffers of all ranks over "
+                        "NVLink and counts arrivals; bounded wait in the combine kernel"
                         if dec_peer is not None else ("none (one rank)" if world == 1 else "one NCCL all-gather")),
            "timing": mode, "us_per_step": t_full, "us_decode_plus_combine": t_local,
            "exchange_share": max(0.0, (t_full - t_local) / t_full) if world > 1 else 0.0,
            "us_per_step_nccl_allgather": t_nccl if world > 1 else None,
+           "us_per_step_decode_kernel_stores_to_peers": t_fused if dec_peer is not None else None,
            "exchange_bytes_per_rank": batch * hq * (d + 1) * 4,
            "algorithmic_mb_all_ranks": nbytes / 1e6, "aggregate_gbs": nbytes / t_full / 1e3}
     if peer_note:

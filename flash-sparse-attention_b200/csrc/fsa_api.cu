@@ -829,6 +829,22 @@ int fsa_decode(const FsaDecArgs* a, void* stream_) {
   p.key_bounds = gather ? a->key_bounds : nullptr;
   p.gather_count = gather ? a->gather_count : nullptr;
   p.gate_ws = a->gate_ws;
+  if (a->peers) {
+    // partials straight into the receive buffers of a context-parallel group: packed layout only
+    const FsaPeerArgs* pe = a->peers;
+    const long long per = (long long)a->batch * a->heads_q * (a->head_dim + 1);
+    if (!a->partial_only || !a->out_partial || pe->world <= 0 || pe->world > FSA_PEER_MAX_RANKS || pe->rank < 0 ||
+        pe->rank >= pe->world || p.op_ss != per || p.lp_ss != per || pe->block_floats != per * ns ||
+        a->lse_partial != a->out_partial + (long long)a->batch * a->heads_q * a->head_dim)
+      return FSA_ERR_INVALID_ARG;
+    for (int r = 0; r < pe->world; ++r) {
+      if (!pe->region[r] || (reinterpret_cast<uintptr_t>(pe->region[r]) & 255)) return FSA_ERR_INVALID_ARG;
+      p.peer_base[r] = reinterpret_cast<unsigned char*>(pe->region[r]);
+    }
+    p.peer_world = pe->world;
+    p.peer_rank = pe->rank;
+    p.peer_block_floats = pe->block_floats;
+  }
   mark(a->ev_before, stream);
   p.D = a->head_dim;
   cudaError_t e = fsa::launch_dec(p, a->kind, a->dtype, head_dim_kernel(a->head_dim), stream);

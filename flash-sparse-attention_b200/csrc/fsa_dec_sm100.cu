@@ -147,6 +147,14 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
   const int b = idx / p.num_splits;
   const int split = idx - b * p.num_splits;
   const bool gather = p.flags & F_GATHER, paged = p.flags & F_PAGED, local = p.flags & F_LOCAL;
+  // peer exchange: which of the two receive buffers this step uses (the count of exchanges sent so far lives in this
+  // rank's region; the last CTA of the grid advances it)
+  unsigned long long peer_step = 0;
+  long long peer_slot = 0;
+  if (p.peer_world > 0) {
+    peer_step = *reinterpret_cast<const volatile unsigned long long*>(p.peer_base[p.peer_rank] + 128);
+    peer_slot = ((long long)(peer_step & 1ull) * p.peer_world + p.peer_rank) * p.peer_block_floats;
+  }
   const int off_k = (p.flags & F_VARLEN_K) ? p.cu_k[b] : 0;
   const int sk = (p.flags & F_USED_K) ? p.used_k[b] : ((p.flags & F_VARLEN_K) ? p.cu_k[b + 1] - off_k : p.sk);
   const int bk = (p.flags & F_VARLEN_K) ? 0 : b;
@@ -610,10 +618,22 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
       const float inv = dead ? 1.f : v_scale / l_tot;
       const int head = hkv * p.G + row;
       if (p.flags & F_SPLIT) {
-        float* dst = p.out_partial + (long long)split * p.op_ss + ((long long)b * p.Hq + head) * p.D + d0;
-        *reinterpret_cast<float4*>(dst) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
-        if (d0 == 0)
-          p.lse_partial[(long long)split * p.lp_ss + (long long)head * p.B + b] = dead ? -INFINITY : m_tot * c + log2f(l_tot);
+        const long long o_at = (long long)split * p.op_ss + ((long long)b * p.Hq + head) * p.D + d0;
+        const long long l_at = (long long)split * p.lp_ss + (long long)head * p.B + b;
+        const float4 ov = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+        const float lv = dead ? -INFINITY : m_tot * c + log2f(l_tot);
+        if (p.peer_world > 0) {
+          // the packed block of this rank, stored into the receive buffer of every rank (plain peer stores)
+          const long long lse_off = p.lse_partial - p.out_partial;
+          for (int r = 0; r < p.peer_world; ++r) {
+            float* blk = reinterpret_cast<float*>(p.peer_base[r] + 256) + peer_slot;
+            *reinterpret_cast<float4*>(blk + o_at) = ov;
+            if (d0 == 0) blk[lse_off + l_at] = lv;
+          }
+        } else {
+          *reinterpret_cast<float4*>(p.out_partial + o_at) = ov;
+          if (d0 == 0) p.lse_partial[l_at] = lv;
+        }
       } else {
         TO* dst = reinterpret_cast<TO*>(p.out) + (long long)b * p.o_sb + (long long)head * p.o_sh + d0;
         uint2 v;
@@ -626,6 +646,21 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
       }
     }
     __syncthreads();
+  }
+  if (p.peer_world > 0) {
+    // every store of this CTA is ordered before its arrivals; the last CTA counts the exchange as sent
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) {
+      for (int r = 0; r < p.peer_world; ++r)
+        atomicAdd_system(reinterpret_cast<unsigned long long*>(p.peer_base[r]) + p.peer_rank, 1ull);
+      unsigned char* mine = p.peer_base[p.peer_rank];
+      unsigned int* done = reinterpret_cast<unsigned int*>(mine + 136);
+      if (atomicAdd(done, 1u) == gridDim.x - 1) {
+        *done = 0u;
+        *reinterpret_cast<volatile unsigned long long*>(mine + 128) = peer_step + 1;
+      }
+    }
   }
 }
 

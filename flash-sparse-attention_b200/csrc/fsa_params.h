@@ -120,6 +120,10 @@ struct DecKernelParams {
   float* gate_ws;          // gated, optional: float2 (max, min) of delta per (sequence, KV head, 16-key tile)
   const int* gather_count; // optional [B]: leading entries of a row of gather_idx that can be valid
   const int* key_bounds;   // optional [B, 2]: gathered positions outside [lo, hi) are masked, others shifted by -lo
+  // peer exchange (optional): partials go to the receive buffer of every rank, arrivals are counted there
+  unsigned char* peer_base[16];
+  long long peer_block_floats;
+  int peer_world, peer_rank;
   int D;  // real head size (<= the kernel's HD)
   unsigned flags;
 };

@@ -126,9 +126,9 @@ extern "C" int fsa_peer_push(const FsaPeerArgs* a, const float* block, void* str
 }
 
 extern "C" int fsa_peer_combine(const FsaPeerArgs* a, void* out, float* lse, int partials_per_rank, int rows, int heads,
-                                int head_dim, int dtype, int* status, void* stream_) {
+                                int head_dim, int dtype, int arrivals_per_step, int* status, void* stream_) {
   if (!a || !out || !lse || !status || a->world <= 0 || a->world > FSA_PEER_MAX_RANKS || a->rank < 0 ||
-      a->rank >= a->world || partials_per_rank <= 0 || rows < 0 || heads <= 0)
+      a->rank >= a->world || partials_per_rank <= 0 || rows < 0 || heads <= 0 || arrivals_per_step < 0)
     return FSA_ERR_INVALID_ARG;
   if (dtype != FSA_DT_BF16 && dtype != FSA_DT_FP16) return FSA_ERR_UNSUPPORTED;
   const long long per = (long long)rows * heads * (head_dim + 1);  // one partial: outputs, then log-sum-exps
@@ -159,7 +159,7 @@ extern "C" int fsa_peer_combine(const FsaPeerArgs* a, void* out, float* lse, int
   c.status = status;
   c.buf_stride = (long long)a->world * a->block_floats;
   c.peer_world = a->world;
-  c.arrivals_per_step = fsa::PUSH_CTAS;
+  c.arrivals_per_step = arrivals_per_step > 0 ? arrivals_per_step : fsa::PUSH_CTAS;
   cudaError_t e = fsa::launch_combine(c, dtype, reinterpret_cast<cudaStream_t>(stream_));
   if (e == cudaErrorInvalidValue) return FSA_ERR_UNSUPPORTED;
   return e == cudaSuccess ? FSA_OK : FSA_ERR_LAUNCH;

@@ -262,6 +262,7 @@ class FsaDecArgs(ctypes.Structure):
         ("gate_ws", c_void_p),
         ("ev_before", c_void_p),
         ("ev_after", c_void_p),
+        ("peers", c_void_p),
     ]
 
 
@@ -377,8 +378,8 @@ def load():
     lib.fsa_peer_push.restype = c_int
     lib.fsa_peer_push.argtypes = [POINTER(FsaPeerArgs), c_void_p, c_void_p]
     lib.fsa_peer_combine.restype = c_int
-    lib.fsa_peer_combine.argtypes = [POINTER(FsaPeerArgs), c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                                     c_void_p]
+    lib.fsa_peer_combine.argtypes = [POINTER(FsaPeerArgs), c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                     c_void_p, c_void_p]
     lib.fsa_fwd_workspace_bytes.restype = c_int
     lib.fsa_fwd_workspace_bytes.argtypes = [POINTER(FsaFwdArgs), POINTER(FsaFwdWorkspace)]
     lib.fsa_bwd_workspace_bytes.restype = c_int

@@ -24,8 +24,10 @@ them in place.
 Exchange: with `exchange="peer"` (ranks on the GPUs of one node, one process per GPU) the all-gather is replaced by
 the library's own kernels: every rank stores its block straight into the receive buffers of all ranks over NVLink
 (`fsa_peer_push`: plain peer stores into memory mapped through CUDA IPC, an arrival counter per sender) and the
-combine kernel waits, bounded, for the arrivals of the step (`fsa_peer_combine`). No multicast is involved. The
-default `exchange="nccl"` keeps the single NCCL all-gather.
+combine kernel waits, bounded, for the arrivals of the step (`fsa_peer_combine`). No multicast is involved. With
+`exchange="fused"` the decode kernel itself stores its partials into the peers' buffers and counts the arrivals of its
+CTAs (no push kernel): the step is localise -> decode -> combine. The default `exchange="nccl"` keeps the single NCCL
+all-gather.
 """
 
 from typing import Callable, Optional, Tuple
@@ -94,7 +96,7 @@ class ContextParallelDecoder:
 
     def __init__(self, batch: int, heads_q: int, head_dim: int, dtype: torch.dtype, device, num_splits: int = 1,
                  group=None, exchange: str = "nccl"):
-        assert exchange in ("nccl", "peer")
+        assert exchange in ("nccl", "peer", "fused")
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.batch, self.heads, self.head_dim, self.dtype, self.ns = batch, heads_q, head_dim, dtype, num_splits
@@ -105,8 +107,10 @@ class ContextParallelDecoder:
         self.lse = torch.empty((batch, heads_q), dtype=torch.float32, device=device)
         self._bounds = self._bounds_key = self._idx = self._count = None
         self.peers = None
-        if exchange == "peer" and self.world > 1:
+        self.fused = exchange == "fused" and self.world > 1
+        if exchange in ("peer", "fused") and self.world > 1:
             self.peers = PeerExchange(num_splits * per, device, group)
+        self._arrivals = 0
 
     def partial(self, query, key_local, value_local, shard_lo, shard_hi, gather_kv_indices=None,
                 seqused_k_global=None, seqused_k_local=None, page_table=None, softmax_scale=None,
@@ -135,14 +139,18 @@ class ContextParallelDecoder:
                     packed_partials=self.send, gather_kv_indices=idx, gather_count=count,
                     seqused_k=seqused_k_global if gather else seqused_k_local,
                     threshold_seqlen_k=None if gather else seqused_k_global, page_table=page_table,
-                    softmax_scale=softmax_scale, softmax_threshold=softmax_threshold)
+                    softmax_scale=softmax_scale, softmax_threshold=softmax_threshold,
+                    peers=self.peers.args if self.fused else None)
+        # arrivals a rank counts per step when the decode kernel stores the partials itself: its CTAs
+        self._arrivals = self.batch * key_local.shape[-2] * self.ns
         return self.send
 
     def exchange(self):
         if self.world == 1:
             return self.send
         if self.peers is not None:
-            self.peers.push(self.send)
+            if not self.fused:
+                self.peers.push(self.send)
             return None  # the partials are in the peer region; combine() waits for them
         dist.all_gather_into_tensor(self.recv, self.send, group=self.group)
         return self.recv
@@ -151,7 +159,8 @@ class ContextParallelDecoder:
         from flash_sparse_attn.ops.triton.flash_dec import combine_packed_partials
 
         if packed is None:
-            return self.peers.combine(self.out, self.lse, self.ns, self.batch, self.heads, self.head_dim)
+            return self.peers.combine(self.out, self.lse, self.ns, self.batch, self.heads, self.head_dim,
+                                      arrivals=self._arrivals if self.fused else 0)
         return combine_packed_partials(packed, packed.shape[0], self.batch, self.heads, self.head_dim, self.dtype,
                                        out=self.out, lse=self.lse)
 
@@ -209,14 +218,14 @@ class PeerExchange:
                                                 self._lib.current_stream_ptr(self.device))
         self._lib.check(rc, "fsa_peer_push")
 
-    def combine(self, out, lse, partials_per_rank, batch, heads, head_dim):
+    def combine(self, out, lse, partials_per_rank, batch, heads, head_dim, arrivals: int = 0):
         import ctypes
 
         status = self._lib.status_word(self.device)
         with torch.cuda.device(self.device):
             rc = self._lib.load().fsa_peer_combine(ctypes.byref(self.args), out.data_ptr(), lse.data_ptr(),
                                                    partials_per_rank, batch, heads, head_dim,
-                                                   self._lib.dtype_code(out.dtype), status.data_ptr(),
+                                                   self._lib.dtype_code(out.dtype), arrivals, status.data_ptr(),
                                                    self._lib.current_stream_ptr(self.device))
         self._lib.check(rc, "fsa_peer_combine")
         return out, lse

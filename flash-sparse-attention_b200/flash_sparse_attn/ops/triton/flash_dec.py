@@ -67,6 +67,7 @@ def attn_decode(
     key_range=None,
     packed_partials: Optional[torch.Tensor] = None,
     gather_count: Optional[torch.Tensor] = None,
+    peers=None,
 ):
     """Returns ``(out, lse)``; with ``partial_only`` returns ``(out_partial [ns,B,Hq,D] fp32,
     lse_partial [ns,Hq,B] fp32 base-2)`` instead (used by context-parallel decode).
@@ -203,6 +204,11 @@ def attn_decode(
             out_partial = _lib.workspace(ws.out_partial, device).view(num_splits, batch, num_heads_q, head_dim)
             lse_partial = _lib.workspace(ws.lse_partial, device).view(num_splits, num_heads_q, batch)
     a.out_partial, a.lse_partial = _lib.ptr(out_partial), _lib.ptr(lse_partial)
+    if peers is not None:
+        # `peers`: the FsaPeerArgs of a context-parallel group - the kernel stores the packed partials into the
+        # receive buffer of every rank and counts its arrivals there (context_parallel.PeerExchange)
+        assert partial_only and packed_partials is not None
+        a.peers = ctypes.cast(ctypes.pointer(peers), ctypes.c_void_p)
     _lib.attach_profile_events(a)
 
     with torch.cuda.device(device):

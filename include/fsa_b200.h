@@ -304,6 +304,12 @@ typedef struct FsaDecArgs {
   float* gate_ws;
   void* ev_before;
   void* ev_after;
+  /* Optional, with partial_only and the packed partial layout (both strides = batch*heads_q*(head_dim + 1)): the
+   * peer regions of a context-parallel group (struct FsaPeerArgs below). The kernel then stores its partials
+   * straight into the receive buffer of EVERY rank instead of out_partial and counts its CTAs' arrivals there, so
+   * the step is fsa_decode -> fsa_peer_combine with arrivals_per_step = batch * heads_kv * num_splits and no
+   * fsa_peer_push. block_floats must equal num_splits * batch*heads_q*(head_dim + 1). */
+  const struct FsaPeerArgs_* peers;
 } FsaDecArgs;
 
 int fsa_decode(const FsaDecArgs* args, void* stream);
@@ -485,7 +491,7 @@ int fsa_kv_append(const FsaKvAppendArgs* args, void* stream);
 typedef struct {
   unsigned char bytes[64];
 } FsaIpcHandle;
-typedef struct {
+typedef struct FsaPeerArgs_ {
   void* region[FSA_PEER_MAX_RANKS]; /* region of rank r as mapped in THIS process (own: from fsa_peer_alloc) */
   int world;
   int rank;
@@ -497,8 +503,10 @@ int fsa_peer_open(const FsaIpcHandle* handle, void** region);           /* FSA_E
 int fsa_peer_close(void* region);
 int fsa_peer_free(void* region);
 int fsa_peer_push(const FsaPeerArgs* args, const float* block, void* stream);
+/* arrivals_per_step: how many arrivals a rank counts per step - 0 for fsa_peer_push (its own grid), the number of
+ * decode CTAs (batch * heads_kv * num_splits) when fsa_decode stored the partials itself (FsaDecArgs.peers). */
 int fsa_peer_combine(const FsaPeerArgs* args, void* out, float* lse, int partials_per_rank, int rows, int heads,
-                     int head_dim, int dtype, int* status, void* stream);
+                     int head_dim, int dtype, int arrivals_per_step, int* status, void* stream);
 
 /*
  * One shard's view of global top-k positions: for every row keep the positions inside [lo, hi) (key_bounds

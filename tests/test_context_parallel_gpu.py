@@ -57,26 +57,29 @@ def _worker(rank, world, port, ret):
     ref4, _ = attn_decode("sparse", qp, k, v, softmax_threshold=-128.0, num_splits=1)
     # the same exchange through peer stores (no collective library): several steps in a row, eagerly and as a
     # replayed CUDA graph (the step counter and the buffer in use live on the device)
-    dec = cp.ContextParallelDecoder(b, hq, d, torch.bfloat16, dev, num_splits=2, exchange="peer")
+    # ("fused": the decode kernel stores into the peers' buffers itself; "peer": a separate push kernel)
     kl, vl = k[:, lo:hi].contiguous(), v[:, lo:hi].contiguous()
     peer_ok = True
-    for step in range(3):
-        o5, l5 = dec(q, kl, vl, lo, hi, gather_kv_indices=idx, seqused_k_global=used, softmax_threshold=-128.0)
+    for mode in ("peer", "fused"):
+        dec = cp.ContextParallelDecoder(b, hq, d, torch.bfloat16, dev, num_splits=2, exchange=mode)
+        for step in range(3):
+            o5, l5 = dec(q, kl, vl, lo, hi, gather_kv_indices=idx, seqused_k_global=used, softmax_threshold=-128.0)
+            torch.cuda.synchronize()
+            peer_ok = peer_ok and (o5.float() - ref.float()).abs().max().item() < 1e-2 and \
+                (l5 - ref_lse).abs().max().item() < 1e-3
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            dec(q, kl, vl, lo, hi, gather_kv_indices=idx, seqused_k_global=used, softmax_threshold=-128.0)
+        for step in range(3):
+            dec.out.zero_()
+            graph.replay()
+            torch.cuda.synchronize()
+            peer_ok = peer_ok and (dec.out.float() - ref.float()).abs().max().item() < 1e-2
         torch.cuda.synchronize()
-        peer_ok = peer_ok and (o5.float() - ref.float()).abs().max().item() < 1e-2 and \
-            (l5 - ref_lse).abs().max().item() < 1e-3
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        dec(q, kl, vl, lo, hi, gather_kv_indices=idx, seqused_k_global=used, softmax_threshold=-128.0)
-    for step in range(3):
-        dec.out.zero_()
-        graph.replay()
-        torch.cuda.synchronize()
-        peer_ok = peer_ok and (dec.out.float() - ref.float()).abs().max().item() < 1e-2
-    torch.cuda.synchronize()
-    fsa.check_status()
-    dist.barrier()
-    dec.peers.close()
+        fsa.check_status()
+        dist.barrier()
+        dec.peers.close()
+        del graph
     close = lambda a, r: bool(((a.float() - r.float()).abs() <= 2e-2 + 2e-2 * r.float().abs()).all())  # noqa: E731
     ok = ((out.float() - ref.float()).abs().max().item() < 1e-2 and (lse - ref_lse).abs().max().item() < 1e-3
           and (out2.float() - ref2.float()).abs().max().item() < 1e-2 and close(out3, ref3) and close(out4, ref4)
