@@ -195,7 +195,7 @@ __global__ void __launch_bounds__(256) gate_ext_kernel(GateExtParams p) {
   if (lane == 0) *reinterpret_cast<float2*>(dst) = make_float2(mx, mn);
 }
 
-constexpr int PP_ITEMS = 4;  // (row, head) items per lane group in the pre / post passes: more loads in flight
+constexpr int PP_ITEMS = 1;  // (row, head) items per lane group in the pre / post passes (4 and 8 measured slower: fewer CTAs)
 
 // head_dim / 8 lanes per (query row, head), 16-byte loads; also clears the row of the fp32 dQ accumulator.
 // flash_sparse_attn/ops/triton/flash_bwd_preprocess.py:170-195.
