@@ -136,7 +136,9 @@ __device__ __forceinline__ bool tile_col_visible(const TileMask& tm, int i) {
          (unsigned(i - tm.lo[2]) < tm.len[2]);
 }
 
-template <int HD, typename T, int KIND>
+// BSCALE: FP8 inputs with one scale per 128-position block (a separate instantiation: as a run-time switch it cost
+// the per-tensor FP8 forward 10 %).
+template <int HD, typename T, int KIND, bool BSCALE = false>
 __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant__ FwdKernelParams p) {
   // T is the element type of Q, K, V and of P: bf16 / fp16 (kind::f16) or FP8 e4m3 / e5m2 (kind::f8f6f4,
   // flash_sparse_attn/ops/triton/flash_sparse_fwd.py:49, :84-86 under IS_QUANT). Outputs and the gate
@@ -625,7 +627,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     // the output accumulator is rescaled when that reference grows (like the running maximum); the output is
     // multiplied by the final reference. Blocks more than 2^9 below the running reference underflow in FP8 P, i.e.
     // contributions that small relative to the largest block a row has seen are dropped.
-    const bool bscaled = F8 && p.k_bscale != nullptr;
+    constexpr bool bscaled = F8 && BSCALE;
     const float* kbs = bscaled ? p.k_bscale + ((long long)si.b * p.Hkv + si.hkv) * p.n_tiles_k : nullptr;
     const float* vbs = bscaled ? p.v_bscale + ((long long)si.b * p.Hkv + si.hkv) * p.n_tiles_k : nullptr;
     const float c = bscaled ? p.scale_log2 * p.q_bscale[((long long)si.b * p.Hq + q_head) * p.num_m_blocks +
@@ -938,9 +940,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
   }
 }
 
-template <int HD, typename T, int KIND>
+template <int HD, typename T, int KIND, bool BSCALE = false>
 cudaError_t launch_one(const FwdKernelParams& p, cudaStream_t stream) {
-  auto kern = fwd_kernel<HD, T, KIND>;
+  auto kern = fwd_kernel<HD, T, KIND, BSCALE>;
   constexpr int smem = FwdSmem<HD, sizeof(T)>::kTotal;
   static std::atomic<unsigned long long> opted_in{0};  // one bit per device: the attribute is per device
   if (cudaError_t e = smem_opt_in(kern, smem, opted_in); e != cudaSuccess) return e;
@@ -956,6 +958,16 @@ cudaError_t launch_one(const FwdKernelParams& p, cudaStream_t stream) {
 // unsupported combinations.
 
 cudaError_t launch_fwd(const FwdKernelParams& p, int kind, int dtype, int head_dim, cudaStream_t stream) {
+  if (p.k_bscale) {  // block-scaled FP8: dense and sparse kinds at head_dim 128
+    if (head_dim != 128 || kind == KIND_GATED) return cudaErrorInvalidValue;
+    if (dtype == DT_E4M3)
+      return kind == KIND_DENSE ? launch_one<128, __nv_fp8_e4m3, KIND_DENSE, true>(p, stream)
+                                : launch_one<128, __nv_fp8_e4m3, KIND_SPARSE, true>(p, stream);
+    if (dtype == DT_E5M2)
+      return kind == KIND_DENSE ? launch_one<128, __nv_fp8_e5m2, KIND_DENSE, true>(p, stream)
+                                : launch_one<128, __nv_fp8_e5m2, KIND_SPARSE, true>(p, stream);
+    return cudaErrorInvalidValue;
+  }
 #define FSA_FWD_CASE(HD_, T_, DT_)                                                  \
   if (head_dim == HD_ && dtype == DT_) {                                            \
     if (kind == KIND_DENSE) return launch_one<HD_, T_, KIND_DENSE>(p, stream);      \
