@@ -216,3 +216,65 @@ def test_sharded_decode_pieces_on_one_gpu(mode, splits):
     _sync()
     assert_close(f"sharded-{mode}", out, ref)
     assert torch.allclose(lse, ref_lse, rtol=0, atol=2e-3)
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_peer_exchange_kernels_single_rank(fused):
+    """The peer-exchange kernels of the context-parallel decode with a group of one rank (no second GPU, no IPC
+    mapping): partials go through the region's two alternating receive buffers, the arrival counters and the
+    device-side step counter, eagerly and as a replayed CUDA graph. `fused`: the decode kernel stores the partials
+    into the region itself; otherwise fsa_peer_push does."""
+    import ctypes
+
+    from flash_sparse_attn import _lib
+    from flash_sparse_attn.ops.triton.flash_dec import attn_decode
+
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(33)
+    b, sk, hq, hkv, d, topk, splits = 3, 1500, 16, 2, 128, 256, 2
+    q = torch.randn(b, hq, d, generator=g).to(torch.bfloat16).to(DEV)
+    k = torch.randn(b, sk, hkv, d, generator=g).to(torch.bfloat16).to(DEV)
+    v = torch.randn(b, sk, hkv, d, generator=g).to(torch.bfloat16).to(DEV)
+    idx = torch.stack([torch.randperm(sk, generator=g)[:topk] for _ in range(b)]).to(torch.int32).to(DEV)
+    per = b * hq * (d + 1)
+    nbytes = ctypes.c_int64()
+    assert lib.fsa_peer_region_bytes(1, splits * per, ctypes.byref(nbytes)) == 0
+    region, handle = ctypes.c_void_p(), _lib.FsaIpcHandle()
+    assert lib.fsa_peer_alloc(nbytes.value, ctypes.byref(region), ctypes.byref(handle)) == 0
+    try:
+        args = _lib.FsaPeerArgs()
+        args.region[0], args.world, args.rank, args.block_floats = region.value, 1, 0, splits * per
+        send = torch.empty(splits, per, dtype=torch.float32, device=DEV)
+        out = torch.empty(b, hq, d, dtype=torch.bfloat16, device=DEV)
+        lse = torch.empty(b, hq, dtype=torch.float32, device=DEV)
+        status = _lib.status_word(torch.device(DEV))
+
+        def step(qq):
+            attn_decode("sparse", qq, k, v, partial_only=True, num_splits=splits, packed_partials=send,
+                        gather_kv_indices=idx, softmax_threshold=-128.0, peers=args if fused else None)
+            stream = _lib.current_stream_ptr(torch.device(DEV))
+            if not fused:
+                assert lib.fsa_peer_push(ctypes.byref(args), send.data_ptr(), stream) == 0
+            arrivals = b * hkv * splits if fused else 0
+            assert lib.fsa_peer_combine(ctypes.byref(args), out.data_ptr(), lse.data_ptr(), splits, b, hq, d,
+                                        _lib.dtype_code(torch.bfloat16), arrivals, status.data_ptr(), stream) == 0
+
+        qs = [q, (q.float() * 0.5).to(torch.bfloat16), (q.float() * -1.0).to(torch.bfloat16)]
+        for qq in qs:  # three steps: both receive buffers, different data each time
+            step(qq)
+            ref, ref_lse = attn_decode("sparse", qq, k, v, gather_kv_indices=idx, softmax_threshold=-128.0, num_splits=1)
+            _sync()
+            assert_close("peer-single", out, ref)
+            assert torch.allclose(lse, ref_lse, rtol=0, atol=2e-3)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step(q)
+        ref, _ = attn_decode("sparse", q, k, v, gather_kv_indices=idx, softmax_threshold=-128.0, num_splits=1)
+        for _ in range(3):
+            out.zero_()
+            graph.replay()
+            _sync()
+            assert_close("peer-single-graph", out, ref)
+    finally:
+        torch.cuda.synchronize()
+        assert lib.fsa_peer_free(region.value) == 0
