@@ -3,7 +3,7 @@
 // One CTA serves one KV head of one sequence (and one KV split). The G query heads of that KV head
 // are the rows of a 16-row tile (packed GQA, like the reference's decode: scheduler.py:2455-2461).
 // The CTA's key range is cut into four contiguous sub-ranges, one per warp; each warp streams its
-// keys in 16-key tiles through a private 3-stage cp.async ring (16-byte copies, zero-fill for
+// keys in 16-key tiles through a private 2-stage cp.async ring (16-byte copies, zero-fill for
 // masked / out-of-range rows), runs a complete flash-decoding recurrence on them with mma.sync
 // m16n8k16 (the arithmetic is ~8 FLOP/byte, far below the tensor roofline, so the legacy MMA path
 // is enough and keeps the kernel free to run several CTAs per SM), and the four partial states are
@@ -28,10 +28,11 @@ namespace fsa {
 namespace {
 
 constexpr int DTN = 16;      // keys per warp tile
-// cp.async ring depth per warp: 3 tiles of 16-bit rows, 6 of FP8 rows (same shared memory, twice as
-// many row fetches in flight: the loaded latency of scattered rows, not bandwidth, bounds the kernel)
+// cp.async ring depth per warp: 2 tiles of 16-bit rows, 4 of FP8 rows (same shared memory, twice as many row
+// fetches in flight). Measured on the paged top-k configuration: depth 2 / 3 = 100.6 / 101.9 us in bf16, 103.4 /
+// 106.1 us in FP8; three CTAs per SM (168 registers, depth 2) 120 us.
 #ifndef FSA_DEC_STAGES16
-#define FSA_DEC_STAGES16 3
+#define FSA_DEC_STAGES16 2
 #endif
 #ifndef FSA_DEC_MINBLOCKS
 #define FSA_DEC_MINBLOCKS 2
