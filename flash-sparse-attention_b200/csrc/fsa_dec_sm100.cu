@@ -193,34 +193,42 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
   const char* kbase = reinterpret_cast<const char*>(p.k);
   const char* vbase = reinterpret_cast<const char*>(p.v);
 
-  // Address (in elements) of key `pos` of this sequence / head inside the K (and V) tensor; -1 = no row.
-  auto row_elem = [&](int pos) -> long long {
-    if (pos < 0 || pos >= capacity) return -1;
-    if (paged) {
-      const int page = ptab[pos >> page_shift];
-      return (long long)page * p.k_sb + (long long)(pos & page_mask) * p.k_sn + (long long)hkv * p.k_sh;
+  // Address translation of a tile runs two tiles ahead of its copies, one dependent load per loop iteration, so that
+  // neither the read of the gathered position nor the page-table look-up behind it stalls the warp in front of the
+  // copies: stage A reads the position of key `lane` of a tile (gathered: from the index row), stage B - one
+  // iteration later, when that load has landed - maps it into this shard and reads its page, and the iteration
+  // after that turns (position, page) into the row address and issues the copies.
+  auto xlat_a = [&](int n) -> int {
+    int raw = -1;
+    if (n >= 0 && lane < DTN) {
+      const int i = n * DTN + lane;
+      if (gather)
+        raw = (i < topk) ? gidx[i] : -1;
+      else
+        raw = (i < sk) ? i : -1;
     }
-    return (long long)bk * p.k_sb + (long long)(off_k + pos) * p.k_sn + (long long)hkv * p.k_sh;
+    return raw;
+  };
+  auto xlat_b = [&](int raw, int* pos_out) -> int {
+    int pos = raw;
+    if (gather && p.key_bounds) pos = (pos >= key_lo && pos < key_hi) ? pos - key_lo : -1;
+    if (pos >= capacity) pos = -1;
+    *pos_out = pos;
+    return (paged && pos >= 0) ? ptab[pos >> page_shift] : 0;
   };
 
-  // Issue the copies of tile n into ring slot `slot`; returns the bitmask of keys that exist.
+  // Issue the copies of tile n (key `lane` at position `pos` in page `page`, from the translation stages) into ring
+  // slot `slot`; returns the bitmask of keys that exist.
   // Gated kernels also fetch delta of key (lane & 15) into *dval (0 for keys that do not exist).
-  auto issue_tile = [&](int n, int slot, float* dval) -> unsigned {
+  auto issue_tile = [&](int n, int pos, int page, int slot, float* dval) -> unsigned {
     long long e = -1;
-    int pos = -1;
-    if (lane < DTN) {
-      const int i = n * DTN + lane;
-      if (gather) {
-        pos = (i < topk) ? gidx[i] : -1;
-        if (p.key_bounds) pos = (pos >= key_lo && pos < key_hi) ? pos - key_lo : -1;
-      } else
-        pos = (i < sk) ? i : -1;
-      e = row_elem(pos);
-    }
+    if (lane < DTN && pos >= 0)
+      e = paged ? (long long)page * p.k_sb + (long long)(pos & page_mask) * p.k_sn + (long long)hkv * p.k_sh
+                : (long long)bk * p.k_sb + (long long)(off_k + pos) * p.k_sn + (long long)hkv * p.k_sh;
     if (KIND == KIND_GATED) {
       float dv = 0.f;
       if (lane < DTN && e >= 0) {
-        const long long de = paged ? (long long)ptab[pos >> page_shift] * p.d_sb + (long long)hkv * p.d_sh +
+        const long long de = paged ? (long long)page * p.d_sb + (long long)hkv * p.d_sh +
                                          (pos & page_mask)
                                    : (long long)bk * p.d_sb + (long long)hkv * p.d_sh + off_k + pos;
         dv = float(reinterpret_cast<const TO*>(p.delta)[de]);
@@ -333,11 +341,30 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
     unsigned present_q[DSTAGES];  // presence masks of the tiles in the ring, oldest first
     int n_q[DSTAGES];             // their tile indices (-1: empty)
     int slot_load = 0;
+    // translation pipeline: tile xa_n has its position read under way, tile xb_n its page
+    int xa_n = next_fetch();
+    int xa_raw = xlat_a(xa_n);
+    int xb_n = xa_n, xb_pos = -1;
+    int xb_page = xlat_b(xa_raw, &xb_pos);
+    xa_n = next_fetch();
+    xa_raw = xlat_a(xa_n);
+    // hands out the tile whose translation is complete and moves the two younger ones up a stage
+    auto xlat_pop = [&](int* pos, int* page) -> int {
+      const int n = xb_n;
+      *pos = xb_pos;
+      *page = xb_page;
+      xb_n = xa_n;
+      xb_page = xlat_b(xa_raw, &xb_pos);
+      xa_n = next_fetch();
+      xa_raw = xlat_a(xa_n);
+      return n;
+    };
 #pragma unroll
     for (int s = 0; s < DSTAGES - 1; ++s) {
       present_q[s] = 0;
-      n_q[s] = next_fetch();
-      if (n_q[s] >= 0) present_q[s] = issue_tile(n_q[s], s, &dlq[s]);
+      int pos, page;
+      n_q[s] = xlat_pop(&pos, &page);
+      if (n_q[s] >= 0) present_q[s] = issue_tile(n_q[s], pos, page, s, &dlq[s]);
       cp_async_commit();
     }
     present_q[DSTAGES - 1] = 0;
@@ -348,8 +375,9 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
       const int n = n_q[0];
       // keep the ring full, then wait for the oldest tile
       unsigned pres_new = 0;
-      const int n_new = next_fetch();
-      if (n_new >= 0) pres_new = issue_tile(n_new, slot_load, &dlq[DSTAGES - 1]);
+      int pos_new, page_new;
+      const int n_new = xlat_pop(&pos_new, &page_new);
+      if (n_new >= 0) pres_new = issue_tile(n_new, pos_new, page_new, slot_load, &dlq[DSTAGES - 1]);
       cp_async_commit();
       present_q[DSTAGES - 1] = pres_new;
       n_q[DSTAGES - 1] = n_new;
