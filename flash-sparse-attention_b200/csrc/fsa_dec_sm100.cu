@@ -19,6 +19,8 @@
 //   rejects this combination, assert_inputs.py:303-305; here it is defined as the composition).
 #include <mma.h>
 #include "fsa_aux.h"
+#include <type_traits>
+
 #include "fsa_params.h"
 #include "fsa_ptx.cuh"
 #include "fsa_schedule.h"
@@ -52,11 +54,21 @@ struct DecSmem {
   static constexpr int kTotal = (DWARPS * kWarp > kMerge ? DWARPS * kWarp : kMerge);
 };
 
-__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
-  const int sz = valid ? 16 : 0;  // src-size 0 -> the 16 bytes are zero-filled
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(sz) : "memory");
+// 16-byte asynchronous copy global -> shared: shared address as a register + compile-time offset, run-time source size
+// (0: the 16 bytes are zero-filled, nothing is read)
+template <int DOFF>
+__device__ __forceinline__ void cp_async16_at(uint32_t dst, const void* src, int sz) {
+  asm volatile("cp.async.cg.shared.global [%0 + %3], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz), "n"(DOFF) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// compile-time loop: f(std::integral_constant<int, I>) for I = BEGIN .. END - 1
+template <int BEGIN, int END, typename F>
+__device__ __forceinline__ void unroll_copy(F&& f) {
+  if constexpr (BEGIN < END) {
+    f(std::integral_constant<int, BEGIN>{});
+    unroll_copy<BEGIN + 1, END>(f);
+  }
+}
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
@@ -193,6 +205,17 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
   const char* kbase = reinterpret_cast<const char*>(p.k);
   const char* vbase = reinterpret_cast<const char*>(p.v);
 
+  // lane constants of the tile copies (see issue_tile)
+  constexpr int RPI = 32 / CH;  // rows per warp instruction
+  static_assert(RPI >= 1 && RPI <= 8 && (RPI & (RPI - 1)) == 0 && DTN % RPI == 0, "copy layout");
+  const int lane_h = lane / CH, lane_ch = lane % CH;
+  const bool lane_col_ok = lane_ch * (16 / ES) < p.D;  // columns past the real head size read as zeros
+  const int lane_sz = lane_col_ok ? 16 : 0;
+  const char* lane_k = kbase + (lane_col_ok ? lane_ch * 16 : 0);
+  const char* lane_v = vbase + (lane_col_ok ? lane_ch * 16 : 0);
+  const uint32_t lane_x4 = uint32_t((lane_ch ^ lane_h) << 4);
+  const uint32_t ring_u32 = smem_u32(ring);
+
   // Address translation of a tile runs two tiles ahead of its copies, one dependent load per loop iteration, so that
   // neither the read of the gathered position nor the page-table look-up behind it stalls the warp in front of the
   // copies: stage A reads the position of key `lane` of a tile (gathered: from the index row), stage B - one
@@ -236,19 +259,25 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
       *dval = __shfl_sync(0xffffffffu, dv, lane & 15);
     }
     const unsigned present = __ballot_sync(0xffffffffu, e >= 0) & 0xffffu;
-    uint8_t* kt = ring + slot * 2 * SM::kTile;
-    uint8_t* vt = kt + SM::kTile;
-#pragma unroll
-    for (int it = 0; it < DTN * CH / 32; ++it) {
-      const int item = it * 32 + lane;
-      const int r = item / CH, ch = item % CH;
-      const long long er = __shfl_sync(0xffffffffu, e, r);
-      const bool ok = er >= 0 && ch * (16 / ES) < p.D;  // columns past the real head size read as zeros
-      const long long src = ok ? (er + ch * (16 / ES)) * ES : 0;
-      const uint32_t dsto = r * SM::kRow + ((ch ^ (r & 7)) << 4);
-      cp_async16(kt + dsto, kbase + src, ok);
-      cp_async16(vt + dsto, vbase + src, ok);
-    }
+    // Lane l copies chunk l % CH of the rows RPI * it + l / CH: a warp instruction moves whole rows (one request per
+    // row; 32-byte pieces of sixteen rows per instruction ran 4.5 times slower). The row's byte offset comes from
+    // its owner lane by shuffle; everything else per copy is lane-constant or compile-time: the chunk's offset in
+    // the row, the swizzled place in the tile (chunk ^ row & 7 = (chunk ^ l / CH) ^ (RPI * it & 7)) and, from the
+    // ballot, whether the row exists.
+    const long long rowb = e >= 0 ? e * ES : 0;  // a row that does not exist copies nothing: any valid address
+    const unsigned rlo = (unsigned)rowb, rhi = (unsigned)(rowb >> 32);
+    const uint32_t kd = ring_u32 + slot * 2 * SM::kTile + lane_h * SM::kRow;
+    const unsigned ph = present >> lane_h;
+    unroll_copy<0, DTN / RPI>([&](auto it_tag) {
+      constexpr int it = decltype(it_tag)::value;
+      const int src_lane = RPI * it + lane_h;
+      const unsigned lo = __shfl_sync(0xffffffffu, rlo, src_lane), hi = __shfl_sync(0xffffffffu, rhi, src_lane);
+      const long long rb = (long long)(((unsigned long long)hi << 32) | lo);
+      const int sz = int((ph >> (RPI * it)) & 1u) * lane_sz;
+      const uint32_t d = kd + (lane_x4 ^ (((RPI * it) & 7) << 4));
+      cp_async16_at<it * RPI * SM::kRow>(d, lane_k + rb, sz);
+      cp_async16_at<it * RPI * SM::kRow + SM::kTile>(d, lane_v + rb, sz);
+    });
     return present;
   };
 
@@ -524,10 +553,15 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
         uint32_t pa[4];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-          float m_new = fmaxf(m_cur[r], m_run[r]);
-          m_new = fmaxf(m_new, -1e6f);
-          scale[r] = ex2_approx((m_run[r] - m_new) * c);
-          m_run[r] = m_new;
+          // the reference maximum moves only when it lags by more than 2^8 (always on the first tile, where it is
+          // -inf): the exponentials stay below 2^8, the sums in fp32, and the rescaling of the 16 x HD accumulator,
+          // which otherwise runs on most tiles of a short walk, becomes rare
+          const float m_cand = fmaxf(fmaxf(m_cur[r], m_run[r]), -1e6f);
+          scale[r] = 1.0f;
+          if (!((m_cand - m_run[r]) * c <= 8.0f)) {
+            scale[r] = ex2_approx((m_run[r] - m_cand) * c);
+            m_run[r] = m_cand;
+          }
         }
         const float mc0 = m_run[0] * c, mc1 = m_run[1] * c;
         float sum0 = 0.f, sum1 = 0.f;
