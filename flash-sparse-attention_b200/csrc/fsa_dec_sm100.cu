@@ -137,8 +137,20 @@ __device__ __forceinline__ void mma16816<__half>(float* c, const uint32_t* a, ui
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <int HD, typename T, int KIND>
-__global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(const DecKernelParams p) {
+// 8 x 8 matrix of 16-bit values held by a warp (lane (g, t): row g, columns 2t, 2t+1) -> its transpose
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+
+// TR (16-bit inputs, at most 8 query heads per KV head): the products run transposed, S^T = K Q^T and
+// O^T = V^T P^T, so that the 16 keys of a tile fill the M = 16 side of mma.m16n8k16 and the (up to) 8 query rows the
+// N = 8 side. With the rows on M, half of every fragment is padding when a KV head serves 8 query heads: transposed, the
+// accumulator takes 32 registers instead of 64, the Q fragments 16 instead of 32, a tile needs 8 + 8 MMAs instead of
+// 16 + 16, and three CTAs fit an SM instead of two. P^T reaches its B-operand layout through movmatrix.
+template <int HD, typename T, int KIND, bool TR>
+__global__ void __launch_bounds__(DWARPS * 32, TR ? 3 : FSA_DEC_MINBLOCKS) dec_kernel(const DecKernelParams p) {
   // T: element type of q, k, v. FP8 (e4m3 / e5m2, head size 128) tiles are copied as bytes and widened
   // exactly to fp16 in registers in front of the fp16 mma.sync; a 16-byte chunk of a key row then holds
   // 16 head columns, used in the order the fragments deliver them (q follows the same order).
@@ -150,6 +162,7 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
   constexpr int CH = HD * ES / 16;  // 16-byte chunks per key row
   constexpr int DSTAGES = DecStages<ES>::value;
   static_assert(!F8 || HD == 128, "FP8 rows are 128 bytes: eight chunks, as the swizzle assumes");
+  static_assert(!(TR && F8), "the transposed products take 16-bit tiles");
   extern __shared__ __align__(128) uint8_t dsm[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -284,8 +297,18 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
   const int n_mtiles = (p.G + 15) / 16;
   for (int mt = 0; mt < n_mtiles; ++mt) {
     // ---- Q fragments of this warp (all warps hold the same rows) --------------------------------
-    uint32_t qa[HD / 16][4];
-    {
+    // TR: this lane's two rows are 2t and 2t+1 (columns of S^T); otherwise g and g + 8
+    uint32_t qa[HD / 16][TR ? 2 : 4];
+    if constexpr (TR) {
+      // B fragments of Q^T: head columns 16 kk + 2t, +1 and 16 kk + 8 + 2t, +1 of query row g
+      const T* q0 = reinterpret_cast<const T*>(p.q) + (long long)b * p.q_sb + (long long)(hkv * p.G + g) * p.q_sh;
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; ++kk) {
+        const bool lo = kk * 16 + 2 * t < p.D, hi = kk * 16 + 8 + 2 * t < p.D;
+        qa[kk][0] = (g < p.G && lo) ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 2 * t) : 0u;
+        qa[kk][1] = (g < p.G && hi) ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 8 + 2 * t) : 0u;
+      }
+    } else {
       const int r0 = mt * 16 + g, r1 = r0 + 8;
       const T* q0 = reinterpret_cast<const T*>(p.q) + (long long)b * p.q_sb + (long long)(hkv * p.G + r0) * p.q_sh;
       const T* q1 = reinterpret_cast<const T*>(p.q) + (long long)b * p.q_sb + (long long)(hkv * p.G + r1) * p.q_sh;
@@ -311,7 +334,8 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
         }
       }
     }
-    const bool row0_ok = mt * 16 + g < p.G, row1_ok = mt * 16 + g + 8 < p.G;
+    const int row0 = TR ? 2 * t : mt * 16 + g, row1 = TR ? 2 * t + 1 : mt * 16 + g + 8;  // this lane's two query rows
+    const bool row0_ok = row0 < p.G, row1_ok = row1 < p.G;
     // ---- gated: alpha of the two rows, its extremes over the real rows, the running gate bound ----
     float al0 = 0.f, al1 = 0.f, a_max = 0.f, a_min = 0.f, gate_max = -INFINITY;
     // Gate decisions taken BEFORE a tile's rows are requested: with the per-tile extremes of delta in gate_ws
@@ -326,8 +350,8 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
     const float gate_thr_log2 = (KIND == KIND_GATED) ? log2f(p.gate_thr) : 0.f;
     if (KIND == KIND_GATED) {
       const TO* ab = reinterpret_cast<const TO*>(p.alpha) + (long long)b * p.a_sb;
-      if (row0_ok) al0 = float(ab[(long long)(hkv * p.G + mt * 16 + g) * p.a_sh]);
-      if (row1_ok) al1 = float(ab[(long long)(hkv * p.G + mt * 16 + g + 8) * p.a_sh]);
+      if (row0_ok) al0 = float(ab[(long long)(hkv * p.G + row0) * p.a_sh]);
+      if (row1_ok) al1 = float(ab[(long long)(hkv * p.G + row1) * p.a_sh]);
       a_max = fmaxf(row0_ok ? al0 : -INFINITY, row1_ok ? al1 : -INFINITY);
       a_min = fminf(row0_ok ? al0 : INFINITY, row1_ok ? al1 : INFINITY);
 #pragma unroll
@@ -338,9 +362,9 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
     }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float lg_l[2] = {-INFINITY, -INFINITY};  // log2(l_run) for the skip test, refreshed after every update of l_run
-    float o[HD / 8][4];
+    float o[TR ? HD / 16 : HD / 8][4];  // TR: O^T, 16 head columns x 8 rows per entry
 #pragma unroll
-    for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    for (int j = 0; j < (TR ? HD / 16 : HD / 8); ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
 
     // ---- ring prologue ----------------------------------------------------------------------------
     // without local windows the visited tiles are one descending range
@@ -463,161 +487,255 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
         }
       }
 
-      // ---- S = Q K^T over this tile: 2 key groups of 8 ------------------------------------------------
-      float s[2][4], s_alt[2][4];  // two accumulators per key group: half as long a chain of dependent MMAs
+      if constexpr (TR) {
+        // ---- S^T = K Q^T: keys g and g + 8 (rows), query rows 2t and 2t + 1 (columns) --------------------
+        float st[4] = {0.f, 0.f, 0.f, 0.f}, st_alt[4] = {0.f, 0.f, 0.f, 0.f};  // two chains of dependent MMAs
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-        s_alt[j][0] = s_alt[j][1] = s_alt[j][2] = s_alt[j][3] = 0.f;
-      }
-      if constexpr (F8) {
-        // one ldmatrix.x4 = four 16-byte chunks = four k-steps; every register carries the four head
-        // columns 4t .. 4t+3 of its chunk for key row g
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const int r = (lane & 7) + 8 * ((lane >> 3) & 1);
+          const int ch = 2 * kk + (lane >> 4);
+          uint32_t a[4];
+          ldsm_x4(kt + r * SM::kRow + ((ch ^ (r & 7)) << 4), a[0], a[1], a[2], a[3]);
+          mma16816<TM>((kk & 1) ? st_alt : st, a, qa[kk][0], qa[kk][1]);
+        }
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; kk += 4) {
+        for (int e = 0; e < 4; ++e) st[e] += st_alt[e];
+        if (KIND == KIND_GATED) {
+          const bool logsig = p.flags & F_LOGSIGMOID;
+          const float dk_lo = __shfl_sync(0xffffffffu, dlq[0], g), dk_hi = __shfl_sync(0xffffffffu, dlq[0], g + 8);
 #pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            const int r = 8 * j + (lane & 7);
-            const int ch = kk + (lane >> 3);
-            uint32_t w[4];
-            ldsm_x4(kt + r * SM::kRow + ((ch ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+          for (int e = 0; e < 4; ++e) {
+            const float x = ((e & 1) ? al1 : al0) * (e < 2 ? dk_lo : dk_hi);
+            st[e] += logsig ? log_sigmoid_fast(x) : x;
+          }
+        }
+        if (vis != 0xffffu) {
+          if (!((vis >> g) & 1u)) st[0] = st[1] = -INFINITY;
+          if (!((vis >> (g + 8)) & 1u)) st[2] = st[3] = -INFINITY;
+        }
+        float m_cur[2] = {fmaxf(st[0], st[2]), fmaxf(st[1], st[3])};
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              mma16816<TM>((i & 1) ? s_alt[j] : s[j], qa[kk + i], fp8x2_to_f16x2<T, 0>(w[i]), fp8x2_to_f16x2<T, 1>(w[i]));
+        for (int r = 0; r < 2; ++r) {
+          m_cur[r] = fmaxf(m_cur[r], __shfl_xor_sync(0xffffffffu, m_cur[r], 4));
+          m_cur[r] = fmaxf(m_cur[r], __shfl_xor_sync(0xffffffffu, m_cur[r], 8));
+          m_cur[r] = fmaxf(m_cur[r], __shfl_xor_sync(0xffffffffu, m_cur[r], 16));
+        }
+        bool skip = false;
+        if (KIND != KIND_DENSE) {
+          // flash_sparse_attn/ops/triton/activations.py:129-138 over the real rows of the tile
+          const float v0 = (m_cur[0] - m_run[0]) * c - lg_l[0] - thr_log2;
+          const float v1 = (m_cur[1] - m_run[1]) * c - lg_l[1] - thr_log2;
+          const bool want = (row0_ok && v0 >= 0.f) || (row1_ok && v1 >= 0.f);
+          const bool drop = (row0_ok && v0 < 0.f) || (row1_ok && v1 < 0.f);
+          skip = !__any_sync(0xffffffffu, want) && __any_sync(0xffffffffu, drop);
+          if (p.tile_map && lane == 0 && mt == 0)
+            p.tile_map[((long long)b * p.Hkv + hkv) * p.n_tiles + n] = skip ? 2 : 1;
+        }
+        if (!skip) {
+          float scale[2];
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            // the reference maximum moves only when it lags by more than 2^8 (always on the first tile)
+            const float m_cand = fmaxf(fmaxf(m_cur[r], m_run[r]), -1e6f);
+            scale[r] = 1.0f;
+            if (!((m_cand - m_run[r]) * c <= 8.0f)) {
+              scale[r] = ex2_approx((m_run[r] - m_cand) * c);
+              m_run[r] = m_cand;
+            }
+          }
+          const float mc0 = m_run[0] * c, mc1 = m_run[1] * c;
+          const float p0 = ex2_approx(fmaf(st[0], c, -mc0)), p1 = ex2_approx(fmaf(st[1], c, -mc1));
+          const float p2 = ex2_approx(fmaf(st[2], c, -mc0)), p3 = ex2_approx(fmaf(st[3], c, -mc1));
+          // P^T as the B operand: (keys 2t, 2t+1 | 2t+8, 2t+9) x row g = the transposes of the two 8 x 8 blocks
+          const uint32_t pb0 = movmatrix_trans(pack2<TM>(p0, p1)), pb1 = movmatrix_trans(pack2<TM>(p2, p3));
+          float sum0 = p0 + p2, sum1 = p1 + p3;
+#pragma unroll
+          for (int sft = 4; sft <= 16; sft <<= 1) {
+            sum0 += __shfl_xor_sync(0xffffffffu, sum0, sft);
+            sum1 += __shfl_xor_sync(0xffffffffu, sum1, sft);
+          }
+          l_run[0] = l_run[0] * scale[0] + sum0;
+          l_run[1] = l_run[1] * scale[1] + sum1;
+          if (KIND != KIND_DENSE) {
+            lg_l[0] = lg2_approx(l_run[0]);
+            lg_l[1] = lg2_approx(l_run[1]);
+          }
+          if (__any_sync(0xffffffffu, scale[0] != 1.f || scale[1] != 1.f)) {
+#pragma unroll
+            for (int j = 0; j < HD / 16; ++j) {
+              o[j][0] *= scale[0];
+              o[j][1] *= scale[1];
+              o[j][2] *= scale[0];
+              o[j][3] *= scale[1];
+            }
+          }
+          // ---- O^T += V^T P^T: 16 head columns per MMA ------------------------------------------------------
+#pragma unroll
+          for (int jd = 0; jd < HD / 16; ++jd) {
+            const int r = (lane & 7) + 8 * (lane >> 4);
+            const int ch = 2 * jd + ((lane >> 3) & 1);
+            uint32_t a[4];
+            ldsm_x4_t(vt + r * SM::kRow + ((ch ^ (r & 7)) << 4), a[0], a[1], a[2], a[3]);
+            mma16816<TM>(o[jd], a, pb0, pb1);
           }
         }
       } else {
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; kk += 2) {
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            const int r = 8 * j + (lane & 7);
-            const int ch = 2 * kk + (lane >> 3);
-            uint32_t b0, b1, b2, b3;
-            ldsm_x4(kt + r * SM::kRow + ((ch ^ (r & 7)) << 4), b0, b1, b2, b3);
-            mma16816<TM>(s[j], qa[kk], b0, b1);
-            mma16816<TM>(s_alt[j], qa[kk + 1], b2, b3);
-          }
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < 2; ++j)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) s[j][e] += s_alt[j][e];
-      if (KIND == KIND_GATED) {
-        // logits = (q.k + g(alpha * delta)) * scale (flash_sparse_attn/ops/triton/flash_gated_dec.py)
-        const bool logsig = p.flags & F_LOGSIGMOID;
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float dk = __shfl_sync(0xffffffffu, dlq[0], 8 * j + 2 * t + (e & 1));
-            const float x = (e < 2 ? al0 : al1) * dk;
-            float gte = x;
-            if (logsig)
-              gte = log_sigmoid_fast(x);
-            s[j][e] += gte;
-          }
-      }
-      // mask: element (j, e) is key 8j + 2t + (e & 1)
-      if (vis != 0xffffu) {
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            if (!((vis >> (8 * j + 2 * t + (e & 1))) & 1u)) s[j][e] = -INFINITY;
-      }
-
-      float m_cur[2];
-      m_cur[0] = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
-      m_cur[1] = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        m_cur[r] = fmaxf(m_cur[r], __shfl_xor_sync(0xffffffffu, m_cur[r], 1));
-        m_cur[r] = fmaxf(m_cur[r], __shfl_xor_sync(0xffffffffu, m_cur[r], 2));
-      }
-
-      bool skip = false;
-      if (KIND != KIND_DENSE) {
-        // flash_sparse_attn/ops/triton/activations.py:129-138 over the real rows of the tile
-        const float v0 = (m_cur[0] - m_run[0]) * c - lg_l[0] - thr_log2;
-        const float v1 = (m_cur[1] - m_run[1]) * c - lg_l[1] - thr_log2;
-        const bool want = (row0_ok && v0 >= 0.f) || (row1_ok && v1 >= 0.f);
-        const bool drop = (row0_ok && v0 < 0.f) || (row1_ok && v1 < 0.f);
-        skip = !__any_sync(0xffffffffu, want) && __any_sync(0xffffffffu, drop);
-        if (p.tile_map && lane == 0 && mt == 0)
-          p.tile_map[((long long)b * p.Hkv + hkv) * p.n_tiles + n] = skip ? 2 : 1;
-      }
-      if (!skip) {
-        float scale[2];
-        uint32_t pa[4];
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          // the reference maximum moves only when it lags by more than 2^8 (always on the first tile, where it is
-          // -inf): the exponentials stay below 2^8, the sums in fp32, and the rescaling of the 16 x HD accumulator,
-          // which otherwise runs on most tiles of a short walk, becomes rare
-          const float m_cand = fmaxf(fmaxf(m_cur[r], m_run[r]), -1e6f);
-          scale[r] = 1.0f;
-          if (!((m_cand - m_run[r]) * c <= 8.0f)) {
-            scale[r] = ex2_approx((m_run[r] - m_cand) * c);
-            m_run[r] = m_cand;
-          }
-        }
-        const float mc0 = m_run[0] * c, mc1 = m_run[1] * c;
-        float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
+        // ---- S = Q K^T over this tile: 2 key groups of 8 ------------------------------------------------
+        float s[2][4], s_alt[2][4];  // two accumulators per key group: half as long a chain of dependent MMAs
+  #pragma unroll
         for (int j = 0; j < 2; ++j) {
-          const float p0 = ex2_approx(fmaf(s[j][0], c, -mc0)), p1 = ex2_approx(fmaf(s[j][1], c, -mc0));
-          const float p2 = ex2_approx(fmaf(s[j][2], c, -mc1)), p3 = ex2_approx(fmaf(s[j][3], c, -mc1));
-          sum0 += p0 + p1;
-          sum1 += p2 + p3;
-          pa[2 * j] = pack2<TM>(p0, p1);
-          pa[2 * j + 1] = pack2<TM>(p2, p3);
+          s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+          s_alt[j][0] = s_alt[j][1] = s_alt[j][2] = s_alt[j][3] = 0.f;
         }
-        sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
-        sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
-        sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
-        sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
-        l_run[0] = l_run[0] * scale[0] + sum0;
-        l_run[1] = l_run[1] * scale[1] + sum1;
-        if (KIND != KIND_DENSE) {  // needed by the next tile's vote: its latency runs under the P V products
-          lg_l[0] = lg2_approx(l_run[0]);
-          lg_l[1] = lg2_approx(l_run[1]);
-        }
-        if (__any_sync(0xffffffffu, scale[0] != 1.f || scale[1] != 1.f)) {
-#pragma unroll
-          for (int j = 0; j < HD / 8; ++j) {
-            o[j][0] *= scale[0];
-            o[j][1] *= scale[0];
-            o[j][2] *= scale[1];
-            o[j][3] *= scale[1];
-          }
-        }
-        // ---- O += P V -----------------------------------------------------------------------------------
         if constexpr (F8) {
-          // The transposing ldmatrix moves byte PAIRS: a register holds head columns (2g, 2g+1) of its
-          // chunk for keys 2t and 2t+1. Even and odd columns are split into two MMAs, whose accumulators
-          // o[2c] / o[2c+1] then stand for head columns 16c + 4t + {0, 2} / {1, 3}.
-#pragma unroll
-          for (int jd = 0; jd < HD / 32; ++jd) {
-            const int r = (lane & 7) + 8 * ((lane >> 3) & 1);
-            const int ch = 2 * jd + (lane >> 4);
-            uint32_t w0, w1, w2, w3;  // chunk 2jd: keys 0-7, keys 8-15; chunk 2jd+1: keys 0-7, keys 8-15
-            ldsm_x4_t(vt + r * SM::kRow + ((ch ^ (r & 7)) << 4), w0, w1, w2, w3);
-            mma16816<TM>(o[4 * jd], pa, fp8x2_to_f16x2<T, 2>(w0), fp8x2_to_f16x2<T, 2>(w1));
-            mma16816<TM>(o[4 * jd + 1], pa, fp8x2_to_f16x2<T, 3>(w0), fp8x2_to_f16x2<T, 3>(w1));
-            mma16816<TM>(o[4 * jd + 2], pa, fp8x2_to_f16x2<T, 2>(w2), fp8x2_to_f16x2<T, 2>(w3));
-            mma16816<TM>(o[4 * jd + 3], pa, fp8x2_to_f16x2<T, 3>(w2), fp8x2_to_f16x2<T, 3>(w3));
+          // one ldmatrix.x4 = four 16-byte chunks = four k-steps; every register carries the four head
+          // columns 4t .. 4t+3 of its chunk for key row g
+  #pragma unroll
+          for (int kk = 0; kk < HD / 16; kk += 4) {
+  #pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const int r = 8 * j + (lane & 7);
+              const int ch = kk + (lane >> 3);
+              uint32_t w[4];
+              ldsm_x4(kt + r * SM::kRow + ((ch ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+  #pragma unroll
+              for (int i = 0; i < 4; ++i)
+                mma16816<TM>((i & 1) ? s_alt[j] : s[j], qa[kk + i], fp8x2_to_f16x2<T, 0>(w[i]), fp8x2_to_f16x2<T, 1>(w[i]));
+            }
           }
         } else {
-#pragma unroll
-          for (int jd = 0; jd < HD / 16; ++jd) {
-            const int r = (lane & 7) + 8 * ((lane >> 3) & 1);
-            const int ch = 2 * jd + (lane >> 4);
-            uint32_t b0, b1, b2, b3;
-            ldsm_x4_t(vt + r * SM::kRow + ((ch ^ (r & 7)) << 4), b0, b1, b2, b3);
-            mma16816<TM>(o[2 * jd], pa, b0, b1);
-            mma16816<TM>(o[2 * jd + 1], pa, b2, b3);
+  #pragma unroll
+          for (int kk = 0; kk < HD / 16; kk += 2) {
+  #pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const int r = 8 * j + (lane & 7);
+              const int ch = 2 * kk + (lane >> 3);
+              uint32_t b0, b1, b2, b3;
+              ldsm_x4(kt + r * SM::kRow + ((ch ^ (r & 7)) << 4), b0, b1, b2, b3);
+              mma16816<TM>(s[j], qa[kk], b0, b1);
+              mma16816<TM>(s_alt[j], qa[kk + 1], b2, b3);
+            }
+          }
+        }
+  #pragma unroll
+        for (int j = 0; j < 2; ++j)
+  #pragma unroll
+          for (int e = 0; e < 4; ++e) s[j][e] += s_alt[j][e];
+        if (KIND == KIND_GATED) {
+          // logits = (q.k + g(alpha * delta)) * scale (flash_sparse_attn/ops/triton/flash_gated_dec.py)
+          const bool logsig = p.flags & F_LOGSIGMOID;
+  #pragma unroll
+          for (int j = 0; j < 2; ++j)
+  #pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float dk = __shfl_sync(0xffffffffu, dlq[0], 8 * j + 2 * t + (e & 1));
+              const float x = (e < 2 ? al0 : al1) * dk;
+              float gte = x;
+              if (logsig)
+                gte = log_sigmoid_fast(x);
+              s[j][e] += gte;
+            }
+        }
+        // mask: element (j, e) is key 8j + 2t + (e & 1)
+        if (vis != 0xffffu) {
+  #pragma unroll
+          for (int j = 0; j < 2; ++j)
+  #pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (!((vis >> (8 * j + 2 * t + (e & 1))) & 1u)) s[j][e] = -INFINITY;
+        }
+
+        float m_cur[2];
+        m_cur[0] = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        m_cur[1] = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+  #pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          m_cur[r] = fmaxf(m_cur[r], __shfl_xor_sync(0xffffffffu, m_cur[r], 1));
+          m_cur[r] = fmaxf(m_cur[r], __shfl_xor_sync(0xffffffffu, m_cur[r], 2));
+        }
+
+        bool skip = false;
+        if (KIND != KIND_DENSE) {
+          // flash_sparse_attn/ops/triton/activations.py:129-138 over the real rows of the tile
+          const float v0 = (m_cur[0] - m_run[0]) * c - lg_l[0] - thr_log2;
+          const float v1 = (m_cur[1] - m_run[1]) * c - lg_l[1] - thr_log2;
+          const bool want = (row0_ok && v0 >= 0.f) || (row1_ok && v1 >= 0.f);
+          const bool drop = (row0_ok && v0 < 0.f) || (row1_ok && v1 < 0.f);
+          skip = !__any_sync(0xffffffffu, want) && __any_sync(0xffffffffu, drop);
+          if (p.tile_map && lane == 0 && mt == 0)
+            p.tile_map[((long long)b * p.Hkv + hkv) * p.n_tiles + n] = skip ? 2 : 1;
+        }
+        if (!skip) {
+          float scale[2];
+          uint32_t pa[4];
+  #pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            // the reference maximum moves only when it lags by more than 2^8 (always on the first tile, where it is
+            // -inf): the exponentials stay below 2^8, the sums in fp32, and the rescaling of the 16 x HD accumulator,
+            // which otherwise runs on most tiles of a short walk, becomes rare
+            const float m_cand = fmaxf(fmaxf(m_cur[r], m_run[r]), -1e6f);
+            scale[r] = 1.0f;
+            if (!((m_cand - m_run[r]) * c <= 8.0f)) {
+              scale[r] = ex2_approx((m_run[r] - m_cand) * c);
+              m_run[r] = m_cand;
+            }
+          }
+          const float mc0 = m_run[0] * c, mc1 = m_run[1] * c;
+          float sum0 = 0.f, sum1 = 0.f;
+  #pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const float p0 = ex2_approx(fmaf(s[j][0], c, -mc0)), p1 = ex2_approx(fmaf(s[j][1], c, -mc0));
+            const float p2 = ex2_approx(fmaf(s[j][2], c, -mc1)), p3 = ex2_approx(fmaf(s[j][3], c, -mc1));
+            sum0 += p0 + p1;
+            sum1 += p2 + p3;
+            pa[2 * j] = pack2<TM>(p0, p1);
+            pa[2 * j + 1] = pack2<TM>(p2, p3);
+          }
+          sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+          sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+          sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
+          sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+          l_run[0] = l_run[0] * scale[0] + sum0;
+          l_run[1] = l_run[1] * scale[1] + sum1;
+          if (KIND != KIND_DENSE) {  // needed by the next tile's vote: its latency runs under the P V products
+            lg_l[0] = lg2_approx(l_run[0]);
+            lg_l[1] = lg2_approx(l_run[1]);
+          }
+          if (__any_sync(0xffffffffu, scale[0] != 1.f || scale[1] != 1.f)) {
+  #pragma unroll
+            for (int j = 0; j < HD / 8; ++j) {
+              o[j][0] *= scale[0];
+              o[j][1] *= scale[0];
+              o[j][2] *= scale[1];
+              o[j][3] *= scale[1];
+            }
+          }
+          // ---- O += P V -----------------------------------------------------------------------------------
+          if constexpr (F8) {
+            // The transposing ldmatrix moves byte PAIRS: a register holds head columns (2g, 2g+1) of its
+            // chunk for keys 2t and 2t+1. Even and odd columns are split into two MMAs, whose accumulators
+            // o[2c] / o[2c+1] then stand for head columns 16c + 4t + {0, 2} / {1, 3}.
+  #pragma unroll
+            for (int jd = 0; jd < HD / 32; ++jd) {
+              const int r = (lane & 7) + 8 * ((lane >> 3) & 1);
+              const int ch = 2 * jd + (lane >> 4);
+              uint32_t w0, w1, w2, w3;  // chunk 2jd: keys 0-7, keys 8-15; chunk 2jd+1: keys 0-7, keys 8-15
+              ldsm_x4_t(vt + r * SM::kRow + ((ch ^ (r & 7)) << 4), w0, w1, w2, w3);
+              mma16816<TM>(o[4 * jd], pa, fp8x2_to_f16x2<T, 2>(w0), fp8x2_to_f16x2<T, 2>(w1));
+              mma16816<TM>(o[4 * jd + 1], pa, fp8x2_to_f16x2<T, 3>(w0), fp8x2_to_f16x2<T, 3>(w1));
+              mma16816<TM>(o[4 * jd + 2], pa, fp8x2_to_f16x2<T, 2>(w2), fp8x2_to_f16x2<T, 2>(w3));
+              mma16816<TM>(o[4 * jd + 3], pa, fp8x2_to_f16x2<T, 3>(w2), fp8x2_to_f16x2<T, 3>(w3));
+            }
+          } else {
+  #pragma unroll
+            for (int jd = 0; jd < HD / 16; ++jd) {
+              const int r = (lane & 7) + 8 * ((lane >> 3) & 1);
+              const int ch = 2 * jd + (lane >> 4);
+              uint32_t b0, b1, b2, b3;
+              ldsm_x4_t(vt + r * SM::kRow + ((ch ^ (r & 7)) << 4), b0, b1, b2, b3);
+              mma16816<TM>(o[2 * jd], pa, b0, b1);
+              mma16816<TM>(o[2 * jd + 1], pa, b2, b3);
+            }
           }
         }
       }
@@ -633,7 +751,15 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
     float* mo = reinterpret_cast<float*>(dsm) + warp * (16 * HD + 32);
     float* mm = mo + 16 * HD;
     float* ml = mm + 16;
-    if constexpr (F8) {
+    if constexpr (TR) {
+#pragma unroll
+      for (int jd = 0; jd < HD / 16; ++jd) {
+        mo[(2 * t) * HD + 16 * jd + g] = o[jd][0];
+        mo[(2 * t + 1) * HD + 16 * jd + g] = o[jd][1];
+        mo[(2 * t) * HD + 16 * jd + g + 8] = o[jd][2];
+        mo[(2 * t + 1) * HD + 16 * jd + g + 8] = o[jd][3];
+      }
+    } else if constexpr (F8) {
 #pragma unroll
       for (int cch = 0; cch < HD / 16; ++cch) {
         *reinterpret_cast<float4*>(mo + g * HD + 16 * cch + 4 * t) =
@@ -648,11 +774,11 @@ __global__ void __launch_bounds__(DWARPS * 32, FSA_DEC_MINBLOCKS) dec_kernel(con
         *reinterpret_cast<float2*>(mo + (g + 8) * HD + 8 * j + 2 * t) = make_float2(o[j][2], o[j][3]);
       }
     }
-    if (t == 0) {
-      mm[g] = m_run[0];
-      mm[g + 8] = m_run[1];
-      ml[g] = l_run[0];
-      ml[g + 8] = l_run[1];
+    if (TR ? g == 0 : t == 0) {
+      mm[row0 - mt * 16] = m_run[0];
+      mm[row1 - mt * 16] = m_run[1];
+      ml[row0 - mt * 16] = l_run[0];
+      ml[row1 - mt * 16] = l_run[1];
     }
     __syncthreads();
     const float* all = reinterpret_cast<const float*>(dsm);
@@ -776,9 +902,12 @@ __global__ void __launch_bounds__(256) dec_gate_ext_kernel(const DecKernelParams
   if (l16 == 0 && item < n_items) reinterpret_cast<float2*>(p.gate_ws)[item] = make_float2(mx, mn);
 }
 
-template <int HD, typename T, int KIND>
+template <int HD, typename T, int KIND, bool TR = false>
 cudaError_t launch_one(const DecKernelParams& p, cudaStream_t stream) {
-  auto kern = dec_kernel<HD, T, KIND>;
+  if constexpr (!TR && sizeof(T) == 2) {
+    if (p.G <= 8) return launch_one<HD, T, KIND, true>(p, stream);  // transposed products: see dec_kernel
+  }
+  auto kern = dec_kernel<HD, T, KIND, TR>;
   constexpr int smem = DecSmem<HD, sizeof(T)>::kTotal;
   static std::atomic<unsigned long long> opted_in{0};  // one bit per device: the attribute is per device
   if (cudaError_t e = smem_opt_in(kern, smem, opted_in); e != cudaSuccess) return e;
