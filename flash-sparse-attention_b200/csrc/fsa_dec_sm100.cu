@@ -149,8 +149,9 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
 // N = 8 side. With the rows on M, half of every fragment is padding when a KV head serves 8 query heads: transposed, the
 // accumulator takes 32 registers instead of 64, the Q fragments 16 instead of 32, a tile needs 8 + 8 MMAs instead of
 // 16 + 16, and three CTAs fit an SM instead of two. P^T reaches its B-operand layout through movmatrix.
-template <int HD, typename T, int KIND, bool TR>
-__global__ void __launch_bounds__(DWARPS * 32, TR ? 3 : FSA_DEC_MINBLOCKS) dec_kernel(const DecKernelParams p) {
+// OCC: CTAs per SM the kernel is compiled for (the transposed variant exists for 2 and for 3).
+template <int HD, typename T, int KIND, bool TR, int OCC>
+__global__ void __launch_bounds__(DWARPS * 32, OCC) dec_kernel(const DecKernelParams p) {
   // T: element type of q, k, v. FP8 (e4m3 / e5m2, head size 128) tiles are copied as bytes and widened
   // exactly to fp16 in registers in front of the fp16 mma.sync; a 16-byte chunk of a key row then holds
   // 16 head columns, used in the order the fragments deliver them (q follows the same order).
@@ -902,13 +903,25 @@ __global__ void __launch_bounds__(256) dec_gate_ext_kernel(const DecKernelParams
   if (l16 == 0 && item < n_items) reinterpret_cast<float2*>(p.gate_ws)[item] = make_float2(mx, mn);
 }
 
-template <int HD, typename T, int KIND, bool TR = false>
+template <int HD, typename T, int KIND, bool TR = false, int OCC = FSA_DEC_MINBLOCKS>
 cudaError_t launch_one(const DecKernelParams& p, cudaStream_t stream) {
   if constexpr (!TR && sizeof(T) == 2) {
-    if (p.G <= 8) return launch_one<HD, T, KIND, true>(p, stream);  // transposed products: see dec_kernel
+    if (p.G <= 8) {
+      // Transposed products (see dec_kernel), at three or at two CTAs per SM. The grid runs in rounds of occ x SMs
+      // CTAs and a CTA takes about occ times longer with occ neighbours (the step is bandwidth bound), so the cost is
+      // rounds x CTAs per SM: 512 CTAs on 148 SMs are two rounds either way and run faster two per SM (92 against
+      // 107 us), 440 CTAs are one round of three (82 us).
+      const long long sms = device_sm_count();
+      const long long ctas = (long long)p.Hkv * p.B * p.num_splits;
+      const long long per_sm = (ctas + sms - 1) / sms;
+      auto cost = [&](long long occ) { return ((ctas + occ * sms - 1) / (occ * sms)) * (per_sm < occ ? per_sm : occ); };
+      return cost(3) <= cost(2) ? launch_one<HD, T, KIND, true, 3>(p, stream) : launch_one<HD, T, KIND, true, 2>(p, stream);
+    }
   }
-  auto kern = dec_kernel<HD, T, KIND, TR>;
-  constexpr int smem = DecSmem<HD, sizeof(T)>::kTotal;
+  auto kern = dec_kernel<HD, T, KIND, TR, OCC>;
+  // the variant for two CTAs per SM asks for enough shared memory that a third cannot join
+  constexpr int ring = DecSmem<HD, sizeof(T)>::kTotal;
+  constexpr int smem = (TR && OCC == 2 && ring < 80 * 1024) ? 80 * 1024 : ring;
   static std::atomic<unsigned long long> opted_in{0};  // one bit per device: the attribute is per device
   if (cudaError_t e = smem_opt_in(kern, smem, opted_in); e != cudaSuccess) return e;
   const long long grid = (long long)p.Hkv * p.B * p.num_splits;
