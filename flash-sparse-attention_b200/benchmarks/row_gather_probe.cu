@@ -6,7 +6,7 @@
 // copies do: the lanes of a warp cover whole rows, 512 bytes per warp instruction), eight independent loads in
 // flight per lane, and fold the data into one word per thread. Eight CTAs of 256 threads per SM: more loads in
 // flight than the decode kernel has, and no arithmetic to speak of. Two more variants fetch the same rows the way a
-// kernel that wants them in shared memory can: cp.async (16 bytes per lane, ring of four stages per warp, twelve
+// kernel that wants them in shared memory can: cp.async (.cg and .ca; 16 bytes per lane, ring of four stages per warp, twelve
 // warps per SM) and one cp.async.bulk per row on an mbarrier (four warps per SM). Prints rows per second and bytes
 // per second for row sizes of 128 / 256 / 512 bytes at the strides the paged cache has (one position = all KV heads
 // side by side).
@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(256) gather_kernel(const uint8_t* __restrict__
 
 // The same fetch through cp.async (16 bytes per lane into a shared-memory ring of four 4 KB stages per warp, as
 // the decode kernel does it), four warps per CTA; the data is not read back.
-template <int LPR>
+template <int LPR, bool CA>
 __global__ void __launch_bounds__(128) gather_cp_async_kernel(const uint8_t* __restrict__ pool,
                                                               const int* __restrict__ rows, long long n_rows,
                                                               long long stride, unsigned* __restrict__ sink) {
@@ -82,9 +82,11 @@ __global__ void __launch_bounds__(128) gather_cp_async_kernel(const uint8_t* __r
       const long long i = base + u * RPI + lane / LPR;
       const long long r = i < n_rows ? rows[i] : 0;
       const uint8_t* src = pool + r * stride + (lane % LPR) * 16;
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ring + (stage * PER_STAGE + u) * 512 + lane * 16),
-                   "l"(src)
-                   : "memory");
+      const uint32_t dst = ring + (stage * PER_STAGE + u) * 512 + lane * 16;
+      if (CA)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+      else
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 1) : "memory");
@@ -151,15 +153,18 @@ __global__ void __launch_bounds__(128) gather_bulk_kernel(const uint8_t* __restr
   if (smem[threadIdx.x + 256] == 0x5a && n_rows < 0) sink[0] = 1;
 }
 
-// how: 0 = ld.global into registers, 1 = cp.async ring, 2 = one bulk copy per row
+// how: 0 = ld.global into registers, 1 = cp.async.cg ring, 2 = one bulk copy per row, 3 = cp.async.ca ring
 float run(int how, int lpr, const uint8_t* pool, const int* rows, long long n_rows, long long stride, unsigned* sink,
           unsigned* status, int sms) {
   constexpr int kCpSmem = 4 * 4 * 8 * 512, kBulkSmem = 128 + 4 * 4 * 16 * 512;
   static bool opted = false;
   if (!opted) {
-    CHECK(cudaFuncSetAttribute(gather_cp_async_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCpSmem));
-    CHECK(cudaFuncSetAttribute(gather_cp_async_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCpSmem));
-    CHECK(cudaFuncSetAttribute(gather_cp_async_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCpSmem));
+    CHECK(cudaFuncSetAttribute(gather_cp_async_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCpSmem));
+    CHECK(cudaFuncSetAttribute(gather_cp_async_kernel<16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCpSmem));
+    CHECK(cudaFuncSetAttribute(gather_cp_async_kernel<32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCpSmem));
+    CHECK(cudaFuncSetAttribute(gather_cp_async_kernel<8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCpSmem));
+    CHECK(cudaFuncSetAttribute(gather_cp_async_kernel<16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCpSmem));
+    CHECK(cudaFuncSetAttribute(gather_cp_async_kernel<32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCpSmem));
     CHECK(cudaFuncSetAttribute(gather_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmem));
     opted = true;
   }
@@ -171,9 +176,14 @@ float run(int how, int lpr, const uint8_t* pool, const int* rows, long long n_ro
       if (lpr == 32) gather_kernel<32><<<grid, 256>>>(pool, rows, n_rows, stride, sink);
     } else if (how == 1) {
       const int grid = sms * 3;  // 64 KB of ring per CTA: three CTAs = twelve warps per SM
-      if (lpr == 8) gather_cp_async_kernel<8><<<grid, 128, kCpSmem>>>(pool, rows, n_rows, stride, sink);
-      if (lpr == 16) gather_cp_async_kernel<16><<<grid, 128, kCpSmem>>>(pool, rows, n_rows, stride, sink);
-      if (lpr == 32) gather_cp_async_kernel<32><<<grid, 128, kCpSmem>>>(pool, rows, n_rows, stride, sink);
+      if (lpr == 8) gather_cp_async_kernel<8, false><<<grid, 128, kCpSmem>>>(pool, rows, n_rows, stride, sink);
+      if (lpr == 16) gather_cp_async_kernel<16, false><<<grid, 128, kCpSmem>>>(pool, rows, n_rows, stride, sink);
+      if (lpr == 32) gather_cp_async_kernel<32, false><<<grid, 128, kCpSmem>>>(pool, rows, n_rows, stride, sink);
+    } else if (how == 3) {
+      const int grid = sms * 3;
+      if (lpr == 8) gather_cp_async_kernel<8, true><<<grid, 128, kCpSmem>>>(pool, rows, n_rows, stride, sink);
+      if (lpr == 16) gather_cp_async_kernel<16, true><<<grid, 128, kCpSmem>>>(pool, rows, n_rows, stride, sink);
+      if (lpr == 32) gather_cp_async_kernel<32, true><<<grid, 128, kCpSmem>>>(pool, rows, n_rows, stride, sink);
     } else {
       gather_bulk_kernel<<<sms, 128, kBulkSmem>>>(pool, rows, n_rows, stride, lpr * 16, sink, status);
     }
@@ -213,8 +223,8 @@ int main() {
   unsigned* status;
   CHECK(cudaMalloc(&status, 4));
   CHECK(cudaMemset(status, 0, 4));
-  std::printf("%-10s %-10s %-10s %-12s %12s %12s\n", "fetch", "row bytes", "stride", "order", "G rows/s", "TB/s");
-  const char* how_names[3] = {"ld.global", "cp.async", "bulk copy"};
+  std::printf("%-12s %-10s %-10s %-12s %12s %12s\n", "fetch", "row bytes", "stride", "order", "G rows/s", "TB/s");
+  const char* how_names[4] = {"ld.global", "cp.async.cg", "bulk copy", "cp.async.ca"};
   uint64_t s = 0x9e3779b97f4a7c15ull;
   auto rnd = [&]() {
     s ^= s << 13;
@@ -232,9 +242,9 @@ int main() {
         for (long long i = 0; i < n_list; ++i)
           h[i] = order == 0 ? (int)(rnd() % (uint64_t)pool_rows) : (int)(i % pool_rows);
         CHECK(cudaMemcpy(rows, h.data(), n_list * 4, cudaMemcpyHostToDevice));
-        for (int how = 0; how < 3; ++how) {
+        for (int how = 0; how < 4; ++how) {
           const float ms = run(how, row / 16, pool, rows, n_list, stride, sink, status, sms);
-          std::printf("%-10s %-10d %-10lld %-12s %12.2f %12.3f\n", how_names[how], row, stride,
+          std::printf("%-12s %-10d %-10lld %-12s %12.2f %12.3f\n", how_names[how], row, stride,
                       order == 0 ? "random" : "ascending", n_list / ms / 1e6, (double)n_list * row / ms / 1e9);
         }
       }
