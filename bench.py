@@ -595,14 +595,20 @@ def run_gpu(args):
     torch.cuda.synchronize()
     barrier()
     e_steps = max(3, args.steps)  # the first copy-in and the last copy-out are not overlapped: amortised over the steps
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    e2e_run(e_steps)
-    e1.record()
-    barrier()
+    # three timed passes, the median counts: the pass is host driven (one Python thread feeds three streams), and a
+    # single stall of that thread (seen once: 27 ms per step in one pass on a box that ran 3.9 ms before and after)
+    # would otherwise be the figure. All three are reported.
+    e2e_all = []
+    for _ in range(3):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        e2e_run(e_steps)
+        e1.record()
+        barrier()
+        torch.cuda.synchronize()
+        e2e_all.append(e0.elapsed_time(e1) / e_steps)
     fsa.check_status()
-    e2e_ms = e0.elapsed_time(e1) / e_steps
-    torch.cuda.synchronize()
+    e2e_ms = sorted(e2e_all)[1]
     if not torch.equal(host_out[(e_steps - 1) & 1][0], out.detach().cpu()):  # same inputs, same forward bits
         raise RuntimeError("end-to-end leg: the output that reached the host differs from the device-resident run")
     # the same copies with no kernels in between: what the host side (PCIe links / switches shared by the ranks,
@@ -675,7 +681,8 @@ def run_gpu(args):
         "executed_tflops": exec_flops_step / (ms_per_step / 1e3) / 1e12,
         "clocks": sampler.summary(),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms,
+                "ms_per_step": e2e_ms, "ms_per_step_passes": e2e_all,
+                "passes": "3 timed passes of the same steps, median reported",
                 "host_copy_gbs_all_ranks": (h2d + d2h) * world / (e2e_ms / 1e3) / 1e9,
                 "copies_only_ms_per_step": copy_ms,
                 "copies_only_note": "the step's host<->device copies alone (no kernels), max over ranks: the floor the "
