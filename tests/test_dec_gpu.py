@@ -278,3 +278,56 @@ def test_peer_exchange_kernels_single_rank(fused):
     finally:
         torch.cuda.synchronize()
         assert lib.fsa_peer_free(region.value) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("head_dim", [64, 128])
+@pytest.mark.parametrize("kind", ["dense", "sparse", "gated"])
+def test_transposed_and_untransposed_kernels_agree(kind, head_dim, dtype):
+    """Up to 8 query heads per KV head run the transposed products (S^T = K Q^T, O^T = V^T P^T), more run the
+    untransposed ones. The same 16 query heads (heads 8-15 repeat heads 0-7, so that every group below holds the same
+    rows and votes alike) are decoded once as one group of 16 over one KV head and once as two groups of 8 over a
+    duplicated KV head: both kernels must give the same outputs (elementwise 2e-2) and log-sum-exps and, with the
+    threshold on, skip the same tiles. The groups of 8 are also checked against the eager oracle."""
+    from flash_sparse_attn.ops.triton.flash_dec import attn_decode
+
+    g = torch.Generator().manual_seed(11)
+    b, sk, topk = 3, 3000, 512
+    k = torch.randn(b, sk, 1, head_dim, generator=g)
+    idx = torch.stack([torch.randperm(sk, generator=g)[:topk].sort().values for _ in range(b)]).to(torch.int32)
+    # queries peaked on one of the gathered keys, so that the threshold skips tiles
+    peak = torch.stack([k[i, int(idx[i, -5]), 0] for i in range(b)])                       # [b, d]
+    q8 = peak[:, None, :] * 3 + torch.randn(b, 8, head_dim, generator=g) * 0.3
+    q = torch.cat([q8, q8], dim=1).to(dtype)
+    k = k.to(dtype)
+    v = torch.randn(b, sk, 1, head_dim, generator=g).to(dtype)
+    a8 = torch.randn(b, 8, generator=g)
+    alpha = torch.cat([a8, a8], dim=1).to(dtype)
+    delta = torch.randn(b, sk, 1, generator=g).to(dtype)
+    n_tiles = (topk + 15) // 16
+
+    def run(rep):  # the KV head is duplicated `rep` times, every copy serves 16 / rep query heads
+        kk, vv = k.repeat_interleave(rep, dim=2), v.repeat_interleave(rep, dim=2)
+        dd = delta.repeat_interleave(rep, dim=2).transpose(1, 2).contiguous()  # the launcher takes [B, Hkv, Sk]
+        tmap = torch.zeros(b * rep * n_tiles, dtype=torch.uint8, device=DEV)
+        kw = dict(gather_kv_indices=idx.to(DEV), num_splits=1)
+        if kind == "sparse":
+            kw.update(softmax_threshold=1.0, tile_map=tmap)
+        elif kind == "gated":
+            kw.update(alpha=alpha.to(DEV), delta=dd.to(DEV), softmax_threshold=-128.0, gate_threshold=-128.0)
+        out, lse = attn_decode(kind, q.to(DEV), kk.to(DEV), vv.to(DEV), **kw)
+        _sync()
+        return out.float().cpu(), lse.cpu(), tmap.view(b, rep, n_tiles).cpu()
+
+    out16, lse16, map16 = run(1)   # 16 query heads per KV head: untransposed
+    out8, lse8, map8 = run(2)      # 8 per KV head: transposed
+    assert torch.allclose(out8, out16, rtol=2e-2, atol=2e-2), float((out8 - out16).abs().max())
+    assert torch.allclose(lse8, lse16, rtol=0, atol=2e-3)
+    if kind == "sparse":
+        assert int((map16 == 2).sum()) > 0, "the peaked inputs were meant to skip tiles"
+        assert (map16 != 0).all() and (map8 != 0).all()
+        assert torch.equal(map8[:, 0], map8[:, 1])
+        assert float((map16[:, 0] == map8[:, 0]).float().mean()) >= 0.999
+    ref = eager.gather_decode(q, k, v, idx, alpha=alpha if kind == "gated" else None,
+                              delta=delta if kind == "gated" else None)
+    assert_close("transposed-vs-oracle", out8.to(dtype), ref, rtol=3e-2, atol=3e-2)
