@@ -22,7 +22,10 @@ namespace fsa {
 
 namespace {
 
-constexpr int PUSH_CTAS = 64;
+#ifndef FSA_PUSH_CTAS
+#define FSA_PUSH_CTAS 64
+#endif
+constexpr int PUSH_CTAS = FSA_PUSH_CTAS;
 constexpr long long HDR_BYTES = 256;
 
 struct PushParams {
@@ -36,10 +39,27 @@ __global__ void __launch_bounds__(256) peer_push_kernel(const PushParams p) {
   unsigned char* mine = p.base[p.rank];
   const unsigned long long step = *reinterpret_cast<const volatile unsigned long long*>(mine + 128);
   const long long slot = ((long long)(step & 1ull) * p.world + p.rank) * p.block_f4;
-  for (int r = 0; r < p.world; ++r) {
-    float4* dst = reinterpret_cast<float4*>(p.base[r] + HDR_BYTES) + slot;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < p.block_f4; i += (long long)gridDim.x * blockDim.x)
-      dst[i] = __ldg(p.src + i);
+  // Every element is read once (four independent loads per thread and pass) and stored to all ranks: the stores are
+  // fire-and-forget, the loads are what a thread waits for, so reading the block again for every destination (as a
+  // rank-by-rank copy would) puts world times the load latency on the path. The destinations are interleaved, so
+  // that all of them receive at the same time.
+  constexpr int U = 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long base = (long long)blockIdx.x * blockDim.x + threadIdx.x; base < p.block_f4; base += stride * U) {
+    float4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = base + u * stride;
+      v[u] = i < p.block_f4 ? __ldg(p.src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int r = 0; r < p.world; ++r) {
+      float4* dst = reinterpret_cast<float4*>(p.base[r] + HDR_BYTES) + slot;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = base + u * stride;
+        if (i < p.block_f4) dst[i] = v[u];
+      }
+    }
   }
   __threadfence_system();
   __syncthreads();
