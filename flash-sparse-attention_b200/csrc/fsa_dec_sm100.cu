@@ -395,13 +395,16 @@ __global__ void __launch_bounds__(DWARPS * 32, OCC) dec_kernel(const DecKernelPa
     unsigned present_q[DSTAGES];  // presence masks of the tiles in the ring, oldest first
     int n_q[DSTAGES];             // their tile indices (-1: empty)
     int slot_load = 0;
-    // translation pipeline: tile xa_n has its position read under way, tile xb_n its page
-    int xa_n = next_fetch();
-    int xa_raw = xlat_a(xa_n);
-    int xb_n = xa_n, xb_pos = -1;
-    int xb_page = xlat_b(xa_raw, &xb_pos);
-    xa_n = next_fetch();
-    xa_raw = xlat_a(xa_n);
+    // translation pipeline: tile xa_n has its position read under way, tile xb_n its page. It is primed with the
+    // first three tiles at once - three position reads in flight, then two page reads - instead of one stage per
+    // dependent load: a CTA's first tile is requested a load latency earlier.
+    const int x0_n = next_fetch(), x1_n = next_fetch(), x2_n = next_fetch();
+    const int x0_raw = xlat_a(x0_n), x1_raw = xlat_a(x1_n), x2_raw = xlat_a(x2_n);
+    int x0_pos = -1, xb_pos = -1;
+    const int x0_page = xlat_b(x0_raw, &x0_pos);
+    int xb_n = x1_n;
+    int xb_page = xlat_b(x1_raw, &xb_pos);
+    int xa_n = x2_n, xa_raw = x2_raw;
     // hands out the tile whose translation is complete and moves the two younger ones up a stage
     auto xlat_pop = [&](int* pos, int* page) -> int {
       const int n = xb_n;
@@ -416,8 +419,8 @@ __global__ void __launch_bounds__(DWARPS * 32, OCC) dec_kernel(const DecKernelPa
 #pragma unroll
     for (int s = 0; s < DSTAGES - 1; ++s) {
       present_q[s] = 0;
-      int pos, page;
-      n_q[s] = xlat_pop(&pos, &page);
+      int pos = x0_pos, page = x0_page;
+      n_q[s] = s == 0 ? x0_n : xlat_pop(&pos, &page);
       if (n_q[s] >= 0) present_q[s] = issue_tile(n_q[s], pos, page, s, &dlq[s]);
       cp_async_commit();
     }
