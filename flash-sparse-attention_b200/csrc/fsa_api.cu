@@ -78,6 +78,9 @@ int cdiv(int a, int b) { return (a + b - 1) / b; }
 // columns of every row with zeros (they add nothing to any dot product) and the epilogues do not write them.
 bool head_dim_ok(int d) { return d >= 8 && d <= 128 && d % 8 == 0; }
 int head_dim_kernel(int d) { return d <= 64 ? 64 : 128; }
+// the decode kernels also come 256 columns wide (16-bit inputs)
+bool head_dim_ok_decode(int d) { return d >= 8 && d <= 256 && d % 8 == 0; }
+int head_dim_kernel_decode(int d) { return d <= 64 ? 64 : (d <= 128 ? 128 : 256); }
 
 // optional per-call timing events around the main kernel
 void mark(void* ev, cudaStream_t s) {
@@ -94,7 +97,7 @@ const char* fsa_status_string(int code) {
   switch (code) {
     case FSA_OK: return "ok";
     case FSA_ERR_INVALID_ARG: return "invalid argument (null pointer, bad size, or stride/base not 16-byte aligned)";
-    case FSA_ERR_UNSUPPORTED: return "unsupported combination (head_dim must be a multiple of 8 up to 128, dtype bf16/fp16/fp8, ...)";
+    case FSA_ERR_UNSUPPORTED: return "unsupported combination (head_dim must be a multiple of 8 up to 128 - decode: up to 256 -, dtype bf16/fp16/fp8, ...)";
     case FSA_ERR_LAUNCH: return "CUDA error at launch or tensor-map creation";
     case FSA_ERR_NO_DRIVER: return "CUDA driver entry point cuTensorMapEncodeTiled unavailable";
     case FSA_ERR_SCRATCH_UNAVAILABLE:
@@ -747,7 +750,7 @@ int fsa_combine(const float* out_partial, const float* lse_partial, void* out, f
 int fsa_decode(const FsaDecArgs* a, void* stream_) {
   if (!a || !a->q || !a->k || !a->v || !a->status) return FSA_ERR_INVALID_ARG;
   if (a->batch <= 0 || a->heads_q <= 0 || a->heads_kv <= 0 || a->heads_q % a->heads_kv) return FSA_ERR_INVALID_ARG;
-  if (!head_dim_ok(a->head_dim)) return FSA_ERR_UNSUPPORTED;
+  if (!head_dim_ok_decode(a->head_dim)) return FSA_ERR_UNSUPPORTED;
   const bool fp8 = a->dtype == FSA_DT_E4M3 || a->dtype == FSA_DT_E5M2;  // q, k, v in FP8; out / alpha / delta bf16
   if (a->dtype != FSA_DT_BF16 && a->dtype != FSA_DT_FP16 && !fp8) return FSA_ERR_UNSUPPORTED;
   if (fp8 && a->head_dim != 128) return FSA_ERR_UNSUPPORTED;
@@ -847,7 +850,7 @@ int fsa_decode(const FsaDecArgs* a, void* stream_) {
   }
   mark(a->ev_before, stream);
   p.D = a->head_dim;
-  cudaError_t e = fsa::launch_dec(p, a->kind, a->dtype, head_dim_kernel(a->head_dim), stream);
+  cudaError_t e = fsa::launch_dec(p, a->kind, a->dtype, head_dim_kernel_decode(a->head_dim), stream);
   mark(a->ev_after, stream);
   if (e == cudaErrorInvalidValue) return FSA_ERR_UNSUPPORTED;
   if (e != cudaSuccess) return FSA_ERR_LAUNCH;

@@ -295,19 +295,21 @@ __global__ void __launch_bounds__(DWARPS * 32, OCC) dec_kernel(const DecKernelPa
     return present;
   };
 
-  const int n_mtiles = (p.G + 15) / 16;
+  constexpr int MROWS = TR ? 8 : 16;  // query rows of a KV head handled per pass over the keys
+  const int n_mtiles = (p.G + MROWS - 1) / MROWS;
   for (int mt = 0; mt < n_mtiles; ++mt) {
     // ---- Q fragments of this warp (all warps hold the same rows) --------------------------------
     // TR: this lane's two rows are 2t and 2t+1 (columns of S^T); otherwise g and g + 8
     uint32_t qa[HD / 16][TR ? 2 : 4];
     if constexpr (TR) {
       // B fragments of Q^T: head columns 16 kk + 2t, +1 and 16 kk + 8 + 2t, +1 of query row g
-      const T* q0 = reinterpret_cast<const T*>(p.q) + (long long)b * p.q_sb + (long long)(hkv * p.G + g) * p.q_sh;
+      const int qrow = mt * 8 + g;
+      const T* q0 = reinterpret_cast<const T*>(p.q) + (long long)b * p.q_sb + (long long)(hkv * p.G + qrow) * p.q_sh;
 #pragma unroll
       for (int kk = 0; kk < HD / 16; ++kk) {
         const bool lo = kk * 16 + 2 * t < p.D, hi = kk * 16 + 8 + 2 * t < p.D;
-        qa[kk][0] = (g < p.G && lo) ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 2 * t) : 0u;
-        qa[kk][1] = (g < p.G && hi) ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 8 + 2 * t) : 0u;
+        qa[kk][0] = (qrow < p.G && lo) ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 2 * t) : 0u;
+        qa[kk][1] = (qrow < p.G && hi) ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 8 + 2 * t) : 0u;
       }
     } else {
       const int r0 = mt * 16 + g, r1 = r0 + 8;
@@ -335,7 +337,7 @@ __global__ void __launch_bounds__(DWARPS * 32, OCC) dec_kernel(const DecKernelPa
         }
       }
     }
-    const int row0 = TR ? 2 * t : mt * 16 + g, row1 = TR ? 2 * t + 1 : mt * 16 + g + 8;  // this lane's two query rows
+    const int row0 = TR ? mt * 8 + 2 * t : mt * 16 + g, row1 = TR ? row0 + 1 : row0 + 8;  // this lane's two query rows
     const bool row0_ok = row0 < p.G, row1_ok = row1 < p.G;
     // ---- gated: alpha of the two rows, its extremes over the real rows, the running gate bound ----
     float al0 = 0.f, al1 = 0.f, a_max = 0.f, a_min = 0.f, gate_max = -INFINITY;
@@ -779,17 +781,17 @@ __global__ void __launch_bounds__(DWARPS * 32, OCC) dec_kernel(const DecKernelPa
       }
     }
     if (TR ? g == 0 : t == 0) {
-      mm[row0 - mt * 16] = m_run[0];
-      mm[row1 - mt * 16] = m_run[1];
-      ml[row0 - mt * 16] = l_run[0];
-      ml[row1 - mt * 16] = l_run[1];
+      mm[row0 - mt * MROWS] = m_run[0];
+      mm[row1 - mt * MROWS] = m_run[1];
+      ml[row0 - mt * MROWS] = l_run[0];
+      ml[row1 - mt * MROWS] = l_run[1];
     }
     __syncthreads();
     const float* all = reinterpret_cast<const float*>(dsm);
     for (int item = tid; item < 16 * (HD / 4); item += DWARPS * 32) {
       const int r = item / (HD / 4), d0 = (item % (HD / 4)) * 4;
-      const int row = mt * 16 + r;
-      if (row >= p.G || d0 >= p.D) continue;
+      const int row = mt * MROWS + r;
+      if (r >= MROWS || row >= p.G || d0 >= p.D) continue;
       float m_tot = -INFINITY;
 #pragma unroll
       for (int ww = 0; ww < DWARPS; ++ww) m_tot = fmaxf(m_tot, all[ww * (16 * HD + 32) + 16 * HD + r]);
@@ -906,21 +908,8 @@ __global__ void __launch_bounds__(256) dec_gate_ext_kernel(const DecKernelParams
   if (l16 == 0 && item < n_items) reinterpret_cast<float2*>(p.gate_ws)[item] = make_float2(mx, mn);
 }
 
-template <int HD, typename T, int KIND, bool TR = false, int OCC = FSA_DEC_MINBLOCKS>
-cudaError_t launch_one(const DecKernelParams& p, cudaStream_t stream) {
-  if constexpr (!TR && sizeof(T) == 2) {
-    if (p.G <= 8) {
-      // Transposed products (see dec_kernel), at three or at two CTAs per SM. The grid runs in rounds of occ x SMs
-      // CTAs and a CTA takes about occ times longer with occ neighbours (the step is bandwidth bound), so the cost is
-      // rounds x CTAs per SM: 512 CTAs on 148 SMs are two rounds either way and run faster two per SM (92 against
-      // 107 us), 440 CTAs are one round of three (82 us).
-      const long long sms = device_sm_count();
-      const long long ctas = (long long)p.Hkv * p.B * p.num_splits;
-      const long long per_sm = (ctas + sms - 1) / sms;
-      auto cost = [&](long long occ) { return ((ctas + occ * sms - 1) / (occ * sms)) * (per_sm < occ ? per_sm : occ); };
-      return cost(3) <= cost(2) ? launch_one<HD, T, KIND, true, 3>(p, stream) : launch_one<HD, T, KIND, true, 2>(p, stream);
-    }
-  }
+template <int HD, typename T, int KIND, bool TR, int OCC>
+cudaError_t launch_variant(const DecKernelParams& p, cudaStream_t stream) {
   auto kern = dec_kernel<HD, T, KIND, TR, OCC>;
   // the variant for two CTAs per SM asks for enough shared memory that a third cannot join
   constexpr int ring = DecSmem<HD, sizeof(T)>::kTotal;
@@ -940,6 +929,31 @@ cudaError_t launch_one(const DecKernelParams& p, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+template <int HD, typename T, int KIND>
+cudaError_t launch_one(const DecKernelParams& p, cudaStream_t stream) {
+  if constexpr (HD > 128) {
+    // head sizes above 128: only the transposed variant (its accumulator still fits the registers: 16 x 4 per lane),
+    // eight query rows per pass over the keys; the 128 KB ring leaves one CTA per SM
+    return launch_variant<HD, T, KIND, true, 2>(p, stream);
+  } else {
+    if constexpr (sizeof(T) == 2) {
+      if (p.G <= 8) {
+        // Transposed products (see dec_kernel), at three or at two CTAs per SM. The grid runs in rounds of occ x SMs
+        // CTAs and a CTA takes about occ times longer with occ neighbours (the step is bandwidth bound), so the cost
+        // is rounds x CTAs per SM: 512 CTAs on 148 SMs are two rounds either way and run faster two per SM (92
+        // against 107 us), 440 CTAs are one round of three (82 us).
+        const long long sms = device_sm_count();
+        const long long ctas = (long long)p.Hkv * p.B * p.num_splits;
+        const long long per_sm = (ctas + sms - 1) / sms;
+        auto cost = [&](long long occ) { return ((ctas + occ * sms - 1) / (occ * sms)) * (per_sm < occ ? per_sm : occ); };
+        return cost(3) <= cost(2) ? launch_variant<HD, T, KIND, true, 3>(p, stream)
+                                  : launch_variant<HD, T, KIND, true, 2>(p, stream);
+      }
+    }
+    return launch_variant<HD, T, KIND, false, FSA_DEC_MINBLOCKS>(p, stream);
+  }
+}
+
 }  // namespace
 
 cudaError_t launch_dec(const DecKernelParams& p, int kind, int dtype, int head_dim, cudaStream_t stream) {
@@ -953,6 +967,8 @@ cudaError_t launch_dec(const DecKernelParams& p, int kind, int dtype, int head_d
   FSA_DEC_CASE(128, __half, DT_FP16)
   FSA_DEC_CASE(64, __nv_bfloat16, DT_BF16)
   FSA_DEC_CASE(64, __half, DT_FP16)
+  FSA_DEC_CASE(256, __nv_bfloat16, DT_BF16)
+  FSA_DEC_CASE(256, __half, DT_FP16)
   FSA_DEC_CASE(128, __nv_fp8_e4m3, DT_E4M3)
   FSA_DEC_CASE(128, __nv_fp8_e5m2, DT_E5M2)
 #undef FSA_DEC_CASE

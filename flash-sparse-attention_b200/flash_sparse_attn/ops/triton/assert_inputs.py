@@ -1,8 +1,9 @@
 """Input contract of the operators, raised as AssertionError like the reference's
 flash_sparse_attn/ops/triton/assert_inputs.py:6-318 (skipped when ``skip_checks=True``).
 
-Same checks and messages as the reference, with three differences: head sizes above 128 are refused here
-(the reference admits up to 512; these kernels hold one 128-column output row per TMEM lane), a page table may be
+Same checks and messages as the reference, with three differences: head sizes above 128 - above 256 for the
+decode operators with 16-bit inputs - are refused here (the reference admits up to 512; the forward and backward
+kernels hold one 128-column output row per TMEM lane), a page table may be
 combined with gather_kv_indices (the reference rejects that, :303-305; here the gathered position goes through
 the page table), and the shapes of the gate vectors, of caller-provided out / lse buffers and of the page table
 are checked as well, because the kernels take their strides on trust."""
@@ -12,6 +13,7 @@ import torch
 _FP8 = (torch.float8_e5m2, torch.float8_e4m3fn)
 _F16 = (torch.float16, torch.bfloat16)
 MAX_HEAD_DIM = 128
+MAX_HEAD_DIM_DECODE = 256  # 16-bit inputs; FP8 decode is built for head size 128
 
 
 def _same_device(device, *tensors):
@@ -27,7 +29,7 @@ def _int32(*tensors, what):
 
 
 def _check_qkv(query, key, value, query_scale, key_scale, value_scale, num_heads_q, num_heads_kv, head_dim, is_quant,
-               device):
+               device, max_head_dim=MAX_HEAD_DIM):
     _same_device(device, query, key, value)
     if is_quant:
         assert query.dtype in _FP8, "Input dtype must be float8_e5m2 or float8_e4m3fn"
@@ -45,7 +47,9 @@ def _check_qkv(query, key, value, query_scale, key_scale, value_scale, num_heads
     assert num_heads_q % num_heads_kv == 0, "num_heads_q must be divisible by num_heads_kv"
     assert head_dim % 16 == 0, "head_dim must be a multiple of 16 for efficient memory access"
     assert head_dim <= 512, "head_dim must be less than or equal to 512 for efficient memory access"
-    assert head_dim <= MAX_HEAD_DIM, f"head_dim must be less than or equal to {MAX_HEAD_DIM} in this build"
+    if is_quant:
+        max_head_dim = min(max_head_dim, MAX_HEAD_DIM)
+    assert head_dim <= max_head_dim, f"head_dim must be less than or equal to {max_head_dim} in this build"
 
 
 def _check_paged(page_size, tile_mn, page_table=None, batch=None):
@@ -131,7 +135,7 @@ def assert_dec_inputs(query, key, value, query_scale=None, key_scale=None, value
                       gather_kv_indices=None, num_heads_q=None, num_heads_kv=None, head_dim=None, page_size=None,
                       is_quant=False, device=None, tile_mn=None):
     _check_qkv(query, key, value, query_scale, key_scale, value_scale, num_heads_q, num_heads_kv, head_dim, is_quant,
-               device)
+               device, max_head_dim=MAX_HEAD_DIM_DECODE)
     _check_paged(page_size, tile_mn, page_table, query.shape[0])
     _check_gate(alpha, delta)
     if gather_kv_indices is not None:

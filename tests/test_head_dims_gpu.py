@@ -87,3 +87,60 @@ def test_decode_other_head_dims(head_dim, mode):
     torch.cuda.synchronize()
     fsa.check_status()
     assert_close(f"hd{head_dim}-decode-{mode}", out, ref, rtol=2.5e-2, atol=2.5e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("hq,hkv", [(8, 2), (16, 2), (24, 2)])
+@pytest.mark.parametrize("head_dim", [160, 192, 256])
+@pytest.mark.parametrize("mode", ["plain_split", "local", "paged_gather", "gated", "skip"])
+def test_decode_head_dims_above_128(mode, head_dim, hq, hkv, dtype):
+    """Decode at head sizes 160 / 192 / 256 (16-bit inputs): the 256-wide transposed kernel, eight query rows of a
+    KV head per pass over the keys (4, 8 and 12 query heads per KV head: one and two passes), against the eager
+    oracle. Forward and backward stay at head sizes up to 128."""
+    fsa = _ops()
+    b, sk = 2, 1200
+    g = torch.Generator().manual_seed(head_dim + hq)
+    mk = lambda *s: torch.randn(*s, generator=g).to(dtype)  # noqa: E731
+    q, k, v = mk(b, hq, head_dim), mk(b, sk, hkv, head_dim), mk(b, sk, hkv, head_dim)
+    if mode == "plain_split":
+        ref = eager.decode(q, k, v)
+        out = fsa.flash_dense_attn_with_kvcache_func(q.to(DEV), k.to(DEV), v.to(DEV), num_splits=3)
+    elif mode == "local":
+        ws = torch.tensor([[32, 200, 100, 160], [0, 300, 0, 64]], dtype=torch.int32)
+        ref = eager.decode(q, k, v, is_local=True, window_sizes=ws)
+        out = fsa.flash_sparse_attn_with_kvcache_func(q.to(DEV), k.to(DEV), v.to(DEV), window_sizes=ws.to(DEV),
+                                                      softmax_threshold=-128.0)
+    elif mode == "paged_gather":
+        page = 64
+        n_pages = b * (1216 // page)
+        kc, vc = mk(n_pages + 3, page, hkv, head_dim), mk(n_pages + 3, page, hkv, head_dim)
+        table = torch.randperm(n_pages + 3, generator=g)[:n_pages].reshape(b, -1).to(torch.int32)
+        kl, vl = eager.unpage(kc, table), eager.unpage(vc, table)
+        idx = torch.stack([torch.randperm(sk, generator=g)[:256] for _ in range(b)]).to(torch.int32)
+        idx[:, 3::17] = -1
+        ref = eager.gather_decode(q, kl, vl, idx)
+        out = fsa.flash_sparse_attn_with_kvcache_func(q.to(DEV), kc.to(DEV), vc.to(DEV), page_table=table.to(DEV),
+                                                      gather_kv_indices=idx.to(DEV), softmax_threshold=-128.0)
+    elif mode == "gated":
+        a, d = mk(b, hq), mk(b, sk, hkv)
+        ref = eager.decode(q, k, v, alpha=a, delta=d)
+        out = fsa.flash_gated_attn_with_kvcache_func(q.to(DEV), k.to(DEV), v.to(DEV), a.to(DEV), d.to(DEV),
+                                                     softmax_threshold=-128.0, gate_threshold=-128.0)
+    else:  # peaked queries with the threshold on: tiles are skipped, the result stays close
+        q = (k[:, -1].float().repeat_interleave(hq // hkv, dim=1) * 3).to(dtype)
+        ref = eager.decode(q, k, v)
+        out = fsa.flash_sparse_attn_with_kvcache_func(q.to(DEV), k.to(DEV), v.to(DEV), softmax_threshold=1.0)
+    torch.cuda.synchronize()
+    fsa.check_status()
+    assert_close(f"hd{head_dim}-decode-{mode}", out, ref, rtol=3e-2, atol=3e-2)
+
+
+def test_head_dims_above_128_are_refused_outside_decode():
+    fsa = _ops()
+    q = torch.randn(1, 256, 4, 192, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(AssertionError):
+        fsa.flash_sparse_attn_func(q, q, q, is_causal=True)
+    qd = torch.randn(2, 4, 320, device=DEV, dtype=torch.bfloat16)
+    kd = torch.randn(2, 64, 4, 320, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(AssertionError):
+        fsa.flash_sparse_attn_with_kvcache_func(qd, kd, kd)
