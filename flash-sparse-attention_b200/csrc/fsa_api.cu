@@ -78,9 +78,9 @@ int cdiv(int a, int b) { return (a + b - 1) / b; }
 // columns of every row with zeros (they add nothing to any dot product) and the epilogues do not write them.
 bool head_dim_ok(int d) { return d >= 8 && d <= 128 && d % 8 == 0; }
 int head_dim_kernel(int d) { return d <= 64 ? 64 : 128; }
-// the decode kernels also come 256 columns wide (16-bit inputs)
-bool head_dim_ok_decode(int d) { return d >= 8 && d <= 256 && d % 8 == 0; }
-int head_dim_kernel_decode(int d) { return d <= 64 ? 64 : (d <= 128 ? 128 : 256); }
+// the forward and decode kernels also come 256 columns wide (16-bit inputs); the backward stops at 128
+bool head_dim_ok_wide(int d) { return d >= 8 && d <= 256 && d % 8 == 0; }
+int head_dim_kernel_wide(int d) { return d <= 64 ? 64 : (d <= 128 ? 128 : 256); }
 
 // optional per-call timing events around the main kernel
 void mark(void* ev, cudaStream_t s) {
@@ -97,7 +97,7 @@ const char* fsa_status_string(int code) {
   switch (code) {
     case FSA_OK: return "ok";
     case FSA_ERR_INVALID_ARG: return "invalid argument (null pointer, bad size, or stride/base not 16-byte aligned)";
-    case FSA_ERR_UNSUPPORTED: return "unsupported combination (head_dim must be a multiple of 8 up to 128 - decode: up to 256 -, dtype bf16/fp16/fp8, ...)";
+    case FSA_ERR_UNSUPPORTED: return "unsupported combination (head_dim must be a multiple of 8 up to 128 - forward and decode with 16-bit inputs: up to 256 -, dtype bf16/fp16/fp8, ...)";
     case FSA_ERR_LAUNCH: return "CUDA error at launch or tensor-map creation";
     case FSA_ERR_NO_DRIVER: return "CUDA driver entry point cuTensorMapEncodeTiled unavailable";
     case FSA_ERR_SCRATCH_UNAVAILABLE:
@@ -226,7 +226,7 @@ size_t fsa_fwd_tile_map_bytes(const FsaFwdArgs* a) {
 int fsa_fwd(const FsaFwdArgs* a, void* stream_) {
   if (!a || !a->q || !a->k || !a->v || !a->out || !a->lse || !a->status) return FSA_ERR_INVALID_ARG;
   if (a->batch <= 0 || a->heads_q <= 0 || a->head_dim <= 0) return FSA_ERR_INVALID_ARG;
-  if (!head_dim_ok(a->head_dim)) return FSA_ERR_UNSUPPORTED;
+  if (!head_dim_ok_wide(a->head_dim)) return FSA_ERR_UNSUPPORTED;
   const bool fp8 = a->dtype == FSA_DT_E4M3 || a->dtype == FSA_DT_E5M2;
   if (a->dtype != FSA_DT_BF16 && a->dtype != FSA_DT_FP16 && !fp8) return FSA_ERR_UNSUPPORTED;
   if (fp8 && a->head_dim != 128) return FSA_ERR_UNSUPPORTED;  // FP8 tiles: one 128-byte swizzle row per head row
@@ -338,7 +338,8 @@ int fsa_fwd(const FsaFwdArgs* a, void* stream_) {
   p.sk = sk_static;
   p.num_splits = ns;
   p.num_m_blocks = num_m_blocks;
-  p.num_pairs = cdiv(num_m_blocks, 2);
+  // head sizes above 128: one query tile per CTA (the 256-wide kernel), otherwise two
+  p.num_pairs = head_dim_kernel_wide(a->head_dim) > 128 ? num_m_blocks : cdiv(num_m_blocks, 2);
   p.hgrid = hgrid;
   p.page_size = a->page_size;
   p.pt_stride = a->page_table_stride;
@@ -406,7 +407,7 @@ int fsa_fwd(const FsaFwdArgs* a, void* stream_) {
   }
   mark(a->ev_before, stream);
   p.D = a->head_dim;
-  cudaError_t e = fsa::launch_fwd(p, a->kind, a->dtype, head_dim_kernel(a->head_dim), stream);
+  cudaError_t e = fsa::launch_fwd(p, a->kind, a->dtype, head_dim_kernel_wide(a->head_dim), stream);
   mark(a->ev_after, stream);
   if (e == cudaErrorInvalidValue) return FSA_ERR_UNSUPPORTED;
   if (e != cudaSuccess) return FSA_ERR_LAUNCH;
@@ -750,7 +751,7 @@ int fsa_combine(const float* out_partial, const float* lse_partial, void* out, f
 int fsa_decode(const FsaDecArgs* a, void* stream_) {
   if (!a || !a->q || !a->k || !a->v || !a->status) return FSA_ERR_INVALID_ARG;
   if (a->batch <= 0 || a->heads_q <= 0 || a->heads_kv <= 0 || a->heads_q % a->heads_kv) return FSA_ERR_INVALID_ARG;
-  if (!head_dim_ok_decode(a->head_dim)) return FSA_ERR_UNSUPPORTED;
+  if (!head_dim_ok_wide(a->head_dim)) return FSA_ERR_UNSUPPORTED;
   const bool fp8 = a->dtype == FSA_DT_E4M3 || a->dtype == FSA_DT_E5M2;  // q, k, v in FP8; out / alpha / delta bf16
   if (a->dtype != FSA_DT_BF16 && a->dtype != FSA_DT_FP16 && !fp8) return FSA_ERR_UNSUPPORTED;
   if (fp8 && a->head_dim != 128) return FSA_ERR_UNSUPPORTED;
@@ -850,7 +851,7 @@ int fsa_decode(const FsaDecArgs* a, void* stream_) {
   }
   mark(a->ev_before, stream);
   p.D = a->head_dim;
-  cudaError_t e = fsa::launch_dec(p, a->kind, a->dtype, head_dim_kernel_decode(a->head_dim), stream);
+  cudaError_t e = fsa::launch_dec(p, a->kind, a->dtype, head_dim_kernel_wide(a->head_dim), stream);
   mark(a->ev_after, stream);
   if (e == cudaErrorInvalidValue) return FSA_ERR_UNSUPPORTED;
   if (e != cudaSuccess) return FSA_ERR_LAUNCH;

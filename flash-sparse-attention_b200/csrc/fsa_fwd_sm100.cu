@@ -37,16 +37,23 @@ constexpr int NTHREADS = 384;  // three warpgroups: softmax 0, softmax 1, {produ
 // arrive on one barrier and one "consumed" barrier per step releases both: every barrier the issuer touches
 // costs it 130-250 cycles even when it is already complete. (A third V stage, loaded a whole step earlier, did
 // not shorten the issuer's wait: it is not load latency.)
-constexpr int KSTAGES = 2;
-constexpr int VSTAGES = 2;
+// Head sizes above 128 (the 256-wide instantiation): a tile is 64 KB, so a CTA holds ONE query tile (the second
+// softmax group idles; its TMEM columns belong to the 256-column output accumulator of the first) and one stage each
+// of K and V - the loads of V(t) and K(t + 1) then start when S(t) has completed and run under the softmax of tile t.
+template <int HD>
+struct FwdShape {
+  static constexpr int QT = HD > 128 ? 1 : 2;       // query tiles (softmax groups at work) per CTA
+  static constexpr int KSTAGES = HD > 128 ? 1 : 2;
+  static constexpr int VSTAGES = HD > 128 ? 1 : 2;
+};
 
 template <int HD, int ES = 2>
 struct FwdSmem {
   static constexpr int kTileBytes = TM * HD * ES;  // one Q / K / V tile of ES-byte elements
   static constexpr int kQ = 0;
-  static constexpr int kK = kQ + 2 * kTileBytes;
-  static constexpr int kV = kK + KSTAGES * kTileBytes;
-  static constexpr int kBar = kV + VSTAGES * kTileBytes;
+  static constexpr int kK = kQ + FwdShape<HD>::QT * kTileBytes;
+  static constexpr int kV = kK + FwdShape<HD>::KSTAGES * kTileBytes;
+  static constexpr int kBar = kV + FwdShape<HD>::VSTAGES * kTileBytes;
   static constexpr int kTotal = kBar + 2048 + 1024;  // barriers/flags/delta ring + alignment slack
 };
 
@@ -151,6 +158,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
   constexpr int KK_QK = HD * ES / 32;  // MMAs per S tile: every MMA consumes 32 bytes of the head dimension
   constexpr int KK_PV = TN * ES / 32;  // MMAs per P V tile: 32 bytes of the key dimension each
   constexpr int OCH = HD / 32;        // 32-column chunks of an O tile
+  constexpr int QT = FwdShape<HD>::QT, KSTAGES = FwdShape<HD>::KSTAGES, VSTAGES = FwdShape<HD>::VSTAGES;
   constexpr bool IS_BF16 = (sizeof(T) == 2) && !__is_same(T, __half);
   static_assert(!F8 || HD == 128, "FP8 tiles are one 128-byte swizzle row wide");
   constexpr uint32_t TMEM_S0 = 0, TMEM_O0 = 256;
@@ -199,8 +207,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
   bool q_valid[2];
 #pragma unroll
   for (int q = 0; q < 2; ++q) {
-    const int mb = pair * 2 + q;
-    q_valid[q] = mb < m_blocks_here;
+    const int mb = pair * QT + q;
+    q_valid[q] = q < QT && mb < m_blocks_here;
     // One query position with windows and split-KV: the reference's rounding drops the first, partial tile of
     // the near band (block_info.py:60-64) although its eager ground truth sees those keys; like the decode
     // kernel, this one visits them (the flag only matters for that combination).
@@ -242,7 +250,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     gw_dext = aext + (long long)p.B * p.hgrid * p.num_m_blocks + ((long long)si.b * p.Hkv + si.hkv) * p.n_tiles_k;
 #pragma unroll
     for (int q = 0; q < 2; ++q) {
-      const int mb = pair * 2 + q;
+      const int mb = pair * QT + q;
       if (mb < p.num_m_blocks) {
         const float2 e = __ldg(aext + ((long long)si.b * p.hgrid + si.head) * p.num_m_blocks + mb);
         gw_amax[q] = e.x;
@@ -275,7 +283,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
           if (!skip) gw_run[q] = fmaxf(gmc, gw_run[q]);
           keep[q] = !skip;
           if (skip && mark_q == q && p.tile_map) {
-            const int mb = pair * 2 + q;
+            const int mb = pair * QT + q;
             p.tile_map[((((long long)si.b * p.hgrid + si.head) * p.num_m_blocks + mb) * p.num_splits + si.split) *
                            p.n_tiles_k + n] = 3;
           }
@@ -340,7 +348,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
           mbar_arrive_expect_tx(&bars->q_full, bytes);
           for (int q = 0; q < 2; ++q) {
             if (!q_valid[q]) continue;
-            const int mb = pair * 2 + q;
+            const int mb = pair * QT + q;
             uint8_t* dst = smem + SM::kQ + q * SM::kTileBytes;
             const int row0 = (mb * TM) / gpack;  // token index of the tile's first row
             const int head0 = (p.flags & F_PACK_GQA) ? si.hkv * p.G : si.head;
@@ -393,7 +401,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
             ++seen;
           }
         };
-        need_signal(t - 1);
+        need_signal(t - KSTAGES + 1);  // one stage each: signal t, i.e. S(t) and P V(t - 1) have completed
         if (!ok) break;
         // V is prefetched like K, before the softmax groups have voted on the tile: waiting for the vote
         // would put a full load latency between every S tile and its P V product, and in this
@@ -597,7 +605,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
     const int q = warp >> 2;        // group / query tile
     const int wq = warp & 3;        // warp within group == TMEM lane quadrant
     const int row = wq * 32 + lane; // row within the tile
-    const int mb = pair * 2 + q;
+    const int mb = pair * QT + q;
     const uint32_t lane_addr = uint32_t(wq * 32) << 16;
     const uint32_t tS = tmem_base + lane_addr + TMEM_S0 + q * 128;
     const uint32_t tO = tmem_base + lane_addr + TMEM_O0 + q * 128;
@@ -978,6 +986,8 @@ cudaError_t launch_fwd(const FwdKernelParams& p, int kind, int dtype, int head_d
   FSA_FWD_CASE(128, __half, DT_FP16)
   FSA_FWD_CASE(64, __nv_bfloat16, DT_BF16)
   FSA_FWD_CASE(64, __half, DT_FP16)
+  FSA_FWD_CASE(256, __nv_bfloat16, DT_BF16)
+  FSA_FWD_CASE(256, __half, DT_FP16)
   FSA_FWD_CASE(128, __nv_fp8_e4m3, DT_E4M3)
   FSA_FWD_CASE(128, __nv_fp8_e5m2, DT_E5M2)
 #undef FSA_FWD_CASE

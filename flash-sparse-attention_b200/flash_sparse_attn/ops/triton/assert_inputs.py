@@ -1,9 +1,8 @@
 """Input contract of the operators, raised as AssertionError like the reference's
 flash_sparse_attn/ops/triton/assert_inputs.py:6-318 (skipped when ``skip_checks=True``).
 
-Same checks and messages as the reference, with three differences: head sizes above 128 - above 256 for the
-decode operators with 16-bit inputs - are refused here (the reference admits up to 512; the forward and backward
-kernels hold one 128-column output row per TMEM lane), a page table may be
+Same checks and messages as the reference, with three differences: head sizes above 256 - above 128 in the
+backward pass and with FP8 inputs - are refused here (the reference admits up to 512), a page table may be
 combined with gather_kv_indices (the reference rejects that, :303-305; here the gathered position goes through
 the page table), and the shapes of the gate vectors, of caller-provided out / lse buffers and of the page table
 are checked as well, because the kernels take their strides on trust."""
@@ -13,7 +12,7 @@ import torch
 _FP8 = (torch.float8_e5m2, torch.float8_e4m3fn)
 _F16 = (torch.float16, torch.bfloat16)
 MAX_HEAD_DIM = 128
-MAX_HEAD_DIM_DECODE = 256  # 16-bit inputs; FP8 decode is built for head size 128
+MAX_HEAD_DIM_WIDE = 256  # forward and decode with 16-bit inputs (FP8: head size 128); the backward stops at 128
 
 
 def _same_device(device, *tensors):
@@ -102,7 +101,7 @@ def assert_fwd_inputs(query, key, value, query_scale=None, key_scale=None, value
                       num_heads_q=None, num_heads_kv=None, head_dim=None, page_size=None, tile_mn=None,
                       is_quant=False, device=None, page_table=None):
     _check_qkv(query, key, value, query_scale, key_scale, value_scale, num_heads_q, num_heads_kv, head_dim, is_quant,
-               device)
+               device, max_head_dim=MAX_HEAD_DIM_WIDE)
     _check_paged(page_size, tile_mn, page_table, query.shape[0] if cu_seqlens_q is None else None)
     _check_gate(alpha, delta)
     _same_device(device, alpha, delta, cu_seqlens_q, cu_seqlens_k, seqused_q, seqused_k, page_table)
@@ -135,7 +134,7 @@ def assert_dec_inputs(query, key, value, query_scale=None, key_scale=None, value
                       gather_kv_indices=None, num_heads_q=None, num_heads_kv=None, head_dim=None, page_size=None,
                       is_quant=False, device=None, tile_mn=None):
     _check_qkv(query, key, value, query_scale, key_scale, value_scale, num_heads_q, num_heads_kv, head_dim, is_quant,
-               device, max_head_dim=MAX_HEAD_DIM_DECODE)
+               device, max_head_dim=MAX_HEAD_DIM_WIDE)
     _check_paged(page_size, tile_mn, page_table, query.shape[0])
     _check_gate(alpha, delta)
     if gather_kv_indices is not None:

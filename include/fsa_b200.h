@@ -248,7 +248,7 @@ int64_t fsa_bwd_padded_rows(int batch, int seqlen_q, int total_q, int is_varlen)
  *     call stops after the partials (no combine), for callers that merge partials of several
  *     devices themselves with fsa_combine.
  *   head_dim: a multiple of 8 up to 256 with 16-bit inputs (sizes above 128 run eight query heads of a KV head per
- *     pass over the keys), 128 with FP8 inputs. The forward and backward entry points stop at 128.
+ *     pass over the keys), 128 with FP8 inputs. fsa_fwd takes the same sizes, fsa_bwd stops at 128.
  */
 typedef struct FsaDecArgs {
   const void* q;

@@ -1,6 +1,6 @@
-"""Head sizes other than 64 / 128 (any multiple of 16 up to 128, the reference's contract
-`assert_inputs.py:39-40` up to that size): forward, backward and decode run on the 64- or 128-wide kernels
-with the missing columns loaded as zeros; results are compared with the eager oracle."""
+"""Head sizes other than 64 / 128 (any multiple of 16, the reference's contract `assert_inputs.py:39-40`): up to
+128 forward, backward and decode run on the 64- or 128-wide kernels with the missing columns loaded as zeros; up to
+256 the forward and the decode run on 256-wide kernels. Results are compared with the eager oracle."""
 
 import pytest
 import torch
@@ -135,12 +135,66 @@ def test_decode_head_dims_above_128(mode, head_dim, hq, hkv, dtype):
     assert_close(f"hd{head_dim}-decode-{mode}", out, ref, rtol=3e-2, atol=3e-2)
 
 
-def test_head_dims_above_128_are_refused_outside_decode():
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("head_dim", [160, 192, 256])
+@pytest.mark.parametrize("mode", ["dense", "causal_sparse", "local_split", "gated", "varlen", "pack_gqa", "skip"])
+def test_forward_head_dims_above_128(mode, head_dim, dtype):
+    """Forward at head sizes 160 / 192 / 256: the 256-wide kernel (one query tile per CTA, one stage of K and V),
+    against the eager oracle, with a ragged sequence length (several key tiles, a partial last tile)."""
     fsa = _ops()
-    q = torch.randn(1, 256, 4, 192, device=DEV, dtype=torch.bfloat16)
-    with pytest.raises(AssertionError):
-        fsa.flash_sparse_attn_func(q, q, q, is_causal=True)
+    b, s, hq, hkv = 2, 600, 4, 2
+    g = torch.Generator().manual_seed(head_dim)
+    mk = lambda *sh: torch.randn(*sh, generator=g).to(dtype)  # noqa: E731
+    q, k, v = mk(b, s, hq, head_dim), mk(b, s, hkv, head_dim), mk(b, s, hkv, head_dim)
+    with torch.no_grad():
+        if mode == "dense":
+            ref = eager.forward(q, k, v, None, False)
+            out = fsa.flash_dense_attn_func(q.to(DEV), k.to(DEV), v.to(DEV), is_causal=False)
+        elif mode == "causal_sparse":
+            ref = eager.forward(q, k, v, None, True)
+            out = fsa.flash_sparse_attn_func(q.to(DEV), k.to(DEV), v.to(DEV), is_causal=True, softmax_threshold=-128.0)
+        elif mode == "local_split":
+            ws = torch.tensor([[16, 100, 50, 120], [0, 200, 0, 64]], dtype=torch.int32)
+            ref = eager.forward(q, k, v, None, True, is_local=True, window_sizes=ws)
+            out = fsa.flash_sparse_attn_func(q.to(DEV), k.to(DEV), v.to(DEV), is_causal=True, window_sizes=ws.to(DEV),
+                                             softmax_threshold=-128.0, is_split_kv=True, num_splits=2)
+        elif mode == "gated":
+            a, d = mk(b, s, hq), mk(b, s, hkv)
+            ref = eager.forward(q, k, v, None, True, alpha=a, delta=d)
+            out = fsa.flash_gated_attn_func(q.to(DEV), k.to(DEV), v.to(DEV), a.to(DEV), d.to(DEV), is_causal=True,
+                                            softmax_threshold=-128.0, gate_threshold=-128.0)
+        elif mode == "varlen":
+            lens = [600, 333]
+            cu = torch.tensor([0, 600, 933], dtype=torch.int32)
+            qp, kp, vp = mk(933, hq, head_dim), mk(933, hkv, head_dim), mk(933, hkv, head_dim)
+            ref = torch.cat([eager.forward(qp[None, cu[i]:cu[i + 1]], kp[None, cu[i]:cu[i + 1]], vp[None, cu[i]:cu[i + 1]],
+                                           None, True)[0] for i in range(2)])
+            out = fsa.flash_sparse_attn_varlen_func(qp.to(DEV), kp.to(DEV), vp.to(DEV), cu.to(DEV), cu.to(DEV),
+                                                    max(lens), max(lens), is_causal=True, softmax_threshold=-128.0)
+        elif mode == "pack_gqa":
+            ref = eager.forward(q[:, :5], k, v, None, True)
+            out = fsa.flash_sparse_attn_func(q[:, :5].to(DEV), k.to(DEV), v.to(DEV), is_causal=True,
+                                             softmax_threshold=-128.0, pack_gqa=True)
+        else:  # peaked queries with the threshold on: tiles are skipped, the result stays close
+            q = (k.float().repeat_interleave(hq // hkv, dim=2) * 3).to(dtype)
+            ref = eager.forward(q, k, v, None, True)
+            out = fsa.flash_sparse_attn_func(q.to(DEV), k.to(DEV), v.to(DEV), is_causal=True, softmax_threshold=1.0)
+    torch.cuda.synchronize()
+    fsa.check_status()
+    assert out.shape == ref.shape
+    assert_close(f"hd{head_dim}-fwd-{mode}", out, ref, rtol=3e-2, atol=3e-2)
+
+
+def test_head_dims_above_128_backward_is_refused():
+    """The backward kernels stop at head size 128: the forward runs, the backward raises."""
+    fsa = _ops()
+    q = torch.randn(1, 256, 4, 192, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    out = fsa.flash_sparse_attn_func(q, q.detach(), q.detach(), is_causal=True)
+    with pytest.raises((AssertionError, RuntimeError)):
+        out.sum().backward()
     qd = torch.randn(2, 4, 320, device=DEV, dtype=torch.bfloat16)
     kd = torch.randn(2, 64, 4, 320, device=DEV, dtype=torch.bfloat16)
     with pytest.raises(AssertionError):
         fsa.flash_sparse_attn_with_kvcache_func(qd, kd, kd)
+    with pytest.raises(AssertionError):
+        fsa.flash_sparse_attn_func(kd, kd, kd)
