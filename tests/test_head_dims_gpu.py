@@ -137,7 +137,7 @@ def test_decode_head_dims_above_128(mode, head_dim, hq, hkv, dtype):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("head_dim", [160, 192, 256])
-@pytest.mark.parametrize("mode", ["dense", "causal_sparse", "local_split", "gated", "varlen", "pack_gqa", "skip"])
+@pytest.mark.parametrize("mode", ["dense", "causal_sparse", "local_split", "gated", "varlen", "pack_gqa", "paged", "skip"])
 def test_forward_head_dims_above_128(mode, head_dim, dtype):
     """Forward at head sizes 160 / 192 / 256: the 256-wide kernel (one query tile per CTA, one stage of K and V),
     against the eager oracle, with a ragged sequence length (several key tiles, a partial last tile)."""
@@ -175,6 +175,18 @@ def test_forward_head_dims_above_128(mode, head_dim, dtype):
             ref = eager.forward(q[:, :5], k, v, None, True)
             out = fsa.flash_sparse_attn_func(q[:, :5].to(DEV), k.to(DEV), v.to(DEV), is_causal=True,
                                              softmax_threshold=-128.0, pack_gqa=True)
+        elif mode == "paged":
+            page, max_pages = 64, 10
+            kc, vc = mk(b * max_pages + 3, page, hkv, head_dim), mk(b * max_pages + 3, page, hkv, head_dim)
+            table = torch.randperm(b * max_pages + 3, generator=g)[: b * max_pages].reshape(b, max_pages).to(torch.int32)
+            used = torch.tensor([max_pages * page - 37, 333], dtype=torch.int32)
+            kl, vl = eager.unpage(kc, table), eager.unpage(vc, table)
+            qs = q[:, :200]
+            ref = torch.stack([eager.forward(qs[i:i + 1], kl[i:i + 1, :used[i]], vl[i:i + 1, :used[i]], None, True)[0]
+                               for i in range(b)])
+            out = fsa.flash_sparse_attn_func(qs.to(DEV), kc.to(DEV), vc.to(DEV), is_causal=True,
+                                             softmax_threshold=-128.0, page_table=table.to(DEV),
+                                             seqused_k=used.to(DEV))
         else:  # peaked queries with the threshold on: tiles are skipped, the result stays close
             q = (k.float().repeat_interleave(hq // hkv, dim=2) * 3).to(dtype)
             ref = eager.forward(q, k, v, None, True)
