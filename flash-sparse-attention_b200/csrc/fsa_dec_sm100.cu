@@ -10,6 +10,9 @@
 // merged in shared memory at the end. In terms of the reference's schedule every warp is one KV
 // split: the tile ranges come from the same functions with 4 x num_splits splits
 // (block_info.py:5-123 for contiguous / paged caches, :321-349 for gathered top-k lists).
+// With 16-bit inputs and at most 8 query heads per KV head - and always at head sizes above 128 - the two
+// products run transposed (keys on the M side of the MMA, query rows on N = 8; see dec_kernel), eight query
+// rows per pass over the keys.
 //
 // Key addressing covers the reference's three modes and their combination:
 //   contiguous  row = key position                               (flash_sparse_dec.py:673-678)
