@@ -97,11 +97,12 @@ __global__ void __launch_bounds__(128) gather_cp_async_kernel(const uint8_t* __r
 }
 
 // The same fetch with one bulk copy (cp.async.bulk, completion on an mbarrier) per row, issued by one lane per row:
-// four stages of 16 rows per warp.
+// four stages of 16 rows per warp and four warps per SM, or two stages and twelve warps per SM.
+template <int STAGES>
 __global__ void __launch_bounds__(128) gather_bulk_kernel(const uint8_t* __restrict__ pool, const int* __restrict__ rows,
                                                           long long n_rows, long long stride, int row_bytes,
                                                           unsigned* __restrict__ sink, unsigned* __restrict__ status) {
-  constexpr int ROWS = 16, STAGES = 4;
+  constexpr int ROWS = 16;
   extern __shared__ __align__(128) uint8_t smem[];
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + w;
@@ -153,10 +154,11 @@ __global__ void __launch_bounds__(128) gather_bulk_kernel(const uint8_t* __restr
   if (smem[threadIdx.x + 256] == 0x5a && n_rows < 0) sink[0] = 1;
 }
 
-// how: 0 = ld.global into registers, 1 = cp.async.cg ring, 2 = one bulk copy per row, 3 = cp.async.ca ring
+// how: 0 = ld.global into registers, 1 = cp.async.cg ring, 2 = one bulk copy per row (4 warps per SM), 3 = cp.async.ca
+// ring, 4 = one bulk copy per row (12 warps per SM)
 float run(int how, int lpr, const uint8_t* pool, const int* rows, long long n_rows, long long stride, unsigned* sink,
           unsigned* status, int sms) {
-  constexpr int kCpSmem = 4 * 4 * 8 * 512, kBulkSmem = 128 + 4 * 4 * 16 * 512;
+  constexpr int kCpSmem = 4 * 4 * 8 * 512, kBulkSmem = 128 + 4 * 4 * 16 * 512, kBulkSmem2 = 128 + 4 * 2 * 16 * 512;
   static bool opted = false;
   if (!opted) {
     CHECK(cudaFuncSetAttribute(gather_cp_async_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCpSmem));
@@ -165,7 +167,8 @@ float run(int how, int lpr, const uint8_t* pool, const int* rows, long long n_ro
     CHECK(cudaFuncSetAttribute(gather_cp_async_kernel<8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCpSmem));
     CHECK(cudaFuncSetAttribute(gather_cp_async_kernel<16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCpSmem));
     CHECK(cudaFuncSetAttribute(gather_cp_async_kernel<32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCpSmem));
-    CHECK(cudaFuncSetAttribute(gather_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmem));
+    CHECK(cudaFuncSetAttribute(gather_bulk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmem));
+    CHECK(cudaFuncSetAttribute(gather_bulk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmem2));
     opted = true;
   }
   auto launch = [&]() {
@@ -184,8 +187,10 @@ float run(int how, int lpr, const uint8_t* pool, const int* rows, long long n_ro
       if (lpr == 8) gather_cp_async_kernel<8, true><<<grid, 128, kCpSmem>>>(pool, rows, n_rows, stride, sink);
       if (lpr == 16) gather_cp_async_kernel<16, true><<<grid, 128, kCpSmem>>>(pool, rows, n_rows, stride, sink);
       if (lpr == 32) gather_cp_async_kernel<32, true><<<grid, 128, kCpSmem>>>(pool, rows, n_rows, stride, sink);
+    } else if (how == 4) {
+      gather_bulk_kernel<2><<<sms * 3, 128, kBulkSmem2>>>(pool, rows, n_rows, stride, lpr * 16, sink, status);
     } else {
-      gather_bulk_kernel<<<sms, 128, kBulkSmem>>>(pool, rows, n_rows, stride, lpr * 16, sink, status);
+      gather_bulk_kernel<4><<<sms, 128, kBulkSmem>>>(pool, rows, n_rows, stride, lpr * 16, sink, status);
     }
   };
   for (int i = 0; i < 3; ++i) launch();
@@ -224,7 +229,7 @@ int main() {
   CHECK(cudaMalloc(&status, 4));
   CHECK(cudaMemset(status, 0, 4));
   std::printf("%-12s %-10s %-10s %-12s %12s %12s\n", "fetch", "row bytes", "stride", "order", "G rows/s", "TB/s");
-  const char* how_names[4] = {"ld.global", "cp.async.cg", "bulk copy", "cp.async.ca"};
+  const char* how_names[5] = {"ld.global", "cp.async.cg", "bulk copy", "cp.async.ca", "bulk x12"};
   uint64_t s = 0x9e3779b97f4a7c15ull;
   auto rnd = [&]() {
     s ^= s << 13;
@@ -242,7 +247,7 @@ int main() {
         for (long long i = 0; i < n_list; ++i)
           h[i] = order == 0 ? (int)(rnd() % (uint64_t)pool_rows) : (int)(i % pool_rows);
         CHECK(cudaMemcpy(rows, h.data(), n_list * 4, cudaMemcpyHostToDevice));
-        for (int how = 0; how < 4; ++how) {
+        for (int how = 0; how < 5; ++how) {
           const float ms = run(how, row / 16, pool, rows, n_list, stride, sink, status, sms);
           std::printf("%-12s %-10d %-10lld %-12s %12.2f %12.3f\n", how_names[how], row, stride,
                       order == 0 ? "random" : "ascending", n_list / ms / 1e6, (double)n_list * row / ms / 1e9);
