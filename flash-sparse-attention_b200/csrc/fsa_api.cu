@@ -81,6 +81,8 @@ int head_dim_kernel(int d) { return d <= 64 ? 64 : 128; }
 // the forward and decode kernels also come 256 columns wide (16-bit inputs); the backward stops at 128
 bool head_dim_ok_wide(int d) { return d >= 8 && d <= 256 && d % 8 == 0; }
 int head_dim_kernel_wide(int d) { return d <= 64 ? 64 : (d <= 128 ? 128 : 256); }
+// the forward also exists 192 columns wide (two stages of K fit there)
+int head_dim_kernel_fwd(int d) { return d <= 128 ? head_dim_kernel_wide(d) : (d <= 192 ? 192 : 256); }
 
 // optional per-call timing events around the main kernel
 void mark(void* ev, cudaStream_t s) {
@@ -407,7 +409,7 @@ int fsa_fwd(const FsaFwdArgs* a, void* stream_) {
   }
   mark(a->ev_before, stream);
   p.D = a->head_dim;
-  cudaError_t e = fsa::launch_fwd(p, a->kind, a->dtype, head_dim_kernel_wide(a->head_dim), stream);
+  cudaError_t e = fsa::launch_fwd(p, a->kind, a->dtype, head_dim_kernel_fwd(a->head_dim), stream);
   mark(a->ev_after, stream);
   if (e == cudaErrorInvalidValue) return FSA_ERR_UNSUPPORTED;
   if (e != cudaSuccess) return FSA_ERR_LAUNCH;

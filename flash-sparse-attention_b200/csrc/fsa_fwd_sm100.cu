@@ -37,13 +37,14 @@ constexpr int NTHREADS = 384;  // three warpgroups: softmax 0, softmax 1, {produ
 // arrive on one barrier and one "consumed" barrier per step releases both: every barrier the issuer touches
 // costs it 130-250 cycles even when it is already complete. (A third V stage, loaded a whole step earlier, did
 // not shorten the issuer's wait: it is not load latency.)
-// Head sizes above 128 (the 256-wide instantiation): a tile is 64 KB, so a CTA holds ONE query tile (the second
-// softmax group idles; its TMEM columns belong to the 256-column output accumulator of the first) and one stage each
-// of K and V - the loads of V(t) and K(t + 1) then start when S(t) has completed and run under the softmax of tile t.
+// Head sizes above 128 (the 192- and 256-wide instantiations): a tile is 48 / 64 KB, so a CTA holds ONE query tile
+// (the second softmax group idles; its TMEM columns belong to the wider output accumulator of the first) and one
+// stage of V - the load of V(t) then starts when P V(t - 1) has completed and runs under the softmax of tile t. K
+// keeps two stages where they fit (192 wide).
 template <int HD>
 struct FwdShape {
   static constexpr int QT = HD > 128 ? 1 : 2;       // query tiles (softmax groups at work) per CTA
-  static constexpr int KSTAGES = HD > 128 ? 1 : 2;
+  static constexpr int KSTAGES = HD > 192 ? 1 : 2;
   static constexpr int VSTAGES = HD > 128 ? 1 : 2;
 };
 
@@ -401,7 +402,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_kernel(const __grid_constant_
             ++seen;
           }
         };
-        need_signal(t - KSTAGES + 1);  // one stage each: signal t, i.e. S(t) and P V(t - 1) have completed
+        // V(t) replaces V(t - VSTAGES), K(t + 1) replaces K(t + 1 - KSTAGES): both are free after this signal
+        need_signal(t - (KSTAGES < VSTAGES ? KSTAGES : VSTAGES) + 1);
         if (!ok) break;
         // V is prefetched like K, before the softmax groups have voted on the tile: waiting for the vote
         // would put a full load latency between every S tile and its P V product, and in this
@@ -986,6 +988,8 @@ cudaError_t launch_fwd(const FwdKernelParams& p, int kind, int dtype, int head_d
   FSA_FWD_CASE(128, __half, DT_FP16)
   FSA_FWD_CASE(64, __nv_bfloat16, DT_BF16)
   FSA_FWD_CASE(64, __half, DT_FP16)
+  FSA_FWD_CASE(192, __nv_bfloat16, DT_BF16)
+  FSA_FWD_CASE(192, __half, DT_FP16)
   FSA_FWD_CASE(256, __nv_bfloat16, DT_BF16)
   FSA_FWD_CASE(256, __half, DT_FP16)
   FSA_FWD_CASE(128, __nv_fp8_e4m3, DT_E4M3)
